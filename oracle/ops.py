@@ -1,0 +1,368 @@
+"""Per-kernel CPU references (test infrastructure, see ``oracle/__init__.py``).
+
+Each function restates one of the reference's numpy oracles; the citation names the file and
+lines (paths relative to the reference project) it follows.  All arithmetic is f32 unless
+noted, tensors travel in the carrier types of ``oracle/codec.py``.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from .codec import from_f32, to_f32
+
+# ---------------------------------------------------------------------------
+# ortho-RoPE tables
+# ---------------------------------------------------------------------------
+
+
+def _pixel_freqs(n: int, max_freq: float) -> np.ndarray:
+    # src/quark/kernels/kv_cache_update/reference.py:50-51 (f64 on purpose: linspace * pi)
+    return np.linspace(1.0, max_freq / 2, n) * math.pi
+
+
+def _lang_freqs(dim: int, theta: float = 10000.0) -> np.ndarray:
+    # src/quark/kernels/kv_cache_update/reference.py:52-55 (f32 exponents -> f32 frequencies)
+    exponents = np.arange(0, dim, 2, dtype=np.float32) / dim
+    freqs = 1.0 / (theta**exponents)
+    return freqs[: dim // 2]
+
+
+def rope_spatial_angles(H: int, W: int, Dh: int = 64) -> np.ndarray:
+    """f32 angles ``[H*W, Dh//4]`` of the x and y parts of the table, for any frame.
+
+    Follows ``_make_ortho_rope_freqs`` (src/quark/kernels/kv_cache_update/reference.py:61-106):
+    positions are an f64 linspace narrowed to f32, multiplied by f64 pixel frequencies, each
+    frequency repeated twice, the result narrowed to f32 when the table is concatenated.
+    """
+    if H <= 0 or W <= 0 or Dh <= 0:
+        raise ValueError(f"H, W and Dh must be > 0; got H={H}, W={W}, Dh={Dh}")
+    max_freq = min(H, W) * 0.8
+    fx = np.linspace(-1 + 1 / W, 1 - 1 / W, W).astype(np.float32)[..., None] * _pixel_freqs(Dh // 16, max_freq)
+    fy = np.linspace(-1 + 1 / H, 1 - 1 / H, H).astype(np.float32)[..., None] * _pixel_freqs(Dh // 16, max_freq)
+    fx = np.repeat(fx, 2, axis=-1)[None, :, :]  # [1, W, Dh/8]
+    fy = np.repeat(fy, 2, axis=-1)[:, None, :]  # [H, 1, Dh/8]
+    fx = np.broadcast_to(fx, (H, W, fx.shape[-1])).reshape(H * W, -1)
+    fy = np.broadcast_to(fy, (H, W, fy.shape[-1])).reshape(H * W, -1)
+    return np.concatenate([fx, fy], axis=-1).astype(np.float32)
+
+
+def rope_temporal_angles(frame_t: int, Dh: int = 64) -> np.ndarray:
+    """f32 angles ``[Dh//4]`` of the temporal part for one frame (reference.py:93-97)."""
+    raw = np.asarray([frame_t]).astype(np.float32)[..., None] * _lang_freqs(Dh // 4)
+    return np.repeat(raw, 2, axis=-1).reshape(-1).astype(np.float32)
+
+
+def rope_tables(H: int, W: int, frame_t: int, Dh: int = 64):
+    """``(cos, sin)`` of shape ``[H*W, Dh//2]`` for frame ``frame_t`` only.
+
+    The reference builds the table for frames ``0..frame_t`` and slices the last frame
+    (reference.py:189-191); the rows of one frame do not depend on the others.
+    """
+    sp = rope_spatial_angles(H, W, Dh)
+    tm = np.broadcast_to(rope_temporal_angles(frame_t, Dh)[None, :], (H * W, Dh // 4))
+    ang = np.concatenate([sp, tm], axis=-1).astype(np.float32)
+    return np.cos(ang), np.sin(ang)
+
+
+def apply_rope(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """Pairs ``(x[2i], x[2i+1])``, output de-interleaved ``cat([y0, y1])`` (reference.py:31-41)."""
+    x32 = x.astype(np.float32, copy=False)
+    x0 = x32[..., 0::2]
+    x1 = x32[..., 1::2]
+    y0 = x0 * cos - x1 * sin
+    y1 = x1 * cos + x0 * sin
+    return np.concatenate([y0, y1], axis=-1)
+
+
+# ---------------------------------------------------------------------------
+# KV-cache append
+# ---------------------------------------------------------------------------
+
+
+def compute_segments(frame_t: int, num_buckets: int, tpf: int, pinned_dilation: int, max_segments: int = 3):
+    """Segment table after the append at ``frame_t`` (reference.py:109-140).
+
+    Returns ``(segments s32[max_segments*2], n_segments int)``.
+    """
+    L = num_buckets * tpf
+    bucket = (frame_t + pinned_dilation - 1) // pinned_dilation
+    is_write = (frame_t % pinned_dilation) == 0
+    post_wrap = bucket >= num_buckets
+    slot = bucket % num_buckets
+    if post_wrap and is_write:
+        rows = [[0, slot * tpf], [(slot + 1) * tpf, (num_buckets - slot - 1) * tpf], [L, tpf]]
+        n = 3
+    else:
+        rows = [[0, min(bucket, num_buckets) * tpf], [L, tpf]]
+        n = 2
+    rows.extend([[0, 0]] * (max_segments - len(rows)))
+    return np.array(rows, dtype=np.int32).reshape(-1), n
+
+
+def kv_cache_update(
+    qkv,
+    frame_t: int,
+    frozen: int,
+    *,
+    n_kv_heads: int,
+    n_q_heads: int,
+    H_spatial: int,
+    W_spatial: int,
+    num_buckets: int,
+    pinned_dilation: int,
+    kv_dtype: str = "bf16",
+    Dh: int = 64,
+    K_cache=None,
+    Vt_cache=None,
+    max_segments: int = 3,
+    reference_quirk: bool = False,
+):
+    """Packed-QKV cache append (src/quark/kernels/kv_cache_update/reference.py:148-251), B = 1.
+
+    ``qkv`` is ``[tpf, (Hq + 2 Hk) * Dh]`` bf16.  When ``K_cache`` / ``Vt_cache`` are given
+    they are updated in place (the read-modify-write the GPU kernel does); when they are
+    None fresh zero caches are returned, which is what the reference function models.
+    Returns ``(K_cache [Hk*capacity, Dh], Vt_cache [Hk*Dh, capacity], segments, n_segments)``.
+    """
+    tpf = H_spatial * W_spatial
+    Hk = n_kv_heads
+    L = num_buckets * tpf
+    cap = L + tpf
+    x = to_f32(qkv, "bf16")
+    k0 = n_q_heads * Dh
+    v0 = (n_q_heads + n_kv_heads) * Dh
+    K4 = x[:, k0 : k0 + Hk * Dh].reshape(tpf, Hk, Dh).transpose(1, 0, 2)  # [Hk, tpf, Dh]
+    V4 = x[:, v0 : v0 + Hk * Dh].reshape(tpf, Hk, Dh).transpose(1, 0, 2)
+    cos, sin = rope_tables(H_spatial, W_spatial, frame_t, Dh)
+    k_rot = apply_rope(K4, cos[None], sin[None])
+    k_c = from_f32(k_rot, kv_dtype, reference_quirk=reference_quirk)
+    v_c = from_f32(np.ascontiguousarray(V4), kv_dtype, reference_quirk=reference_quirk)
+
+    carrier = np.uint16 if kv_dtype == "bf16" else np.uint8
+    if K_cache is None:
+        K_cache = np.zeros((Hk * cap, Dh), dtype=carrier)
+    if Vt_cache is None:
+        Vt_cache = np.zeros((Hk * Dh, cap), dtype=carrier)
+    Kc = K_cache.reshape(Hk, cap, Dh)
+    Vc = Vt_cache.reshape(Hk, Dh, cap)
+    Kc[:, L : L + tpf, :] = k_c
+    Vc[:, :, L : L + tpf] = v_c.transpose(0, 2, 1)
+    if not frozen and frame_t % pinned_dilation == 0:
+        slot = ((frame_t + pinned_dilation - 1) // pinned_dilation) % num_buckets
+        Kc[:, slot * tpf : (slot + 1) * tpf, :] = k_c
+        Vc[:, :, slot * tpf : (slot + 1) * tpf] = v_c.transpose(0, 2, 1)
+    segs, n = compute_segments(frame_t, num_buckets, tpf, pinned_dilation, max_segments)
+    return K_cache, Vt_cache, segs, np.array([n], dtype=np.int32)
+
+
+# ---------------------------------------------------------------------------
+# owl_attn
+# ---------------------------------------------------------------------------
+
+
+def segment_mask(segments, n_segments: int, capacity: int) -> np.ndarray:
+    """Boolean validity mask ``[capacity]`` (src/quark/kernels/owl_attn/reference.py:29-45)."""
+    valid = np.zeros(capacity, dtype=bool)
+    segs = np.asarray(segments, dtype=np.int64).reshape(-1, 2)
+    for i in range(int(n_segments)):
+        st, ln = int(segs[i, 0]), int(segs[i, 1])
+        end = min(st + ln, capacity)
+        if st < end:
+            valid[st:end] = True
+    return valid
+
+
+def owl_attn(
+    qkv,
+    K_cache,
+    Vt_cache,
+    segments,
+    n_segments,
+    frame_t: int,
+    *,
+    n_kv_heads: int,
+    gqa_ratio: int,
+    H_spatial: int,
+    W_spatial: int,
+    kv_dtype: str = "bf16",
+    Dh: int = 64,
+    packed_qkv: bool = True,
+    out_dtype: str = "bf16",
+    q_quant: str | None = None,
+    return_f32: bool = False,
+):
+    """Segment-masked GQA attention with Q-side RoPE (owl_attn/reference.py:47-111), B = 1.
+
+    Same arithmetic as the reference (f32 scores, exact softmax, f32 ``P @ V``), evaluated one
+    Q head at a time over the valid key columns only: masked columns contribute
+    ``exp(-inf) = 0`` in the reference, so dropping them changes no result bit except the order
+    of the f32 sums.  ``q_quant="e4m3"`` additionally rounds the rotated Q through e4m3, which
+    is what the fp8 compute path of the GPU kernels feeds its MMAs (the reference oracle itself
+    keeps Q in f32); it is used only for "same quantised operands" comparisons.
+    """
+    tpf = H_spatial * W_spatial
+    Hk = n_kv_heads
+    Hq = Hk * gqa_ratio
+    cap = K_cache.shape[0] // Hk
+    cos, sin = rope_tables(H_spatial, W_spatial, int(frame_t), Dh)
+    q = to_f32(qkv, "bf16")
+    if packed_qkv:
+        Q4 = q[:, : Hq * Dh].reshape(tpf, Hq, Dh).transpose(1, 0, 2)
+    else:
+        Q4 = q.reshape(Hq, tpf, Dh)
+    Q_rot = apply_rope(Q4, cos[None], sin[None])
+    if q_quant is not None:
+        Q_rot = to_f32(from_f32(Q_rot, q_quant), q_quant)
+    Kc = to_f32(K_cache, kv_dtype).reshape(Hk, cap, Dh)
+    Vc = to_f32(Vt_cache, kv_dtype).reshape(Hk, Dh, cap)
+    valid = segment_mask(segments, int(np.asarray(n_segments).reshape(-1)[0]), cap)
+    idx = np.nonzero(valid)[0]
+    out = np.zeros((Hq, tpf, Dh), dtype=np.float32)
+    scale = np.float32(1.0 / np.sqrt(Dh))
+    if idx.size:
+        for h in range(Hq):
+            kh = h // gqa_ratio
+            Ks = Kc[kh][idx]  # [S, Dh]
+            Vs = Vc[kh][:, idx]  # [Dh, S]
+            s = (Q_rot[h] @ Ks.T) * scale
+            m = s.max(axis=-1, keepdims=True)
+            ex = np.exp(s - m)
+            den = ex.sum(axis=-1, keepdims=True)
+            out[h] = (ex / den) @ Vs.T
+    if packed_qkv:
+        res = out.transpose(1, 0, 2).reshape(tpf, Hq * Dh)
+    else:
+        res = out.reshape(Hq * tpf, Dh)
+    return res if return_f32 else from_f32(res, out_dtype)
+
+
+# ---------------------------------------------------------------------------
+# GEMM and its epilogue
+# ---------------------------------------------------------------------------
+
+
+def silu_f32(x: np.ndarray) -> np.ndarray:
+    return x * (1.0 / (1.0 + np.exp(-x)))
+
+
+def gemm(
+    A,
+    B,
+    *,
+    a_dtype: str = "bf16",
+    b_dtype: str = "bf16",
+    out_dtype: str = "bf16",
+    bias=None,
+    activation: str | None = None,
+    gate=None,
+    residual=None,
+    gate_groups: int = 1,
+    a_quant: str | None = None,
+    return_f32: bool = False,
+):
+    """``C = A @ B.T`` with the epilogue order bias -> SiLU -> gate*acc + residual -> cast.
+
+    Follows ``src/quark/kernels/gemm/reference.py:18-48``.  The reference keeps A in f32 even
+    when the kernel computes in e4m3; ``a_quant="e4m3"`` rounds A through e4m3 first so that a
+    GPU fp8 result can be compared against the oracle on the same quantised operands.
+    """
+    a = to_f32(A, a_dtype)
+    if a_quant is not None and a_dtype != a_quant:
+        a = to_f32(from_f32(a, a_quant), a_quant)
+    b = to_f32(B, b_dtype)
+    c = a.reshape(-1, a.shape[-1]) @ b.T
+    if bias is not None:
+        c = c + to_f32(bias, out_dtype).reshape(1, -1)
+    if activation == "silu":
+        c = silu_f32(c)
+    elif activation is not None:
+        raise ValueError(f"unsupported activation {activation!r}")
+    if gate is not None and residual is not None:
+        g = to_f32(gate, out_dtype).reshape(gate_groups, -1)
+        r = to_f32(residual, out_dtype)
+        c = r + np.repeat(g, c.shape[0] // gate_groups, axis=0) * c
+    return c if return_f32 else from_f32(c, out_dtype)
+
+
+def quantize_e4m3(X, src_dtype: str = "bf16", *, reference_quirk: bool = False):
+    """Unscaled RN-even, saturating narrow (src/quark/nn/layers.py:291-304, npconv.py:109-148)."""
+    return from_f32(to_f32(X, src_dtype), "e4m3", reference_quirk=reference_quirk)
+
+
+# ---------------------------------------------------------------------------
+# norm / elementwise glue
+# ---------------------------------------------------------------------------
+
+
+def ada_rmsnorm(X, scale, bias, *, eps: float = 1e-6, activation: str | None = None, dtype: str = "bf16", return_f32=False):
+    """``rmsnorm(x) * (1 + scale) + bias`` (+ SiLU) (src/quark/kernels/ada_rmsnorm/reference.py:10-29)."""
+    x = to_f32(X, dtype)
+    s = to_f32(scale, dtype).reshape(-1, x.shape[-1])
+    b = to_f32(bias, dtype).reshape(-1, x.shape[-1])
+    inv = 1.0 / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
+    y = x * inv
+    rep = x.shape[0] // s.shape[0]
+    y = y * (1.0 + np.repeat(s, rep, axis=0)) + np.repeat(b, rep, axis=0)
+    if activation == "silu":
+        y = silu_f32(y)
+    y = y.astype(np.float32)
+    return y if return_f32 else from_f32(y, dtype)
+
+
+def head_rmsnorm(X, *, n_q_heads: int, n_kv_heads: int, Dh: int = 64, eps: float = 1e-6, dtype: str = "bf16"):
+    """Per-head RMS norm of the Q and K columns, V copied (head_rmsnorm/reference.py:10-26)."""
+    x = to_f32(X, dtype).copy()
+    nh = n_q_heads + n_kv_heads
+    seg = x[:, : nh * Dh].reshape(x.shape[0], nh, Dh)
+    inv = 1.0 / np.sqrt(np.mean(seg * seg, axis=-1, keepdims=True) + eps)
+    x[:, : nh * Dh] = (seg * inv).reshape(x.shape[0], nh * Dh)
+    return from_f32(x.astype(np.float32), dtype)
+
+
+def value_residual_packed(QKV_curr, QKV_first, lamb: float, *, v_col_offset: int, v_width: int, dtype: str = "bf16"):
+    """``v += lamb * (v_first - v)`` on the V columns (value_residual_packed/reference.py:8-20)."""
+    cur = to_f32(QKV_curr, dtype)
+    first = to_f32(QKV_first, dtype)
+    lam = np.float32(lamb)
+    out = cur.copy()
+    sl = slice(v_col_offset, v_col_offset + v_width)
+    out[:, sl] = cur[:, sl] + lam * (first[:, sl] - cur[:, sl])
+    return from_f32(out, dtype)
+
+
+def ada_gate_residual(X, Y, gate, *, dtype: str = "bf16"):
+    """``x + gate * y`` (src/quark/kernels/ada_gate_residual/reference.py:10-22)."""
+    x = to_f32(X, dtype)
+    y = to_f32(Y, dtype)
+    g = to_f32(gate, dtype).reshape(-1, x.shape[-1])
+    return from_f32(x + np.repeat(g, x.shape[0] // g.shape[0], axis=0) * y, dtype)
+
+
+def silu(X, *, dtype: str = "bf16"):
+    """``x * sigmoid(x)`` (src/quark/kernels/silu/reference.py:10-18)."""
+    return from_f32(silu_f32(to_f32(X, dtype)), dtype)
+
+
+def euler_step(X, V, dsig: float, *, dtype: str = "bf16"):
+    """``x + dsig * v`` (src/quark/functional/euler_step.py:36-41)."""
+    return from_f32(to_f32(X, dtype) + np.float32(dsig) * to_f32(V, dtype), dtype)
+
+
+def patchify(X, W, *, C: int, H: int, Wd: int, ph: int = 2, pw: int = 2, dtype: str = "bf16"):
+    """``[1, C*H*W] -> [Hp*Wp, d_model]`` (src/quark/kernels/patchify/reference.py:8-23)."""
+    x = to_f32(X, dtype).reshape(1, C, H // ph, ph, Wd // pw, pw).transpose(0, 2, 4, 1, 3, 5)
+    x = x.reshape((H // ph) * (Wd // pw), C * ph * pw)
+    return from_f32(x @ to_f32(W, dtype).T, dtype)
+
+
+def unpatchify(X, W, bias, *, C: int, H: int, Wd: int, ph: int = 2, pw: int = 2, dtype: str = "bf16"):
+    """``[Hp*Wp, d_model] -> [1, C*H*W]`` (src/quark/kernels/unpatchify/reference.py:8-24)."""
+    h = to_f32(X, dtype) @ to_f32(W, dtype).T
+    if bias is not None:
+        h = h + to_f32(bias, dtype).reshape(1, -1)
+    Hp, Wp = H // ph, Wd // pw
+    h = h.reshape(1, Hp, Wp, C, ph, pw).transpose(0, 3, 1, 4, 2, 5)
+    return from_f32(np.ascontiguousarray(h).reshape(1, C * H * Wd), dtype)
