@@ -1,0 +1,220 @@
+/*
+ * quark_b200 - C ABI of the sm_100a kernel library for the Waypoint-1.5 DiT per-NFE hot path.
+ *
+ * One shared library (libquark_b200.so) replaces everything below the reference's
+ * `quark.functional` (qf.*) layer for this path.  The reference reaches its kernels through
+ * Python: qf.* -> Launcher -> PTX text -> cuModuleLoadData / cuLaunchKernel via ctypes
+ * (src/quark/drivers/cuda.py:159-239, src/quark/runtime/cuda.py:81-110) or cublasLtMatmul via
+ * ctypes (src/quark/runtime/cublas.py:265-459).  A maintainer binds these entry points with
+ * ctypes in the same way.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in `_host`;
+ *   - `stream` is a cudaStream_t / CUstream passed as void* (NULL = default stream);
+ *   - tensors are row-major and contiguous; bf16 and e4m3 are raw 16- and 8-bit words;
+ *   - every function returns QB_OK (0) or a negative qb_status, never aborts the process,
+ *     never synchronises the device and never allocates device memory except where the
+ *     comment says so (the qb_malloc family and qb_device_status);
+ *   - after an error qb_last_error_string() holds a message for the calling thread;
+ *   - compute calls are stream-capturable: scalars that change per step (frame_t, frozen,
+ *     segments) live in device memory, so a captured CUDA graph can be replayed.
+ *
+ * Paths relative to the reference project are cited as "ref:".
+ */
+#ifndef QUARK_B200_H
+#define QUARK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  QB_OK = 0,
+  QB_ERR_INVALID_ARG = -1, /* bad shape / NULL pointer / inconsistent sizes */
+  QB_ERR_UNSUPPORTED = -2, /* legal in the reference, not implemented here (e.g. quilt_factor > 1) */
+  QB_ERR_ALIGN = -3,       /* pointer or row pitch not 16-byte aligned */
+  QB_ERR_LAUNCH = -4,      /* CUDA reported an error at launch */
+  QB_ERR_DEVICE = -5,      /* no CUDA device, or not compute capability 10.0 */
+  QB_ERR_WORKSPACE = -6,   /* workspace missing or too small */
+  QB_ERR_CUDA = -7         /* a CUDA runtime call failed (message has the detail) */
+} qb_status;
+
+/* dtype codes; names follow ref: src/quark/runtime/tensor.py:57-69 */
+typedef enum { QB_BF16 = 0, QB_E4M3 = 1, QB_F32 = 2, QB_S32 = 3 } qb_dtype;
+
+/* ------------------------------------------------------------------ library / device */
+int32_t qb_version(void);
+const char* qb_last_error_string(void);
+/* Number of CUDA devices, 0 when there is none (never fails). */
+int32_t qb_device_count(void);
+/* QB_OK iff `device` exists and is compute capability 10.0. */
+int32_t qb_device_check(int32_t device);
+int32_t qb_set_device(int32_t device);
+/* Reads and clears the device status word that kernels set when a bounded wait ran out
+ * (bit 0 GEMM, bit 1 attention) or a segment table was malformed (bit 2).  Synchronises. */
+int32_t qb_device_status(uint32_t* status_host);
+
+/* ------------------------------------------------------------------ memory / streams / graphs
+ * Replaces the ctypes libcuda subset the reference's tensor class uses
+ * (ref: src/quark/runtime/cuda.py:118-800: mem_alloc, memcpy_htod/dtoh/dtod, memset,
+ * stream/event helpers, and src/quark/graph.py:105-173 for capture). */
+int32_t qb_malloc(void** ptr_host, size_t bytes);
+int32_t qb_free(void* ptr);
+int32_t qb_host_alloc(void** ptr_host, size_t bytes); /* pinned host memory */
+int32_t qb_host_free(void* ptr_hostmem);
+/* kind: 0 host->device, 1 device->host, 2 device->device; asynchronous on `stream` */
+int32_t qb_memcpy_async(void* dst, const void* src, size_t bytes, int32_t kind, void* stream);
+int32_t qb_memset_async(void* dst, int32_t byte_value, size_t bytes, void* stream);
+int32_t qb_memset32_async(void* dst, uint32_t value, size_t count, void* stream);
+int32_t qb_stream_create(void** stream_host);
+int32_t qb_stream_destroy(void* stream);
+int32_t qb_stream_sync(void* stream);
+int32_t qb_device_sync(void);
+int32_t qb_event_create(void** event_host);
+int32_t qb_event_destroy(void* event);
+int32_t qb_event_record(void* event, void* stream);
+int32_t qb_event_sync(void* event);
+int32_t qb_event_elapsed_ms(void* start, void* stop, float* ms_host);
+int32_t qb_graph_begin(void* stream);
+int32_t qb_graph_end(void* stream, void** graph_exec_host);
+int32_t qb_graph_launch(void* graph_exec, void* stream);
+int32_t qb_graph_destroy(void* graph_exec);
+
+/* ------------------------------------------------------------------ GEMM
+ * C[M,N] = epilogue(A[M,K] . B[N,K]^T), f32 accumulation, epilogue order
+ *   acc * (a_scale * w_scale[n]) -> + bias[n] -> SiLU -> * gate[m / (M/G), n] + residual[m, n] -> cast
+ * Replaces qf.gemm (ref: src/quark/functional/gemm.py:597-635), i.e. GemmKernel
+ * (ref: src/quark/kernels/gemm/kernel.py:831-895, epilogue order src/quark/lang/epilogue.py:387-420)
+ * and the cublasLtMatmul path (ref: src/quark/runtime/cublas.py:265-459).
+ *
+ * compute_dtype QB_BF16 needs A and B in bf16; QB_E4M3 needs B in e4m3 and A in e4m3 or bf16.
+ * A bf16 A is first narrowed to e4m3 (round-to-nearest-even, saturating, unscaled) into the
+ * workspace, which is what the reference's cuBLAS route does with a separate launch
+ * (ref: src/quark/kernels/gemm/cublas_dispatch.py:164-168).
+ * bias / gate / residual / a_scale / w_scale may be NULL (scales default to 1: the reference
+ * has no scales).  gate and residual come together.  C may be bf16, f32 or e4m3.
+ * Needs K % 16 == 0, N % 8 == 0 and 16-byte aligned pointers. */
+typedef struct {
+  int32_t M, N, K;
+  int32_t a_dtype, b_dtype, c_dtype; /* qb_dtype */
+  int32_t compute_dtype;             /* QB_BF16 or QB_E4M3 */
+  int32_t activation;                /* 0 none, 1 SiLU */
+  int32_t gate_groups;               /* G: gate is [G, N], each row covers M/G rows */
+  int32_t split_k;                   /* 0 = choose; >= 1 forces the number of K slices */
+  int32_t tile_n;                    /* 0 = choose; 64, 128 or 256 */
+  int32_t reserved;
+  const float* a_scale; /* [1]  optional */
+  const float* w_scale; /* [N]  optional */
+} qb_gemm_params;
+
+/* Bytes of workspace qb_gemm needs for `p` (K-slice partial sums, tile counters, and the
+ * e4m3 copy of a bf16 A).  The counter area must be zero before the first use; qb_gemm leaves
+ * it zero.  Calls that share a workspace must not overlap on the GPU. */
+size_t qb_gemm_workspace_bytes(const qb_gemm_params* p);
+int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* X -> e4m3, round-to-nearest-even, saturate to +-448, NaN -> 0x7F, no scale.
+ * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
+ * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */
+int32_t qb_quantize_e4m3(const void* X, void* out, size_t n, int32_t src_dtype, void* stream);
+
+/* ------------------------------------------------------------------ KV-cache append
+ * Reads the K and V columns of packed qkv [tpf, (Hq + 2 Hk) * 64] bf16, applies ortho-RoPE to K
+ * in f32, narrows to kv_dtype, writes K rows and transposed V columns to the tail slot
+ * (rows [L, L + tpf)) always and to ring slot ((ft + pd - 1) / pd) % nb iff ft % pd == 0 and
+ * frozen == 0, and rewrites the 3-entry segment table.
+ * Replaces qf.kv_cache_update (ref: src/quark/functional/kv_cache_update.py:187-265,
+ * src/quark/kernels/kv_cache_update/kernel.py:395-766; cache layout
+ * src/quark/kernels/kv_cache_update/spec.py:11-14).
+ *   K_cache  [Hk * capacity, 64]    Vt_cache [Hk * 64, capacity]    capacity = (nb + 1) * tpf
+ *   segments s32[6], n_segments s32[1], frame_t s32[1], frozen s32[1]: device scalars.
+ * rope_xy: f32 [tpf, 16] = per token 8 cosines then 8 sines of the 4 x- and 4 y-angles
+ * (build with qb_rope_table_build, or on the host as the reference's numpy table does). */
+typedef struct {
+  int32_t n_q_heads, n_kv_heads;
+  int32_t H_spatial, W_spatial;
+  int32_t num_buckets, pinned_dilation;
+  int32_t kv_dtype;     /* QB_BF16 or QB_E4M3 */
+  int32_t max_segments; /* 3 */
+  int32_t quilt_factor; /* must be 1 */
+  int32_t packed_qkv;   /* must be 1 */
+} qb_kv_params;
+
+int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
+                           int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p, void* stream);
+
+/* Fills rope_xy [H*W, 16] on the device: token t -> (h, w) = (t / W, t % W).  The angles follow
+ * ref: src/quark/kernels/kv_cache_update/reference.py:61-106 (f64 position x frequency, narrowed
+ * to f32); cos/sin are the CUDA single-precision functions. */
+int32_t qb_rope_table_build(float* rope_xy, int32_t H_spatial, int32_t W_spatial, void* stream);
+
+/* ------------------------------------------------------------------ owl_attn
+ * Segment-sparse GQA flash attention with inline ortho-RoPE on Q, head_dim 64.
+ * Replaces qf.owl_attn (ref: src/quark/functional/owl_attn.py:322-394,
+ * src/quark/kernels/owl_attn/kernel.py:324-790).  qkv packed [tpf, (Hq + 2 Hk) * 64] bf16 (only
+ * the Q columns are read), caches as above, out [tpf, Hq * 64] bf16.  Attends to the union of
+ * the first n_segments (start, length) entries; starts and lengths must be multiples of 128.
+ * compute_dtype QB_BF16 (bf16 caches) or QB_E4M3 (e4m3 caches; Q after RoPE and P are narrowed
+ * to e4m3).  k_scale / v_scale: optional f32 [Hk] per-head dequantisation scales (NULL = 1). */
+typedef struct {
+  int32_t n_kv_heads, gqa_ratio;
+  int32_t H_spatial, W_spatial;
+  int32_t num_buckets, pinned_dilation;
+  int32_t kv_dtype;      /* QB_BF16 or QB_E4M3 */
+  int32_t compute_dtype; /* QB_BF16 or QB_E4M3 */
+  int32_t max_segments;  /* 3 */
+  int32_t packed_qkv;    /* must be 1 */
+  int32_t quilt_factor;  /* must be 1 */
+  int32_t kv_splits;     /* 0 = choose; > 1 splits the keys over CTAs (needs workspace) */
+  const float* k_scale;
+  const float* v_scale;
+} qb_attn_params;
+
+size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p);
+int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
+                    const int32_t* n_segments, const int32_t* frame_t, void* out, const float* rope_xy,
+                    const qb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ norm / elementwise ops
+ * bf16 in, f32 math, bf16 out unless noted.  `out_q` (optional) receives the same result
+ * narrowed to e4m3 so the next fp8 GEMM needs no separate cast. */
+
+/* y = x * rsqrt(mean(x^2) + eps) * (1 + scale[g]) + bias[g], then SiLU if activation == 1.
+ * X [rows, D], scale / bias [G, D].  ref: src/quark/functional/ada_rmsnorm.py:61,
+ * src/quark/kernels/ada_rmsnorm/reference.py:10-29. */
+int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void* out, void* out_q, int32_t rows, int32_t D,
+                       int32_t groups, float eps, int32_t activation, void* stream);
+/* RMS norm of each 64-wide Q and K head of packed qkv [rows, (Hq + 2 Hk) * Dh]; V copied.
+ * ref: src/quark/kernels/head_rmsnorm/reference.py:10-26. */
+int32_t qb_head_rmsnorm(const void* X, void* out, int32_t rows, int32_t n_q_heads, int32_t n_kv_heads, int32_t Dh, float eps,
+                        void* stream);
+/* out = cur with V columns v + lamb * (v_first - v); lamb f32[1] on the device.
+ * ref: src/quark/kernels/value_residual_packed/reference.py:8-20. */
+int32_t qb_value_residual_packed(const void* cur, const void* first, const float* lamb, void* out, int32_t rows, int32_t D_full,
+                                 int32_t v_col_offset, int32_t v_width, void* stream);
+/* out = x + gate[g] * y.  ref: src/quark/kernels/ada_gate_residual/reference.py:10-22. */
+int32_t qb_ada_gate_residual(const void* X, const void* Y, const void* gate, void* out, int32_t rows, int32_t D, int32_t groups,
+                             void* stream);
+/* out = x * sigmoid(x).  ref: src/quark/kernels/silu/reference.py:10-18. */
+int32_t qb_silu(const void* X, void* out, void* out_q, size_t n, void* stream);
+/* out = x + dsig[0] * v; dsig f32[1] on the device.  ref: src/quark/functional/euler_step.py:36-41. */
+int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out, size_t n, void* stream);
+/* counter[0] += 1.  ref: src/quark/kernels/increment/kernel.py:1-7. */
+int32_t qb_increment(int32_t* counter, void* stream);
+/* latent [1, C*H*W] -> tokens [(H/ph)*(W/pw), d_model] = patches . W[d_model, C*ph*pw]^T.
+ * ref: src/quark/kernels/patchify/reference.py:8-23. */
+int32_t qb_patchify(const void* X, const void* W, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw,
+                    int32_t d_model, void* stream);
+/* tokens [(H/ph)*(W/pw), d_model] -> latent [1, C*H*W] = scatter(tokens . W[C*ph*pw, d_model]^T + bias).
+ * ref: src/quark/kernels/unpatchify/reference.py:8-24. */
+int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph,
+                      int32_t pw, int32_t d_model, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUARK_B200_H */

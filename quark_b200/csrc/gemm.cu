@@ -1,0 +1,497 @@
+// C[M,N] = epilogue(A[M,K] . B[N,K]^T) on the sm_100a tensor cores.
+//
+// One CTA computes one 128 x BN output tile over one K slice.  Warp 0 feeds a ring of
+// shared-memory stages with TMA (128-byte swizzle, no multicast), one thread of warp 1 issues
+// tcgen05.mma into a TMEM accumulator, warps 2-5 read the accumulator back (one row per
+// thread) and run the epilogue.  bf16 operands use kind::f16 (K = 16 per instruction), e4m3
+// operands kind::f8f6f4 (K = 32); both move 128 bytes of K per stage row, so the two paths share
+// every address computation.
+//
+// K can be split over `splits` CTAs per tile: each writes its f32 partial tile to the
+// workspace, takes a ticket on the tile's counter, and the CTA that draws the last ticket adds
+// the partials in slice order (so the sum does not depend on which CTA came last), applies the
+// epilogue and stores.  No CTA ever waits for another.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace qb {
+
+constexpr int kBM = 128;          // rows of A per tile = TMEM lanes
+constexpr int kRowBytes = 128;    // bytes of K per stage row = one swizzle atom
+constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
+constexpr int kSmemBudget = 200 * 1024;
+
+struct GemmArgs {
+  int M, N, K;
+  int kb_total, kb_per_split, splits;
+  int c_dtype, activation, rows_per_gate;
+  const float* a_scale;
+  const float* w_scale;
+  const uint16_t* bias;
+  const uint16_t* gate;
+  const uint16_t* residual;
+  void* C;
+  float* partials;
+  int* counters;
+  unsigned int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStageBytes = kBM * kRowBytes + BN * kRowBytes;
+  static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+// Applies the epilogue to 8 consecutive columns of one row and stores them.
+__device__ __forceinline__ void epilogue_store8(const GemmArgs& g, float (&v)[8], int m, int n) {
+  if (g.a_scale != nullptr || g.w_scale != nullptr) {
+    const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= g.w_scale ? sa * __ldg(g.w_scale + n + j) : sa;
+  }
+  if (g.bias != nullptr) {
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(g.bias + n));
+    const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] += bf16lo(w[j]);
+      v[2 * j + 1] += bf16hi(w[j]);
+    }
+  }
+  if (g.activation == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = silu_f(v[j]);
+  }
+  if (g.gate != nullptr) {
+    const size_t grow = static_cast<size_t>(m / g.rows_per_gate) * g.N;
+    const uint4 gt = __ldg(reinterpret_cast<const uint4*>(g.gate + grow + n));
+    const uint4 rs = __ldg(reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n));
+    const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
+    const uint32_t rw[4] = {rs.x, rs.y, rs.z, rs.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __fadd_rn(bf16lo(rw[j]), __fmul_rn(bf16lo(gw[j]), v[2 * j]));
+      v[2 * j + 1] = __fadd_rn(bf16hi(rw[j]), __fmul_rn(bf16hi(gw[j]), v[2 * j + 1]));
+    }
+  }
+  const size_t off = static_cast<size_t>(m) * g.N + n;
+  if (g.c_dtype == QB_BF16) {
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]);
+    o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(g.C) + off) = o;
+  } else if (g.c_dtype == QB_E4M3) {
+    uint2 o;
+    o.x = pack_e4m3x4(v[0], v[1], v[2], v[3]);
+    o.y = pack_e4m3x4(v[4], v[5], v[6], v[7]);
+    *reinterpret_cast<uint2*>(static_cast<uint8_t*>(g.C) + off) = o;
+  } else {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.C) + off);
+    dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+    dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+template <int BN, bool FP8>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  using L = GemmSmem<BN>;
+  constexpr int kStages = L::kStages;
+  constexpr int kKElems = FP8 ? 128 : 64;  // elements of K per stage
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  constexpr uint32_t kIdesc = FP8 ? umma_idesc(0, 0, kBM, BN) : umma_idesc(1, 1, kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* acc_bar = bars + 2 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
+  volatile int* drain_flag = abort_flag + 2;  // never set: lets the drain waits below run their own limit
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int split = blockIdx.z;
+  const int kb0 = split * g.kb_per_split;
+  const int kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+  const int n_iter = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(acc_bar), 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    *drain_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (elect_one()) {
+      int issued = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM)) break;
+        const uint32_t fb = smem_u32(&full_bar[s]);
+        mbar_arrive_expect_tx(fb, L::kStageBytes);
+        uint8_t* a_s = smem + s * L::kStageBytes;
+        tma_load_2d(smem_u32(a_s), &tmA, fb, (kb0 + it) * kKElems, m0);
+        tma_load_2d(smem_u32(a_s + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, n0);
+        issued = it + 1;
+      }
+      if (*abort_flag) {
+        // Giving up: let the copies already in flight land before this CTA's memory goes away.
+        for (int it = max(0, issued - kStages); it < issued; ++it)
+          mbar_wait(smem_u32(&full_bar[it % kStages]), (it / kStages) & 1, drain_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM);
+      } else {
+        // Tail: the MMA warp's last stage releases arrive on barriers in this CTA's shared memory;
+        // see them land before the CTA can exit.
+        for (int it = max(0, n_iter - kStages); it < n_iter; ++it)
+          if (!mbar_wait(smem_u32(&empty_bar[it % kStages]), (it / kStages) & 1, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (elect_one()) {
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        ok = mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
+        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_sw128(a_addr + kBM * kRowBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per stage row
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          if (FP8)
+            umma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, acc);
+          else
+            umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, kIdesc, acc);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));
+      }
+      umma_commit(smem_u32(acc_bar));
+    }
+  } else {
+    // ---------------- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+    const int lane_grp = warp & 3;
+    const int row = lane_grp * 32 + lane;
+    const int m = m0 + row;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_bar), 0, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM));
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
+    if (ok) {
+      if (g.splits == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_wait_ld();
+          if (m < g.M) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int n = n0 + c * 32 + q * 8;
+              if (n < g.N) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[q * 8 + j]);
+                epilogue_store8(g, v, m, n);
+              }
+            }
+          }
+        }
+      } else {
+        float* part = g.partials + static_cast<size_t>(split) * g.M * g.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_wait_ld();
+          if (m < g.M) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int n = n0 + c * 32 + q * 4;
+              if (n < g.N)
+                __stcg(reinterpret_cast<float4*>(part + static_cast<size_t>(m) * g.N + n),
+                       make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                   __uint_as_float(r[q * 4 + 3])));
+            }
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        int* counter = g.counters + blockIdx.y * gridDim.x + blockIdx.x;
+        if (threadIdx.x == 64) {
+          const int ticket = atomicAdd(counter, 1);
+          *last_flag = (ticket == g.splits - 1) ? 1 : 0;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          if (m < g.M) {
+#pragma unroll 1
+            for (int c8 = 0; c8 < BN / 8; ++c8) {
+              const int n = n0 + c8 * 8;
+              if (n >= g.N) break;
+              float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              for (int s = 0; s < g.splits; ++s) {
+                const float4* src =
+                    reinterpret_cast<const float4*>(g.partials + (static_cast<size_t>(s) * g.M + m) * g.N + n);
+                const float4 x = __ldcg(src), y = __ldcg(src + 1);
+                v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+                v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+              }
+              epilogue_store8(g, v, m, n);
+            }
+          }
+          if (threadIdx.x == 64) *counter = 0;  // ready for the next launch
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map of a contiguous row-major tensor [rows, cols] of 1- or 2-byte elements with a box of
+// [box_rows, box_cols] elements; box_cols * elem_bytes must equal the swizzle span (64 or 128).
+// Out-of-range parts of a box are filled with zeros.
+int32_t make_tmap_2d_sw(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                        uint32_t box_cols, int swizzle_bytes) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  QB_REQUIRE(enc != nullptr, QB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  QB_REQUIRE((cols * elem_bytes) % 16 == 0, QB_ERR_ALIGN, "tensor map: row pitch of %llu bytes is not a multiple of 16",
+             static_cast<unsigned long long>(cols * elem_bytes));
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * elem_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapSwizzle sw = swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  QB_REQUIRE(r == CUDA_SUCCESS, QB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return QB_OK;
+}
+
+static int32_t make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  return make_tmap_2d_sw(tm, base, elem_bytes, rows, cols, box_rows, static_cast<uint32_t>(kRowBytes / elem_bytes), 128);
+}
+
+struct GemmPlan {
+  int bn, splits, kb_total, kb_per_split;
+  size_t counters_bytes, aq_bytes, partial_bytes;
+};
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+// Picks the tile width and the number of K slices from a small cost model (cycles per CTA:
+// the slower of tensor-core issue and operand delivery per 128 bytes of K, plus fixed costs),
+// so that every call with the same shape makes the same choice.
+static GemmPlan plan_gemm(const qb_gemm_params& p) {
+  const bool fp8 = p.compute_dtype == QB_E4M3;
+  const int k_elems = fp8 ? 128 : 64;
+  GemmPlan best{};
+  double best_cost = 1e30;
+  const int sms = num_sms();
+  const int kb_total = (p.K + k_elems - 1) / k_elems;
+  const int bns[3] = {256, 128, 64};
+  const int ss[10] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
+  for (int bn : bns) {
+    if (p.tile_n != 0 && p.tile_n != bn) continue;
+    if (p.tile_n == 0 && bn > 64 && bn / 2 >= p.N) continue;  // tile mostly empty
+    const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + bn - 1) / bn);
+    for (int s : ss) {
+      if (p.split_k != 0 && p.split_k != s) continue;
+      if (s > kb_total) continue;
+      const int kbps = (kb_total + s - 1) / s;
+      const int s_eff = (kb_total + kbps - 1) / kbps;
+      if (s_eff != s) continue;
+      const long ctas = static_cast<long>(tiles) * s;
+      const long waves = (ctas + sms - 1) / sms;
+      const double per_kb = fmax(2.0 * bn, (kBM + bn) * 128.0 / 56.0);
+      double cta = kbps * per_kb + 1500.0 + bn * 6.0;
+      if (s > 1) cta += bn * 10.0 + s * bn * 3.0;
+      const double cost = waves * cta;
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.bn = bn;
+        best.splits = s;
+        best.kb_total = kb_total;
+        best.kb_per_split = kbps;
+      }
+    }
+  }
+  if (best.bn == 0) {  // forced values that fit nothing: fall back to the plain configuration
+    best.bn = p.tile_n ? p.tile_n : 128;
+    best.splits = 1;
+    best.kb_total = kb_total;
+    best.kb_per_split = kb_total;
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + best.bn - 1) / best.bn);
+  best.counters_bytes = round_up(static_cast<size_t>(tiles) * sizeof(int), 1024);
+  best.aq_bytes = (fp8 && p.a_dtype == QB_BF16) ? round_up(static_cast<size_t>(p.M) * p.K, 1024) : 0;
+  best.partial_bytes = best.splits > 1 ? static_cast<size_t>(best.splits) * p.M * p.N * sizeof(float) : 0;
+  return best;
+}
+
+static int32_t validate_gemm(const qb_gemm_params* p) {
+  QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "gemm params are NULL");
+  QB_REQUIRE(p->M > 0 && p->N > 0 && p->K > 0, QB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", p->M, p->N, p->K);
+  QB_REQUIRE(p->compute_dtype == QB_BF16 || p->compute_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "gemm: compute_dtype %d", p->compute_dtype);
+  if (p->compute_dtype == QB_BF16) {
+    QB_REQUIRE(p->a_dtype == QB_BF16 && p->b_dtype == QB_BF16, QB_ERR_INVALID_ARG, "gemm: bf16 compute needs bf16 A and B");
+  } else {
+    QB_REQUIRE(p->b_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "gemm: e4m3 compute needs an e4m3 B (weights are quantised ahead of time)");
+    QB_REQUIRE(p->a_dtype == QB_E4M3 || p->a_dtype == QB_BF16, QB_ERR_INVALID_ARG, "gemm: A must be bf16 or e4m3");
+  }
+  QB_REQUIRE(p->c_dtype == QB_BF16 || p->c_dtype == QB_F32 || p->c_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "gemm: c_dtype %d", p->c_dtype);
+  QB_REQUIRE(p->K % 16 == 0, QB_ERR_ALIGN, "gemm: K = %d must be a multiple of 16", p->K);
+  QB_REQUIRE(p->N % 8 == 0, QB_ERR_ALIGN, "gemm: N = %d must be a multiple of 8", p->N);
+  QB_REQUIRE(p->activation == 0 || p->activation == 1, QB_ERR_INVALID_ARG, "gemm: activation %d", p->activation);
+  QB_REQUIRE(p->tile_n == 0 || p->tile_n == 64 || p->tile_n == 128 || p->tile_n == 256, QB_ERR_INVALID_ARG, "gemm: tile_n %d", p->tile_n);
+  QB_REQUIRE(p->split_k >= 0 && p->split_k <= 16, QB_ERR_INVALID_ARG, "gemm: split_k %d", p->split_k);
+  return QB_OK;
+}
+
+template <int BN, bool FP8>
+static int32_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, dim3 grid, cudaStream_t st) {
+  using L = GemmSmem<BN>;
+  QB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<BN, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  gemm_kernel<BN, FP8><<<grid, kGemmThreads, L::kTotal, st>>>(tmA, tmB, args);
+  return check_launch("gemm kernel");
+}
+
+int32_t quantize_e4m3_launch(const void* X, void* out, size_t n, int32_t src_dtype, cudaStream_t st);
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" size_t qb_gemm_workspace_bytes(const qb_gemm_params* p) {
+  if (validate_gemm(p) != QB_OK) return 0;
+  const GemmPlan pl = plan_gemm(*p);
+  return pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
+}
+
+extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                           const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int32_t rc = validate_gemm(p);
+  if (rc != QB_OK) return rc;
+  QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
+  QB_REQUIRE((gate == nullptr) == (residual == nullptr), QB_ERR_INVALID_ARG, "gemm: gate and residual come together");
+  QB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && aligned16(bias) && aligned16(gate) && aligned16(residual), QB_ERR_ALIGN,
+             "gemm: every pointer must be 16-byte aligned");
+  int rows_per_gate = p->M;
+  if (gate != nullptr) {
+    QB_REQUIRE(p->gate_groups >= 1 && p->M % p->gate_groups == 0, QB_ERR_INVALID_ARG, "gemm: gate_groups %d does not divide M = %d",
+               p->gate_groups, p->M);
+    rows_per_gate = p->M / p->gate_groups;
+  }
+  const GemmPlan pl = plan_gemm(*p);
+  const size_t need = pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
+  const bool uses_ws = pl.aq_bytes > 0 || pl.partial_bytes > 0;
+  if (uses_ws) {
+    QB_REQUIRE(workspace != nullptr && workspace_bytes >= need, QB_ERR_WORKSPACE, "gemm: workspace of %zu bytes needed, %zu given", need,
+               workspace_bytes);
+    QB_REQUIRE(aligned16(workspace), QB_ERR_ALIGN, "gemm: workspace must be 16-byte aligned");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fp8 = p->compute_dtype == QB_E4M3;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const void* a_ptr = A;
+  if (pl.aq_bytes > 0) {
+    uint8_t* aq = ws + pl.counters_bytes;
+    rc = quantize_e4m3_launch(A, aq, static_cast<size_t>(p->M) * p->K, QB_BF16, st);
+    if (rc != QB_OK) return rc;
+    a_ptr = aq;
+  }
+  CUtensorMap tmA, tmB;
+  const int es = fp8 ? 1 : 2;
+  rc = make_tmap_2d(&tmA, a_ptr, es, p->M, p->K, kBM);
+  if (rc != QB_OK) return rc;
+  rc = make_tmap_2d(&tmB, B, es, p->N, p->K, pl.bn);
+  if (rc != QB_OK) return rc;
+
+  GemmArgs g{};
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.kb_total = pl.kb_total; g.kb_per_split = pl.kb_per_split; g.splits = pl.splits;
+  g.c_dtype = p->c_dtype; g.activation = p->activation; g.rows_per_gate = rows_per_gate;
+  g.a_scale = p->a_scale; g.w_scale = p->w_scale;
+  g.bias = static_cast<const uint16_t*>(bias);
+  g.gate = static_cast<const uint16_t*>(gate);
+  g.residual = static_cast<const uint16_t*>(residual);
+  g.C = C;
+  g.counters = reinterpret_cast<int*>(ws);
+  g.partials = pl.partial_bytes ? reinterpret_cast<float*>(ws + pl.counters_bytes + pl.aq_bytes) : nullptr;
+  g.status = status_word();
+  QB_REQUIRE(g.status != nullptr, QB_ERR_CUDA, "gemm: device status word unavailable");
+
+  dim3 grid((p->N + pl.bn - 1) / pl.bn, (p->M + kBM - 1) / kBM, pl.splits);
+  if (fp8) {
+    if (pl.bn == 256) return launch_gemm<256, true>(tmA, tmB, g, grid, st);
+    if (pl.bn == 128) return launch_gemm<128, true>(tmA, tmB, g, grid, st);
+    return launch_gemm<64, true>(tmA, tmB, g, grid, st);
+  }
+  if (pl.bn == 256) return launch_gemm<256, false>(tmA, tmB, g, grid, st);
+  if (pl.bn == 128) return launch_gemm<128, false>(tmA, tmB, g, grid, st);
+  return launch_gemm<64, false>(tmA, tmB, g, grid, st);
+}

@@ -1,0 +1,449 @@
+// HBM-bound norm / elementwise kernels that chain the GEMMs and the attention into a block:
+// AdaRMSNorm, per-head RMSNorm, value residual, gate + residual, SiLU, Euler step, e4m3 narrowing,
+// patchify / unpatchify and the frame counter.  bf16 in and out, f32 arithmetic written as
+// separate multiplies and adds where the CPU oracle does so, 16-byte accesses throughout.
+#include "common.cuh"
+
+namespace qb {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = bf16lo(u.x); f[1] = bf16hi(u.x); f[2] = bf16lo(u.y); f[3] = bf16hi(u.y);
+  f[4] = bf16lo(u.z); f[5] = bf16hi(u.z); f[6] = bf16lo(u.w); f[7] = bf16hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+  return o;
+}
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8]) {
+  uint2 o;
+  o.x = pack_e4m3x4(f[0], f[1], f[2], f[3]);
+  o.y = pack_e4m3x4(f[4], f[5], f[6], f[7]);
+  return o;
+}
+// The e4m3 side output is narrowed from the bf16-rounded value, i.e. it equals what a separate
+// bf16 -> e4m3 cast of the main output would give.
+__device__ __forceinline__ void round_through_bf16(float (&f)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j]));
+}
+
+// ---------------------------------------------------------------- AdaRMSNorm
+// One CTA per row; each thread owns D / (8 * blockDim) groups of 8 consecutive elements.
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ scale,
+                                                                const uint16_t* __restrict__ bias, uint16_t* __restrict__ out,
+                                                                uint8_t* __restrict__ out_q, int D, int rows_per_group, float eps,
+                                                                int activation) {
+  const int row = blockIdx.x;
+  const uint16_t* x = X + static_cast<size_t>(row) * D;
+  const size_t goff = static_cast<size_t>(row / rows_per_group) * D;
+  constexpr int kMaxVec = 4;  // D <= 8 * kThreads * kMaxVec
+  uint4 xv[kMaxVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * kThreads + threadIdx.x) * 8;
+    if (c < D) {
+      xv[i] = *reinterpret_cast<const uint4*>(x + c);
+      float f[8];
+      unpack8(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+  __shared__ float red[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) tot += red[w];
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(D) + eps);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * kThreads + threadIdx.x) * 8;
+    if (c < D) {
+      float f[8], s[8], b[8];
+      unpack8(xv[i], f);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(scale + goff + c)), s);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(bias + goff + c)), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float y = __fmul_rn(f[j], inv);
+        y = __fadd_rn(__fmul_rn(y, __fadd_rn(1.0f, s[j])), b[j]);
+        f[j] = activation == 1 ? silu_f(y) : y;
+      }
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * D + c) = pack8(f);
+      if (out_q != nullptr) {
+        round_through_bf16(f);
+        *reinterpret_cast<uint2*>(out_q + static_cast<size_t>(row) * D + c) = pack8_e4m3(f);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- per-head RMSNorm on packed qkv
+// 8 threads per (row, head): 8 x 8 = 64 elements; heads >= n_norm_heads (the V heads) are copied.
+__global__ void __launch_bounds__(256) head_rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, int rows,
+                                                            int heads_total, int n_norm_heads, float eps) {
+  const size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  const size_t item = gid >> 3;  // (row, head)
+  const int sub = gid & 7;
+  const bool active = item < static_cast<size_t>(rows) * heads_total;
+  const int head = active ? static_cast<int>(item % heads_total) : 0;
+  const size_t off = (active ? item : 0) * 64 + sub * 8;
+  float f[8];
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (active) v = *reinterpret_cast<const uint4*>(X + off);
+  unpack8(v, f);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  if (!active) return;
+  if (head < n_norm_heads) {
+    const float inv = 1.0f / sqrtf(ss * (1.0f / 64.0f) + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(f[j], inv);
+    v = pack8(f);
+  }
+  *reinterpret_cast<uint4*>(out + off) = v;
+}
+
+// ---------------------------------------------------------------- value residual on the V columns
+__global__ void __launch_bounds__(256) value_residual_kernel(const uint16_t* __restrict__ cur, const uint16_t* __restrict__ first,
+                                                              const float* __restrict__ lamb, uint16_t* __restrict__ out, int rows,
+                                                              int D_full, int v_off, int v_width) {
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i8 >= static_cast<size_t>(rows) * D_full) return;
+  const int col = static_cast<int>(i8 % D_full);
+  uint4 c = *reinterpret_cast<const uint4*>(cur + i8);
+  if (col >= v_off && col < v_off + v_width) {
+    const float lam = __ldg(lamb);
+    float a[8], b[8];
+    unpack8(c, a);
+    unpack8(*reinterpret_cast<const uint4*>(first + i8), b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = __fadd_rn(a[j], __fmul_rn(lam, __fsub_rn(b[j], a[j])));
+    c = pack8(a);
+  }
+  *reinterpret_cast<uint4*>(out + i8) = c;
+}
+
+// ---------------------------------------------------------------- x + gate * y
+__global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ Y,
+                                                             const uint16_t* __restrict__ gate, uint16_t* __restrict__ out, int rows,
+                                                             int D, int rows_per_group) {
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i8 >= static_cast<size_t>(rows) * D) return;
+  const int row = static_cast<int>(i8 / D), col = static_cast<int>(i8 % D);
+  float x[8], y[8], g[8];
+  unpack8(*reinterpret_cast<const uint4*>(X + i8), x);
+  unpack8(*reinterpret_cast<const uint4*>(Y + i8), y);
+  unpack8(__ldg(reinterpret_cast<const uint4*>(gate + static_cast<size_t>(row / rows_per_group) * D + col)), g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(g[j], y[j]));
+  *reinterpret_cast<uint4*>(out + i8) = pack8(x);
+}
+
+// ---------------------------------------------------------------- SiLU / Euler / quantise
+__global__ void __launch_bounds__(256) silu_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, uint8_t* __restrict__ out_q,
+                                                    size_t n) {
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i8 + 8 <= n) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(X + i8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = silu_f(f[j]);
+    if (out != nullptr) *reinterpret_cast<uint4*>(out + i8) = pack8(f);
+    if (out_q != nullptr) {
+      round_through_bf16(f);
+      *reinterpret_cast<uint2*>(out_q + i8) = pack8_e4m3(f);
+    }
+  } else {
+    for (size_t i = i8; i < n; ++i) {
+      const float y = silu_f(bf16_bits_to_f32(X[i]));
+      const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+      if (out != nullptr) out[i] = *reinterpret_cast<const uint16_t*>(&yb);
+      if (out_q != nullptr) out_q[i] = static_cast<uint8_t>(pack_e4m3x2(__bfloat162float(yb), 0.f) & 0xFF);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) euler_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ V,
+                                                     const float* __restrict__ dsig, uint16_t* __restrict__ out, size_t n) {
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  const float d = __ldg(dsig);
+  if (i8 + 8 <= n) {
+    float x[8], v[8];
+    unpack8(*reinterpret_cast<const uint4*>(X + i8), x);
+    unpack8(*reinterpret_cast<const uint4*>(V + i8), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(d, v[j]));
+    *reinterpret_cast<uint4*>(out + i8) = pack8(x);
+  } else {
+    for (size_t i = i8; i < n; ++i) {
+      const __nv_bfloat16 y = __float2bfloat16_rn(__fadd_rn(bf16_bits_to_f32(X[i]), __fmul_rn(d, bf16_bits_to_f32(V[i]))));
+      out[i] = *reinterpret_cast<const uint16_t*>(&y);
+    }
+  }
+}
+
+template <bool kFromF32>
+__global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ X, uint8_t* __restrict__ out, size_t n) {
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i8 + 8 <= n) {
+    float f[8];
+    if (kFromF32) {
+      const float4 a = reinterpret_cast<const float4*>(X)[i8 / 4], b = reinterpret_cast<const float4*>(X)[i8 / 4 + 1];
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+      unpack8(*reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(X) + i8), f);
+    }
+    *reinterpret_cast<uint2*>(out + i8) = pack8_e4m3(f);
+  } else {
+    for (size_t i = i8; i < n; ++i) {
+      const float v = kFromF32 ? static_cast<const float*>(X)[i] : bf16_bits_to_f32(static_cast<const uint16_t*>(X)[i]);
+      out[i] = static_cast<uint8_t>(pack_e4m3x2(v, 0.f) & 0xFF);
+    }
+  }
+}
+
+__global__ void increment_kernel(int32_t* c) { c[0] += 1; }
+
+// ---------------------------------------------------------------- patchify / unpatchify
+// Both are thin GEMMs (K = C*ph*pw = 128 in, N = 128 out for the model) run once per NFE.
+// A CTA stages kTok token rows in shared memory as f32; each thread owns one output feature and
+// reads its weight row once for all staged tokens.
+constexpr int kPatchTok = 8;
+
+__global__ void __launch_bounds__(256) patchify_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ W,
+                                                        uint16_t* __restrict__ out, int C, int H, int Wd, int ph, int pw, int d_model,
+                                                        int tokens) {
+  extern __shared__ float patch[];  // [kPatchTok][K]
+  const int K = C * ph * pw;
+  const int Wp = Wd / pw;
+  const int t0 = blockIdx.x * kPatchTok;
+  for (int i = threadIdx.x; i < kPatchTok * K; i += blockDim.x) {
+    const int tt = i / K, k = i % K;
+    const int tok = t0 + tt;
+    float v = 0.f;
+    if (tok < tokens) {
+      const int c = k / (ph * pw), r = (k / pw) % ph, q = k % pw;
+      const int hp = tok / Wp, wp = tok % Wp;
+      v = bf16_bits_to_f32(X[static_cast<size_t>(c) * H * Wd + static_cast<size_t>(hp * ph + r) * Wd + wp * pw + q]);
+    }
+    patch[i] = v;
+  }
+  __syncthreads();
+  const int d = blockIdx.y * blockDim.x + threadIdx.x;
+  if (d >= d_model) return;
+  float acc[kPatchTok];
+#pragma unroll
+  for (int t = 0; t < kPatchTok; ++t) acc[t] = 0.f;
+  const uint16_t* w = W + static_cast<size_t>(d) * K;
+  for (int k = 0; k < K; k += 8) {
+    float wf[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int t = 0; t < kPatchTok; ++t) acc[t] = fmaf(patch[t * K + k + j], wf[j], acc[t]);
+  }
+  for (int t = 0; t < kPatchTok; ++t) {
+    if (t0 + t < tokens) {
+      const __nv_bfloat16 y = __float2bfloat16_rn(acc[t]);
+      out[static_cast<size_t>(t0 + t) * d_model + d] = *reinterpret_cast<const uint16_t*>(&y);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ W,
+                                                          const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int C, int H,
+                                                          int Wd, int ph, int pw, int d_model, int tokens) {
+  extern __shared__ float xs[];  // [kPatchTok][d_model]
+  const int Nout = C * ph * pw;
+  const int Wp = Wd / pw;
+  const int t0 = blockIdx.x * kPatchTok;
+  for (int i = threadIdx.x * 8; i < kPatchTok * d_model; i += blockDim.x * 8) {
+    const int tt = i / d_model, k = i % d_model;
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (t0 + tt < tokens) unpack8(*reinterpret_cast<const uint4*>(X + static_cast<size_t>(t0 + tt) * d_model + k), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xs[i + j] = f[j];
+  }
+  __syncthreads();
+  const int o = blockIdx.y * blockDim.x + threadIdx.x;
+  if (o >= Nout) return;
+  float acc[kPatchTok];
+#pragma unroll
+  for (int t = 0; t < kPatchTok; ++t) acc[t] = 0.f;
+  const uint16_t* w = W + static_cast<size_t>(o) * d_model;
+  for (int k = 0; k < d_model; k += 8) {
+    float wf[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(w + k)), wf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int t = 0; t < kPatchTok; ++t) acc[t] = fmaf(xs[t * d_model + k + j], wf[j], acc[t]);
+  }
+  const float b = bias != nullptr ? bf16_bits_to_f32(bias[o]) : 0.f;
+  const int c = o / (ph * pw), r = (o / pw) % ph, q = o % pw;
+  for (int t = 0; t < kPatchTok; ++t) {
+    const int tok = t0 + t;
+    if (tok < tokens) {
+      const int hp = tok / Wp, wp = tok % Wp;
+      const __nv_bfloat16 y = __float2bfloat16_rn(acc[t] + b);
+      out[static_cast<size_t>(c) * H * Wd + static_cast<size_t>(hp * ph + r) * Wd + wp * pw + q] = *reinterpret_cast<const uint16_t*>(&y);
+    }
+  }
+}
+
+int32_t quantize_e4m3_launch(const void* X, void* out, size_t n, int32_t src_dtype, cudaStream_t st) {
+  if (n == 0) return QB_OK;
+  const unsigned blocks = static_cast<unsigned>((n + 2047) / 2048);
+  if (src_dtype == QB_F32)
+    quantize_kernel<true><<<blocks, 256, 0, st>>>(X, static_cast<uint8_t*>(out), n);
+  else
+    quantize_kernel<false><<<blocks, 256, 0, st>>>(X, static_cast<uint8_t*>(out), n);
+  return check_launch("quantize_e4m3");
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+static inline unsigned blocks_for(size_t n_elems) { return static_cast<unsigned>((n_elems + 2047) / 2048); }
+
+extern "C" {
+
+int32_t qb_quantize_e4m3(const void* X, void* out, size_t n, int32_t src_dtype, void* stream) {
+  QB_REQUIRE(src_dtype == QB_BF16 || src_dtype == QB_F32, QB_ERR_INVALID_ARG, "quantize_e4m3: src_dtype %d", src_dtype);
+  QB_REQUIRE(n == 0 || (X && out), QB_ERR_INVALID_ARG, "quantize_e4m3: NULL pointer");
+  QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "quantize_e4m3: pointers must be 16-byte aligned");
+  return quantize_e4m3_launch(X, out, n, src_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void* out, void* out_q, int32_t rows, int32_t D,
+                       int32_t groups, float eps, int32_t activation, void* stream) {
+  QB_REQUIRE(X && scale && bias && out, QB_ERR_INVALID_ARG, "ada_rmsnorm: NULL pointer");
+  QB_REQUIRE(rows > 0 && D > 0 && groups > 0 && rows % groups == 0, QB_ERR_INVALID_ARG, "ada_rmsnorm: rows %d, D %d, groups %d", rows, D,
+             groups);
+  QB_REQUIRE(D % 8 == 0 && D <= 8192, QB_ERR_UNSUPPORTED, "ada_rmsnorm: D = %d must be a multiple of 8 and at most 8192", D);
+  QB_REQUIRE(activation == 0 || activation == 1, QB_ERR_INVALID_ARG, "ada_rmsnorm: activation %d", activation);
+  QB_REQUIRE(aligned16(X) && aligned16(scale) && aligned16(bias) && aligned16(out) && aligned16(out_q), QB_ERR_ALIGN,
+             "ada_rmsnorm: pointers must be 16-byte aligned");
+  ada_rmsnorm_kernel<256><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(scale), static_cast<const uint16_t*>(bias),
+      static_cast<uint16_t*>(out), static_cast<uint8_t*>(out_q), D, rows / groups, eps, activation);
+  return check_launch("ada_rmsnorm");
+}
+
+int32_t qb_head_rmsnorm(const void* X, void* out, int32_t rows, int32_t n_q_heads, int32_t n_kv_heads, int32_t Dh, float eps,
+                        void* stream) {
+  QB_REQUIRE(X && out, QB_ERR_INVALID_ARG, "head_rmsnorm: NULL pointer");
+  QB_REQUIRE(Dh == 64, QB_ERR_UNSUPPORTED, "head_rmsnorm: head_dim %d (only 64)", Dh);
+  QB_REQUIRE(rows > 0 && n_q_heads >= 0 && n_kv_heads >= 0 && n_q_heads + n_kv_heads > 0, QB_ERR_INVALID_ARG, "head_rmsnorm: bad sizes");
+  QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "head_rmsnorm: pointers must be 16-byte aligned");
+  const int heads_total = n_q_heads + 2 * n_kv_heads;
+  const size_t threads = static_cast<size_t>(rows) * heads_total * 8;
+  head_rmsnorm_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(X), static_cast<uint16_t*>(out), rows, heads_total, n_q_heads + n_kv_heads, eps);
+  return check_launch("head_rmsnorm");
+}
+
+int32_t qb_value_residual_packed(const void* cur, const void* first, const float* lamb, void* out, int32_t rows, int32_t D_full,
+                                 int32_t v_col_offset, int32_t v_width, void* stream) {
+  QB_REQUIRE(cur && first && lamb && out, QB_ERR_INVALID_ARG, "value_residual_packed: NULL pointer");
+  QB_REQUIRE(rows > 0 && D_full > 0 && v_col_offset >= 0 && v_width >= 0 && v_col_offset + v_width <= D_full, QB_ERR_INVALID_ARG,
+             "value_residual_packed: bad sizes");
+  QB_REQUIRE(D_full % 8 == 0 && v_col_offset % 8 == 0 && v_width % 8 == 0, QB_ERR_ALIGN, "value_residual_packed: columns must be multiples of 8");
+  QB_REQUIRE(aligned16(cur) && aligned16(first) && aligned16(out), QB_ERR_ALIGN, "value_residual_packed: pointers must be 16-byte aligned");
+  value_residual_kernel<<<blocks_for(static_cast<size_t>(rows) * D_full), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(cur), static_cast<const uint16_t*>(first), lamb, static_cast<uint16_t*>(out), rows, D_full,
+      v_col_offset, v_width);
+  return check_launch("value_residual_packed");
+}
+
+int32_t qb_ada_gate_residual(const void* X, const void* Y, const void* gate, void* out, int32_t rows, int32_t D, int32_t groups,
+                             void* stream) {
+  QB_REQUIRE(X && Y && gate && out, QB_ERR_INVALID_ARG, "ada_gate_residual: NULL pointer");
+  QB_REQUIRE(rows > 0 && D > 0 && groups > 0 && rows % groups == 0, QB_ERR_INVALID_ARG, "ada_gate_residual: bad sizes");
+  QB_REQUIRE(D % 8 == 0, QB_ERR_ALIGN, "ada_gate_residual: D must be a multiple of 8");
+  QB_REQUIRE(aligned16(X) && aligned16(Y) && aligned16(gate) && aligned16(out), QB_ERR_ALIGN, "ada_gate_residual: pointers must be 16-byte aligned");
+  gate_residual_kernel<<<blocks_for(static_cast<size_t>(rows) * D), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(Y), static_cast<const uint16_t*>(gate), static_cast<uint16_t*>(out),
+      rows, D, rows / groups);
+  return check_launch("ada_gate_residual");
+}
+
+int32_t qb_silu(const void* X, void* out, void* out_q, size_t n, void* stream) {
+  QB_REQUIRE(X && (out || out_q), QB_ERR_INVALID_ARG, "silu: NULL pointer");
+  QB_REQUIRE(aligned16(X) && aligned16(out) && aligned16(out_q), QB_ERR_ALIGN, "silu: pointers must be 16-byte aligned");
+  if (n == 0) return QB_OK;
+  silu_kernel<<<blocks_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<uint16_t*>(out),
+                                                                            static_cast<uint8_t*>(out_q), n);
+  return check_launch("silu");
+}
+
+int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out, size_t n, void* stream) {
+  QB_REQUIRE(X && V && dsig && out, QB_ERR_INVALID_ARG, "euler_step: NULL pointer");
+  QB_REQUIRE(aligned16(X) && aligned16(V) && aligned16(out), QB_ERR_ALIGN, "euler_step: pointers must be 16-byte aligned");
+  if (n == 0) return QB_OK;
+  euler_kernel<<<blocks_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(V),
+                                                                             dsig, static_cast<uint16_t*>(out), n);
+  return check_launch("euler_step");
+}
+
+int32_t qb_increment(int32_t* counter, void* stream) {
+  QB_REQUIRE(counter != nullptr, QB_ERR_INVALID_ARG, "increment: NULL pointer");
+  increment_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter);
+  return check_launch("increment");
+}
+
+static int32_t check_patch_geometry(const char* who, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, int32_t d_model) {
+  QB_REQUIRE(C > 0 && H > 0 && Wd > 0 && ph > 0 && pw > 0 && d_model > 0, QB_ERR_INVALID_ARG, "%s: sizes must be positive", who);
+  QB_REQUIRE(H % ph == 0 && Wd % pw == 0, QB_ERR_INVALID_ARG, "%s: H=%d W=%d not divisible by patch (%d,%d)", who, H, Wd, ph, pw);
+  QB_REQUIRE((C * ph * pw) % 8 == 0 && d_model % 8 == 0, QB_ERR_ALIGN, "%s: C*ph*pw and d_model must be multiples of 8", who);
+  return QB_OK;
+}
+
+int32_t qb_patchify(const void* X, const void* W, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw,
+                    int32_t d_model, void* stream) {
+  QB_REQUIRE(X && W && out, QB_ERR_INVALID_ARG, "patchify: NULL pointer");
+  int32_t rc = check_patch_geometry("patchify", C, H, Wd, ph, pw, d_model);
+  if (rc != QB_OK) return rc;
+  QB_REQUIRE(aligned16(W), QB_ERR_ALIGN, "patchify: W must be 16-byte aligned");
+  const int tokens = (H / ph) * (Wd / pw);
+  const int K = C * ph * pw;
+  const size_t smem = static_cast<size_t>(kPatchTok) * K * sizeof(float);
+  QB_REQUIRE(smem <= 48 * 1024, QB_ERR_UNSUPPORTED, "patchify: C*ph*pw = %d too large", K);
+  dim3 grid((tokens + kPatchTok - 1) / kPatchTok, (d_model + 255) / 256);
+  patchify_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(W),
+                                                                           static_cast<uint16_t*>(out), C, H, Wd, ph, pw, d_model, tokens);
+  return check_launch("patchify");
+}
+
+int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph,
+                      int32_t pw, int32_t d_model, void* stream) {
+  QB_REQUIRE(X && W && out, QB_ERR_INVALID_ARG, "unpatchify: NULL pointer");
+  int32_t rc = check_patch_geometry("unpatchify", C, H, Wd, ph, pw, d_model);
+  if (rc != QB_OK) return rc;
+  QB_REQUIRE(aligned16(X) && aligned16(W), QB_ERR_ALIGN, "unpatchify: X and W must be 16-byte aligned");
+  const int tokens = (H / ph) * (Wd / pw);
+  const int Nout = C * ph * pw;
+  const size_t smem = static_cast<size_t>(kPatchTok) * d_model * sizeof(float);
+  QB_REQUIRE(smem <= 96 * 1024, QB_ERR_UNSUPPORTED, "unpatchify: d_model = %d too large", d_model);
+  QB_CUDA_OK(cudaFuncSetAttribute(unpatchify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  dim3 grid((tokens + kPatchTok - 1) / kPatchTok, (Nout + 127) / 128);
+  unpatchify_kernel<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(W),
+                                                                             static_cast<const uint16_t*>(bias), static_cast<uint16_t*>(out),
+                                                                             C, H, Wd, ph, pw, d_model, tokens);
+  return check_launch("unpatchify");
+}
+
+}  // extern "C"

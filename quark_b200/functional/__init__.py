@@ -1,0 +1,455 @@
+"""``qf.*``: the reference's functional call surface on ``QuarkTensor``, over the C ABI.
+
+Same names, positional order, keyword names and error behaviour as ``quark.functional``
+(``src/quark/functional/__init__.py:20-79``); each wrapper validates shapes and dtypes the way
+the reference's ``spec_from_tensors`` does (``ValueError`` / ``TypeError``), picks or allocates the
+output, and makes exactly one call into ``libquark_b200.so`` on the active stream.  Calls are
+allocation-free once their output and workspace buffers exist, so they can be captured into a
+CUDA graph after one eager run.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from .. import _lib
+from ..runtime import stream as _stream
+from ..runtime.tensor import QuarkTensor
+
+__all__ = [
+    "gemm", "owl_attn", "kv_cache_update", "quantize_e4m3", "ada_rmsnorm", "head_rmsnorm", "value_residual_packed",
+    "ada_gate_residual", "silu", "euler_step", "patchify", "unpatchify", "increment", "rope_table",
+]  # fmt: skip
+
+
+def _p(t) -> C.c_void_p:
+    return C.c_void_p(t.data_ptr() if t is not None else None)
+
+
+def _s() -> C.c_void_p:
+    return C.c_void_p(_stream.active_stream())
+
+
+def _dt(t) -> str:
+    d = getattr(t, "dtype", None)
+    if not isinstance(d, str):
+        raise TypeError(f"expected a QuarkTensor, got {type(t).__name__}")
+    return d
+
+
+def _code(name: str | None, default: str) -> int:
+    name = default if name is None else (name.value if hasattr(name, "value") else name)
+    if name not in _lib.DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {name!r}")
+    return _lib.DTYPE_CODE[name]
+
+
+# ---------------------------------------------------------------------------
+# workspace (K-slice partials, tile counters, e4m3 copies of bf16 activations)
+# ---------------------------------------------------------------------------
+
+_WS: QuarkTensor | None = None
+
+
+def _workspace(nbytes: int) -> QuarkTensor | None:
+    """One zero-initialised scratch buffer shared by every call (calls on one stream never overlap)."""
+    global _WS
+    if nbytes <= 0:
+        return _WS
+    if _WS is None or _WS.nbytes < nbytes:
+        _WS = QuarkTensor.zeros(max(int(nbytes), 1 << 20), dtype="e4m3")
+    return _WS
+
+
+# ---------------------------------------------------------------------------
+# RoPE tables
+# ---------------------------------------------------------------------------
+
+_ROPE: dict[tuple[int, int], QuarkTensor] = {}
+
+
+def rope_table_numpy(H: int, W: int, Dh: int = 64) -> np.ndarray:
+    """f32 ``[H*W, 16]``: 8 cosines then 8 sines of the 4 x- and 4 y-angles of every token.
+
+    Same arithmetic as the reference table (``src/quark/kernels/kv_cache_update/reference.py:61-106``):
+    f64 linspace positions narrowed to f32, times f64 pixel frequencies ``linspace(1, 0.4*min(H,W), 4)*pi``,
+    narrowed to f32, then numpy's single-precision cos / sin.
+    """
+    if H <= 0 or W <= 0:
+        raise ValueError(f"H_spatial and W_spatial must be > 0; got H={H}, W={W}")
+    if Dh != 64:
+        raise ValueError("only head_dim 64 is supported")
+    freqs = np.linspace(1.0, min(H, W) * 0.8 / 2, Dh // 16) * np.pi
+    fx = np.linspace(-1 + 1 / W, 1 - 1 / W, W).astype(np.float32)[:, None] * freqs  # [W, 4] f64
+    fy = np.linspace(-1 + 1 / H, 1 - 1 / H, H).astype(np.float32)[:, None] * freqs  # [H, 4] f64
+    ang = np.concatenate(
+        [np.broadcast_to(fx[None, :, :], (H, W, 4)), np.broadcast_to(fy[:, None, :], (H, W, 4))], axis=-1
+    ).reshape(H * W, 8).astype(np.float32)
+    return np.concatenate([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
+def rope_table(H: int, W: int) -> QuarkTensor:
+    key = (int(H), int(W))
+    t = _ROPE.get(key)
+    if t is None:
+        t = QuarkTensor.from_numpy(rope_table_numpy(*key))
+        _ROPE[key] = t
+    return t
+
+
+# ---------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------
+
+
+def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=None, bias=None, gate=None,
+         residual=None, gate_groups=1, out=None, *, a_scale=None, w_scale=None, split_k=0, tile_n=0):  # fmt: skip
+    """``C = A @ B.T`` (+ bias, SiLU, ``residual + gate * C``); ``src/quark/functional/gemm.py:597-635``.
+
+    ``a_scale`` / ``w_scale`` (f32 device tensors) and ``split_k`` / ``tile_n`` are extensions; left
+    at their defaults the call is the reference's.
+    """
+    if b_shuffled:
+        raise NotImplementedError("qf.gemm: b_shuffled=True is not supported (disabled upstream as well)")
+    if A.ndim < 2 or B.ndim != 2:
+        raise ValueError(f"qf.gemm: A must be at least rank-2 and B rank-2, got {A.shape} and {B.shape}")
+    K = int(A.shape[-1])
+    M = A.numel // K
+    N = int(B.shape[0])
+    if int(B.shape[1]) != K:
+        raise ValueError(f"qf.gemm: A is [..., {K}] but B is {B.shape} (expected [N, {K}])")
+    a_dt, b_dt = _dt(A), _dt(B)
+    cd = compute_dtype.value if hasattr(compute_dtype, "value") else compute_dtype
+    if cd is None:
+        cd = b_dt if b_dt == "e4m3" else a_dt
+    if cd not in ("bf16", "e4m3"):
+        raise TypeError(f"qf.gemm: compute_dtype {cd!r} is not supported")
+    if activation not in (None, "silu"):
+        raise ValueError(f"qf.gemm: unsupported activation {activation!r}")
+    if (gate is None) != (residual is None):
+        raise ValueError("qf.gemm: gate and residual must be given together")
+    od = out_dtype.value if hasattr(out_dtype, "value") else out_dtype
+    if od is None:
+        od = out.dtype if out is not None else "bf16"
+    if out is None:
+        out = QuarkTensor.empty(M, N, dtype=od)
+    elif out.numel != M * N or out.dtype != od:
+        raise ValueError(f"qf.gemm: out is {out.shape} {out.dtype}, expected ({M}, {N}) {od}")
+    if bias is not None and bias.numel != N:
+        raise ValueError(f"qf.gemm: bias has {bias.numel} elements, expected {N}")
+    if gate is not None:
+        if gate.numel != gate_groups * N or residual.numel != M * N:
+            raise ValueError(f"qf.gemm: gate must be [{gate_groups}, {N}] and residual [{M}, {N}]")
+        if M % gate_groups:
+            raise ValueError(f"qf.gemm: gate_groups={gate_groups} does not divide M={M}")
+    p = _lib.GemmParams(
+        M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code(od, "bf16"),
+        compute_dtype=_code(cd, "bf16"), activation=1 if activation == "silu" else 0, gate_groups=int(gate_groups),
+        split_k=int(split_k), tile_n=int(tile_n), reserved=0,
+        a_scale=a_scale.data_ptr() if a_scale is not None else None,
+        w_scale=w_scale.data_ptr() if w_scale is not None else None,
+    )  # fmt: skip
+    lib = _lib.load()
+    need = int(lib.qb_gemm_workspace_bytes(C.byref(p)))
+    ws = _workspace(need)
+    _lib.check(
+        lib.qb_gemm(_p(A), _p(B), _p(out), _p(bias), _p(gate), _p(residual), C.byref(p), _p(ws), ws.nbytes if ws is not None else 0, _s())
+    )
+    return out
+
+
+def quantize_e4m3(X, *, out=None):
+    """bf16 / f32 -> e4m3, unscaled, RN-even, saturating (``src/quark/functional/quantize_e4m3.py:25-69``)."""
+    dt = _dt(X)
+    if dt not in ("bf16", "f32"):
+        raise TypeError(f"qf.quantize_e4m3: source dtype {dt!r} is not supported")
+    if out is None:
+        out = QuarkTensor.empty(*X.shape, dtype="e4m3")
+    elif out.numel != X.numel or out.dtype != "e4m3":
+        raise ValueError("qf.quantize_e4m3: out must be an e4m3 tensor of the same size")
+    _lib.check(_lib.load().qb_quantize_e4m3(_p(X), _p(out), X.numel, _lib.DTYPE_CODE[dt], _s()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# KV cache append and attention
+# ---------------------------------------------------------------------------
+
+
+def _quilt_checks(who: str, tpf: int, quilt_factor: int, quilt_offset: int) -> None:
+    if quilt_factor < 1 or (quilt_factor & (quilt_factor - 1)) != 0:
+        raise ValueError(f"{who}: quilt_factor must be a power of 2 (>=1), got {quilt_factor}")
+    if quilt_offset < 0 or quilt_offset >= quilt_factor:
+        raise ValueError(f"{who}: quilt_offset must be in [0, quilt_factor); got offset={quilt_offset} factor={quilt_factor}")
+    if tpf % quilt_factor != 0:
+        raise ValueError(f"{who}: H_spatial*W_spatial={tpf} must be divisible by quilt_factor={quilt_factor}")
+    if quilt_factor != 1:
+        raise NotImplementedError(f"{who}: quilt_factor > 1 is not supported")
+
+
+def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, B, n_kv_heads, H_spatial,
+                    W_spatial, num_buckets, pinned_dilation, kv_dtype=None, max_segments=3, packed_qkv=False,
+                    n_q_heads=0, rope_n_frames=1, quilt_factor=1, quilt_offset=0):  # fmt: skip
+    """In-place RoPE + cache append (``src/quark/functional/kv_cache_update.py:187-265``).
+
+    ``K`` is the packed QKV tensor when ``packed_qkv=True`` (``V`` is then ignored, as upstream).
+    Returns ``(K_cache, Vt_cache, segments, n_segments)``, the very tensors that were passed in.
+    """
+    del V, rope_n_frames
+    tpf = int(H_spatial) * int(W_spatial)
+    _quilt_checks("qf.kv_cache_update", tpf, quilt_factor, quilt_offset)
+    if B != 1:
+        raise NotImplementedError("qf.kv_cache_update: only B=1 is supported (the model is batch 1)")
+    if not packed_qkv:
+        raise NotImplementedError("qf.kv_cache_update: only packed_qkv=True is supported")
+    Dh = 64
+    qkv_dim = (n_q_heads + 2 * n_kv_heads) * Dh
+    if K.ndim != 2 or tuple(K.shape) != (B * tpf, qkv_dim):
+        raise ValueError(f"qf.kv_cache_update: packed QKV shape {tuple(K.shape)} != ({B * tpf}, {qkv_dim})")
+    if _dt(K) != "bf16":
+        raise TypeError(f"qf.kv_cache_update: input dtype {_dt(K)!r} (expected bf16)")
+    cap = num_buckets * tpf + tpf
+    if tuple(K_cache.shape) != (B * n_kv_heads * cap, Dh):
+        raise ValueError(f"qf.kv_cache_update: K_cache shape {tuple(K_cache.shape)} != ({B * n_kv_heads * cap}, {Dh})")
+    if tuple(Vt_cache.shape) != (B * n_kv_heads * Dh, cap):
+        raise ValueError(f"qf.kv_cache_update: Vt_cache shape {tuple(Vt_cache.shape)} != ({B * n_kv_heads * Dh}, {cap})")
+    if int(segments.shape[0]) != B * max_segments * 2:
+        raise ValueError(f"qf.kv_cache_update: segments shape {tuple(segments.shape)} != ({B * max_segments * 2},)")
+    if int(n_segments.shape[0]) != B:
+        raise ValueError(f"qf.kv_cache_update: n_segments shape {tuple(n_segments.shape)} != ({B},)")
+    kvd = _dt(K_cache)
+    want = kv_dtype.value if hasattr(kv_dtype, "value") else kv_dtype
+    if want is not None and want != kvd:
+        raise TypeError(f"qf.kv_cache_update: kv_dtype={want!r} but the caches are {kvd!r}")
+    if _dt(Vt_cache) != kvd or kvd not in ("bf16", "e4m3"):
+        raise TypeError(f"qf.kv_cache_update: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
+    p = _lib.KvParams(
+        n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+    )  # fmt: skip
+    _lib.check(
+        _lib.load().qb_kv_cache_update(
+            _p(K), _p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments),
+            _p(rope_table(H_spatial, W_spatial)), C.byref(p), _s(),
+        )
+    )  # fmt: skip
+    return K_cache, Vt_cache, segments, n_segments
+
+
+_DUMMY_FRAME_T: QuarkTensor | None = None
+
+
+def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_ratio, H_spatial, W_spatial, num_buckets,
+             pinned_dilation, out_dtype=None, compute_dtype=None, max_segments=3, packed_qkv=False, quilt_factor=1,
+             quilt_offset=0, frame_t=None, *, out=None, k_scale=None, v_scale=None):  # fmt: skip
+    """Segment-sparse GQA attention with inline Q RoPE (``src/quark/functional/owl_attn.py:322-394``)."""
+    global _DUMMY_FRAME_T
+    if Q.ndim != 2:
+        raise ValueError(f"qf.owl_attn: Q must be rank-2 (flat), got {Q.shape}")
+    tpf = int(H_spatial) * int(W_spatial)
+    _quilt_checks("qf.owl_attn", tpf, quilt_factor, quilt_offset)
+    if B != 1:
+        raise NotImplementedError("qf.owl_attn: only B=1 is supported (the model is batch 1)")
+    if not packed_qkv:
+        raise NotImplementedError("qf.owl_attn: only packed_qkv=True is supported")
+    n_q = n_kv_heads * gqa_ratio
+    Dh = int(Q.shape[1]) // (n_q + 2 * n_kv_heads)
+    if Dh != 64 or int(Q.shape[1]) != (n_q + 2 * n_kv_heads) * 64 or int(Q.shape[0]) != B * tpf:
+        raise ValueError(f"qf.owl_attn: packed QKV shape {tuple(Q.shape)} != ({B * tpf}, {(n_q + 2 * n_kv_heads) * 64})")
+    cap = num_buckets * tpf + tpf
+    if tuple(K_cache.shape) != (B * n_kv_heads * cap, Dh):
+        raise ValueError(f"qf.owl_attn: K_cache shape {tuple(K_cache.shape)} != ({B * n_kv_heads * cap}, {Dh})")
+    if tuple(Vt_cache.shape) != (B * n_kv_heads * Dh, cap):
+        raise ValueError(f"qf.owl_attn: Vt_cache shape {tuple(Vt_cache.shape)} != ({B * n_kv_heads * Dh}, {cap})")
+    if int(segments.shape[0]) != B * max_segments * 2:
+        raise ValueError(f"qf.owl_attn: segments shape {tuple(segments.shape)} != ({B * max_segments * 2},)")
+    if int(n_segments.shape[0]) != B:
+        raise ValueError(f"qf.owl_attn: n_segments shape {tuple(n_segments.shape)} != ({B},)")
+    if _dt(Q) != "bf16":
+        raise TypeError(f"qf.owl_attn: Q dtype {_dt(Q)!r} (expected bf16)")
+    kvd = _dt(K_cache)
+    cd = compute_dtype.value if hasattr(compute_dtype, "value") else compute_dtype
+    if cd is None:
+        cd = "bf16"
+    if cd != kvd:
+        raise NotImplementedError(
+            f"qf.owl_attn: compute_dtype={cd!r} with a {kvd!r} cache; supported pairs are bf16/bf16 and e4m3/e4m3"
+        )
+    od = out_dtype.value if hasattr(out_dtype, "value") else out_dtype
+    if od not in (None, "bf16"):
+        raise NotImplementedError(f"qf.owl_attn: out_dtype {od!r} (only bf16)")
+    if out is None:
+        out = QuarkTensor.empty(B * tpf, n_q * Dh, dtype="bf16")
+    elif out.numel != B * tpf * n_q * Dh or out.dtype != "bf16":
+        raise ValueError(f"qf.owl_attn: out is {out.shape} {out.dtype}, expected ({B * tpf}, {n_q * Dh}) bf16")
+    if frame_t is None:
+        if _DUMMY_FRAME_T is None:
+            _DUMMY_FRAME_T = QuarkTensor.zeros(1, dtype="s32")
+        frame_t = _DUMMY_FRAME_T
+    p = _lib.AttnParams(
+        n_kv_heads=n_kv_heads, gqa_ratio=gqa_ratio, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], compute_dtype=_lib.DTYPE_CODE[cd],
+        max_segments=max_segments, packed_qkv=1, quilt_factor=1, kv_splits=0,
+        k_scale=k_scale.data_ptr() if k_scale is not None else None,
+        v_scale=v_scale.data_ptr() if v_scale is not None else None,
+    )  # fmt: skip
+    lib = _lib.load()
+    need = int(lib.qb_owl_attn_workspace_bytes(C.byref(p)))
+    ws = _workspace(need) if need else None
+    _lib.check(
+        lib.qb_owl_attn(
+            _p(Q), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(frame_t), _p(out),
+            _p(rope_table(H_spatial, W_spatial)), C.byref(p), _p(ws), ws.nbytes if ws is not None else 0, _s(),
+        )
+    )  # fmt: skip
+    return out
+
+
+# ---------------------------------------------------------------------------
+# norm / elementwise ops
+# ---------------------------------------------------------------------------
+
+
+def _like(X, out, who):
+    if out is None:
+        return QuarkTensor.empty(*X.shape, dtype=X.dtype)
+    if out.numel != X.numel or out.dtype != X.dtype:
+        raise ValueError(f"{who}: out is {out.shape} {out.dtype}, expected {X.shape} {X.dtype}")
+    return out
+
+
+def _bf16_only(who, *ts):
+    for t in ts:
+        if _dt(t) != "bf16":
+            raise TypeError(f"{who}: dtype {_dt(t)!r} (expected bf16)")
+
+
+def ada_rmsnorm(X, scale, bias, eps: float = 1e-6, activation: str | None = None, *, out=None, out_q=None):
+    """``rmsnorm(x) * (1 + scale) + bias`` (+ SiLU) (``src/quark/functional/ada_rmsnorm.py:61``).
+
+    ``out_q`` (extension): an e4m3 tensor that also receives the result, for a following fp8 GEMM.
+    """
+    _bf16_only("qf.ada_rmsnorm", X, scale, bias)
+    D = int(X.shape[-1])
+    rows = X.numel // D
+    G = scale.numel // D
+    if scale.numel != G * D or bias.numel != G * D or G == 0 or rows % G:
+        raise ValueError(f"qf.ada_rmsnorm: X {X.shape}, scale {scale.shape}, bias {bias.shape} do not broadcast")
+    if activation not in (None, "silu"):
+        raise ValueError(f"qf.ada_rmsnorm: unsupported activation {activation!r}")
+    out = _like(X, out, "qf.ada_rmsnorm")
+    if out_q is not None and (out_q.dtype != "e4m3" or out_q.numel != X.numel):
+        raise ValueError("qf.ada_rmsnorm: out_q must be an e4m3 tensor of the same size")
+    _lib.check(
+        _lib.load().qb_ada_rmsnorm(_p(X), _p(scale), _p(bias), _p(out), _p(out_q), rows, D, G, float(eps), 1 if activation == "silu" else 0, _s())
+    )
+    return out
+
+
+def head_rmsnorm(X, n_q_heads: int, n_kv_heads: int, Dh: int, eps: float = 1e-6, *, out=None):
+    """Per-head RMS norm of the Q and K heads of packed QKV (``src/quark/functional/head_rmsnorm.py:33``)."""
+    _bf16_only("qf.head_rmsnorm", X)
+    if X.ndim != 2 or int(X.shape[1]) != (n_q_heads + 2 * n_kv_heads) * Dh:
+        raise ValueError(f"qf.head_rmsnorm: X shape {X.shape} is not [M, (n_q + 2 n_kv) * Dh]")
+    out = _like(X, out, "qf.head_rmsnorm")
+    _lib.check(_lib.load().qb_head_rmsnorm(_p(X), _p(out), int(X.shape[0]), n_q_heads, n_kv_heads, Dh, float(eps), _s()))
+    return out
+
+
+def value_residual_packed(QKV_curr, QKV_first, lamb, *, v_col_offset, v_width, out=None):
+    """``v += lamb * (v_first - v)`` on the V columns; ``lamb`` is an f32 device scalar."""
+    _bf16_only("qf.value_residual_packed", QKV_curr, QKV_first)
+    if QKV_curr.ndim != 2 or tuple(QKV_curr.shape) != tuple(QKV_first.shape):
+        raise ValueError(f"qf.value_residual_packed: shapes {QKV_curr.shape} and {QKV_first.shape}")
+    if _dt(lamb) != "f32":
+        raise TypeError("qf.value_residual_packed: lamb must be an f32 tensor")
+    out = _like(QKV_curr, out, "qf.value_residual_packed")
+    _lib.check(
+        _lib.load().qb_value_residual_packed(
+            _p(QKV_curr), _p(QKV_first), _p(lamb), _p(out), int(QKV_curr.shape[0]), int(QKV_curr.shape[1]), v_col_offset, v_width, _s()
+        )
+    )
+    return out
+
+
+def ada_gate_residual(X, Y, gate, *, out=None):
+    """``x + gate * y`` with the gate broadcast over groups of rows."""
+    _bf16_only("qf.ada_gate_residual", X, Y, gate)
+    D = int(X.shape[-1])
+    rows = X.numel // D
+    G = gate.numel // D
+    if Y.numel != X.numel or gate.numel != G * D or G == 0 or rows % G:
+        raise ValueError(f"qf.ada_gate_residual: X {X.shape}, Y {Y.shape}, gate {gate.shape} do not broadcast")
+    out = _like(X, out, "qf.ada_gate_residual")
+    _lib.check(_lib.load().qb_ada_gate_residual(_p(X), _p(Y), _p(gate), _p(out), rows, D, G, _s()))
+    return out
+
+
+def silu(X, *, out=None, out_q=None):
+    _bf16_only("qf.silu", X)
+    out = _like(X, out, "qf.silu")
+    if out_q is not None and (out_q.dtype != "e4m3" or out_q.numel != X.numel):
+        raise ValueError("qf.silu: out_q must be an e4m3 tensor of the same size")
+    _lib.check(_lib.load().qb_silu(_p(X), _p(out), _p(out_q), X.numel, _s()))
+    return out
+
+
+def euler_step(X, V, Dsig, *, out=None):
+    """``cast(f32(X) + f32(Dsig[0]) * f32(V), X.dtype)`` (``src/quark/functional/euler_step.py:36-41``)."""
+    _bf16_only("qf.euler_step", X, V)
+    if V.numel != X.numel:
+        raise ValueError(f"qf.euler_step: X {X.shape} and V {V.shape}")
+    if _dt(Dsig) != "f32":
+        raise TypeError("qf.euler_step: Dsig must be an f32 tensor")
+    out = _like(X, out, "qf.euler_step")
+    _lib.check(_lib.load().qb_euler_step(_p(X), _p(V), _p(Dsig), _p(out), X.numel, _s()))
+    return out
+
+
+def increment(counter):
+    if _dt(counter) != "s32":
+        raise TypeError("qf.increment: counter must be an s32 tensor")
+    _lib.check(_lib.load().qb_increment(_p(counter), _s()))
+    return counter
+
+
+def patchify(X, W, *, B: int, C: int, H: int, W_spatial: int, ph: int = 2, pw: int = 2, out=None):
+    """``[B, C*H*W] -> [B*Hp*Wp, d_model]`` (``src/quark/nn/layers.py:524-550``)."""
+    _bf16_only("qf.patchify", X, W)
+    if B != 1:
+        raise NotImplementedError("qf.patchify: only B=1 is supported")
+    if H % ph or W_spatial % pw:
+        raise ValueError(f"qf.patchify: H={H} W={W_spatial} not divisible by patch ({ph},{pw})")
+    d_model = int(W.shape[0])
+    if X.numel != C * H * W_spatial or int(W.shape[1]) != C * ph * pw:
+        raise ValueError(f"qf.patchify: X {X.shape} / W {W.shape} do not match C={C}, H={H}, W={W_spatial}")
+    tokens = (H // ph) * (W_spatial // pw)
+    if out is None:
+        out = QuarkTensor.empty(tokens, d_model, dtype="bf16")
+    elif out.numel != tokens * d_model:
+        raise ValueError(f"qf.patchify: out is {out.shape}, expected ({tokens}, {d_model})")
+    _lib.check(_lib.load().qb_patchify(_p(X), _p(W), _p(out), C, H, W_spatial, ph, pw, d_model, _s()))
+    return out
+
+
+def unpatchify(X, weight, bias, *, B: int, C: int, H: int, W: int, ph: int = 2, pw: int = 2, out=None):
+    """``[M, d_model] -> [B, C*H*W]`` (``src/quark/functional/unpatchify.py:18-20``)."""
+    _bf16_only("qf.unpatchify", X, weight)
+    if B != 1:
+        raise NotImplementedError("qf.unpatchify: only B=1 is supported")
+    if H % ph or W % pw:
+        raise ValueError(f"qf.unpatchify: H={H} W={W} not divisible by patch ({ph},{pw})")
+    d_model = int(weight.shape[1])
+    tokens = (H // ph) * (W // pw)
+    if X.numel != tokens * d_model or int(weight.shape[0]) != C * ph * pw:
+        raise ValueError(f"qf.unpatchify: X {X.shape} / weight {weight.shape} do not match C={C}, H={H}, W={W}")
+    if bias is not None and bias.numel != C * ph * pw:
+        raise ValueError(f"qf.unpatchify: bias has {bias.numel} elements, expected {C * ph * pw}")
+    if out is None:
+        out = QuarkTensor.empty(B, C * H * W, dtype="bf16")
+    elif out.numel != C * H * W:
+        raise ValueError(f"qf.unpatchify: out is {out.shape}, expected ({B}, {C * H * W})")
+    _lib.check(_lib.load().qb_unpatchify(_p(X), _p(weight), _p(bias), _p(out), C, H, W, ph, pw, d_model, _s()))
+    return out

@@ -1,0 +1,311 @@
+"""``quark.nn`` modules on the hot path, same class names and constructor keywords.
+
+Mirrors ``src/quark/nn/module.py:145-465`` (``Module`` / ``Parameter``) and the layers the
+Waypoint-1.5 block uses (``src/quark/nn/layers.py``): ``Linear``, ``MLP``, ``AdaRMSNorm``,
+``HeadRMSNorm``, ``ValueResidualPacked``, ``KVCacheUpdate``, ``OwlAttn``, ``AdaGateResidual``,
+``Patchify``, ``Unpatchify``, ``EulerStep``, ``SiLU``.  Every module owns its output buffer, so a
+forward pass allocates nothing after the first call and can be captured into a CUDA graph.
+"""
+
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import numpy as np
+
+from .. import functional as qf
+from ..runtime.tensor import QuarkTensor
+
+
+class Parameter:
+    """A tensor that appears in ``state_dict()`` (``src/quark/nn/module.py:129-142``)."""
+
+    __slots__ = ("data",)
+
+    def __init__(self, data):
+        self.data = data
+
+
+class Module:
+    def __call__(self, *args, **kwargs):
+        return self.forward(*args, **kwargs)
+
+    def forward(self, *args, **kwargs):
+        raise NotImplementedError
+
+    def _members(self):
+        for k, v in self.__dict__.items():
+            if isinstance(v, (Parameter, Module)):
+                yield k, v
+
+    def named_parameters(self, prefix: str = ""):
+        for name, v in self._members():
+            full = f"{prefix}.{name}" if prefix else name
+            if isinstance(v, Parameter):
+                yield full, v
+            else:
+                yield from v.named_parameters(full)
+
+    def named_modules(self, prefix: str = ""):
+        yield prefix, self
+        for name, v in self._members():
+            if isinstance(v, Module):
+                yield from v.named_modules(f"{prefix}.{name}" if prefix else name)
+
+    def state_dict(self):
+        return OrderedDict((k, p.data) for k, p in self.named_parameters())
+
+    def load_state_dict(self, sd: dict, strict: bool = True):
+        """Copy host arrays (carrier dtypes) or tensors into the parameters by name."""
+        own = dict(self.named_parameters())
+        missing = [k for k in own if k not in sd]
+        unexpected = [k for k in sd if k not in own]
+        if strict and (missing or unexpected):
+            raise KeyError(f"load_state_dict: missing {missing[:5]}, unexpected {unexpected[:5]}")
+        for k, p in own.items():
+            if k not in sd:
+                continue
+            v = sd[k]
+            if isinstance(v, QuarkTensor):
+                p.data = v
+            else:
+                v = np.asarray(v)
+                if v.size != p.data.numel:
+                    raise ValueError(f"load_state_dict: {k} has {v.size} elements, expected {p.data.numel}")
+                p.data = QuarkTensor.from_numpy(v.reshape(p.data.shape), dtype=p.data.dtype)
+
+    def prepare(self, **kwargs):
+        for _, v in self._members():
+            if isinstance(v, Module):
+                v.prepare(**kwargs)
+
+
+class ModuleList(Module):
+    def __init__(self, modules=()):
+        self._list = list(modules)
+
+    def _members(self):
+        for i, m in enumerate(self._list):
+            yield str(i), m
+
+    def __iter__(self):
+        return iter(self._list)
+
+    def __len__(self):
+        return len(self._list)
+
+    def __getitem__(self, i):
+        return self._list[i]
+
+
+def _cached(module, key: str, shape, dtype) -> QuarkTensor:
+    """Per-module output buffers keyed by (name, shape, dtype) (``src/quark/nn/layers.py:236-258``)."""
+    cache = module.__dict__.setdefault("_bufs", {})
+    k = (key, tuple(shape), dtype)
+    buf = cache.get(k)
+    if buf is None:
+        buf = QuarkTensor.empty(*shape, dtype=dtype)
+        cache[k] = buf
+    return buf
+
+
+class Linear(Module):
+    """``y = x @ weight.T`` through ``qf.gemm`` (``src/quark/nn/layers.py:261-467``).
+
+    ``prepare(fp8=True)`` narrows the bf16 weight to unscaled e4m3 with ``qf.quantize_e4m3`` like
+    the reference (``layers.py:291-304``).  Unlike the reference there is no per-call memset of
+    the output: split-K partials live in the workspace, not in the output buffer.
+    """
+
+    def __init__(self, in_features: int, out_features: int, *, bias: bool = False, out_dtype: str = "bf16", fp8_skip: bool = False):
+        self.weight = Parameter(QuarkTensor.zeros(out_features, in_features, dtype="bf16"))
+        self._has_bias = bias
+        self._out_dtype = out_dtype
+        self._fp8_skip = fp8_skip
+        self._fp8 = False
+        if bias:
+            self.bias = Parameter(QuarkTensor.zeros(out_features, dtype="bf16"))
+
+    def prepare(self, *, shuffle: bool = False, fp8: bool = False, **kwargs):
+        if shuffle:
+            raise RuntimeError("weight shuffling is not supported (it is disabled upstream as well)")
+        if fp8 and not self._fp8_skip and not self._fp8:
+            self.weight.data = qf.quantize_e4m3(self.weight.data)
+            self._fp8 = True
+
+    def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None):
+        a_dt = x.dtype
+        if a_dt not in ("bf16", "e4m3"):
+            raise TypeError(f"Linear: activation dtype {a_dt!r} not in ('bf16', 'e4m3'). Insert a cast upstream.")
+        fused_gate = gate is not None and residual is not None
+        if fused_gate and bias is not None:
+            raise ValueError("Linear.forward: gate/residual fusion is incompatible with bias")
+        if self._has_bias and bias is not None:
+            raise ValueError("Linear: call-time bias= conflicts with a layer constructed with bias=True")
+        b_dt = self.weight.data.dtype
+        if a_dt == "e4m3" and b_dt != "e4m3":
+            raise TypeError("Linear: an e4m3 activation needs an e4m3 weight (call prepare(fp8=True))")
+        od = out_dtype or self._out_dtype
+        M = x.numel // int(x.shape[-1])
+        N = int(self.weight.data.shape[0])
+        if out is None:
+            out = _cached(self, "out", (M, N), od)
+        return qf.gemm(
+            x, self.weight.data, out_dtype=od, compute_dtype=b_dt if b_dt == "e4m3" else None, activation=activation,
+            bias=self.bias.data if self._has_bias else bias, gate=gate, residual=residual, gate_groups=gate_groups, out=out,
+        )  # fmt: skip
+
+
+class SiLU(Module):
+    def forward(self, x, *, emit_e4m3: bool = False):
+        out = _cached(self, "out", x.shape, x.dtype)
+        out_q = _cached(self, "out_q", x.shape, "e4m3") if emit_e4m3 else None
+        qf.silu(x, out=out, out_q=out_q)
+        return out_q if emit_e4m3 else out
+
+
+class MLP(Module):
+    """``fc2(silu(fc1(x)))`` with the optional gate/residual epilogue on fc2 (``layers.py:700-757``).
+
+    ``fuse_silu=True`` folds SiLU into fc1's epilogue (the reference does so on its PTX and Metal
+    GEMMs, ``src/quark/kernels/gemm/spec.py:54-59``); otherwise SiLU is its own launch as on the
+    reference's cuBLAS route.  With an fp8 fc2 the hidden activation is handed over in e4m3.
+    """
+
+    def __init__(self, d_in: int, d_mid: int, d_out: int, out_dtype: str = "bf16", *, hidden_out_dtype: str | None = None, fuse_silu: bool = False):
+        self.fc1 = Linear(d_in, d_mid, out_dtype=hidden_out_dtype or out_dtype)
+        self.fc2 = Linear(d_mid, d_out, out_dtype=out_dtype)
+        self.silu = SiLU()
+        self._fuse_silu = fuse_silu
+
+    def forward(self, x, *, gate=None, residual=None, gate_groups: int = 1, out=None):
+        fp8 = self.fc2.weight.data.dtype == "e4m3"
+        if self._fuse_silu:
+            h = self.fc1(x, activation="silu", out_dtype="e4m3" if fp8 else None)
+        else:
+            h = self.silu(self.fc1(x), emit_e4m3=fp8)
+        return self.fc2(h, gate=gate, residual=residual, gate_groups=gate_groups, out=out)
+
+
+class AdaRMSNorm(Module):
+    """Stateless ``rmsnorm(x) * (1 + scale) + bias`` (``layers.py:609-619``)."""
+
+    def forward(self, x, scale, bias, *, activation=None, emit_e4m3: bool = False):
+        out = _cached(self, "out", x.shape, x.dtype)
+        out_q = _cached(self, "out_q", x.shape, "e4m3") if emit_e4m3 else None
+        qf.ada_rmsnorm(x, scale, bias, activation=activation, out=out, out_q=out_q)
+        return out_q if emit_e4m3 else out
+
+
+class AdaGateResidual(Module):
+    def forward(self, x, y, gate):
+        return qf.ada_gate_residual(x, y, gate, out=_cached(self, "out", x.shape, x.dtype))
+
+
+class HeadRMSNorm(Module):
+    def __init__(self, n_q_heads: int, n_kv_heads: int, Dh: int):
+        self._nq, self._Hk, self._Dh = n_q_heads, n_kv_heads, Dh
+
+    def forward(self, qkv):
+        return qf.head_rmsnorm(qkv, n_q_heads=self._nq, n_kv_heads=self._Hk, Dh=self._Dh, out=_cached(self, "out", qkv.shape, qkv.dtype))
+
+
+class ValueResidualPacked(Module):
+    """``v += lamb * (v_first - v)`` with a learnable f32 scalar (``layers.py:825-843``)."""
+
+    def __init__(self, v_col_offset: int, v_width: int, lamb: float = 0.5):
+        self._vo, self._vw = v_col_offset, v_width
+        self.lamb = Parameter(QuarkTensor.from_numpy(np.array([lamb], dtype=np.float32)))
+
+    def forward(self, qkv, qkv_first):
+        return qf.value_residual_packed(
+            qkv, qkv_first, self.lamb.data, v_col_offset=self._vo, v_width=self._vw, out=_cached(self, "out", qkv.shape, qkv.dtype)
+        )
+
+
+class EulerStep(Module):
+    def forward(self, x, v, dsig):
+        return qf.euler_step(x, v, dsig, out=_cached(self, "out", x.shape, x.dtype))
+
+
+class Patchify(Module):
+    def __init__(self, C: int, d_model: int, H: int, W: int, ph: int = 2, pw: int = 2):
+        self.weight = Parameter(QuarkTensor.zeros(d_model, C * ph * pw, dtype="bf16"))
+        self._C, self._H, self._W, self._ph, self._pw = C, H, W, ph, pw
+
+    def forward(self, x):
+        d_model = int(self.weight.data.shape[0])
+        rows = (self._H // self._ph) * (self._W // self._pw)
+        out = _cached(self, "out", (rows, d_model), "bf16")
+        return qf.patchify(x, self.weight.data, B=1, C=self._C, H=self._H, W_spatial=self._W, ph=self._ph, pw=self._pw, out=out)
+
+
+class Unpatchify(Module):
+    def __init__(self, d_model: int, C: int, H: int, W: int, ph: int = 2, pw: int = 2):
+        self.weight = Parameter(QuarkTensor.zeros(C * ph * pw, d_model, dtype="bf16"))
+        self.bias = Parameter(QuarkTensor.zeros(C * ph * pw, dtype="bf16"))
+        self._C, self._H, self._W, self._ph, self._pw = C, H, W, ph, pw
+
+    def forward(self, x, B: int = 1):
+        out = _cached(self, "out", (B, self._C * self._H * self._W), "bf16")
+        return qf.unpatchify(x, self.weight.data, self.bias.data, B=B, C=self._C, H=self._H, W=self._W, ph=self._ph, pw=self._pw, out=out)
+
+
+class KVCacheUpdate(Module):
+    """Per-layer cache state and its append (``src/quark/nn/layers.py:846-970``)."""
+
+    def __init__(self, *, B: int, n_kv_heads: int, n_q_heads: int, H_spatial: int, W_spatial: int, Dh: int, num_buckets: int,
+                 pinned_dilation: int, packed_qkv: bool, rope_n_frames: int = 1, dtype: str = "bf16", quilt_factor: int = 1,
+                 quilt_offset: int = 0):  # fmt: skip
+        tpf = H_spatial * W_spatial
+        if tpf % quilt_factor != 0:
+            raise ValueError(f"KVCacheUpdate: tpf={tpf} not divisible by quilt_factor={quilt_factor}")
+        if quilt_factor != 1:
+            raise NotImplementedError("KVCacheUpdate: quilt_factor > 1 is not supported")
+        L = num_buckets * tpf
+        cap = L + tpf
+        self.K_cache = QuarkTensor.zeros(B * n_kv_heads * cap, Dh, dtype=dtype)
+        self.Vt_cache = QuarkTensor.zeros(B * n_kv_heads * Dh, cap, dtype=dtype)
+        self.segments = QuarkTensor.from_numpy(np.array([0, 0, L, tpf, 0, 0], dtype=np.int32))
+        self.n_segments = QuarkTensor.from_numpy(np.array([2], dtype=np.int32))
+        self.frame_t = QuarkTensor.zeros(1, dtype="s32")
+        # frozen = 1 and frozen = 0 as two constant device scalars: no per-call memset in the graph
+        self._frozen = (QuarkTensor.from_numpy(np.array([0], dtype=np.int32)), QuarkTensor.from_numpy(np.array([1], dtype=np.int32)))
+        self._L, self._tpf = L, tpf
+        self._kw = dict(B=B, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
+                        pinned_dilation=pinned_dilation, packed_qkv=packed_qkv, n_q_heads=n_q_heads, quilt_factor=quilt_factor,
+                        quilt_offset=quilt_offset)  # fmt: skip
+
+    def forward(self, qkv, frame_t=None, frozen: bool = False):
+        ft = frame_t if frame_t is not None else self.frame_t
+        qf.kv_cache_update(qkv, qkv, ft, self._frozen[1 if frozen else 0], self.Vt_cache, self.segments, self.n_segments, self.K_cache, **self._kw)
+
+    def set_frame_t(self, value: int) -> None:
+        self.frame_t.copy_from_numpy(np.array([value], dtype=np.int32))
+
+    def reset(self) -> None:
+        self.K_cache.zero_()
+        self.Vt_cache.zero_()
+        self.segments.copy_from_numpy(np.array([0, 0, self._L, self._tpf, 0, 0], dtype=np.int32))
+        self.n_segments.copy_from_numpy(np.array([2], dtype=np.int32))
+        self.set_frame_t(0)
+
+
+class OwlAttn(Module):
+    """Carries the per-layer attention keywords (``src/quark/nn/layers.py:973-1038``)."""
+
+    def __init__(self, *, B: int, n_kv_heads: int, gqa_ratio: int, H_spatial: int, W_spatial: int, num_buckets: int,
+                 pinned_dilation: int, packed_qkv: bool, rope_n_frames: int = 1, compute_dtype: str | None = "e4m3",
+                 quilt_factor: int = 1, quilt_offset: int = 0):  # fmt: skip
+        self._kw = dict(B=B, n_kv_heads=n_kv_heads, gqa_ratio=gqa_ratio, H_spatial=H_spatial, W_spatial=W_spatial,
+                        num_buckets=num_buckets, pinned_dilation=pinned_dilation, packed_qkv=packed_qkv,
+                        quilt_factor=quilt_factor, quilt_offset=quilt_offset)  # fmt: skip
+        self._compute_dtype = compute_dtype
+
+    def forward(self, qkv, kv_cache: KVCacheUpdate, frame_t=None):
+        n_kv, gqa = self._kw["n_kv_heads"], self._kw["gqa_ratio"]
+        n_q = n_kv * gqa
+        Dh = int(qkv.shape[1]) // (n_q + 2 * n_kv)
+        out = _cached(self, "out", (int(qkv.shape[0]), n_q * Dh), qkv.dtype)
+        return qf.owl_attn(qkv, kv_cache.K_cache, kv_cache.Vt_cache, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
+                           out=out, compute_dtype=self._compute_dtype, **self._kw)  # fmt: skip

@@ -1,0 +1,386 @@
+"""GPU parity of every kernel against the CPU oracle, through the qf.* layer and the C ABI.
+
+Inputs are seeded; small shapes come from the golden fixtures (so the CUDA result is also tied
+to what the reference's own numpy oracles produced), large shapes are the BASELINE shapes
+(360p: 128 tokens, 720p: 512 tokens; d_model 2048, 32 Q / 16 KV heads of 64).
+"""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import codec, ops
+from tests import util
+from tests.util import assert_close_bf16, bf16_randn, e4m3_randn, f32
+
+pytestmark = pytest.mark.gpu
+G = Path(__file__).parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def qb():
+    import quark_b200 as q
+
+    q._lib.require_device(0)
+    yield q
+    q.runtime.synchronize()
+    assert q._lib.device_status() == 0, "a kernel reported a timed-out wait or a bad segment table"
+
+
+def T(qb, arr, dtype=None):
+    return qb.QuarkTensor.from_numpy(np.asarray(arr), dtype=dtype)
+
+
+# --------------------------------------------------------------------------- e4m3 narrowing
+
+
+def test_quantize_e4m3_every_bf16_value_bit_exact(qb):
+    allb = np.arange(65536, dtype=np.uint16)
+    got = qb.qf.quantize_e4m3(T(qb, allb, "bf16")).to_numpy()
+    want = codec.f32_to_e4m3(codec.bf16_to_f32(allb))
+    nan = np.isnan(codec.bf16_to_f32(allb))
+    np.testing.assert_array_equal(got[~nan], want[~nan])
+    assert np.all((got[nan] & 0x7F) == 0x7F)
+    # the reference's own encoder differs only in its documented subnormal band
+    ref = np.load(G / "codec.npz")["e4m3_of_all_bf16"]
+    assert int(np.count_nonzero(got[~nan] != ref[~nan])) == 32
+
+
+def test_quantize_e4m3_from_f32_and_ragged_tail(qb):
+    r = util.rng(1)
+    x = (r.standard_normal(1000 + 13) * 30).astype(np.float32)
+    x[:6] = [0.0, -0.0, 448.0, 1e9, -1e9, 0.0146484375]
+    got = qb.qf.quantize_e4m3(T(qb, x)).to_numpy()
+    np.testing.assert_array_equal(got, codec.f32_to_e4m3(x))
+
+
+# --------------------------------------------------------------------------- glue ops
+
+
+@pytest.mark.parametrize("rows,D", [(32, 256), (128, 2048), (512, 2048)])
+@pytest.mark.parametrize("act", [None, "silu"])
+def test_ada_rmsnorm(qb, rows, D, act):
+    r = util.rng(2)
+    X, s, b = bf16_randn(r, (rows, D)), bf16_randn(r, (1, D), 0.1), bf16_randn(r, (1, D), 0.1)
+    outq = qb.QuarkTensor.empty(rows, D, dtype="e4m3")
+    got = qb.qf.ada_rmsnorm(T(qb, X, "bf16"), T(qb, s, "bf16"), T(qb, b, "bf16"), activation=act, out_q=outq).to_numpy()
+    want = ops.ada_rmsnorm(X, s, b, activation=act)
+    assert_close_bf16(got, want, "ada_rmsnorm")
+    assert np.percentile(util.bf16_ulp_diff(got, want), 99.9) <= 1
+    # the e4m3 side output is the narrowing of the bf16 output, byte for byte
+    np.testing.assert_array_equal(outq.to_numpy(), codec.f32_to_e4m3(codec.bf16_to_f32(got)))
+
+
+def test_glue_ops_against_golden_inputs(qb):
+    z = np.load(G / "glue.npz")
+    qf = qb.qf
+    X, Y, sc = T(qb, z["X"], "bf16"), T(qb, z["Y"], "bf16"), T(qb, z["scale"], "bf16")
+    assert_close_bf16(qf.silu(X).to_numpy().ravel(), z["silu"].ravel(), "silu")
+    assert_close_bf16(qf.ada_gate_residual(X, Y, sc).to_numpy(), z["ada_gate_residual"], "ada_gate_residual")
+    assert_close_bf16(qf.ada_rmsnorm(X, sc, T(qb, z["bias"], "bf16")).to_numpy(), z["ada_rmsnorm"], "ada_rmsnorm")
+    QKV, QKV0 = T(qb, z["QKV"], "bf16"), T(qb, z["QKV0"], "bf16")
+    got = qf.head_rmsnorm(QKV, n_q_heads=2, n_kv_heads=1, Dh=64).to_numpy()
+    assert_close_bf16(got, z["head_rmsnorm"], "head_rmsnorm")
+    np.testing.assert_array_equal(got[:, 192:], z["QKV"][:, 192:])  # V columns are copied
+    lam = T(qb, np.array([0.37], dtype=np.float32))
+    got = qf.value_residual_packed(QKV, QKV0, lam, v_col_offset=192, v_width=64).to_numpy()
+    assert_close_bf16(got, z["value_residual_packed"], "value_residual_packed")
+    np.testing.assert_array_equal(got[:, :192], z["QKV"][:, :192])  # Q and K columns are copied
+    got = qf.patchify(T(qb, z["lat"], "bf16"), T(qb, z["Wp"], "bf16"), B=1, C=4, H=8, W_spatial=12, ph=2, pw=2).to_numpy()
+    assert_close_bf16(got, z["patchify"], "patchify")
+    got = qf.unpatchify(T(qb, z["tok"], "bf16"), T(qb, z["Wu"], "bf16"), T(qb, z["bu"], "bf16"), B=1, C=4, H=8, W=12).to_numpy()
+    assert_close_bf16(got, z["unpatchify"], "unpatchify")
+
+
+def test_glue_ops_at_model_size(qb):
+    r = util.rng(3)
+    qf = qb.qf
+    tpf, d = 512, 2048
+    X, Y, g = bf16_randn(r, (tpf, d)), bf16_randn(r, (tpf, d)), bf16_randn(r, (1, d))
+    assert_close_bf16(qf.ada_gate_residual(T(qb, X, "bf16"), T(qb, Y, "bf16"), T(qb, g, "bf16")).to_numpy(), ops.ada_gate_residual(X, Y, g), "gate")
+    H1 = bf16_randn(r, (tpf, 8192), 2.0)
+    oq = qb.QuarkTensor.empty(tpf, 8192, dtype="e4m3")
+    got = qf.silu(T(qb, H1, "bf16"), out_q=oq).to_numpy()
+    assert_close_bf16(got, ops.silu(H1), "silu")
+    np.testing.assert_array_equal(oq.to_numpy(), codec.f32_to_e4m3(codec.bf16_to_f32(got)))
+    QKV, QKV0 = bf16_randn(r, (tpf, 4096)), bf16_randn(r, (tpf, 4096))
+    assert_close_bf16(qf.head_rmsnorm(T(qb, QKV, "bf16"), 32, 16, 64).to_numpy(), ops.head_rmsnorm(QKV, n_q_heads=32, n_kv_heads=16), "head_rmsnorm")
+    lam = T(qb, np.array([0.5], dtype=np.float32))
+    got = qf.value_residual_packed(T(qb, QKV, "bf16"), T(qb, QKV0, "bf16"), lam, v_col_offset=3072, v_width=1024).to_numpy()
+    assert_close_bf16(got, ops.value_residual_packed(QKV, QKV0, 0.5, v_col_offset=3072, v_width=1024), "value_residual")
+    lat, v = bf16_randn(r, (1, 32 * 32 * 64)), bf16_randn(r, (1, 32 * 32 * 64))
+    ds = T(qb, np.array([-0.15], dtype=np.float32))
+    assert_close_bf16(qf.euler_step(T(qb, lat, "bf16"), T(qb, v, "bf16"), ds).to_numpy(), ops.euler_step(lat, v, -0.15), "euler")
+    Wp = bf16_randn(r, (d, 128), 0.02)
+    got = qf.patchify(T(qb, lat, "bf16"), T(qb, Wp, "bf16"), B=1, C=32, H=32, W_spatial=64, ph=2, pw=2).to_numpy()
+    assert_close_bf16(got, ops.patchify(lat, Wp, C=32, H=32, Wd=64), "patchify")
+    Wu, bu = bf16_randn(r, (128, d), 0.02), bf16_randn(r, (128,), 0.1)
+    got = qf.unpatchify(T(qb, X, "bf16"), T(qb, Wu, "bf16"), T(qb, bu, "bf16"), B=1, C=32, H=32, W=64).to_numpy()
+    assert_close_bf16(got, ops.unpatchify(X, Wu, bu, C=32, H=32, Wd=64), "unpatchify")
+    c = T(qb, np.array([41], dtype=np.int32))
+    qf.increment(c)
+    assert c.to_numpy().tolist() == [42]
+
+
+def test_rope_table_device_builder_matches_numpy(qb):
+    import ctypes as C
+
+    for H, W in [(16, 8), (8, 16), (32, 16), (8, 8)]:
+        want = qb.qf.rope_table_numpy(H, W)
+        t = qb.QuarkTensor.empty(H * W, 16, dtype="f32")
+        qb._lib.check(qb._lib.load().qb_rope_table_build(C.c_void_p(t.data_ptr()), H, W, C.c_void_p(qb.runtime.active_stream())))
+        got = t.to_numpy()
+        assert np.max(np.abs(got - want)) <= 2.5e-7, (H, W)
+        # and the host table equals the oracle's table column for column
+        c, s = ops.rope_tables(H, W, 0)
+        np.testing.assert_array_equal(want[:, :8], c[:, 0:16:2])
+        np.testing.assert_array_equal(want[:, 8:], s[:, 0:16:2])
+
+
+# --------------------------------------------------------------------------- KV-cache append
+
+
+def _kv_run(qb, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt, prefill=None):
+    tpf, cap = H * W, (nb + 1) * H * W
+    carrier = np.uint16 if kv_dt == "bf16" else np.uint8
+    K0 = np.zeros((Hk * cap, 64), carrier) if prefill is None else np.full((Hk * cap, 64), prefill, carrier)
+    V0 = np.zeros((Hk * 64, cap), carrier) if prefill is None else np.full((Hk * 64, cap), prefill, carrier)
+    Kc, Vc = T(qb, K0, kv_dt), T(qb, V0, kv_dt)
+    segs, nseg = T(qb, np.full(6, -7, np.int32)), T(qb, np.array([-7], np.int32))
+    out = qb.qf.kv_cache_update(
+        T(qb, qkv, "bf16"), None, T(qb, np.array([ft], np.int32)), T(qb, np.array([frozen], np.int32)), Vc, segs, nseg, Kc,
+        B=1, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, packed_qkv=True, n_q_heads=Hq,
+    )  # fmt: skip
+    assert out[0] is Kc and out[1] is Vc
+    return Kc.to_numpy(), Vc.to_numpy(), segs.to_numpy(), nseg.to_numpy()
+
+
+def _check_kv(K, Vt, segs, nseg, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt):
+    wK, wV, wsegs, wn = ops.kv_cache_update(
+        qkv, ft, frozen, n_kv_heads=Hk, n_q_heads=Hq, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, kv_dtype=kv_dt
+    )
+    np.testing.assert_array_equal(segs, wsegs)
+    np.testing.assert_array_equal(nseg, wn)
+    np.testing.assert_array_equal(Vt != 0, wV != 0)  # slot indexing: exactly the same cells written
+    if kv_dt == "e4m3":
+        np.testing.assert_array_equal(Vt, wV)  # e4m3 encodings of given values: bit-exact
+        # K bytes depend on sin/cos of the temporal angle: allow the encoding to flip by one step
+        # where the rotated value sits on a rounding boundary, nothing more, and only rarely
+        diff = K != wK
+        assert diff.mean() <= 2e-3, f"{diff.sum()} of {K.size} K bytes differ"
+        assert np.all(np.abs(K.astype(np.int16)[diff] - wK.astype(np.int16)[diff]) <= 1)
+    else:
+        np.testing.assert_array_equal(Vt, wV)  # a bf16 V value is copied
+        assert np.max(util.bf16_ulp_diff(K, wK)[np.abs(f32(wK, "bf16")) > 1e-2]) <= 2  # RN on the GPU, truncation in the oracle
+        assert_close_bf16(K, wK, "K_cache")
+    np.testing.assert_array_equal(K.any(axis=1), wK.any(axis=1))  # same rows written
+
+
+def test_kv_cache_update_golden_cases(qb):
+    z = np.load(G / "kv_cache_update.npz")
+    Hq, Hk, H, W, nb = (int(v) for v in z["geometry"])
+    for tag in z["cases"].tolist():
+        kv_dt, pd, ft, frozen = tag.split("_")
+        geo = dict(Hq=Hq, Hk=Hk, H=H, W=W, nb=nb, pd=int(pd), kv_dt=kv_dt)
+        K, Vt, segs, nseg = _kv_run(qb, z["qkv"], int(ft), int(frozen), **geo)
+        _check_kv(K, Vt, segs, nseg, z["qkv"], int(ft), int(frozen), **geo)
+        np.testing.assert_array_equal(segs, z[f"{tag}.segments"])  # and against the reference's own output
+        np.testing.assert_array_equal(nseg, z[f"{tag}.n_segments"])
+
+
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,pd,ft,frozen", [(16, 8, 1, 16, 1), (16, 8, 8, 128, 0), (8, 16, 8, 129, 0), (32, 16, 1, 5, 0), (32, 16, 8, 1000, 1)])
+def test_kv_cache_update_model_geometry(qb, kv_dt, H, W, pd, ft, frozen):
+    r = util.rng(ft)
+    geo = dict(Hq=32, Hk=16, H=H, W=W, nb=16, pd=pd, kv_dt=kv_dt)
+    qkv = bf16_randn(r, (H * W, 4096))
+    K, Vt, segs, nseg = _kv_run(qb, qkv, ft, frozen, **geo)
+    _check_kv(K, Vt, segs, nseg, qkv, ft, frozen, **geo)
+
+
+def test_kv_cache_update_is_read_modify_write(qb):
+    r = util.rng(5)
+    geo = dict(Hq=4, Hk=2, H=8, W=8, nb=4, pd=1, kv_dt="bf16")
+    qkv = bf16_randn(r, (64, 512))
+    K, Vt, _, _ = _kv_run(qb, qkv, 3, 0, prefill=0x1234, **geo)
+    cap = 5 * 64
+    written = np.zeros(cap, bool)
+    written[3 * 64 : 4 * 64] = True
+    written[4 * 64 :] = True
+    assert np.all(K.reshape(2, cap, 64)[:, ~written] == 0x1234)
+    assert np.all(Vt.reshape(2, 64, cap)[:, :, ~written] == 0x1234)
+    assert not np.any(K.reshape(2, cap, 64)[:, written] == 0x1234)
+
+
+# --------------------------------------------------------------------------- GEMM
+
+
+def _gemm_case(qb, M, N, K, *, fp8=False, a_fp8=False, bias=False, act=None, gate_groups=0, split_k=0, tile_n=0, out_dtype="bf16", seed=0):
+    r = util.rng(seed)
+    A = bf16_randn(r, (M, K))
+    if fp8:
+        B = e4m3_randn(r, (N, K), 0.5)
+        Aq = codec.f32_to_e4m3(f32(A, "bf16"))
+    else:
+        B = bf16_randn(r, (N, K), 0.05)
+    kw, okw = {}, {}
+    if bias:
+        b = bf16_randn(r, (N,))
+        kw["bias"], okw["bias"] = T(qb, b, "bf16"), b
+    if gate_groups:
+        g, res = bf16_randn(r, (gate_groups, N)), bf16_randn(r, (M, N))
+        kw.update(gate=T(qb, g, "bf16"), residual=T(qb, res, "bf16"), gate_groups=gate_groups)
+        okw.update(gate=g, residual=res, gate_groups=gate_groups)
+    a_dev = T(qb, Aq, "e4m3") if (fp8 and a_fp8) else T(qb, A, "bf16")
+    got = qb.qf.gemm(a_dev, T(qb, B, "e4m3" if fp8 else "bf16"), out_dtype=out_dtype, compute_dtype="e4m3" if fp8 else None,
+                     activation=act, split_k=split_k, tile_n=tile_n, **kw)  # fmt: skip
+    want32 = ops.gemm(A, B, b_dtype="e4m3" if fp8 else "bf16", a_quant="e4m3" if fp8 else None, activation=act, return_f32=True, **okw)
+    return got, want32
+
+
+def _check_gemm(got, want32, what, fp8):
+    if got.dtype == "bf16":
+        g = f32(got.to_numpy(), "bf16")
+    elif got.dtype == "f32":
+        g = got.to_numpy()
+    else:
+        g = f32(got.to_numpy(), "e4m3")
+    assert np.all(np.isfinite(g)), what
+    cs, mr = util.cosine(g, want32), util.max_rel(g, want32)
+    if got.dtype == "e4m3":
+        assert cs >= 0.995, f"{what}: cosine={cs:.6f}"  # 3 mantissa bits in the output itself
+    elif fp8:
+        assert cs >= util.COS_MIN and mr <= util.BF16_MAX_REL, f"{what}: cosine={cs:.6f} max_rel={mr:.3e}"
+    else:
+        assert mr <= util.BF16_MAX_REL and cs >= util.COS_MIN, f"{what}: max_rel={mr:.3e} cosine={cs:.6f}"
+
+
+SMALL = [(64, 128, 256), (32, 64, 128), (128, 128, 256), (32, 64, 64), (200, 72, 80), (1, 8, 16), (130, 264, 2048 + 64)]
+
+
+@pytest.mark.parametrize("M,N,K", SMALL)
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_small_and_ragged_shapes(qb, M, N, K, fp8):
+    got, want = _gemm_case(qb, M, N, K, fp8=fp8, seed=M + N + K)
+    _check_gemm(got, want, f"gemm {M}x{N}x{K} fp8={fp8}", fp8)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_epilogues(qb, fp8):
+    for kw in [dict(bias=True), dict(act="silu"), dict(bias=True, act="silu"), dict(gate_groups=1), dict(gate_groups=4),
+               dict(out_dtype="f32"), dict(out_dtype="e4m3", act="silu"), dict(a_fp8=True)]:  # fmt: skip
+        if kw.get("a_fp8") and not fp8:
+            continue
+        got, want = _gemm_case(qb, 128, 256, 512, fp8=fp8, seed=11, **kw)
+        _check_gemm(got, want, f"epilogue {kw} fp8={fp8}", fp8)
+
+
+def test_gemm_matches_golden_fixture(qb):
+    z = np.load(G / "gemm.npz")
+    A, B = T(qb, z["A"], "bf16"), T(qb, z["B"], "bf16")
+    qf = qb.qf
+    assert_close_bf16(qf.gemm(A, B).to_numpy(), z["plain"], "plain")
+    assert_close_bf16(qf.gemm(A, B, bias=T(qb, z["bias"], "bf16"), activation="silu").to_numpy(), z["bias_silu"], "bias_silu")
+    assert_close_bf16(qf.gemm(A, B, gate=T(qb, z["gate"][:1], "bf16"), residual=T(qb, z["resid"], "bf16")).to_numpy(), z["gate1"], "gate1")
+    assert_close_bf16(qf.gemm(A, B, gate=T(qb, z["gate"], "bf16"), residual=T(qb, z["resid"], "bf16"), gate_groups=4).to_numpy(), z["gate4"], "gate4")
+
+
+@pytest.mark.parametrize("M", [128, 512])
+@pytest.mark.parametrize("name,N,K,extra", [("qkv", 4096, 2048, {}), ("out", 2048, 2048, dict(gate_groups=1)), ("fc1", 8192, 2048, {}), ("fc2", 2048, 8192, dict(gate_groups=1))])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_production_shapes(qb, M, name, N, K, extra, fp8):
+    got, want = _gemm_case(qb, M, N, K, fp8=fp8, seed=7, **extra)
+    _check_gemm(got, want, f"{name} M={M} fp8={fp8}", fp8)
+
+
+@pytest.mark.parametrize("split_k,tile_n", [(1, 64), (1, 128), (1, 256), (2, 128), (4, 64), (8, 256), (3, 128)])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_forced_tiles_and_k_slices_agree(qb, split_k, tile_n, fp8):
+    got, want = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, seed=3)
+    _check_gemm(got, want, f"split_k={split_k} tile_n={tile_n}", fp8)
+    again, _ = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, seed=3)
+    np.testing.assert_array_equal(got.to_numpy(), again.to_numpy())  # slice order is fixed: run-to-run identical
+
+
+def test_gemm_scales_extension(qb):
+    r = util.rng(9)
+    A, B = bf16_randn(r, (128, 256)), e4m3_randn(r, (64, 256))
+    ws = (0.5 + r.random(64)).astype(np.float32)
+    got = qb.qf.gemm(T(qb, A, "bf16"), T(qb, B, "e4m3"), compute_dtype="e4m3", a_scale=T(qb, np.array([0.25], np.float32)), w_scale=T(qb, ws))
+    want = ops.gemm(A, B, b_dtype="e4m3", a_quant="e4m3", return_f32=True) * 0.25 * ws[None, :]
+    _check_gemm(got, want, "scaled fp8", True)
+
+
+# --------------------------------------------------------------------------- owl_attn
+
+
+def _attn_run(qb, qkv, Kc, Vc, segs, nseg, ft, *, Hk, gqa, H, W, nb, pd, kv_dt):
+    return qb.qf.owl_attn(
+        T(qb, qkv, "bf16"), T(qb, Kc, kv_dt), T(qb, Vc, kv_dt), T(qb, np.asarray(segs, np.int32)), T(qb, np.asarray(nseg, np.int32).reshape(1)),
+        1, Hk, gqa, H, W, nb, pd, compute_dtype="e4m3" if kv_dt == "e4m3" else None, packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32)),
+    ).to_numpy()  # fmt: skip
+
+
+def _attn_check(got, want_u16, what, fp8):
+    g, w = f32(got, "bf16"), f32(want_u16, "bf16")
+    assert np.all(np.isfinite(g)), what
+    cs, mr = util.cosine(g, w), util.max_rel(g, w)
+    if fp8:
+        assert cs >= util.COS_MIN, f"{what}: cosine={cs:.6f} max_rel={mr:.3e}"
+    else:
+        assert mr <= util.BF16_MAX_REL and cs >= util.COS_MIN, f"{what}: max_rel={mr:.3e} cosine={cs:.6f}"
+
+
+def test_owl_attn_golden_cases(qb):
+    z = np.load(G / "owl_attn.npz")
+    Hk, gqa, H, W, nb = (int(v) for v in z["geometry"])
+    for tag in z["cases"].tolist():
+        kv_dt, pd, ft = tag.split("_")
+        got = _attn_run(qb, z["qkv"], z[f"K_{kv_dt}"], z[f"Vt_{kv_dt}"], z[f"{tag}.segments"], z[f"{tag}.n_segments"], int(ft),
+                        Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=int(pd), kv_dt=kv_dt)  # fmt: skip
+        _attn_check(got, z[f"{tag}.out"], f"golden {tag}", kv_dt == "e4m3")
+
+
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,pd,ft", [(16, 8, 1, 16), (16, 8, 8, 129), (8, 16, 1, 3), (32, 16, 8, 128), (32, 16, 1, 129)])
+def test_owl_attn_model_geometry(qb, kv_dt, H, W, pd, ft):
+    r = util.rng(100 + ft)
+    Hk, gqa, nb = 16, 2, 16
+    tpf, cap = H * W, 17 * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 4096)), n_q_heads=32, n_kv_heads=16)
+    if kv_dt == "bf16":
+        Kc, Vc = bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap))
+    else:
+        Kc, Vc = e4m3_randn(r, (Hk * cap, 64)), e4m3_randn(r, (Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    got = _attn_run(qb, qkv, Kc, Vc, segs, [n], ft, Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=pd, kv_dt=kv_dt)
+    want = ops.owl_attn(qkv, Kc, Vc, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                        q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
+    _attn_check(got, want, f"attn {H}x{W} pd={pd} ft={ft} {kv_dt}", kv_dt == "e4m3")
+
+
+def test_owl_attn_masked_bucket_is_never_read(qb):
+    """NaN-poison the bucket the segment table masks: the output must not change."""
+    r = util.rng(77)
+    Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 8, 4, 1, 6  # post-wrap write frame: slot 2 masked
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = bf16_randn(r, (tpf, 8 * 64))
+    Kc, Vc = bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    assert n == 3
+    base = _attn_run(qb, qkv, Kc, Vc, segs, [n], ft, Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=pd, kv_dt="bf16")
+    Kp, Vp = Kc.copy().reshape(Hk, cap, 64), Vc.copy().reshape(Hk, 64, cap)
+    Kp[:, 2 * tpf : 3 * tpf, :] = 0x7FC0
+    Vp[:, :, 2 * tpf : 3 * tpf] = 0x7FC0
+    poisoned = _attn_run(qb, qkv, Kp.reshape(Hk * cap, 64), Vp.reshape(Hk * 64, cap), segs, [n], ft, Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=pd, kv_dt="bf16")
+    np.testing.assert_array_equal(base, poisoned)
+
+
+def test_owl_attn_empty_segments_give_zero(qb):
+    r = util.rng(78)
+    Hk, gqa, H, W, nb = 2, 2, 8, 8, 4
+    tpf, cap = 64, 5 * 64
+    got = _attn_run(qb, bf16_randn(r, (tpf, 512)), bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap)), [0, 0, 0, 0, 0, 0], [2], 0,
+                    Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=1, kv_dt="bf16")  # fmt: skip
+    assert not got.any()
