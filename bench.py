@@ -1,0 +1,416 @@
+"""Benchmark of the Waypoint-1.5 DiT hot path: 720p fp8 generated frames per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one ``gen_frame`` at 720p with linear, kv_cache and attn_compute all fp8: 5 network
+evaluations (4 denoise + 1 commit) of the 24-layer DiT on 512 tokens, every layer's KV cache
+holding 16 buckets of seeded e4m3 K/V, replayed from one CUDA graph.  Weights and inputs are
+synthetic (seeded random init, no checkpoint exists on the box).  ``value`` is latent frames per
+second with the noise latent already on the device; ``e2e`` is the same through
+``Engine.gen_frame`` with the noise coming from pinned host memory and the latent copied back
+every frame.  With N > 1 every rank runs its own independent session on its own GPU (the
+reference has no multi-GPU mode; sessions do not communicate), and ``value`` is the sum.
+
+``--impl reference`` times the CPU oracle of the same path on the host cores, on a bounded sample
+(one transformer block per step), scaled to a full frame.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PUBLISHED_LATENT_FPS_720P_FP8 = 20.0  # RTX 4090, the reference's README table
+HEIGHT, WIDTH = 32, 16  # 720p token grid in the orientation BASELINE.json states (32 x 16 = 512 tokens)
+FRAME_T0 = 128  # caches pre-filled as if 128 frames had been appended
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    except Exception:
+        return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, device: int):
+        self.device, self.rows, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=mx or None, reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------- algorithmic work per launch
+
+
+def attn_flops(tpf, S, Hq=32, Dh=64):
+    return 4.0 * Hq * tpf * S * Dh
+
+
+def gemm_flops(M, N, K):
+    return 2.0 * M * N * K
+
+
+# --------------------------------------------------------------------------- our arm
+
+
+def build_engine(seed: int, device: int, n_layers: int = 24):
+    import quark_b200 as qb
+    from quark_b200.models import QuantConfig, Waypoint15Config
+
+    cfg = Waypoint15Config(height=HEIGHT, width=WIDTH, n_layers=n_layers, quant=QuantConfig.all_fp8())
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, seed=seed, device=device)
+    # pre-fill every layer's cache with seeded N(0,1) -> e4m3 K/V, as after 128 appended frames
+    r = np.random.default_rng([seed, 99])
+    for blk in eng.model.blocks:
+        kc = blk.kv_cache
+        for t in (kc.K_cache, kc.Vt_cache):
+            a = r.standard_normal(t.numel, dtype=np.float32)
+            src = qb.QuarkTensor.from_numpy(a)
+            qb.qf.quantize_e4m3(src, out=t)
+    eng.set_frame_t(FRAME_T0)
+    qb.runtime.synchronize()
+    return qb, eng
+
+
+def time_kernels(qb, eng, peaks):
+    """Per-launch device time of the hot kernels, each timed alone with CUDA events over the 24 layers'
+    own buffers (24 distinct weight / cache sets, far larger than L2 together)."""
+    blocks = list(eng.model.blocks)
+    cfg = eng.cfg
+    tpf = cfg.tpf
+    ft = eng.gen.frame_t
+    res = {}
+
+    def timed(fn, reps=3):
+        for b in blocks:  # warm-up pass
+            fn(b)
+        e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+        e0.record()
+        for _ in range(reps):
+            for b in blocks:
+                fn(b)
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_ms(e1) * 1e3 / (reps * len(blocks))  # us per launch
+
+    xq = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="e4m3")
+    hq = qb.QuarkTensor.zeros(tpf, cfg.mlp_dim, dtype="e4m3")
+    xr = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="bf16")
+    aq = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="bf16")
+    g = eng.model.blocks[0]._cond_lut[0][2]
+    qkv = qb.QuarkTensor.zeros(tpf, cfg.qkv_dim, dtype="bf16")
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    shapes = {
+        "gemm_qkv": (lambda b: b.qkv_proj(xq), gemm_flops(tpf, cfg.qkv_dim, cfg.d_model)),
+        "gemm_out": (lambda b: b.out_proj(aq, gate=g, residual=xr), gemm_flops(tpf, cfg.d_model, cfg.d_model)),
+        "gemm_fc1": (lambda b: b.mlp.fc1(xq, activation="silu", out_dtype="e4m3"), gemm_flops(tpf, cfg.mlp_dim, cfg.d_model)),
+        "gemm_fc2": (lambda b: b.mlp.fc2(hq, gate=g, residual=xr), gemm_flops(tpf, cfg.d_model, cfg.mlp_dim)),
+        "owl_attn": (lambda b: b.attn(qkv, b.kv_cache, ft), None),
+        "kv_cache_update": (lambda b: b.kv_cache(qkv, ft, frozen=True), None),
+    }
+    for name, (fn, flops) in shapes.items():
+        us = timed(fn)
+        entry = dict(us_per_launch=round(us, 2))
+        if name == "owl_attn":
+            # keys attended per layer at this frame: local layers 16 buckets, global layers 17 (non-write frame)
+            S = np.mean([sum(b.kv_cache.segments.to_numpy()[1::2][: int(b.kv_cache.n_segments.to_numpy()[0])]) for b in blocks])
+            flops = attn_flops(tpf, float(S))
+            entry["keys_attended_mean"] = float(S)
+        if flops is not None:
+            entry.update(tflops=round(flops / us / 1e6, 1), frac_of_peak=round(flops / us / 1e6 / fp8_peak, 3))
+        else:
+            bytes_ = 2 * tpf * 1024 * 2 + 2 * tpf * 1024 * 1 + 28
+            entry.update(gbs=round(bytes_ / us / 1e3, 1), frac_of_peak=round(bytes_ / us / 1e3 / peaks["hbm_gbs"], 3))
+        res[name] = entry
+    return res
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    qb, eng = build_engine(seed=rank, device=local)
+    cfg = eng.cfg
+    n = cfg.latent_numel
+    rng = np.random.default_rng([1234, rank])
+    noises = [rng.standard_normal(n, dtype=np.float32) for _ in range(4)]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        qb.runtime.synchronize()
+
+    # warm-up (the first call also captures the graph), through the public API
+    for i in range(max(args.warmup, 3)):
+        eng.gen_frame(noise=noises[i % 4])
+    launches_per_frame = eng.launches_per_frame
+    eng.set_frame_t(FRAME_T0 + 1)
+
+    # ---- device-resident timing: graph replays between two events
+    peaks = measured_peaks()
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+        e0.record()
+        for _ in range(args.steps):
+            eng.gen(eng._noise_dev)
+        e1.record()
+        e1.synchronize()
+        barrier()
+        dev_ms = e0.elapsed_ms(e1)
+        # ---- end to end: host noise -> pinned -> device, replay, latent back to the host, every step
+        barrier()
+        t0 = time.perf_counter()
+        e2, e3 = qb.runtime.Event(), qb.runtime.Event()
+        e2.record()
+        for i in range(args.steps):
+            eng.gen_frame(noise=noises[i % 4])
+        e3.record()
+        e3.synchronize()
+        e2e_ms = max(e2.elapsed_ms(e3), (time.perf_counter() - t0) * 1e3)
+        barrier()
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    status = qb._lib.device_status()
+
+    kernels = time_kernels(qb, eng, peaks) if rank == 0 else None
+    cpu = cpu_baseline_sample() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+
+    if rank == 0:
+        ms_per_step = dev_ms / args.steps
+        fps = world * 1000.0 / ms_per_step
+        e2e_fps = world * 1000.0 * args.steps / e2e_ms
+        # every one of these runs once per layer: the dominant kernel is the slowest launch
+        dom = max(("owl_attn", "gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"), key=lambda k: kernels[k]["us_per_launch"])
+        gemm_us = sum(kernels[k]["us_per_launch"] for k in ("gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"))
+        dk = kernels[dom]
+        fp8_peak = 2.0 * peaks["bf16_tflops"]
+        line = {
+            "metric": "latent_fps_720p_fp8",
+            "value": round(fps, 3),
+            "unit": "frames/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4),
+            "ms_per_nfe": round(ms_per_step / 5.0, 4),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": round(fps / PUBLISHED_LATENT_FPS_720P_FP8, 3),
+            "dtype": "e4m3",
+            "data": "synthetic",
+            "impl": "ours",
+            "config": {
+                "workload": "gen_frame 720p fp8: 5 NFE x 24 layers, 512 tokens, d_model 2048, GQA 32/16 x 64, 16-bucket e4m3 KV per layer (BASELINE configs[2])",
+                "grid": [HEIGHT, WIDTH],
+                "frame_t": FRAME_T0 + 1,
+                "quant": "linear=fp8 kv_cache=fp8 attn_compute=fp8 (unscaled e4m3, as the reference)",
+                "parallelism": "1 session per GPU, no collective" if world > 1 else "1 GPU",
+                "l2": "inputs larger than L2: each NFE streams ~1.1 GB of e4m3 weights and ~0.4 GB of KV cache",
+                "weights": "seeded random init N(0, 0.02)",
+            },
+            "e2e": {
+                "value": round(e2e_fps, 3),
+                "unit": "frames/s",
+                "h2d_bytes_per_step": eng.h2d_bytes_per_frame,
+                "d2h_bytes_per_step": eng.d2h_bytes_per_frame,
+            },
+            "gpu_launches": int(launches_per_frame * args.steps),
+            "launches_per_frame": int(launches_per_frame),
+            "roofline": {
+                "kernel": dom,
+                "bound": "tensor",
+                "achieved": dk["tflops"],
+                "peak": round(fp8_peak, 1),
+                "unit": "TFLOP/s",
+                "frac": dk["frac_of_peak"],
+                "traffic": None,
+                "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s (no e4m3 peak was measured)",
+            },
+            "kernels": kernels,
+            "gemm_us_per_layer": round(gemm_us, 2),
+            "clocks": clocks.summary(),
+            "device_status": status,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- CPU oracle arm
+
+
+def blas_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+
+        return max([int(i.get("num_threads", 1)) for i in threadpool_info()] or [1])
+    except Exception:
+        return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+
+def oracle_block_seconds(seed=0):
+    """One 720p fp8 local block through the chained CPU oracle (the bounded sample)."""
+    from oracle import codec
+    from oracle import model as om
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    cfg = Waypoint15Config(n_layers=1, height=HEIGHT, width=WIDTH, quant=QuantConfig.all_fp8())
+    params = make_params(cfg, seed)
+    for k in ("qkv.weight", "out.weight", "fc1.weight", "fc2.weight"):
+        params["blocks"][0][k] = codec.f32_to_e4m3(codec.bf16_to_f32(params["blocks"][0][k]))
+    q = om.Quant(linear="fp8", kv_cache="fp8", attn_compute="fp8")
+    st = om.new_state(cfg, q)
+    r = np.random.default_rng(seed)
+    for name in ("K_cache", "Vt_cache"):
+        st[0][name][...] = codec.f32_to_e4m3(r.standard_normal(st[0][name].shape).astype(np.float32))
+    x = codec.f32_to_bf16(r.standard_normal((cfg.tpf, cfg.d_model)).astype(np.float32))
+    t0 = time.perf_counter()
+    om.block_forward(cfg, 0, params["blocks"][0], st[0], x, 0, FRAME_T0 + 1, qkv_first=None, frozen=True, quant=q)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline_sample(reps=2):
+    secs = min(oracle_block_seconds(i) for i in range(reps))
+    frame_s = secs * 24 * 5
+    return {
+        "value": round(1.0 / frame_s, 5),
+        "unit": "frames/s",
+        "cores": blas_threads(),
+        "kind": "port",
+        "sample": f"one 720p fp8 transformer block through the chained numpy oracle: {secs:.2f} s (best of {reps}); frame = 24 blocks x 5 NFE",
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    for _ in range(min(args.warmup, 1)):
+        oracle_block_seconds(0)
+    steps = max(1, min(args.steps, 5))
+    secs = [oracle_block_seconds(i) for i in range(steps)]
+    block_s = float(np.mean(secs))
+    frame_s = block_s * 24 * 5
+    fps = 1.0 / frame_s
+    cpu = {
+        "value": round(fps, 5),
+        "unit": "frames/s",
+        "cores": blas_threads(),
+        "kind": "port",
+        "sample": f"per step one 720p fp8 transformer block through the chained numpy oracle ({block_s:.2f} s mean of {steps}); frame = 24 blocks x 5 NFE",
+    }
+    print(json.dumps({
+        "metric": "latent_fps_720p_fp8", "value": round(fps, 5), "unit": "frames/s", "n_gpus": world, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": round(frame_s * 1e3, 1), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(fps / PUBLISHED_LATENT_FPS_720P_FP8, 6), "dtype": "e4m3", "data": "synthetic", "impl": "reference",
+        "config": {"workload": "gen_frame 720p fp8 (BASELINE configs[2]) on the host cores through the CPU oracle of the path",
+                   "note": "the reference's GPU path needs its Python tree, which is not present on the GPU box; its own CPU implementation of this path is the numpy oracle restated in oracle/"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": round(fps, 5), "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)  # fmt: skip
+
+
+def run_profile_nfe(args):
+    """For profilers: build the engine, run eager (ungraphed) NFEs of the bench workload and exit.
+
+    Prints how many kernels were launched before the last NFE and how many it has, so that a
+    profiler can skip straight to it (`ncu -s <before> -c <per_nfe>`).
+    """
+    qb, eng = build_engine(seed=0, device=0, n_layers=args.layers)
+    eng.set_frame_t(FRAME_T0 + 1)
+    noise = qb.QuarkTensor.from_numpy(np.random.default_rng(0).standard_normal((1, eng.cfg.latent_numel), dtype=np.float32), dtype="bf16")
+    for _ in range(2):  # the first pass allocates every cached buffer
+        eng.model(noise, sigma_idx=0, frame_t=eng.gen.frame_t, frozen=True)
+    qb.runtime.synchronize()
+    before = qb._lib.kernel_launch_count()
+    eng.model(noise, sigma_idx=0, frame_t=eng.gen.frame_t, frozen=True)
+    qb.runtime.synchronize()
+    per_nfe = qb._lib.kernel_launch_count() - before
+    print(json.dumps({"launches_before": before, "launches_per_nfe": per_nfe, "device_status": qb._lib.device_status()}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-nfe", action="store_true", help="run eager NFEs of the workload and exit (for ncu)")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=24, help="model depth for --profile-nfe (smaller = less device memory under a profiler)")
+    args = ap.parse_args()
+    if args.profile_nfe:
+        run_profile_nfe(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

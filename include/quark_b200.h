@@ -56,6 +56,9 @@ int32_t qb_set_device(int32_t device);
 /* Reads and clears the device status word that kernels set when a bounded wait ran out
  * (bit 0 GEMM, bit 1 attention) or a segment table was malformed (bit 2).  Synchronises. */
 int32_t qb_device_status(uint32_t* status_host);
+/* Number of kernels this library has launched since it was loaded (launches recorded into a CUDA
+ * graph during capture count once, replays do not count). */
+uint64_t qb_kernel_launch_count(void);
 
 /* ------------------------------------------------------------------ memory / streams / graphs
  * Replaces the ctypes libcuda subset the reference's tensor class uses

@@ -29,8 +29,36 @@ def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
     return (np.asarray(u16, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
 
 
+_BF16_MODE = "trunc"
+
+
+class bf16_rounding:
+    """``with bf16_rounding("rne"):`` makes every f32 -> bf16 narrowing of the oracle round to nearest
+    even, the rule of the hardware ``cvt.rn.bf16.f32`` that the reference's GPU kernels and ours use.
+    The default ("trunc") is what the reference's numpy oracles do.  Truncation shrinks every result by
+    half an ulp on average, a bias that accumulates along a chain of ops; comparing a chained GPU run
+    against both variants separates that bias from kernel error."""
+
+    def __init__(self, mode: str):
+        if mode not in ("trunc", "rne"):
+            raise ValueError(mode)
+        self.mode = mode
+
+    def __enter__(self):
+        global _BF16_MODE
+        self.prev, _BF16_MODE = _BF16_MODE, self.mode
+        return self
+
+    def __exit__(self, *exc):
+        global _BF16_MODE
+        _BF16_MODE = self.prev
+        return False
+
+
 def f32_to_bf16(arr: np.ndarray) -> np.ndarray:
-    """Truncating narrow, as the reference oracle does."""
+    """Truncating narrow, as the reference oracle does (unless ``bf16_rounding("rne")`` is active)."""
+    if _BF16_MODE == "rne":
+        return f32_to_bf16_rne(arr)
     f32 = np.ascontiguousarray(arr, dtype=np.float32)
     return (f32.view(np.uint32) >> np.uint32(16)).astype(np.uint16)
 

@@ -80,6 +80,7 @@ SIGNATURES = {
     "qb_device_check": (_I, [_I]),
     "qb_set_device": (_I, [_I]),
     "qb_device_status": (_I, [C.POINTER(_U)]),
+    "qb_kernel_launch_count": (C.c_uint64, []),
     "qb_malloc": (_I, [C.POINTER(_P), _Z]),
     "qb_free": (_I, [_P]),
     "qb_host_alloc": (_I, [C.POINTER(_P), _Z]),
@@ -159,6 +160,10 @@ def device_count() -> int:
 def require_device(device: int = 0) -> None:
     """Raise unless ``device`` is a compute-capability 10.0 GPU."""
     check(load().qb_device_check(device))
+
+
+def kernel_launch_count() -> int:
+    return int(load().qb_kernel_launch_count())
 
 
 def device_status() -> int:

@@ -30,7 +30,11 @@ unsigned int* status_word();
     if (!(cond)) return qb::fail(code, __VA_ARGS__); \
   } while (0)
 
+// Kernels launched by this library since it was loaded (qb_kernel_launch_count).
+extern unsigned long long g_launch_count;
+
 inline int32_t check_launch(const char* what) {
+  ++g_launch_count;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(QB_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
   return QB_OK;

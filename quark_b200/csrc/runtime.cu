@@ -6,6 +6,7 @@
 namespace qb {
 
 __device__ unsigned int g_qb_status = 0;
+unsigned long long g_launch_count = 0;
 
 // Device address of the status word for the current device (one copy of the symbol per device).
 unsigned int* status_word() {
@@ -77,6 +78,8 @@ int32_t qb_device_status(uint32_t* status_host) {
   *status_host = v;
   return QB_OK;
 }
+
+uint64_t qb_kernel_launch_count(void) { return g_launch_count; }
 
 int32_t qb_malloc(void** ptr_host, size_t bytes) {
   QB_REQUIRE(ptr_host != nullptr, QB_ERR_INVALID_ARG, "ptr_host is NULL");

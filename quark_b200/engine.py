@@ -1,0 +1,157 @@
+"""``Engine``: the session API of the reference (``quark.Engine``), minus the VAE.
+
+Mirrors ``src/quark/engine/cuda.py:38-51`` / ``:169-266`` and the factory in
+``src/quark/engine/base.py:155-165``: ``Engine(cfg, quant=...)``, ``append_frame``, ``gen_frame``,
+``reset``.  The reference wraps the DiT between a torch VAE encoder and decoder; the VAE is outside
+the hot path, so here ``append_frame`` takes a latent ``[1, C, 2H, 2W]`` and ``gen_frame`` returns
+the generated latent (documented deviation).  Each ``gen_frame`` copies the noise latent from
+pinned host memory to the device, replays the captured 5-NFE CUDA graph, and copies the
+result back: those copies are the only host <-> device traffic per frame.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .models.waypoint_15 import GenerateFrame, QuantConfig, Waypoint15, Waypoint15Config, make_params
+from .runtime import stream as _stream
+from .runtime.tensor import QuarkTensor
+
+
+class _Pinned:
+    """A pinned host buffer viewed as a numpy array."""
+
+    def __init__(self, nbytes: int, dtype):
+        p = C.c_void_p()
+        _lib.check(_lib.load().qb_host_alloc(C.byref(p), nbytes))
+        self.ptr = int(p.value)
+        self.array = np.frombuffer((C.c_uint8 * nbytes).from_address(self.ptr), dtype=dtype)
+
+    def __del__(self):
+        try:
+            _lib.load().qb_host_free(C.c_void_p(self.ptr))
+        except Exception:
+            pass
+
+
+class Engine:
+    def __init__(self, model_uri=None, *, cfg: Waypoint15Config | None = None, quant="fp8", load_weights=True, seed: int = 0,
+                 params: dict | None = None, device: int = 0, use_graph: bool = True):  # fmt: skip
+        if isinstance(model_uri, Waypoint15Config):
+            cfg, model_uri = model_uri, None
+        if model_uri is not None:
+            raise NotImplementedError(
+                "Engine: loading a checkpoint by URI (safetensors / YAML / hub download) is not implemented; "
+                "pass cfg=Waypoint15Config(...) and optionally params=<dict of host arrays>"
+            )
+        _lib.require_device(device)
+        _lib.check(_lib.load().qb_set_device(device))
+        if isinstance(quant, str):
+            quant = QuantConfig.all_fp8() if quant == "fp8" else QuantConfig.all_bf16() if quant == "bf16" else None
+            if quant is None:
+                raise ValueError("Engine: quant must be 'fp8', 'bf16' or a QuantConfig")
+        base = cfg or Waypoint15Config()
+        self.cfg = cfg = Waypoint15Config(**{**base.__dict__, "quant": quant})
+        self.model = Waypoint15(cfg)
+        if load_weights:
+            self.model.load_params(params if params is not None else make_params(cfg, seed))
+            self.model.prepare()
+        self.gen = GenerateFrame(self.model)
+        self._use_graph = use_graph
+        self._frame = 0
+        n = cfg.latent_numel
+        self._noise_host = _Pinned(n * 2, np.uint16)
+        self._out_host = _Pinned(n * 2, np.uint16)
+        self._noise_dev = QuarkTensor.empty(1, n, dtype="bf16")
+        self._append_dev = QuarkTensor.empty(1, n, dtype="bf16")
+        self._rng = np.random.default_rng([seed, 7])
+        self.h2d_bytes_per_frame = n * 2
+        self.d2h_bytes_per_frame = n * 2
+
+    # ---- helpers
+    def _latent_shape(self):
+        c = self.cfg
+        return (1, c.channels, c.height * c.patch[0], c.width * c.patch[1])
+
+    def _to_bf16(self, latent) -> np.ndarray:
+        a = np.asarray(latent)
+        if a.dtype == np.uint16:
+            out = a
+        else:
+            out = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> np.uint32(16)).astype(np.uint16)
+        if out.size != self.cfg.latent_numel:
+            raise ValueError(f"Engine: latent has {out.size} elements, expected {self._latent_shape()}")
+        return out.reshape(-1)
+
+    def _h2d(self, dev: QuarkTensor, host_ptr: int, nbytes: int):
+        _lib.check(_lib.load().qb_memcpy_async(C.c_void_p(dev.data_ptr()), C.c_void_p(host_ptr), nbytes, 0, C.c_void_p(_stream.active_stream())))
+
+    def _d2h(self, host_ptr: int, dev: QuarkTensor, nbytes: int):
+        _lib.check(_lib.load().qb_memcpy_async(C.c_void_p(host_ptr), C.c_void_p(dev.data_ptr()), nbytes, 1, C.c_void_p(_stream.active_stream())))
+
+    @property
+    def launches_per_frame(self) -> int:
+        """Kernels in the captured frame graph (0 before the first ``gen_frame``)."""
+        return int(self.gen.launches_per_frame)
+
+    # ---- session API
+    def reset(self) -> None:
+        self.gen.reset()
+        self._frame = 0
+
+    def set_frame_t(self, value: int) -> None:
+        self.gen.set_frame_t(value)
+        self._frame = int(value)
+
+    def append_frame(self, latent):
+        """Commit a given latent frame to the KV caches (one NFE at the last sigma, ring writes on) and
+        advance the frame counter (``src/quark/engine/cuda.py:177-195`` without the VAE)."""
+        self._noise_host.array[:] = self._to_bf16(latent)
+        self._h2d(self._append_dev, self._noise_host.ptr, self.cfg.latent_numel * 2)
+        self.model(self._append_dev, sigma_idx=self.gen.n_denoise, frame_t=self.gen.frame_t, frozen=False)
+        from . import functional as qf
+
+        qf.increment(self.gen.frame_t)
+        _stream.synchronize()
+        self._frame += 1
+        return np.asarray(latent)
+
+    def gen_frame(self, ctrl=None, return_img: bool = True, *, noise=None):
+        """Generate the next latent frame: 4 denoise NFEs + 1 commit NFE (``engine/cuda.py:197-255``).
+
+        ``noise`` (optional) is a latent-shaped array used instead of the engine's own seeded normal
+        noise.  Returns the latent as a bf16-carrier ``uint16`` array ``[1, C, 2H, 2W]`` when
+        ``return_img`` is true (there is no VAE to make pixels), else None.
+        """
+        if ctrl is not None:
+            raise NotImplementedError("Engine.gen_frame: controller input is not implemented")
+        n = self.cfg.latent_numel
+        if noise is None:
+            noise = self._rng.standard_normal(n, dtype=np.float32)
+        self._noise_host.array[:] = self._to_bf16(noise)
+        self._h2d(self._noise_dev, self._noise_host.ptr, n * 2)
+        if self._use_graph and self.gen._graph is None:
+            self._capture()
+        out = self.gen(self._noise_dev)
+        self._frame += 1
+        if not return_img:
+            return None
+        self._d2h(self._out_host.ptr, out, n * 2)
+        _stream.synchronize()
+        return self._out_host.array.reshape(self._latent_shape()).copy()
+
+    def _capture(self) -> None:
+        """Capture the frame graph without disturbing the session: the warm-up and capture passes
+        write the tail slot and (commit pass) a ring slot of every layer, so snapshot and restore."""
+        saved = []
+        for blk in self.model.blocks:
+            kc = blk.kv_cache
+            saved.append([(t, t.to_numpy()) for t in (kc.K_cache, kc.Vt_cache, kc.segments, kc.n_segments)])
+        self.gen.prepare_graph(self._noise_dev, start_frame_t=self._frame)
+        for items in saved:
+            for t, host in items:
+                t.copy_from_numpy(host)
+        _stream.synchronize()

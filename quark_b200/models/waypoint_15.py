@@ -1,0 +1,362 @@
+"""Waypoint-1.5 DiT: config, block wiring, one NFE, one generated frame.
+
+Mirrors ``src/quark/models/waypoint_15.py``: ``QuantConfig`` (``:46-76``), ``Waypoint15Config``
+(``:79-171``), ``TransformerBlock`` (``:259-440``), ``Waypoint15`` (``:448-661``) and
+``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: the
+controller-conditioning branch (``ctrl_emb`` is always None here), MoE, quilt, checkpoint
+download.  Weights come from ``make_params`` (seeded random init, the stand-in for the real
+checkpoint) or any dict of the same layout via ``Waypoint15.load_params``.
+"""
+
+from __future__ import annotations
+
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .. import functional as qf
+from .. import nn
+from ..runtime import stream as _stream
+from ..runtime.tensor import QuarkTensor
+from . import _cond
+
+
+@dataclass(frozen=True)
+class QuantConfig:
+    """Per-component ``"fp8"`` / ``"bf16"`` switches (``src/quark/models/waypoint_15.py:46-76``)."""
+
+    linear: str = "fp8"
+    kv_cache: str = "fp8"
+    attn_compute: str = "fp8"
+    moe: str = "fp8"
+
+    def __post_init__(self) -> None:
+        for name in ("linear", "kv_cache", "attn_compute", "moe"):
+            v = getattr(self, name)
+            if v not in ("fp8", "bf16"):
+                raise ValueError(f"QuantConfig.{name}: must be 'fp8' or 'bf16', got {v!r}")
+        if self.kv_cache != self.attn_compute:
+            raise NotImplementedError("QuantConfig: kv_cache and attn_compute must match (cast-on-load is not implemented)")
+
+    @classmethod
+    def all_bf16(cls) -> "QuantConfig":
+        return cls(linear="bf16", kv_cache="bf16", attn_compute="bf16", moe="bf16")
+
+    @classmethod
+    def all_fp8(cls) -> "QuantConfig":
+        return cls()
+
+
+@dataclass(frozen=True)
+class Waypoint15Config:
+    d_model: int = 2048
+    n_layers: int = 24
+    n_heads: int = 32
+    n_kv_heads: int = 16
+    mlp_ratio: int = 4
+    channels: int = 32
+    patch: tuple[int, int] = (2, 2)
+    height: int = 16
+    width: int = 32
+    local_window: int = 16
+    global_window: int = 128
+    global_pinned_dilation: int = 8
+    global_attn_period: int = 4
+    global_attn_offset: int = -1
+    value_residual: bool = True
+    fourier_dim: int = 512
+    scheduler_sigmas: tuple[float, ...] = (1.0, 0.9, 0.75, 0.3, 0.0)
+    ctrl_conditioning: bool = False
+    quant: QuantConfig = field(default_factory=QuantConfig.all_bf16)
+    quilt_factor: int = 1
+    moe: bool = False
+    # Fold `x + gate * y` into the out-proj / fc2 GEMM epilogue (upstream field, default off there).
+    fuse_gate_residual: bool = True
+    # Fold SiLU into fc1's epilogue (upstream does on its PTX / Metal GEMMs, not on the cuBLAS route).
+    fuse_silu: bool = True
+
+    def __post_init__(self):
+        if self.ctrl_conditioning:
+            raise NotImplementedError("Waypoint15Config: controller conditioning is not implemented")
+        if self.moe or self.quilt_factor != 1:
+            raise NotImplementedError("Waypoint15Config: MoE and quilt are not implemented")
+        if self.d_model // self.n_heads != 64:
+            raise NotImplementedError("Waypoint15Config: only head_dim 64 is supported")
+
+    @property
+    def Dh(self):
+        return self.d_model // self.n_heads
+
+    @property
+    def mlp_dim(self):
+        return self.d_model * self.mlp_ratio
+
+    @property
+    def gqa_ratio(self):
+        return self.n_heads // self.n_kv_heads
+
+    @property
+    def tpf(self):
+        return self.height * self.width
+
+    @property
+    def qkv_dim(self):
+        return (self.n_heads + 2 * self.n_kv_heads) * self.Dh
+
+    @property
+    def v_col_offset(self):
+        return (self.n_heads + self.n_kv_heads) * self.Dh
+
+    @property
+    def v_width(self):
+        return self.n_kv_heads * self.Dh
+
+    @property
+    def latent_numel(self):
+        return self.channels * self.height * self.patch[0] * self.width * self.patch[1]
+
+    def is_global(self, layer):
+        return (layer - self.global_attn_offset) % self.global_attn_period == 0
+
+    def num_buckets(self, layer):
+        return self.global_window // self.global_pinned_dilation if self.is_global(layer) else self.local_window
+
+    def pinned_dilation(self, layer):
+        return self.global_pinned_dilation if self.is_global(layer) else 1
+
+
+# ---------------------------------------------------------------------------
+# seeded random-init parameters (host numpy, bf16 carriers)
+# ---------------------------------------------------------------------------
+
+
+def _randn_bf16(rng, shape, std):
+    a = rng.standard_normal(shape, dtype=np.float32)
+    a *= np.float32(std)
+    return _cond._bf16(a)
+
+
+def make_params(cfg: Waypoint15Config, seed: int = 0, *, weight_std: float = 0.02, threads: int = 8) -> dict:
+    """Random-init parameters of the hot path, as host arrays.
+
+    Linear weights are N(0, ``weight_std``) in bf16; the per-sigma noise embedding is a seeded
+    N(0, 1) vector of d_model; the conditioning rows follow from it through random-init cond heads
+    with the reference's host arithmetic (``_cond.block_rows``).  Layer ``i`` uses the generator
+    ``default_rng([seed, i])`` so layers are independent and reproducible one at a time.
+
+    Layout: ``patchify.weight``, ``unpatchify.weight``, ``unpatchify.bias``, ``out_norm.lut`` (list over
+    sigma of two rows) and ``blocks`` (list of dicts: ``qkv.weight``, ``out.weight``, ``fc1.weight``,
+    ``fc2.weight``, ``lamb``, ``lut`` = list over sigma of six rows).
+    """
+    d, ns = cfg.d_model, len(cfg.scheduler_sigmas)
+    kpatch = cfg.channels * cfg.patch[0] * cfg.patch[1]
+    r0 = np.random.default_rng([seed, 1_000_000])
+    emb = r0.standard_normal((ns, d), dtype=np.float32)
+    params = {
+        "patchify.weight": _randn_bf16(r0, (d, kpatch), weight_std),
+        "unpatchify.weight": _randn_bf16(r0, (kpatch, d), weight_std),
+        "unpatchify.bias": _randn_bf16(r0, (kpatch,), weight_std),
+    }
+    on_w = _cond.bf16_to_f32(_randn_bf16(r0, (2 * d, d), weight_std))
+    params["out_norm.lut"] = [_cond.out_norm_rows(emb[si], on_w) for si in range(ns)]
+
+    def one_layer(i):
+        r = np.random.default_rng([seed, i])
+        blk = {
+            "qkv.weight": _randn_bf16(r, (cfg.qkv_dim, d), weight_std),
+            "out.weight": _randn_bf16(r, (d, cfg.n_heads * cfg.Dh), weight_std),
+            "fc1.weight": _randn_bf16(r, (cfg.mlp_dim, d), weight_std),
+            "fc2.weight": _randn_bf16(r, (d, cfg.mlp_dim), weight_std),
+            "lamb": 0.5,
+        }
+        ab = _cond.bf16_to_f32(_randn_bf16(r, (d,), weight_std))
+        mb = _cond.bf16_to_f32(_randn_bf16(r, (d,), weight_std))
+        projs = [_cond.bf16_to_f32(_randn_bf16(r, (d, d), weight_std)) for _ in range(6)]
+        blk["lut"] = [_cond.block_rows(emb[si], ab, mb, projs) for si in range(ns)]
+        return blk
+
+    with ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
+        params["blocks"] = list(ex.map(one_layer, range(cfg.n_layers)))
+    return params
+
+
+# ---------------------------------------------------------------------------
+# model
+# ---------------------------------------------------------------------------
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, cfg: Waypoint15Config, layer_idx: int):
+        d = cfg.d_model
+        self._cfg = cfg
+        self._cond_lut: list[tuple] = []
+        self.pre_attn_norm = nn.AdaRMSNorm()
+        self.qkv_proj = nn.Linear(d, cfg.qkv_dim, out_dtype="bf16")
+        self.head_norm = nn.HeadRMSNorm(cfg.n_heads, cfg.n_kv_heads, cfg.Dh)
+        if cfg.value_residual:
+            self.v_residual = nn.ValueResidualPacked(cfg.v_col_offset, cfg.v_width)
+        kv_dt = "e4m3" if cfg.quant.kv_cache == "fp8" else "bf16"
+        geo = dict(B=1, n_kv_heads=cfg.n_kv_heads, H_spatial=cfg.height, W_spatial=cfg.width, num_buckets=cfg.num_buckets(layer_idx),
+                   pinned_dilation=cfg.pinned_dilation(layer_idx), packed_qkv=True)  # fmt: skip
+        self.kv_cache = nn.KVCacheUpdate(n_q_heads=cfg.n_heads, Dh=cfg.Dh, dtype=kv_dt, **geo)
+        self.attn = nn.OwlAttn(gqa_ratio=cfg.gqa_ratio, compute_dtype="e4m3" if cfg.quant.attn_compute == "fp8" else None, **geo)
+        self.out_proj = nn.Linear(cfg.n_heads * cfg.Dh, d, out_dtype="bf16")
+        self.attn_gate = nn.AdaGateResidual()
+        self.pre_mlp_norm = nn.AdaRMSNorm()
+        self.mlp = nn.MLP(d, cfg.mlp_dim, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
+        self.mlp_gate = nn.AdaGateResidual()
+
+    def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None):
+        """Returns ``(x, qkv)`` (``src/quark/models/waypoint_15.py:389-440``)."""
+        if ctrl_emb is not None:
+            raise NotImplementedError("controller conditioning is not implemented")
+        s0, b0, g0, s1, b1, g1 = self._cond_lut[sigma_idx]
+        fp8 = self.qkv_proj.weight.data.dtype == "e4m3"
+        fuse = self._cfg.fuse_gate_residual
+
+        qkv = self.head_norm(self.qkv_proj(self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)))
+        if hasattr(self, "v_residual") and qkv_first is not None:
+            qkv = self.v_residual(qkv, qkv_first)
+        self.kv_cache(qkv, frame_t, frozen=frozen)
+        attn_out = self.attn(qkv, self.kv_cache, frame_t)
+        if fuse:
+            x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
+        else:
+            x = self.attn_gate(x, self.out_proj(attn_out), g0)
+        h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8)
+        if fuse:
+            x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
+        else:
+            x = self.mlp_gate(x, self.mlp(h), g1)
+        return x, qkv
+
+
+class Waypoint15(nn.Module):
+    def __init__(self, cfg: Waypoint15Config | None = None):
+        self.cfg = cfg = cfg or Waypoint15Config()
+        ph, pw = cfg.patch
+        self.patchify = nn.Patchify(cfg.channels, cfg.d_model, cfg.height * ph, cfg.width * pw, ph, pw)
+        self.blocks = nn.ModuleList([TransformerBlock(cfg, i) for i in range(cfg.n_layers)])
+        self.out_norm = nn.AdaRMSNorm()
+        self.unpatchify = nn.Unpatchify(cfg.d_model, cfg.channels, cfg.height * ph, cfg.width * pw, ph, pw)
+        self._out_norm_luts: list[tuple] = []
+        # Two residual-stream buffers used alternately by consecutive blocks when the gate/residual
+        # epilogue is fused: a GEMM must not write the tensor it reads its residual from.
+        self._x_bufs = None
+
+    def load_params(self, params: dict) -> "Waypoint15":
+        """Upload a ``make_params``-style dict; call ``prepare()`` afterwards."""
+        up = lambda a: QuarkTensor.from_numpy(np.asarray(a), dtype="bf16")  # noqa: E731
+        self.patchify.weight.data = up(params["patchify.weight"])
+        self.unpatchify.weight.data = up(params["unpatchify.weight"])
+        self.unpatchify.bias.data = up(params["unpatchify.bias"])
+        self._out_norm_luts = [tuple(up(r) for r in rows) for rows in params["out_norm.lut"]]
+        for blk, p in zip(self.blocks, params["blocks"]):
+            blk.qkv_proj.weight.data = up(p["qkv.weight"])
+            blk.out_proj.weight.data = up(p["out.weight"])
+            blk.mlp.fc1.weight.data = up(p["fc1.weight"])
+            blk.mlp.fc2.weight.data = up(p["fc2.weight"])
+            if hasattr(blk, "v_residual"):
+                blk.v_residual.lamb.data = QuarkTensor.from_numpy(np.array([p["lamb"]], dtype=np.float32))
+            blk._cond_lut = [tuple(up(r) for r in rows) for rows in p["lut"]]
+        return self
+
+    def prepare(self, **kwargs):
+        """Quantise linear weights when ``cfg.quant.linear == "fp8"`` (``waypoint_15.py:502-535``)."""
+        kwargs.setdefault("fp8", self.cfg.quant.linear == "fp8")
+        for blk in self.blocks:
+            for lin in (blk.qkv_proj, blk.out_proj, blk.mlp.fc1, blk.mlp.fc2):
+                lin.prepare(**kwargs)
+        _stream.synchronize()
+
+    def set_frame_t(self, value: int) -> None:
+        for blk in self.blocks:
+            blk.kv_cache.set_frame_t(value)
+
+    def reset(self) -> None:
+        for blk in self.blocks:
+            blk.kv_cache.reset()
+
+    def forward(self, latent, sigma_idx: int, frame_t=None, ctrl_emb=None, frozen: bool = False):
+        """One NFE on a ``[1, C*2H*2W]`` bf16 latent (``src/quark/models/waypoint_15.py:626-661``)."""
+        if latent.dtype != "bf16" or latent.numel != self.cfg.latent_numel:
+            raise TypeError(f"Waypoint15: latent must be bf16 with {self.cfg.latent_numel} elements, got {latent.dtype} {latent.shape}")
+        s_on, b_on = self._out_norm_luts[sigma_idx]
+        x = self.patchify(latent)
+        if self._x_bufs is None:
+            self._x_bufs = (QuarkTensor.empty(*x.shape, dtype="bf16"), QuarkTensor.empty(*x.shape, dtype="bf16"))
+        qkv_first = None
+        for li, block in enumerate(self.blocks):
+            x, qkv = block(x, sigma_idx, frame_t, qkv_first=qkv_first, ctrl_emb=ctrl_emb, frozen=frozen, x_out=self._x_bufs[li & 1])
+            if li == 0 and self.cfg.value_residual:
+                qkv_first = qkv
+        x = self.out_norm(x, s_on, b_on, activation="silu")
+        return self.unpatchify(x)
+
+
+class GenerateFrame(nn.Module):
+    """encode (none) -> 4 Euler denoise steps -> commit pass -> ``frame_t += 1`` (``waypoint_15.py:664-766``).
+
+    ``prepare_graph`` runs the frame once eagerly (so every cached buffer exists), captures it into
+    one CUDA graph, and rewinds ``frame_t``; afterwards ``__call__`` copies the noise into the
+    captured input buffer and replays.
+    """
+
+    def __init__(self, model: Waypoint15):
+        self.model = model
+        sig = model.cfg.scheduler_sigmas
+        self.n_denoise = len(sig) - 1
+        self.dsig_tensors = [QuarkTensor.from_numpy(np.array([float(sig[i + 1] - sig[i])], dtype=np.float32)) for i in range(self.n_denoise)]
+        self.euler_steps = nn.ModuleList([nn.EulerStep() for _ in range(self.n_denoise)])
+        self.frame_t = QuarkTensor.zeros(1, dtype="s32")
+        self._graph = None
+        self._in = None
+        self._out = None
+        self.launches_per_frame = 0  # kernels in the captured frame graph
+
+    def set_frame_t(self, value: int) -> None:
+        self.frame_t.copy_from_numpy(np.array([value], dtype=np.int32))
+
+    def reset(self) -> None:
+        self.model.reset()
+        self.set_frame_t(0)
+
+    def forward(self, latent, ctrl_input=None):
+        if ctrl_input is not None:
+            raise NotImplementedError("controller conditioning is not implemented")
+        ft = self.frame_t
+        x = latent
+        for si in range(self.n_denoise):
+            v = self.model(x, sigma_idx=si, frame_t=ft, frozen=True)
+            x = self.euler_steps[si](x, v, self.dsig_tensors[si])
+        self.model(x, sigma_idx=self.n_denoise, frame_t=ft)
+        qf.increment(ft)
+        return x
+
+    def prepare_graph(self, example_latent, example_ctrl_input=None, *, start_frame_t: int = 0) -> None:
+        """Warm up and capture.  The KV state after this call is what the warm-up and capture
+        passes left (two commits of the example latent at ``start_frame_t``); callers that care
+        restore or reset the caches afterwards."""
+        self._in = QuarkTensor.empty(*example_latent.shape, dtype="bf16")
+        self._in.copy_from(example_latent)
+        self.set_frame_t(start_frame_t)
+        self.forward(self._in)
+        _stream.synchronize()
+        self.set_frame_t(start_frame_t)
+        from .. import _lib
+
+        n0 = _lib.kernel_launch_count()
+        with _stream.capture_graph() as cap:
+            self._out = self.forward(self._in)
+        self.launches_per_frame = _lib.kernel_launch_count() - n0
+        self._graph = cap.graph
+        self.set_frame_t(start_frame_t)
+        _stream.synchronize()
+
+    def __call__(self, latent, ctrl_input=None):
+        if self._graph is None:
+            return self.forward(latent, ctrl_input)
+        self._in.copy_from(latent)
+        self._graph.launch()
+        return self._out

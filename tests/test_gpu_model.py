@@ -1,0 +1,191 @@
+"""Chained parity on the GPU: one block, a full NFE, a generated frame, against the chained CPU oracle.
+
+The oracle chain (``oracle/model.py``) consumes the same host parameter dict the model uploads.
+For fp8 runs the oracle is fed the same quantised bytes: weights narrowed with the oracle's e4m3
+encoder (the GPU narrowing is tested bit-exact against it elsewhere) and activations / Q rounded
+where the tensor cores need 8-bit operands.
+"""
+
+import copy
+
+import numpy as np
+import pytest
+
+from oracle import codec
+from oracle import model as omodel
+from tests import util
+from tests.util import f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def qb():
+    import quark_b200 as q
+
+    q._lib.require_device(0)
+    yield q
+    q.runtime.synchronize()
+    assert q._lib.device_status() == 0
+
+
+def small_cfg(qb, quant, **kw):
+    from quark_b200.models import QuantConfig, Waypoint15Config
+
+    q = QuantConfig.all_fp8() if quant == "fp8" else QuantConfig.all_bf16()
+    base = dict(d_model=128, n_layers=4, n_heads=2, n_kv_heads=1, height=8, width=8, channels=4, local_window=2,
+                global_window=4, global_pinned_dilation=2, quant=q)  # fmt: skip
+    base.update(kw)
+    return Waypoint15Config(**base)
+
+
+def oracle_params(params, quant):
+    """The oracle's view of the uploaded parameters (weights narrowed to e4m3 for fp8 linears)."""
+    p = copy.copy(params)
+    if quant == "fp8":
+        p["blocks"] = []
+        for b in params["blocks"]:
+            nb = dict(b)
+            for k in ("qkv.weight", "out.weight", "fc1.weight", "fc2.weight"):
+                nb[k] = codec.f32_to_e4m3(codec.bf16_to_f32(b[k]))
+            p["blocks"].append(nb)
+    return p
+
+
+def oquant(quant):
+    return omodel.Quant(linear=quant, kv_cache=quant, attn_compute=quant) if quant == "fp8" else omodel.Quant()
+
+
+def compare(got_u16, want_u16, what, fp8, max_rel=util.BF16_MAX_REL, cos_min=util.COS_MIN):
+    g, w = f32(got_u16, "bf16").ravel(), f32(want_u16, "bf16").ravel()
+    assert np.all(np.isfinite(g)), what
+    cs, mr = util.cosine(g, w), util.max_rel(g, w)
+    print(f"{what}: cosine={cs:.6f} max_rel={mr:.3e}")
+    if fp8:
+        assert cs >= cos_min, f"{what}: cosine={cs:.6f} max_rel={mr:.3e}"
+    else:
+        assert cs >= cos_min and mr <= max_rel, f"{what}: cosine={cs:.6f} max_rel={mr:.3e}"
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+@pytest.mark.parametrize("fused", [True, False])
+def test_small_model_session_matches_oracle(qb, quant, fused):
+    """append 5 frames (the rings wrap), then generate 2 frames; compare latents and cache bytes."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, quant, fuse_gate_residual=fused, fuse_silu=fused)
+    params = make_params(cfg, seed=3, weight_std=0.08)
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=False)
+    op, oq = oracle_params(params, quant), oquant(quant)
+    r = util.rng(11)
+    lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(5)]
+    noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(2)]
+
+    def oracle_session(mode):
+        """The same session through the chained oracle, narrowing to bf16 by truncation (what the
+        reference's numpy oracles do) or by round-to-nearest (what the GPU kernels do)."""
+        with codec.bf16_rounding(mode):
+            state = omodel.new_state(cfg, oq)
+            ft = 0
+            for lat in lats:
+                omodel.nfe_forward(cfg, op, state, lat, len(cfg.scheduler_sigmas) - 1, ft, frozen=False, quant=oq)
+                ft += 1
+            mid = copy.deepcopy(state)
+            outs = []
+            for nz in noises:
+                want, ft = omodel.gen_frame(cfg, op, state, codec.f32_to_bf16(nz), ft, quant=oq)
+                outs.append(want)
+        return mid, outs, ft
+
+    mid, want_trunc, ft = oracle_session("trunc")
+    _, want_rne, _ = oracle_session("rne")
+    for lat in lats:
+        eng.append_frame(lat)
+    for li, blk in enumerate(eng.model.blocks):
+        np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), mid[li]["segments"], err_msg=f"layer {li}")
+        np.testing.assert_array_equal(blk.kv_cache.n_segments.to_numpy(), mid[li]["n_segments"])
+        kd = "e4m3" if quant == "fp8" else "bf16"
+        gK, wK = f32(blk.kv_cache.K_cache.to_numpy(), kd), f32(mid[li]["K_cache"], kd)
+        np.testing.assert_array_equal(gK.any(axis=1), wK.any(axis=1), err_msg=f"layer {li}: rows written")
+        assert util.cosine(gK, wK) >= 0.999, f"layer {li} K cache"
+    for k, nz in enumerate(noises):
+        got = eng.gen_frame(noise=nz)
+        # 40+ chained blocks: against the truncating oracle the accumulated half-ulp bias of its
+        # narrowing dominates, so the chained bound is looser; against the round-to-nearest variant
+        # the per-tensor 2e-2 bound holds
+        compare(got.reshape(-1), want_trunc[k].reshape(-1), f"gen_frame {k} {quant} fused={fused} vs truncating oracle", quant == "fp8", max_rel=5e-2)
+        compare(got.reshape(-1), want_rne[k].reshape(-1), f"gen_frame {k} {quant} fused={fused} vs round-to-nearest oracle", quant == "fp8")
+    assert int(eng.gen.frame_t.to_numpy()[0]) == ft == 7
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_graph_replay_equals_eager(qb, quant):
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, quant)
+    params = make_params(cfg, seed=5, weight_std=0.08)
+    r = util.rng(12)
+    lats = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(6)]
+    outs = []
+    for use_graph in (False, True):
+        eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=use_graph)
+        eng.append_frame(lats[0])
+        eng.append_frame(lats[1])
+        outs.append([eng.gen_frame(noise=lats[2 + k]) for k in range(4)])
+        assert int(eng.gen.frame_t.to_numpy()[0]) == 6
+    for a, b in zip(*outs):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_config1_block_360p_bf16(qb):
+    """BASELINE config 1: one local block at 360p (128 tokens, d_model 2048), cache pre-filled with 16 frames."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    cfg = Waypoint15Config(n_layers=1, height=16, width=8, quant=QuantConfig.all_bf16())
+    params = make_params(cfg, seed=0)
+    model = qb.Waypoint15(cfg).load_params(params)
+    model.prepare()
+    r = util.rng(0)
+    tpf, cap = cfg.tpf, 17 * cfg.tpf
+    Kc = codec.f32_to_bf16(r.standard_normal((16 * cap, 64)).astype(np.float32))
+    Vc = codec.f32_to_bf16(r.standard_normal((16 * 64, cap)).astype(np.float32))
+    x = codec.f32_to_bf16(r.standard_normal((tpf, 2048)).astype(np.float32))
+    blk = model.blocks[0]
+    blk.kv_cache.K_cache.copy_from_numpy(Kc)
+    blk.kv_cache.Vt_cache.copy_from_numpy(Vc)
+    ft = qb.QuarkTensor.from_numpy(np.array([16], dtype=np.int32))
+    xg, qkv = blk(qb.QuarkTensor.from_numpy(x, dtype="bf16"), 0, ft, qkv_first=None, frozen=True)
+    state = [dict(K_cache=Kc.copy(), Vt_cache=Vc.copy(), segments=np.zeros(6, np.int32), n_segments=np.zeros(1, np.int32))]
+    xo, qkvo = omodel.block_forward(cfg, 0, params["blocks"][0], state[0], x, 0, 16, qkv_first=None, frozen=True, quant=omodel.Quant())
+    compare(qkv.to_numpy().ravel(), qkvo.ravel(), "config1 qkv", False)
+    compare(xg.to_numpy().ravel(), xo.ravel(), "config1 block output", False)
+    np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), [0, 0, 128, 1920, 2048, 128])
+
+
+@pytest.mark.parametrize("quant,height,width", [("bf16", 16, 8), ("fp8", 16, 8)])
+def test_full_depth_nfe_360p(qb, quant, height, width):
+    """BASELINE config 2: 24 layers, 360p, caches holding 128 frames of seeded K/V, frame_t = 128 and 129."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    q = QuantConfig.all_fp8() if quant == "fp8" else QuantConfig.all_bf16()
+    cfg = Waypoint15Config(height=height, width=width, quant=q)
+    params = make_params(cfg, seed=0)
+    model = qb.Waypoint15(cfg).load_params(params)
+    model.prepare()
+    op, oq = oracle_params(params, quant), oquant(quant)
+    state = omodel.new_state(cfg, oq)
+    kd = "e4m3" if quant == "fp8" else "bf16"
+    for li, blk in enumerate(model.blocks):
+        r = util.rng([9, li])
+        for name in ("K_cache", "Vt_cache"):
+            a = r.standard_normal(state[li][name].shape).astype(np.float32)
+            state[li][name][...] = codec.from_f32(a, kd)
+            getattr(blk.kv_cache, name).copy_from_numpy(state[li][name])
+    lat = codec.f32_to_bf16(util.rng(1).standard_normal((1, cfg.latent_numel)).astype(np.float32))
+    for ft_val, sigma_idx, frozen in [(128, 0, True), (129, 4, False)]:
+        ft = qb.QuarkTensor.from_numpy(np.array([ft_val], dtype=np.int32))
+        got = model(qb.QuarkTensor.from_numpy(lat, dtype="bf16"), sigma_idx, ft, frozen=frozen).to_numpy()
+        want = omodel.nfe_forward(cfg, op, state, lat, sigma_idx, ft_val, frozen=frozen, quant=oq)
+        compare(got.ravel(), want.ravel(), f"24-layer NFE {quant} frame_t={ft_val}", quant == "fp8")
+        for li, blk in enumerate(model.blocks):
+            np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), state[li]["segments"], err_msg=f"layer {li}")
