@@ -68,4 +68,14 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 // x * sigmoid(x) with the exact exponential (the reference oracle uses exp, not an approximation).
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
+// The same with the hardware approximations (2^x and 1/x, ~2^-22 relative error each), which is what
+// the reference's GEMM epilogue uses (ref: src/quark/lang/epilogue.py:43-69): a handful of
+// instructions instead of ~50, for epilogues that sit on the critical path of a tensor-core kernel.
+__device__ __forceinline__ float silu_fast(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
+}
+
 }  // namespace qb

@@ -64,7 +64,7 @@ __device__ __forceinline__ void epilogue_store8(const GemmArgs& g, float (&v)[8]
   }
   if (g.activation == 1) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = silu_f(v[j]);
+    for (int j = 0; j < 8; ++j) v[j] = silu_fast(v[j]);
   }
   if (g.gate != nullptr) {
     const size_t grow = static_cast<size_t>(m / g.rows_per_gate) * g.N;
@@ -256,21 +256,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
-          if (m < g.M) {
+          // The tile is re-read from the workspace, so any thread-to-element mapping works: consecutive
+          // threads take consecutive groups of 8 columns (coalesced), slices are added in index order.
+          const int et = threadIdx.x - 64;  // 0..127
 #pragma unroll 1
-            for (int c8 = 0; c8 < BN / 8; ++c8) {
-              const int n = n0 + c8 * 8;
-              if (n >= g.N) break;
-              float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-              for (int s = 0; s < g.splits; ++s) {
-                const float4* src =
-                    reinterpret_cast<const float4*>(g.partials + (static_cast<size_t>(s) * g.M + m) * g.N + n);
-                const float4 x = __ldcg(src), y = __ldcg(src + 1);
-                v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-                v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-              }
-              epilogue_store8(g, v, m, n);
+          for (int i8 = et; i8 < kBM * (BN / 8); i8 += 128) {
+            const int mm = m0 + i8 / (BN / 8);
+            const int n = n0 + (i8 % (BN / 8)) * 8;
+            if (mm >= g.M || n >= g.N) continue;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < g.splits; ++s) {
+              const float4* src = reinterpret_cast<const float4*>(g.partials + (static_cast<size_t>(s) * g.M + mm) * g.N + n);
+              const float4 x = __ldcg(src), y = __ldcg(src + 1);
+              v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+              v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
             }
+            epilogue_store8(g, v, mm, n);
           }
           if (threadIdx.x == 64) *counter = 0;  // ready for the next launch
         }
@@ -367,9 +368,12 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       if (s_eff != s) continue;
       const long ctas = static_cast<long>(tiles) * s;
       const long waves = (ctas + sms - 1) / sms;
-      const double per_kb = fmax(2.0 * bn, (kBM + bn) * 128.0 / 56.0);
-      double cta = kbps * per_kb + 1500.0 + bn * 6.0;
-      if (s > 1) cta += bn * 10.0 + s * bn * 3.0;
+      // cycles per 128 bytes of K, fitted to measured steady-state rates of this kernel on B200
+      // (1045 / 620 cycles at BN = 256 / 128), a fixed launch + prologue cost, the epilogue, and for
+      // K slices the partial-tile store plus the last CTA's pass over all slices
+      const double per_kb = 300.0 + 2.6 * bn;
+      double cta = kbps * per_kb + 3000.0 + bn * 12.0;
+      if (s > 1) cta += bn * 8.0 + s * bn * 4.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
         best_cost = cost;

@@ -107,7 +107,9 @@ def test_small_model_session_matches_oracle(qb, quant, fused):
         kd = "e4m3" if quant == "fp8" else "bf16"
         gK, wK = f32(blk.kv_cache.K_cache.to_numpy(), kd), f32(mid[li]["K_cache"], kd)
         np.testing.assert_array_equal(gK.any(axis=1), wK.any(axis=1), err_msg=f"layer {li}: rows written")
-        assert util.cosine(gK, wK) >= 0.999, f"layer {li} K cache"
+        # state after 5 chained frames: in fp8 a tiny upstream difference flips whole e4m3 codes (6 % steps),
+        # so the chained cache is held to a looser bound than a single append (tested bit-level elsewhere)
+        assert util.cosine(gK, wK) >= (0.99 if quant == "fp8" else 0.999), f"layer {li} K cache"
     for k, nz in enumerate(noises):
         got = eng.gen_frame(noise=nz)
         # 40+ chained blocks: against the truncating oracle the accumulated half-ulp bias of its
@@ -173,19 +175,39 @@ def test_full_depth_nfe_360p(qb, quant, height, width):
     model = qb.Waypoint15(cfg).load_params(params)
     model.prepare()
     op, oq = oracle_params(params, quant), oquant(quant)
-    state = omodel.new_state(cfg, oq)
     kd = "e4m3" if quant == "fp8" else "bf16"
+    # Two oracle runs that differ only in how f32 is narrowed to bf16: truncation (the reference's numpy
+    # oracles) and round-to-nearest (its GPU kernels, and ours).  Over 24 chained layers these two
+    # legitimate variants of the same reference drift apart; that drift is the noise floor of a
+    # full-depth comparison, so the GPU result is held to it instead of the single-kernel tolerance.
+    states = {m: omodel.new_state(cfg, oq) for m in ("trunc", "rne")}
     for li, blk in enumerate(model.blocks):
         r = util.rng([9, li])
         for name in ("K_cache", "Vt_cache"):
-            a = r.standard_normal(state[li][name].shape).astype(np.float32)
-            state[li][name][...] = codec.from_f32(a, kd)
-            getattr(blk.kv_cache, name).copy_from_numpy(state[li][name])
+            a = codec.from_f32(r.standard_normal(states["trunc"][li][name].shape).astype(np.float32), kd)
+            for st in states.values():
+                st[li][name][...] = a
+            getattr(blk.kv_cache, name).copy_from_numpy(a)
     lat = codec.f32_to_bf16(util.rng(1).standard_normal((1, cfg.latent_numel)).astype(np.float32))
+
+    def err(a_u16, b_u16):
+        a, b = f32(a_u16, "bf16").ravel(), f32(b_u16, "bf16").ravel()
+        return 1.0 - util.cosine(a, b), util.max_rel(a, b)
+
     for ft_val, sigma_idx, frozen in [(128, 0, True), (129, 4, False)]:
         ft = qb.QuarkTensor.from_numpy(np.array([ft_val], dtype=np.int32))
         got = model(qb.QuarkTensor.from_numpy(lat, dtype="bf16"), sigma_idx, ft, frozen=frozen).to_numpy()
-        want = omodel.nfe_forward(cfg, op, state, lat, sigma_idx, ft_val, frozen=frozen, quant=oq)
-        compare(got.ravel(), want.ravel(), f"24-layer NFE {quant} frame_t={ft_val}", quant == "fp8")
+        want = {}
+        for mode, st in states.items():
+            with codec.bf16_rounding(mode):
+                want[mode] = omodel.nfe_forward(cfg, op, st, lat, sigma_idx, ft_val, frozen=frozen, quant=oq)
+        assert np.all(np.isfinite(f32(got, "bf16")))
+        floor_c, floor_m = err(want["trunc"], want["rne"])
+        for mode in ("trunc", "rne"):
+            c, m = err(got, want[mode])
+            print(f"24-layer NFE {quant} frame_t={ft_val} vs {mode} oracle: 1-cos={c:.2e} max_rel={m:.2e} (oracle-vs-oracle floor 1-cos={floor_c:.2e} max_rel={floor_m:.2e})")
+            assert c <= max(1.0 - util.COS_MIN, 1.5 * floor_c), (mode, c, floor_c)
+            if quant == "bf16":
+                assert m <= max(util.BF16_MAX_REL, 1.5 * floor_m), (mode, m, floor_m)
         for li, blk in enumerate(model.blocks):
-            np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), state[li]["segments"], err_msg=f"layer {li}")
+            np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), states["rne"][li]["segments"], err_msg=f"layer {li}")
