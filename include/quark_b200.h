@@ -120,6 +120,25 @@ size_t qb_gemm_workspace_bytes(const qb_gemm_params* p);
 int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                 const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
+/* qb_gemm without a workspace argument, for callers that must not allocate device memory.
+ * No counterpart in the reference.
+ * Some hosts cannot call cudaMalloc where they call the GEMM: a frame loop with a hard latency
+ * budget (cudaMalloc may synchronise the whole device), a plugin that was handed a fixed memory
+ * budget by the application that embeds it, or code that runs while another allocator (a game
+ * engine's, a framework's caching allocator) owns all of the device memory.  This entry point gives
+ * them the same GEMM on scratch memory that is part of the library image: a file-scope device array
+ * of qb_gemm_static_scratch_capacity() = 8 MiB bytes, present on every GPU that loads the library
+ * until the process exits.  It performs no cudaMalloc / cudaFree and calls no allocating routine.
+ * Limits: a GEMM whose scratch need (qb_gemm_workspace_bytes) exceeds the capacity is rejected with
+ * QB_ERR_WORKSPACE and a message that states both numbers.  All calls share the one array, which
+ * keeps the previous call's contents (the part that must start at zero is cleared on the stream by
+ * every call): two calls that overlap on the GPU (different streams, no ordering) race on it.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before any stream capture begins.  Results are bit-identical to qb_gemm. */
+size_t qb_gemm_static_scratch_capacity(void);
+int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                               const qb_gemm_params* p, void* stream);
+
 /* X -> e4m3, round-to-nearest-even, saturate to +-448, NaN -> 0x7F, no scale.
  * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
  * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */

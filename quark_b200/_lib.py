@@ -103,6 +103,8 @@ SIGNATURES = {
     "qb_graph_destroy": (_I, [_P]),
     "qb_gemm_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
     "qb_gemm": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(GemmParams), _P, _Z, _P]),
+    "qb_gemm_static_scratch_capacity": (_Z, []),
+    "qb_gemm_static_scratch": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(GemmParams), _P]),
     "qb_quantize_e4m3": (_I, [_P, _P, _Z, _I, _P]),
     "qb_kv_cache_update": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
     "qb_rope_table_build": (_I, [_P, _I, _I, _P]),

@@ -499,3 +499,49 @@ extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bi
   if (pl.bn == 128) return launch_gemm<128, false>(tmA, tmB, g, grid, st);
   return launch_gemm<64, false>(tmA, tmB, g, grid, st);
 }
+
+// ---------------------------------------------------------------- GEMM on built-in scratch memory
+// Scratch for qb_gemm_static_scratch: lives in the library image, so every GPU that loads the library
+// holds these 8 MiB until the process exits.  In host code the name below is only a handle for
+// cudaGetSymbolAddress; the device address it yields is what the kernels receive.
+namespace qb {
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[kStaticScratchBytes];
+
+// Device address of the scratch array on the current device, looked up once per device.
+static int32_t static_scratch_ptr(void** out) {
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  QB_CUDA_OK(cudaGetDevice(&dev));
+  QB_REQUIRE(dev >= 0 && dev < 64, QB_ERR_DEVICE, "gemm_static_scratch: device ordinal %d out of range", dev);
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    QB_CUDA_OK(cudaGetSymbolAddress(&p, g_gemm_static_scratch));
+    QB_REQUIRE(p != nullptr, QB_ERR_CUDA, "gemm_static_scratch: cudaGetSymbolAddress returned a null address");
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return QB_OK;
+}
+}  // namespace qb
+
+extern "C" size_t qb_gemm_static_scratch_capacity(void) { return qb::kStaticScratchBytes; }
+
+extern "C" int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void* bias, const void* gate,
+                                          const void* residual, const qb_gemm_params* p, void* stream) {
+  int32_t rc = validate_gemm(p);
+  if (rc != QB_OK) return rc;
+  const GemmPlan pl = plan_gemm(*p);
+  const size_t need = pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
+  QB_REQUIRE(need <= kStaticScratchBytes, QB_ERR_WORKSPACE,
+             "gemm_static_scratch: this GEMM needs %zu bytes of scratch but the built-in scratch holds %zu; "
+             "use qb_gemm with a caller-provided workspace, or force a smaller split_k",
+             need, static_cast<size_t>(kStaticScratchBytes));
+  void* scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc != QB_OK) return rc;
+  // The array keeps whatever the previous call left.  Only the tile counters must start at zero;
+  // the e4m3 copy of A and the K-slice partials are fully written before they are read.
+  QB_CUDA_OK(cudaMemsetAsync(scratch, 0, pl.counters_bytes, static_cast<cudaStream_t>(stream)));
+  return qb_gemm(A, B, C, bias, gate, residual, p, scratch, kStaticScratchBytes, stream);
+}
