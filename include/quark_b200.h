@@ -179,7 +179,8 @@ int32_t qb_rope_table_build(float* rope_xy, int32_t H_spatial, int32_t W_spatial
  * Replaces qf.owl_attn (ref: src/quark/functional/owl_attn.py:322-394,
  * src/quark/kernels/owl_attn/kernel.py:324-790).  qkv packed [tpf, (Hq + 2 Hk) * 64] bf16 (only
  * the Q columns are read), caches as above, out [tpf, Hq * 64] bf16.  Attends to the union of
- * the first n_segments (start, length) entries; starts and lengths must be multiples of 128.
+ * the first n_segments (start, length) entries; starts must be multiples of 16.  out_q (optional,
+ * may be NULL) receives the same result narrowed to e4m3 for a following fp8 GEMM.
  * compute_dtype QB_BF16 (bf16 caches) or QB_E4M3 (e4m3 caches; Q after RoPE and P are narrowed
  * to e4m3).  k_scale / v_scale: optional f32 [Hk] per-head dequantisation scales (NULL = 1). */
 typedef struct {
@@ -198,7 +199,7 @@ typedef struct {
 
 size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p);
 int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
-                    const int32_t* n_segments, const int32_t* frame_t, void* out, const float* rope_xy,
+                    const int32_t* n_segments, const int32_t* frame_t, void* out, void* out_q, const float* rope_xy,
                     const qb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ norm / elementwise ops

@@ -1,24 +1,26 @@
 // owl_attn: segment-sparse GQA flash attention with inline ortho-RoPE on Q, head_dim 64.
 //
 // One CTA owns 128 query tokens of one Q head and walks the valid keys in tiles of 128, enumerated
-// from the (start, length) segment table, so a masked bucket is never loaded.  320 threads:
+// from the (start, length) segment table, so a masked bucket is never loaded.  384 threads:
 //   warp 0        TMA producer: K tile [128 keys x 64] and V^T tile [64 x 128 keys] per stage
-//   warp 1        one thread issues tcgen05.mma: S = Q K^T and PV = P V, accumulators in TMEM
-//   warps 2-5     softmax group 0: even key tiles        warps 6-9   softmax group 1: odd key tiles
-// Each softmax group runs its own online softmax (own S buffer in TMEM, own P buffer in shared
-// memory, own PV buffer in TMEM, one query row per thread) over its half of the tiles; the two
-// partial results (row max, row sum, 64 outputs) are merged once at the end.  Two independent
-// groups give every SM sub-partition two warps of exp/FMA work to interleave, which a single group
-// (one warp per sub-partition, latency bound) cannot.
+//   warps 1, 2    one thread each issues tcgen05.mma for softmax group 0 / 1: S = Q K^T and PV = P V
+//   warp 3        idle (keeps the softmax warps aligned to the TMEM lane quarters)
+//   warps 4-7     softmax group 0: even key tiles        warps 8-11  softmax group 1: odd key tiles
+// Each softmax group runs its own online softmax over its half of the tiles, one query row per
+// thread, with two S buffers in TMEM (S(i+1) is computed while the group works on S(i)), its own P
+// buffer in shared memory, and PV(i) written over the TMEM columns of the S(i) it came from.  The two
+// partial results (row max, row sum, 64 outputs) are merged once at the end.  Two independent groups
+// give every SM sub-partition two warps of exp / FMA work to interleave; a single group (one warp
+// per sub-partition) is latency bound.
 //
 // The row sum of P comes out of the tensor core: 16 rows of ones follow the 64 V^T rows of every
 // stage, so PV has 80 columns and column 64 is sum_k P[q, k] of exactly the rounded P that is
-// multiplied with V.  bf16 path: kind::f16 MMAs, exp2 in f32, P rounded to bf16.  fp8 path: Q (after
-// RoPE), K, V, P are e4m3 (kind::f8f6f4); exp2 is evaluated two at a time in f16x2 (P keeps only 3
-// mantissa bits) and narrowed straight to e4m3x2; P is scaled by 2^8 so small probabilities keep
-// mantissa bits (the factor cancels in the division by the row sum).
+// multiplied with V.  bf16 path: kind::f16 MMAs, P rounded to bf16.  fp8 path: Q (after RoPE), K, V
+// and P are e4m3 (kind::f8f6f4); P is scaled by 2^8 so small probabilities keep mantissa bits (the
+// factor cancels in the division by the row sum).  exp2 is ex2.approx.f32 in both paths: measured on
+// B200, ex2.approx.f16x2 issues at half the rate of the f32 form (no gain per element) and the
+// f16x2 -> e4m3x2 conversion is four times slower than f32 -> e4m3x2.
 #include <cuda.h>
-#include <cuda_fp16.h>
 
 #include "common.cuh"
 #include "rope.cuh"
@@ -40,6 +42,7 @@ struct AttnArgs {
   const int32_t* n_segments;
   const int32_t* frame_t;
   uint16_t* out;
+  uint8_t* out_q;  // optional e4m3 copy of the output
   const float* rope_xy;
   const float* k_scale;
   const float* v_scale;
@@ -70,23 +73,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// two f32 -> f16x2 (lo in the low half), 2^x on both halves, -> e4m3x2
-__device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t f16x2_to_e4m3x2(uint32_t x) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(x));
-  return r;
-}
-
 // UMMA descriptor for a K-major tile with 64-byte rows and the 64-byte swizzle (fp8, head_dim 64).
 __device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -455,11 +441,8 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         if (kFp8) {
           uint32_t w[8];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const uint32_t lo = f16x2_to_e4m3x2(ex2_f16x2(f32x2_to_f16x2(x[2 * q].x, x[2 * q].y)));
-            const uint32_t hi = f16x2_to_e4m3x2(ex2_f16x2(f32x2_to_f16x2(x[2 * q + 1].x, x[2 * q + 1].y)));
-            w[q] = lo | (hi << 16);
-          }
+          for (int q = 0; q < 8; ++q)
+            w[q] = pack_e4m3x4(ex2_approx(x[2 * q].x), ex2_approx(x[2 * q].y), ex2_approx(x[2 * q + 1].x), ex2_approx(x[2 * q + 1].y));
           uint8_t* rowp = p_s + r * 128;
           const int sw = r & 7;
           *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -517,6 +500,11 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           w[q] = pack_bf16x2(e0, e1);
         }
         dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
+          *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
+              make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
+                         pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
+        }
       }
     }
   }
@@ -539,7 +527,7 @@ extern "C" size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p) {
 }
 
 extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
-                               const int32_t* n_segments, const int32_t* frame_t, void* out, const float* rope_xy,
+                               const int32_t* n_segments, const int32_t* frame_t, void* out, void* out_q, const float* rope_xy,
                                const qb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   (void)workspace;
   (void)workspace_bytes;
@@ -557,7 +545,7 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   const int tpf = p->H_spatial * p->W_spatial;
   const int cap = (p->num_buckets + 1) * tpf;
   QB_REQUIRE(cap % 16 == 0, QB_ERR_UNSUPPORTED, "owl_attn: capacity %d must be a multiple of 16", cap);
-  QB_REQUIRE(aligned16(qkv) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(out) && aligned16(rope_xy), QB_ERR_ALIGN,
+  QB_REQUIRE(aligned16(qkv) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(out) && aligned16(out_q) && aligned16(rope_xy), QB_ERR_ALIGN,
              "owl_attn: pointers must be 16-byte aligned");
   const bool fp8 = p->kv_dtype == QB_E4M3;
   const int es = fp8 ? 1 : 2;
@@ -572,6 +560,7 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   a.qkv = static_cast<const uint16_t*>(qkv);
   a.segments = segments; a.n_segments = n_segments; a.frame_t = frame_t;
   a.out = static_cast<uint16_t*>(out);
+  a.out_q = static_cast<uint8_t*>(out_q);
   a.rope_xy = rope_xy;
   a.k_scale = p->k_scale; a.v_scale = p->v_scale;
   a.status = status_word();

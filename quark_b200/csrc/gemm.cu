@@ -373,7 +373,10 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       // K slices the partial-tile store plus the last CTA's pass over all slices
       const double per_kb = 300.0 + 2.6 * bn;
       double cta = kbps * per_kb + 3000.0 + bn * 12.0;
-      if (s > 1) cta += bn * 8.0 + s * bn * 4.0;
+      // measured: a K slice costs far more than its arithmetic share (row-per-thread f32 partial
+      // stores, a second pass by the last CTA): ~12 us at 512 x 2048 x 8192, so slices only pay
+      // when they multiply the number of busy SMs
+      if (s > 1) cta += 20000.0 + bn * 8.0 + s * bn * 4.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
         best_cost = cost;

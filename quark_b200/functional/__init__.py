@@ -243,7 +243,7 @@ _DUMMY_FRAME_T: QuarkTensor | None = None
 
 def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_ratio, H_spatial, W_spatial, num_buckets,
              pinned_dilation, out_dtype=None, compute_dtype=None, max_segments=3, packed_qkv=False, quilt_factor=1,
-             quilt_offset=0, frame_t=None, *, out=None, k_scale=None, v_scale=None):  # fmt: skip
+             quilt_offset=0, frame_t=None, *, out=None, out_q=None, k_scale=None, v_scale=None):  # fmt: skip
     """Segment-sparse GQA attention with inline Q RoPE (``src/quark/functional/owl_attn.py:322-394``)."""
     global _DUMMY_FRAME_T
     if Q.ndim != 2:
@@ -284,6 +284,8 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
         out = QuarkTensor.empty(B * tpf, n_q * Dh, dtype="bf16")
     elif out.numel != B * tpf * n_q * Dh or out.dtype != "bf16":
         raise ValueError(f"qf.owl_attn: out is {out.shape} {out.dtype}, expected ({B * tpf}, {n_q * Dh}) bf16")
+    if out_q is not None and (out_q.dtype != "e4m3" or out_q.numel != out.numel):
+        raise ValueError("qf.owl_attn: out_q must be an e4m3 tensor of the output's size")
     if frame_t is None:
         if _DUMMY_FRAME_T is None:
             _DUMMY_FRAME_T = QuarkTensor.zeros(1, dtype="s32")
@@ -300,7 +302,7 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     ws = _workspace(need) if need else None
     _lib.check(
         lib.qb_owl_attn(
-            _p(Q), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(frame_t), _p(out),
+            _p(Q), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(frame_t), _p(out), _p(out_q),
             _p(rope_table(H_spatial, W_spatial)), C.byref(p), _p(ws), ws.nbytes if ws is not None else 0, _s(),
         )
     )  # fmt: skip

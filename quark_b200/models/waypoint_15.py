@@ -219,7 +219,7 @@ class TransformerBlock(nn.Module):
         if hasattr(self, "v_residual") and qkv_first is not None:
             qkv = self.v_residual(qkv, qkv_first)
         self.kv_cache(qkv, frame_t, frozen=frozen)
-        attn_out = self.attn(qkv, self.kv_cache, frame_t)
+        attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8)
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
         else:

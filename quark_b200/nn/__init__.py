@@ -302,10 +302,12 @@ class OwlAttn(Module):
                         quilt_factor=quilt_factor, quilt_offset=quilt_offset)  # fmt: skip
         self._compute_dtype = compute_dtype
 
-    def forward(self, qkv, kv_cache: KVCacheUpdate, frame_t=None):
+    def forward(self, qkv, kv_cache: KVCacheUpdate, frame_t=None, *, emit_e4m3: bool = False):
         n_kv, gqa = self._kw["n_kv_heads"], self._kw["gqa_ratio"]
         n_q = n_kv * gqa
         Dh = int(qkv.shape[1]) // (n_q + 2 * n_kv)
         out = _cached(self, "out", (int(qkv.shape[0]), n_q * Dh), qkv.dtype)
-        return qf.owl_attn(qkv, kv_cache.K_cache, kv_cache.Vt_cache, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
-                           out=out, compute_dtype=self._compute_dtype, **self._kw)  # fmt: skip
+        out_q = _cached(self, "out_q", out.shape, "e4m3") if emit_e4m3 else None
+        qf.owl_attn(qkv, kv_cache.K_cache, kv_cache.Vt_cache, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
+                    out=out, out_q=out_q, compute_dtype=self._compute_dtype, **self._kw)  # fmt: skip
+        return out_q if emit_e4m3 else out

@@ -60,6 +60,6 @@ def test_argument_validation_needs_no_gpu():
     assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -2  # quilt unsupported
     ap = _lib.AttnParams(n_kv_heads=2, gqa_ratio=2, H_spatial=8, W_spatial=8, num_buckets=4, pinned_dilation=1, kv_dtype=0,
                          compute_dtype=1, max_segments=3, packed_qkv=1, quilt_factor=1)  # fmt: skip
-    assert lib.qb_owl_attn(one, one, one, one, one, one, one, one, C.byref(ap), None, 0, None) == -2  # mixed dtypes
+    assert lib.qb_owl_attn(one, one, one, one, one, one, one, None, one, C.byref(ap), None, 0, None) == -2  # mixed dtypes
     assert lib.qb_rope_table_build(one, 0, 8, None) == -1
     assert lib.qb_device_check(9999) == -5

@@ -360,6 +360,19 @@ def test_owl_attn_model_geometry(qb, kv_dt, H, W, pd, ft):
     _attn_check(got, want, f"attn {H}x{W} pd={pd} ft={ft} {kv_dt}", kv_dt == "e4m3")
 
 
+def test_owl_attn_e4m3_side_output_is_the_narrowed_bf16_output(qb):
+    r = util.rng(31)
+    Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 8, 4, 1, 9
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = bf16_randn(r, (tpf, 8 * 64))
+    Kc, Vc = e4m3_randn(r, (Hk * cap, 64)), e4m3_randn(r, (Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    oq = qb.QuarkTensor.empty(tpf, 4 * 64, dtype="e4m3")
+    out = qb.qf.owl_attn(T(qb, qkv, "bf16"), T(qb, Kc, "e4m3"), T(qb, Vc, "e4m3"), T(qb, segs), T(qb, np.array([n], np.int32)), 1, Hk, gqa, H, W,
+                         nb, pd, compute_dtype="e4m3", packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32)), out_q=oq).to_numpy()  # fmt: skip
+    np.testing.assert_array_equal(oq.to_numpy(), codec.f32_to_e4m3(codec.bf16_to_f32(out)))
+
+
 def test_owl_attn_masked_bucket_is_never_read(qb):
     """NaN-poison the bucket the segment table masks: the output must not change."""
     r = util.rng(77)
