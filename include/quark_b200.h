@@ -169,6 +169,16 @@ typedef struct {
 int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
                            int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p, void* stream);
 
+/* head_rmsnorm + value_residual_packed + kv_cache_update in one pass over the packed QKV projection
+ * (ref: the three calls of TransformerBlock.forward, src/quark/models/waypoint_15.py:398-407).
+ * qkv_out receives the normalised Q and K heads and the mixed V (what owl_attn reads, and what the
+ * first block hands to later blocks as qkv_first); the caches and the segment table are updated as by
+ * qb_kv_cache_update.  qkv_first / lamb may both be NULL (first block: no value residual).  Results
+ * are bit-identical to the three separate entry points.  n_q_heads must be a multiple of n_kv_heads. */
+int32_t qb_qkv_post(const void* qkv_in, const void* qkv_first, const float* lamb, void* qkv_out, const int32_t* frame_t,
+                    const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments, int32_t* n_segments,
+                    const float* rope_xy, const qb_kv_params* p, float eps, void* stream);
+
 /* Fills rope_xy [H*W, 16] on the device: token t -> (h, w) = (t / W, t % W).  The angles follow
  * ref: src/quark/kernels/kv_cache_update/reference.py:61-106 (f64 position x frequency, narrowed
  * to f32); cos/sin are the CUDA single-precision functions. */

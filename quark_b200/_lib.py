@@ -107,6 +107,7 @@ SIGNATURES = {
     "qb_gemm_static_scratch": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(GemmParams), _P]),
     "qb_quantize_e4m3": (_I, [_P, _P, _Z, _I, _P]),
     "qb_kv_cache_update": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
+    "qb_qkv_post": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _F, _P]),
     "qb_rope_table_build": (_I, [_P, _I, _I, _P]),
     "qb_owl_attn_workspace_bytes": (_Z, [C.POINTER(AttnParams)]),
     "qb_owl_attn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(AttnParams), _P, _Z, _P]),

@@ -73,6 +73,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // UMMA descriptor for a K-major tile with 64-byte rows and the 64-byte swizzle (fp8, head_dim 64).
 __device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -369,7 +374,6 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       if (!ok) return;
       tc_fence_after();
       const uint32_t tmem_pv = tmem_g + (i & 1) * 128;
-      const float2 a2 = make_float2(alpha_prev, alpha_prev);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rr[32];
@@ -377,7 +381,10 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         tmem_wait_ld();
 #pragma unroll
         for (int q = 0; q < 16; ++q)
-          o2[c * 16 + q] = ffma2(o2[c * 16 + q], a2, make_float2(__uint_as_float(rr[2 * q]), __uint_as_float(rr[2 * q + 1])));
+          {
+            o2[c * 16 + q].x = fmaf(o2[c * 16 + q].x, alpha_prev, __uint_as_float(rr[2 * q]));
+            o2[c * 16 + q].y = fmaf(o2[c * 16 + q].y, alpha_prev, __uint_as_float(rr[2 * q + 1]));
+          }
       }
       uint32_t r16[16];
       tmem_ld16(tmem_pv + 64, r16);
@@ -402,11 +409,11 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         tmem_ld32(tmem_s + c * 32, rr);
         tmem_wait_ld();
         if (valid == kKeyTile) {
-          float m0 = mx, m1 = -INFINITY;
+          float m0 = mx, m1 = -INFINITY;  // two chains of 3-input max: 16 instructions for 32 values
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            m0 = fmaxf(m0, __uint_as_float(rr[2 * q]));
-            m1 = fmaxf(m1, __uint_as_float(rr[2 * q + 1]));
+          for (int q = 0; q < 8; ++q) {
+            m0 = max3f(m0, __uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]));
+            m1 = max3f(m1, __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
           }
           mx = fmaxf(m0, m1);
         } else {
@@ -423,7 +430,6 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       }
       // pass 2: probabilities -> shared memory
       const float nshift = kPShift - m_new;
-      const float2 sl22 = make_float2(sl2, sl2), ns2 = make_float2(nshift, nshift);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t rr[32];
@@ -432,7 +438,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         float2 x[16];
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          x[q] = ffma2(make_float2(__uint_as_float(rr[2 * q]), __uint_as_float(rr[2 * q + 1])), sl22, ns2);
+          x[q] = make_float2(fmaf(__uint_as_float(rr[2 * q]), sl2, nshift), fmaf(__uint_as_float(rr[2 * q + 1]), sl2, nshift));
           if (valid != kKeyTile) {
             if (c * 32 + 2 * q >= valid) x[q].x = -INFINITY;
             if (c * 32 + 2 * q + 1 >= valid) x[q].y = -INFINITY;

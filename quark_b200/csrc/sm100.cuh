@@ -53,7 +53,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      // the last operand is a suspend-time hint in ns: the thread may sleep that long inside the
+      // instruction (it is woken when the phase completes), so a waiting warp issues few instructions
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, 100000;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)

@@ -20,7 +20,7 @@ from ..runtime.tensor import QuarkTensor
 
 __all__ = [
     "gemm", "owl_attn", "kv_cache_update", "quantize_e4m3", "ada_rmsnorm", "head_rmsnorm", "value_residual_packed",
-    "ada_gate_residual", "silu", "euler_step", "patchify", "unpatchify", "increment", "rope_table",
+    "ada_gate_residual", "silu", "euler_step", "patchify", "unpatchify", "increment", "rope_table", "qkv_post",
 ]  # fmt: skip
 
 
@@ -236,6 +236,43 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
         )
     )  # fmt: skip
     return K_cache, Vt_cache, segments, n_segments
+
+
+def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, n_q_heads, n_kv_heads, H_spatial,
+             W_spatial, num_buckets, pinned_dilation, eps: float = 1e-6, max_segments=3, out=None):  # fmt: skip
+    """``head_rmsnorm`` + ``value_residual_packed`` + ``kv_cache_update`` in one launch (no reference
+    counterpart as a single call; bit-identical to the three calls of
+    ``src/quark/models/waypoint_15.py:398-407``).  ``QKV_first`` / ``lamb`` may both be None.
+    Returns the normalised / mixed packed QKV; the caches and segment table are updated in place."""
+    _bf16_only("qf.qkv_post", QKV)
+    tpf = int(H_spatial) * int(W_spatial)
+    qkv_dim = (n_q_heads + 2 * n_kv_heads) * 64
+    if QKV.ndim != 2 or tuple(QKV.shape) != (tpf, qkv_dim):
+        raise ValueError(f"qf.qkv_post: packed QKV shape {tuple(QKV.shape)} != ({tpf}, {qkv_dim})")
+    if (QKV_first is None) != (lamb is None):
+        raise ValueError("qf.qkv_post: QKV_first and lamb must be given together")
+    if QKV_first is not None and (tuple(QKV_first.shape) != tuple(QKV.shape) or _dt(QKV_first) != "bf16" or _dt(lamb) != "f32"):
+        raise ValueError("qf.qkv_post: QKV_first must match QKV (bf16) and lamb must be an f32 tensor")
+    cap = num_buckets * tpf + tpf
+    if tuple(K_cache.shape) != (n_kv_heads * cap, 64) or tuple(Vt_cache.shape) != (n_kv_heads * 64, cap):
+        raise ValueError(f"qf.qkv_post: cache shapes {tuple(K_cache.shape)} / {tuple(Vt_cache.shape)} do not match capacity {cap}")
+    if int(segments.shape[0]) != max_segments * 2 or int(n_segments.shape[0]) != 1:
+        raise ValueError("qf.qkv_post: segments / n_segments shapes")
+    kvd = _dt(K_cache)
+    if _dt(Vt_cache) != kvd or kvd not in ("bf16", "e4m3"):
+        raise TypeError(f"qf.qkv_post: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
+    out = _like(QKV, out, "qf.qkv_post")
+    p = _lib.KvParams(
+        n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+    )  # fmt: skip
+    _lib.check(
+        _lib.load().qb_qkv_post(
+            _p(QKV), _p(QKV_first), _p(lamb), _p(out), _p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments),
+            _p(n_segments), _p(rope_table(H_spatial, W_spatial)), C.byref(p), float(eps), _s(),
+        )
+    )  # fmt: skip
+    return out
 
 
 _DUMMY_FRAME_T: QuarkTensor | None = None

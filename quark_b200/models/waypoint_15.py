@@ -75,6 +75,8 @@ class Waypoint15Config:
     fuse_gate_residual: bool = True
     # Fold SiLU into fc1's epilogue (upstream does on its PTX / Metal GEMMs, not on the cuBLAS route).
     fuse_silu: bool = True
+    # head_rmsnorm + value residual + KV append as one launch (bit-identical to the three).
+    fuse_qkv_post: bool = True
 
     def __post_init__(self):
         if self.ctrl_conditioning:
@@ -215,10 +217,22 @@ class TransformerBlock(nn.Module):
         fp8 = self.qkv_proj.weight.data.dtype == "e4m3"
         fuse = self._cfg.fuse_gate_residual
 
-        qkv = self.head_norm(self.qkv_proj(self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)))
-        if hasattr(self, "v_residual") and qkv_first is not None:
-            qkv = self.v_residual(qkv, qkv_first)
-        self.kv_cache(qkv, frame_t, frozen=frozen)
+        qkv = self.qkv_proj(self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8))
+        use_first = hasattr(self, "v_residual") and qkv_first is not None
+        if self._cfg.fuse_qkv_post:
+            kc = self.kv_cache
+            qkv = qf.qkv_post(
+                qkv, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
+                frame_t if frame_t is not None else kc.frame_t, kc._frozen[1 if frozen else 0], kc.Vt_cache, kc.segments, kc.n_segments,
+                kc.K_cache, n_q_heads=self._cfg.n_heads, n_kv_heads=self._cfg.n_kv_heads, H_spatial=self._cfg.height,
+                W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
+                out=nn._cached(self, "qkv_post", qkv.shape, "bf16"),
+            )  # fmt: skip
+        else:
+            qkv = self.head_norm(qkv)
+            if use_first:
+                qkv = self.v_residual(qkv, qkv_first)
+            self.kv_cache(qkv, frame_t, frozen=frozen)
         attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8)
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))

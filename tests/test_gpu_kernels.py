@@ -213,6 +213,38 @@ def test_kv_cache_update_is_read_modify_write(qb):
     assert not np.any(K.reshape(2, cap, 64)[:, written] == 0x1234)
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,Hq,Hk,nb,pd,ft,frozen,with_first", [(8, 8, 4, 2, 4, 1, 6, 0, True), (16, 8, 32, 16, 16, 8, 128, 0, True),
+                                                                  (32, 16, 32, 16, 16, 1, 129, 1, True), (8, 16, 32, 16, 16, 8, 64, 0, False)])  # fmt: skip
+def test_qkv_post_is_bit_identical_to_the_three_kernels(qb, kv_dt, H, W, Hq, Hk, nb, pd, ft, frozen, with_first):
+    r = util.rng(H * W + ft)
+    qf = qb.qf
+    tpf, cap, D = H * W, (nb + 1) * H * W, (Hq + 2 * Hk) * 64
+    raw, first = bf16_randn(r, (tpf, D), 3.0), bf16_randn(r, (tpf, D))
+    lam = T(qb, np.array([0.37], np.float32))
+    geo = dict(B=1, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, packed_qkv=True, n_q_heads=Hq)
+
+    def state():
+        carrier = np.uint16 if kv_dt == "bf16" else np.uint8
+        return (T(qb, np.full((Hk * cap, 64), 0x11, carrier), kv_dt), T(qb, np.full((Hk * 64, cap), 0x22, carrier), kv_dt),
+                T(qb, np.full(6, -7, np.int32)), T(qb, np.array([-7], np.int32)))  # fmt: skip
+
+    ftt, frz = T(qb, np.array([ft], np.int32)), T(qb, np.array([frozen], np.int32))
+    Ka, Va, sa, na = state()
+    q1 = qf.head_rmsnorm(T(qb, raw, "bf16"), Hq, Hk, 64)
+    if with_first:
+        q1 = qf.value_residual_packed(q1, T(qb, first, "bf16"), lam, v_col_offset=(Hq + Hk) * 64, v_width=Hk * 64)
+    qf.kv_cache_update(q1, None, ftt, frz, Va, sa, na, Ka, **geo)
+    Kb, Vb, sb, nb_ = state()
+    q2 = qf.qkv_post(T(qb, raw, "bf16"), T(qb, first, "bf16") if with_first else None, lam if with_first else None, ftt, frz, Vb, sb, nb_, Kb,
+                     n_q_heads=Hq, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd)  # fmt: skip
+    np.testing.assert_array_equal(q2.to_numpy(), q1.to_numpy())
+    np.testing.assert_array_equal(Kb.to_numpy(), Ka.to_numpy())
+    np.testing.assert_array_equal(Vb.to_numpy(), Va.to_numpy())
+    np.testing.assert_array_equal(sb.to_numpy(), sa.to_numpy())
+    np.testing.assert_array_equal(nb_.to_numpy(), na.to_numpy())
+
+
 # --------------------------------------------------------------------------- GEMM
 
 
