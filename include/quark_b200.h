@@ -108,7 +108,8 @@ typedef struct {
   int32_t gate_groups;               /* G: gate is [G, N], each row covers M/G rows */
   int32_t split_k;                   /* 0 = choose; >= 1 forces the number of K slices */
   int32_t tile_n;                    /* 0 = choose; 64, 128 or 256 */
-  int32_t reserved;
+  int32_t reserved;                  /* slice mode: 0 = sum K slices inside a thread-block cluster when there are 2, 4 or 8
+                                        of them (no workspace traffic); 1 = always through the workspace */
   const float* a_scale; /* [1]  optional */
   const float* w_scale; /* [N]  optional */
 } qb_gemm_params;
@@ -246,6 +247,14 @@ int32_t qb_patchify(const void* X, const void* W, void* out, int32_t C, int32_t 
  * ref: src/quark/kernels/unpatchify/reference.py:8-24. */
 int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph,
                       int32_t pw, int32_t d_model, void* stream);
+
+/* The data movement of patchify / unpatchify alone (bf16): latent [C, H, W] <-> tokens
+ * [(H/ph)*(W/pw), C*ph*pw] with feature index c*ph*pw + r*pw + q, so that the contraction can run on
+ * qb_gemm: patchify = qb_patch_gather + qb_gemm, unpatchify = qb_gemm (with bias) + qb_patch_scatter.
+ * Same results as qb_patchify / qb_unpatchify up to the f32 summation order
+ * (ref: src/quark/kernels/patchify/reference.py:8-23, src/quark/kernels/unpatchify/reference.py:8-24). */
+int32_t qb_patch_gather(const void* latent, void* tokens_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream);
+int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream);
 
 #ifdef __cplusplus
 }

@@ -120,6 +120,8 @@ SIGNATURES = {
     "qb_increment": (_I, [_P, _P]),
     "qb_patchify": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "qb_unpatchify": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
+    "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
 }
 
 _lib = None

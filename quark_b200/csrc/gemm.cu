@@ -26,6 +26,7 @@ constexpr int kSmemBudget = 200 * 1024;
 struct GemmArgs {
   int M, N, K;
   int kb_total, kb_per_split, splits;
+  int cluster;  // K slices are the CTAs of one thread-block cluster and are summed through distributed shared memory
   int c_dtype, activation, rows_per_gate;
   const float* a_scale;
   const float* w_scale;
@@ -98,6 +99,22 @@ __device__ __forceinline__ void epilogue_store8(const GemmArgs& g, float (&v)[8]
   }
 }
 
+// Thread-block cluster helpers: hardware barrier over all threads of the cluster, and loads from
+// the shared memory of another CTA of the cluster.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, int cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
 template <int BN, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
@@ -106,6 +123,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int kKElems = FP8 ? 128 : 64;  // elements of K per stage
   constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
   constexpr uint32_t kIdesc = FP8 ? umma_idesc(0, 0, kBM, BN) : umma_idesc(1, 1, kBM, BN);
+  constexpr int kStgPitch = BN + 4;  // f32 words per staged row: the pad spreads a column of rows over the banks
+  static_assert(kBM * kStgPitch * 4 <= L::kStages * L::kStageBytes, "staging tile must fit in the stage memory");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -126,6 +145,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int kb0 = split * g.kb_per_split;
   const int kb1 = min(kb0 + g.kb_per_split, g.kb_total);
   const int n_iter = kb1 - kb0;
+  const bool clustered = g.cluster != 0 && g.splits > 1;
+  const bool use_staging = clustered;  // a single slice goes straight from TMEM to global memory (measured faster)
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -201,85 +222,136 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       umma_commit(smem_u32(acc_bar));
     }
   } else {
-    // ---------------- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+    // ---------------- epilogue, part 1: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
     const int m = m0 + row;
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_bar), 0, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM));
     tc_fence_after();
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
-    if (ok) {
-      if (g.splits == 1) {
+    if (ok && g.splits == 1) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c * 32, r);
-          tmem_wait_ld();
-          if (m < g.M) {
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_wait_ld();
+        if (m < g.M) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int n = n0 + c * 32 + q * 8;
-              if (n < g.N) {
-                float v[8];
+          for (int q = 0; q < 4; ++q) {
+            const int n = n0 + c * 32 + q * 8;
+            if (n < g.N) {
+              float v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[q * 8 + j]);
-                epilogue_store8(g, v, m, n);
-              }
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[q * 8 + j]);
+              epilogue_store8(g, v, m, n);
             }
           }
         }
-      } else {
-        float* part = g.partials + static_cast<size_t>(split) * g.M * g.N;
+      }
+    } else if (ok && use_staging) {
+      // accumulator row -> staging tile in the (now idle) stage memory, f32, padded pitch: one row per thread
+      float* dst = reinterpret_cast<float*>(smem) + static_cast<size_t>(row) * kStgPitch;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c * 32, r);
-          tmem_wait_ld();
-          if (m < g.M) {
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_wait_ld();
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const int n = n0 + c * 32 + q * 4;
-              if (n < g.N)
-                __stcg(reinterpret_cast<float4*>(part + static_cast<size_t>(m) * g.N + n),
-                       make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
-                                   __uint_as_float(r[q * 4 + 3])));
-            }
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(dst + c * 32 + q * 4) = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                                                                        __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+      }
+    } else if (ok) {
+      // K slices through the global workspace: partial tile out, ticket, last CTA adds the slices in order
+      float* part = g.partials + static_cast<size_t>(split) * g.M * g.N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_wait_ld();
+        if (m < g.M) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int n = n0 + c * 32 + q * 4;
+            if (n < g.N)
+              __stcg(reinterpret_cast<float4*>(part + static_cast<size_t>(m) * g.N + n),
+                     make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                 __uint_as_float(r[q * 4 + 3])));
           }
         }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      int* counter = g.counters + blockIdx.y * gridDim.x + blockIdx.x;
+      if (threadIdx.x == 64) {
+        const int ticket = atomicAdd(counter, 1);
+        *last_flag = (ticket == g.splits - 1) ? 1 : 0;
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        int* counter = g.counters + blockIdx.y * gridDim.x + blockIdx.x;
-        if (threadIdx.x == 64) {
-          const int ticket = atomicAdd(counter, 1);
-          *last_flag = (ticket == g.splits - 1) ? 1 : 0;
-          __threadfence();
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          // The tile is re-read from the workspace, so any thread-to-element mapping works: consecutive
-          // threads take consecutive groups of 8 columns (coalesced), slices are added in index order.
-          const int et = threadIdx.x - 64;  // 0..127
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        const int et = threadIdx.x - 64;  // 0..127
 #pragma unroll 1
-          for (int i8 = et; i8 < kBM * (BN / 8); i8 += 128) {
-            const int mm = m0 + i8 / (BN / 8);
-            const int n = n0 + (i8 % (BN / 8)) * 8;
-            if (mm >= g.M || n >= g.N) continue;
-            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int s = 0; s < g.splits; ++s) {
-              const float4* src = reinterpret_cast<const float4*>(g.partials + (static_cast<size_t>(s) * g.M + mm) * g.N + n);
-              const float4 x = __ldcg(src), y = __ldcg(src + 1);
-              v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-              v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-            }
-            epilogue_store8(g, v, mm, n);
+        for (int i8 = et; i8 < kBM * (BN / 8); i8 += 128) {
+          const int mm = m0 + i8 / (BN / 8);
+          const int n = n0 + (i8 % (BN / 8)) * 8;
+          if (mm >= g.M || n >= g.N) continue;
+          float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < g.splits; ++s) {
+            const float4* src = reinterpret_cast<const float4*>(g.partials + (static_cast<size_t>(s) * g.M + mm) * g.N + n);
+            const float4 x = __ldcg(src), y = __ldcg(src + 1);
+            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+            v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
           }
-          if (threadIdx.x == 64) *counter = 0;  // ready for the next launch
+          epilogue_store8(g, v, mm, n);
         }
+        if (threadIdx.x == 64) *counter = 0;  // ready for the next launch
       }
     }
   }
 
+  // ---------------- epilogue, part 2: every staged tile of the cluster is complete after this barrier
   tc_fence_before();
+  if (clustered) {
+    cluster_sync();
+  } else {
+    __syncthreads();
+  }
+  if (use_staging && warp >= 2 && *abort_flag == 0) {
+    // Rows are dealt out to the CTAs of the cluster; each sums its rows over all slices, in slice order,
+    // reading the peers' staging tiles through distributed shared memory.  Consecutive threads take
+    // consecutive groups of 8 columns, so global loads and stores are coalesced.
+    const int n_slices = clustered ? g.splits : 1;
+    const int rows_per_cta = kBM / n_slices;
+    const int row_begin = clustered ? split * rows_per_cta : 0;
+    const uint32_t stg_base = smem_u32(smem);
+    const int et = threadIdx.x - 64;  // 0..127
+#pragma unroll 1
+    for (int i8 = et; i8 < rows_per_cta * (BN / 8); i8 += 128) {
+      const int rr = row_begin + i8 / (BN / 8);
+      const int c8 = (i8 % (BN / 8)) * 8;
+      const int mm = m0 + rr, n = n0 + c8;
+      if (mm >= g.M || n >= g.N) continue;
+      const uint32_t local = stg_base + (static_cast<uint32_t>(rr) * kStgPitch + c8) * 4u;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (clustered) {
+        for (int s = 0; s < n_slices; ++s) {
+          const uint32_t remote = map_to_cta(local, s);
+          const float4 x = ld_dsmem_f4(remote), y = ld_dsmem_f4(remote + 16);
+          v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+          v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+        }
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(smem) + static_cast<size_t>(rr) * kStgPitch + c8);
+        const float4 x = src[0], y = src[1];
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+        v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+      }
+      epilogue_store8(g, v, mm, n);
+    }
+  }
+  if (clustered) cluster_sync();  // nobody leaves while a peer may still read its staging tile
+
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -331,6 +403,7 @@ static int32_t make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, u
 
 struct GemmPlan {
   int bn, splits, kb_total, kb_per_split;
+  int cluster;  // slices summed inside a thread-block cluster (2, 4 or 8 slices) instead of through the workspace
   size_t counters_bytes, aq_bytes, partial_bytes;
 };
 
@@ -376,7 +449,9 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       // measured: a K slice costs far more than its arithmetic share (row-per-thread f32 partial
       // stores, a second pass by the last CTA): ~12 us at 512 x 2048 x 8192, so slices only pay
       // when they multiply the number of busy SMs
-      if (s > 1) cta += 20000.0 + bn * 8.0 + s * bn * 4.0;
+      const bool cl = p.reserved != 1 && (s == 2 || s == 4 || s == 8);
+      // measured at 512 x 2048 x 8192: 4 workspace slices +12 us, 4 cluster slices +7 us over one slice
+      if (s > 1) cta += (cl ? 12000.0 : 20000.0) + bn * 8.0 + s * bn * 4.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
         best_cost = cost;
@@ -384,6 +459,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
         best.splits = s;
         best.kb_total = kb_total;
         best.kb_per_split = kbps;
+        best.cluster = (s > 1 && cl) ? 1 : 0;
       }
     }
   }
@@ -396,7 +472,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + best.bn - 1) / best.bn);
   best.counters_bytes = round_up(static_cast<size_t>(tiles) * sizeof(int), 1024);
   best.aq_bytes = (fp8 && p.a_dtype == QB_BF16) ? round_up(static_cast<size_t>(p.M) * p.K, 1024) : 0;
-  best.partial_bytes = best.splits > 1 ? static_cast<size_t>(best.splits) * p.M * p.N * sizeof(float) : 0;
+  best.partial_bytes = (best.splits > 1 && !best.cluster) ? static_cast<size_t>(best.splits) * p.M * p.N * sizeof(float) : 0;
   return best;
 }
 
@@ -416,6 +492,7 @@ static int32_t validate_gemm(const qb_gemm_params* p) {
   QB_REQUIRE(p->activation == 0 || p->activation == 1, QB_ERR_INVALID_ARG, "gemm: activation %d", p->activation);
   QB_REQUIRE(p->tile_n == 0 || p->tile_n == 64 || p->tile_n == 128 || p->tile_n == 256, QB_ERR_INVALID_ARG, "gemm: tile_n %d", p->tile_n);
   QB_REQUIRE(p->split_k >= 0 && p->split_k <= 16, QB_ERR_INVALID_ARG, "gemm: split_k %d", p->split_k);
+  QB_REQUIRE(p->reserved == 0 || p->reserved == 1, QB_ERR_INVALID_ARG, "gemm: slice_mode %d", p->reserved);
   return QB_OK;
 }
 
@@ -423,6 +500,24 @@ template <int BN, bool FP8>
 static int32_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, dim3 grid, cudaStream_t st) {
   using L = GemmSmem<BN>;
   QB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<BN, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  if (args.cluster && args.splits > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = L::kTotal;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = static_cast<unsigned>(args.splits);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, FP8>, tmA, tmB, args);
+    ++g_launch_count;
+    if (e != cudaSuccess) return fail(QB_ERR_LAUNCH, "gemm kernel (cluster of %d): %s", args.splits, cudaGetErrorString(e));
+    return QB_OK;
+  }
   gemm_kernel<BN, FP8><<<grid, kGemmThreads, L::kTotal, st>>>(tmA, tmB, args);
   return check_launch("gemm kernel");
 }
@@ -481,6 +576,7 @@ extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bi
   GemmArgs g{};
   g.M = p->M; g.N = p->N; g.K = p->K;
   g.kb_total = pl.kb_total; g.kb_per_split = pl.kb_per_split; g.splits = pl.splits;
+  g.cluster = pl.cluster;
   g.c_dtype = p->c_dtype; g.activation = p->activation; g.rows_per_gate = rows_per_gate;
   g.a_scale = p->a_scale; g.w_scale = p->w_scale;
   g.bias = static_cast<const uint16_t*>(bias);

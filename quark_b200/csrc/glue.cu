@@ -303,6 +303,26 @@ __global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* __restr
   }
 }
 
+// Pure data movement between the latent layout [C, H, W] and the token layout [tokens, C*ph*pw]
+// (token = patch (hp, wp), feature k = c*ph*pw + r*pw + q), so that patchify / unpatchify can run
+// their contraction on the tensor-core GEMM.  kToTokens: latent -> tokens, else tokens -> latent.
+template <bool kToTokens>
+__global__ void __launch_bounds__(256) patch_move_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C, int H, int Wd,
+                                                          int ph, int pw, int tokens) {
+  const int K = C * ph * pw;
+  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= static_cast<size_t>(tokens) * K) return;
+  const int tok = static_cast<int>(i / K), k = static_cast<int>(i % K);
+  const int Wp = Wd / pw;
+  const int c = k / (ph * pw), r = (k / pw) % ph, q = k % pw;
+  const int hp = tok / Wp, wp = tok % Wp;
+  const size_t lat = static_cast<size_t>(c) * H * Wd + static_cast<size_t>(hp * ph + r) * Wd + wp * pw + q;
+  if (kToTokens)
+    dst[i] = src[lat];
+  else
+    dst[lat] = src[i];
+}
+
 int32_t quantize_e4m3_launch(const void* X, void* out, size_t n, int32_t src_dtype, cudaStream_t st) {
   if (n == 0) return QB_OK;
   const unsigned blocks = static_cast<unsigned>((n + 2047) / 2048);
@@ -426,6 +446,26 @@ int32_t qb_patchify(const void* X, const void* W, void* out, int32_t C, int32_t 
   patchify_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(W),
                                                                            static_cast<uint16_t*>(out), C, H, Wd, ph, pw, d_model, tokens);
   return check_launch("patchify");
+}
+
+int32_t qb_patch_gather(const void* latent, void* tokens_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream) {
+  QB_REQUIRE(latent && tokens_out, QB_ERR_INVALID_ARG, "patch_gather: NULL pointer");
+  QB_REQUIRE(C > 0 && H > 0 && Wd > 0 && ph > 0 && pw > 0 && H % ph == 0 && Wd % pw == 0, QB_ERR_INVALID_ARG, "patch_gather: bad geometry");
+  const int tokens = (H / ph) * (Wd / pw);
+  const size_t n = static_cast<size_t>(tokens) * C * ph * pw;
+  patch_move_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(latent), static_cast<uint16_t*>(tokens_out), C, H, Wd, ph, pw, tokens);
+  return check_launch("patch_gather");
+}
+
+int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream) {
+  QB_REQUIRE(tokens_in && latent_out, QB_ERR_INVALID_ARG, "patch_scatter: NULL pointer");
+  QB_REQUIRE(C > 0 && H > 0 && Wd > 0 && ph > 0 && pw > 0 && H % ph == 0 && Wd % pw == 0, QB_ERR_INVALID_ARG, "patch_scatter: bad geometry");
+  const int tokens = (H / ph) * (Wd / pw);
+  const size_t n = static_cast<size_t>(tokens) * C * ph * pw;
+  patch_move_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(tokens_in), static_cast<uint16_t*>(latent_out), C, H, Wd, ph, pw, tokens);
+  return check_launch("patch_scatter");
 }
 
 int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph,

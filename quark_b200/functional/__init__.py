@@ -63,6 +63,19 @@ def _workspace(nbytes: int) -> QuarkTensor | None:
     return _WS
 
 
+_SCRATCH: dict = {}
+
+
+def _scratch(tag: str, shape, dtype: str) -> QuarkTensor:
+    """Persistent intermediate buffers of composed ops, keyed by use and shape (allocated once)."""
+    key = (tag, tuple(shape), dtype)
+    t = _SCRATCH.get(key)
+    if t is None:
+        t = QuarkTensor.empty(*shape, dtype=dtype)
+        _SCRATCH[key] = t
+    return t
+
+
 # ---------------------------------------------------------------------------
 # RoPE tables
 # ---------------------------------------------------------------------------
@@ -105,10 +118,10 @@ def rope_table(H: int, W: int) -> QuarkTensor:
 
 
 def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=None, bias=None, gate=None,
-         residual=None, gate_groups=1, out=None, *, a_scale=None, w_scale=None, split_k=0, tile_n=0):  # fmt: skip
+         residual=None, gate_groups=1, out=None, *, a_scale=None, w_scale=None, split_k=0, tile_n=0, slice_mode=0):  # fmt: skip
     """``C = A @ B.T`` (+ bias, SiLU, ``residual + gate * C``); ``src/quark/functional/gemm.py:597-635``.
 
-    ``a_scale`` / ``w_scale`` (f32 device tensors) and ``split_k`` / ``tile_n`` are extensions; left
+    ``a_scale`` / ``w_scale`` (f32 device tensors) and ``split_k`` / ``tile_n`` / ``slice_mode`` are extensions; left
     at their defaults the call is the reference's.
     """
     if b_shuffled:
@@ -147,7 +160,7 @@ def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=
     p = _lib.GemmParams(
         M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code(od, "bf16"),
         compute_dtype=_code(cd, "bf16"), activation=1 if activation == "silu" else 0, gate_groups=int(gate_groups),
-        split_k=int(split_k), tile_n=int(tile_n), reserved=0,
+        split_k=int(split_k), tile_n=int(tile_n), reserved=int(slice_mode),
         a_scale=a_scale.data_ptr() if a_scale is not None else None,
         w_scale=w_scale.data_ptr() if w_scale is not None else None,
     )  # fmt: skip
@@ -469,6 +482,11 @@ def patchify(X, W, *, B: int, C: int, H: int, W_spatial: int, ph: int = 2, pw: i
         out = QuarkTensor.empty(tokens, d_model, dtype="bf16")
     elif out.numel != tokens * d_model:
         raise ValueError(f"qf.patchify: out is {out.shape}, expected ({tokens}, {d_model})")
+    K = C * ph * pw
+    if K % 16 == 0 and d_model % 8 == 0:  # tensor-core route: gather the patches, then one GEMM
+        tmp = _scratch("patchify", (tokens, K), "bf16")
+        _lib.check(_lib.load().qb_patch_gather(_p(X), _p(tmp), C, H, W_spatial, ph, pw, _s()))
+        return gemm(tmp, W, out_dtype="bf16", out=out.reshape(tokens, d_model))
     _lib.check(_lib.load().qb_patchify(_p(X), _p(W), _p(out), C, H, W_spatial, ph, pw, d_model, _s()))
     return out
 
@@ -490,5 +508,11 @@ def unpatchify(X, weight, bias, *, B: int, C: int, H: int, W: int, ph: int = 2, 
         out = QuarkTensor.empty(B, C * H * W, dtype="bf16")
     elif out.numel != C * H * W:
         raise ValueError(f"qf.unpatchify: out is {out.shape}, expected ({B}, {C * H * W})")
+    n_out = C * ph * pw
+    if d_model % 16 == 0 and n_out % 8 == 0:  # tensor-core route: one GEMM (bias in its epilogue), then scatter
+        tmp = _scratch("unpatchify", (tokens, n_out), "bf16")
+        gemm(X.reshape(tokens, d_model), weight, out_dtype="bf16", bias=bias, out=tmp)
+        _lib.check(_lib.load().qb_patch_scatter(_p(tmp), _p(out), C, H, W, ph, pw, _s()))
+        return out
     _lib.check(_lib.load().qb_unpatchify(_p(X), _p(weight), _p(bias), _p(out), C, H, W, ph, pw, d_model, _s()))
     return out

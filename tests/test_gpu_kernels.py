@@ -248,7 +248,7 @@ def test_qkv_post_is_bit_identical_to_the_three_kernels(qb, kv_dt, H, W, Hq, Hk,
 # --------------------------------------------------------------------------- GEMM
 
 
-def _gemm_case(qb, M, N, K, *, fp8=False, a_fp8=False, bias=False, act=None, gate_groups=0, split_k=0, tile_n=0, out_dtype="bf16", seed=0):
+def _gemm_case(qb, M, N, K, *, fp8=False, a_fp8=False, bias=False, act=None, gate_groups=0, split_k=0, tile_n=0, slice_mode=0, out_dtype="bf16", seed=0):
     r = util.rng(seed)
     A = bf16_randn(r, (M, K))
     if fp8:
@@ -266,7 +266,7 @@ def _gemm_case(qb, M, N, K, *, fp8=False, a_fp8=False, bias=False, act=None, gat
         okw.update(gate=g, residual=res, gate_groups=gate_groups)
     a_dev = T(qb, Aq, "e4m3") if (fp8 and a_fp8) else T(qb, A, "bf16")
     got = qb.qf.gemm(a_dev, T(qb, B, "e4m3" if fp8 else "bf16"), out_dtype=out_dtype, compute_dtype="e4m3" if fp8 else None,
-                     activation=act, split_k=split_k, tile_n=tile_n, **kw)  # fmt: skip
+                     activation=act, split_k=split_k, tile_n=tile_n, slice_mode=slice_mode, **kw)  # fmt: skip
     want32 = ops.gemm(A, B, b_dtype="e4m3" if fp8 else "bf16", a_quant="e4m3" if fp8 else None, activation=act, return_f32=True, **okw)
     return got, want32
 
@@ -326,12 +326,14 @@ def test_gemm_production_shapes(qb, M, name, N, K, extra, fp8):
     _check_gemm(got, want, f"{name} M={M} fp8={fp8}", fp8)
 
 
-@pytest.mark.parametrize("split_k,tile_n", [(1, 64), (1, 128), (1, 256), (2, 128), (4, 64), (8, 256), (3, 128)])
+@pytest.mark.parametrize("split_k,tile_n,slice_mode", [(1, 64, 0), (1, 128, 0), (1, 256, 0), (2, 128, 0), (4, 64, 0), (8, 256, 0), (3, 128, 0),
+                                                       (2, 256, 1), (4, 128, 1), (4, 256, 0), (2, 64, 0)])  # fmt: skip
 @pytest.mark.parametrize("fp8", [False, True])
-def test_gemm_forced_tiles_and_k_slices_agree(qb, split_k, tile_n, fp8):
-    got, want = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, seed=3)
+def test_gemm_forced_tiles_and_k_slices_agree(qb, split_k, tile_n, slice_mode, fp8):
+    """K slices summed inside a thread-block cluster (2, 4, 8 slices, mode 0) or through the workspace."""
+    got, want = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, slice_mode=slice_mode, seed=3)
     _check_gemm(got, want, f"split_k={split_k} tile_n={tile_n}", fp8)
-    again, _ = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, seed=3)
+    again, _ = _gemm_case(qb, 256, 512, 2048, fp8=fp8, gate_groups=1, split_k=split_k, tile_n=tile_n, slice_mode=slice_mode, seed=3)
     np.testing.assert_array_equal(got.to_numpy(), again.to_numpy())  # slice order is fixed: run-to-run identical
 
 

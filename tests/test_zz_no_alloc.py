@@ -45,7 +45,8 @@ def test_static_scratch_gemm_equals_workspace_gemm_twice_in_a_row(M, N, K, split
     res = qb.QuarkTensor.from_numpy(r.standard_normal((M, N)).astype(np.float32), dtype="bf16")
     code = qb._lib.DTYPE_CODE
     p = qb._lib.GemmParams(M=M, N=N, K=K, a_dtype=code["bf16"], b_dtype=code["e4m3" if fp8 else "bf16"], c_dtype=code["bf16"],
-                           compute_dtype=code["e4m3" if fp8 else "bf16"], activation=0, gate_groups=1, split_k=split_k, tile_n=tile_n)  # fmt: skip
+                           compute_dtype=code["e4m3" if fp8 else "bf16"], activation=0, gate_groups=1, split_k=split_k, tile_n=tile_n,
+                           reserved=1)  # slice mode 1: partial tiles and tile counters go through the scratch  # fmt: skip
     need = int(lib.qb_gemm_workspace_bytes(C.byref(p)))
     assert 0 < need <= int(lib.qb_gemm_static_scratch_capacity()), "the case must use scratch and fit the built-in array"
     ws = qb.QuarkTensor.zeros(need, dtype="e4m3")
@@ -67,7 +68,7 @@ def test_static_scratch_rejects_oversized_requests():
     code = qb._lib.DTYPE_CODE
     # 8 K-slices of a 2048 x 4096 f32 tile set: far beyond 8 MiB
     p = qb._lib.GemmParams(M=2048, N=4096, K=8192, a_dtype=code["bf16"], b_dtype=code["bf16"], c_dtype=code["bf16"],
-                           compute_dtype=code["bf16"], gate_groups=1, split_k=8, tile_n=128)  # fmt: skip
+                           compute_dtype=code["bf16"], gate_groups=1, split_k=8, tile_n=128, reserved=1)  # fmt: skip
     assert int(lib.qb_gemm_workspace_bytes(C.byref(p))) > int(lib.qb_gemm_static_scratch_capacity())
     one = C.c_void_p(256)
     rc = lib.qb_gemm_static_scratch(one, one, one, None, None, None, C.byref(p), None)
