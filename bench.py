@@ -175,6 +175,22 @@ def time_kernels(qb, eng, peaks):
     return res
 
 
+def max_over_ranks(values, dist, device="cpu"):
+    """Element-wise maximum of a list of floats over all ranks (identity without a process group)."""
+    if dist is None:
+        return [float(v) for v in values]
+    import torch
+
+    t = torch.tensor(list(values), device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.cpu()]
+
+
+def aggregate_fps(world: int, steps: int, elapsed_ms_max: float) -> float:
+    """Whole-job frames per second: every rank generated `steps` frames in the slowest rank's time."""
+    return world * steps * 1000.0 / elapsed_ms_max
+
+
 def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -226,12 +242,7 @@ def run_ours(args):
         e3.synchronize()
         e2e_ms = max(e2.elapsed_ms(e3), (time.perf_counter() - t0) * 1e3)
         barrier()
-    if dist is not None:
-        import torch
-
-        t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    dev_ms, e2e_ms = max_over_ranks([dev_ms, e2e_ms], dist, "cuda")
     status = qb._lib.device_status()
 
     kernels = time_kernels(qb, eng, peaks) if rank == 0 else None
@@ -239,8 +250,8 @@ def run_ours(args):
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
-        fps = world * 1000.0 / ms_per_step
-        e2e_fps = world * 1000.0 * args.steps / e2e_ms
+        fps = aggregate_fps(world, args.steps, dev_ms)
+        e2e_fps = aggregate_fps(world, args.steps, e2e_ms)
         # every one of these runs once per layer: the dominant kernel is the slowest launch
         dom = max(("owl_attn", "gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"), key=lambda k: kernels[k]["us_per_launch"])
         gemm_us = sum(kernels[k]["us_per_launch"] for k in ("gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"))

@@ -105,6 +105,39 @@ __device__ __forceinline__ void locate_tile(const int (&seg)[6], int nseg, int j
   }
 }
 
+// 32 columns of one score row -> probabilities -> the P tile in shared memory (layout of a TMA tile).
+template <bool kFp8, bool kMasked>
+__device__ __forceinline__ void p_chunk(uint32_t tmem_s, int c, int valid, float sl2, float nshift, uint8_t* p_s, int r) {
+  uint32_t rr[32];
+  tmem_ld32(tmem_s + c * 32, rr);
+  tmem_wait_ld();
+  float e[32];
+#pragma unroll
+  for (int q = 0; q < 32; ++q) {
+    float x = fmaf(__uint_as_float(rr[q]), sl2, nshift);
+    if (kMasked && c * 32 + q >= valid) x = -INFINITY;
+    e[q] = ex2_approx(x);
+  }
+  const int sw = r & 7;
+  if (kFp8) {
+    uint32_t w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) w[q] = pack_e4m3x4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
+    uint8_t* rowp = p_s + r * 128;
+    *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    // keys 0..63 in the first half of the P buffer, 64..127 in the second; 128-byte rows
+    uint32_t w[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) w[q] = pack_bf16x2(e[2 * q], e[2 * q + 1]);
+    uint8_t* rowp = p_s + (c >> 1) * (kQTile * kKeyTile) + r * 128;
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+      *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + h) ^ sw) << 4)) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+  }
+}
+
 template <bool kFp8>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
@@ -428,42 +461,15 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         fold_pv(i - 1);
         if (!ok) break;
       }
-      // pass 2: probabilities -> shared memory
+      // pass 2: probabilities -> shared memory.  Full tiles (all but the last tile of a segment whose
+      // length is not a multiple of 128) take the path without per-element masking.
       const float nshift = kPShift - m_new;
+      if (valid == kKeyTile) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_s + c * 32, rr);
-        tmem_wait_ld();
-        float2 x[16];
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          x[q] = make_float2(fmaf(__uint_as_float(rr[2 * q]), sl2, nshift), fmaf(__uint_as_float(rr[2 * q + 1]), sl2, nshift));
-          if (valid != kKeyTile) {
-            if (c * 32 + 2 * q >= valid) x[q].x = -INFINITY;
-            if (c * 32 + 2 * q + 1 >= valid) x[q].y = -INFINITY;
-          }
-        }
-        if (kFp8) {
-          uint32_t w[8];
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            w[q] = pack_e4m3x4(ex2_approx(x[2 * q].x), ex2_approx(x[2 * q].y), ex2_approx(x[2 * q + 1].x), ex2_approx(x[2 * q + 1].y));
-          uint8_t* rowp = p_s + r * 128;
-          const int sw = r & 7;
-          *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-        } else {
-          // keys 0..63 in the first half of the P buffer, 64..127 in the second; 128-byte rows
-          uint32_t w[16];
-#pragma unroll
-          for (int q = 0; q < 16; ++q) w[q] = pack_bf16x2(ex2_approx(x[q].x), ex2_approx(x[q].y));
-          uint8_t* rowp = p_s + (c >> 1) * (L::kPBytes / 2) + r * 128;
-          const int sw = r & 7;
-#pragma unroll
-          for (int h = 0; h < 4; ++h)
-            *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + h) ^ sw) << 4)) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
-        }
+        for (int c = 0; c < 4; ++c) p_chunk<kFp8, false>(tmem_s, c, valid, sl2, nshift, p_s, r);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) p_chunk<kFp8, true>(tmem_s, c, valid, sl2, nshift, p_s, r);
       }
       m_run = m_new;
       alpha_prev = alpha;
