@@ -3,23 +3,38 @@
 // One CTA owns 128 query tokens of one Q head and walks the valid keys in tiles of 128, enumerated
 // from the (start, length) segment table, so a masked bucket is never loaded.  384 threads:
 //   warp 0        TMA producer: K tile [128 keys x 64] and V^T tile [64 x 128 keys] per stage
-//   warps 1, 2    one thread each issues tcgen05.mma for softmax group 0 / 1: S = Q K^T and PV = P V
+//   warps 1, 2    one thread each issues tcgen05.mma for softmax group 0 / 1: S = Q K^T and O += P V
 //   warp 3        idle (keeps the softmax warps aligned to the TMEM lane quarters)
 //   warps 4-7     softmax group 0: even key tiles        warps 8-11  softmax group 1: odd key tiles
-// Each softmax group runs its own online softmax over its half of the tiles, one query row per
-// thread, with two S buffers in TMEM (S(i+1) is computed while the group works on S(i)), its own P
-// buffer in shared memory, and PV(i) written over the TMEM columns of the S(i) it came from.  The two
-// partial results (row max, row sum, 64 outputs) are merged once at the end.  Two independent groups
-// give every SM sub-partition two warps of exp / FMA work to interleave; a single group (one warp
-// per sub-partition) is latency bound.
+// After set-up the control warps hand registers to the softmax warps (setmaxnreg), each of whose
+// threads keeps a whole score row of one query (128 values) in registers.
+//
+// Per group, TMEM holds one S tile (128 columns) and the output accumulator O (80 columns).  A softmax
+// thread copies its row of S(i) to registers (S(i + 1) may then be computed), takes the row maximum,
+// writes P(i) = 2^(score - m) to shared memory, and the MMA warp accumulates O += P(i) V(i) in TMEM.
+// m is the maximum the row was last rescaled to, not the running maximum: O (and the row sum) are
+// multiplied by 2^(m - m') only when a tile's maximum exceeds m by more than kSlack, which is rare after
+// the first tiles; P then stays below 2^(kPShift + kSlack), inside the range of e4m3 / bf16.  The two
+// partial results (m, row sum, 64 outputs) are merged once at the end.
+//
+// The exponentials bound this kernel (the special-function unit makes 16 per clock and SM; head_dim 64
+// gives it only 256 tensor-core flops per exponential to hide behind), so the two groups take turns on
+// them: while one group runs its exponentials the other loads its next row, finds the maximum and
+// synchronises with the MMA warp.  The turn passes when half of a tile's exponentials are issued, so the
+// unit always has two warps per scheduler to draw from.  Measured on B200 (720p, 8320 keys): free-running
+// groups fall into lock step and leave the unit idle half of the time (73 us); strict alternation 60 us;
+// alternation with the half-tile overlap 54 us.  A polynomial 2^x on the FMA pipe for part of the elements
+// (QB_POLY_OF8 > 0) is slower here, because the softmax warps are issue bound as well: 57 / 61 / 63 us for
+// 1 / 2 / 3 of every 8 elements.
 //
 // The row sum of P comes out of the tensor core: 16 rows of ones follow the 64 V^T rows of every
 // stage, so PV has 80 columns and column 64 is sum_k P[q, k] of exactly the rounded P that is
 // multiplied with V.  bf16 path: kind::f16 MMAs, P rounded to bf16.  fp8 path: Q (after RoPE), K, V
-// and P are e4m3 (kind::f8f6f4); P is scaled by 2^8 so small probabilities keep mantissa bits (the
-// factor cancels in the division by the row sum).  exp2 is ex2.approx.f32 in both paths: measured on
-// B200, ex2.approx.f16x2 issues at half the rate of the f32 form (no gain per element) and the
-// f16x2 -> e4m3x2 conversion is four times slower than f32 -> e4m3x2.
+// and P are e4m3 (kind::f8f6f4); P is scaled by 2^kPShift so small probabilities keep mantissa bits (the
+// factor cancels in the division by the row sum), and has two shared-memory tiles per group so that
+// writing P(i) never waits for PV(i - 1).  exp2 is ex2.approx.f32 in both paths: measured on B200,
+// ex2.approx.f16x2 issues at half the rate of the f32 form (no gain per element) and the f16x2 -> e4m3x2
+// conversion is four times slower than f32 -> e4m3x2.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -31,7 +46,27 @@ namespace qb {
 int32_t make_tmap_2d_sw(CUtensorMap* tm, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows,
                         uint32_t box_cols, int swizzle_bytes);
 
+#ifdef QB_ATTN_TRACE
+__device__ long long g_attn_trace[5][80][8];  // [role: softmax g0, g1, mma g0, g1][tile][point]
+#define QB_TR(role, i, pt)                                                                    \
+  do {                                                                                        \
+    if (blockIdx.x == 1 && blockIdx.y == 5 && lane == 0 && (i) < 80) g_attn_trace[role][i][pt] = clock64(); \
+  } while (0)
+#else
+#define QB_TR(role, i, pt) do { } while (0)
+#endif
+
 constexpr int kAttnThreads = 384;
+#ifndef QB_HANDOFF
+#define QB_HANDOFF 2
+#endif
+constexpr int kHandoffChunk = QB_HANDOFF;  // the exponentials' turn passes to the other group before this 32-key chunk
+#ifndef QB_POLY_OF8
+#define QB_POLY_OF8 0
+#endif
+constexpr int kPolyOf8 = QB_POLY_OF8;      // exponentials out of every 8 that run as a polynomial on the FMA pipe
+constexpr int kCtrlRegs = 64;      // per thread, warps 0-3 (128 x 64 + 256 x 216 <= 64 K registers)
+constexpr int kSoftmaxRegs = 216;  // per thread, warps 4-11
 constexpr int kQTile = 128;
 constexpr int kKeyTile = 128;
 constexpr int kVRows = 80;  // 64 channels + 16 rows of ones (row sum of P)
@@ -58,11 +93,12 @@ struct AttnSmem {
   static constexpr int kKBytes = kKeyTile * 64 * kEs;        // 16 KB | 8 KB
   static constexpr int kVTile = kVRows * 128;                // one 128-byte-wide V^T tile incl. ones rows: 10 KB
   static constexpr int kVBytes = kVTile * kEs;               // bf16: two tiles (keys 0-63, 64-127)
-  static constexpr int kPBytes = kQTile * kKeyTile * kEs;    // 32 KB | 16 KB, per softmax group
+  static constexpr int kPBytes = kQTile * kKeyTile * kEs;    // 32 KB | 16 KB, one P tile
+  static constexpr int kPBufs = kFp8 ? 2 : 1;                // P tiles per softmax group (bf16: no room for two)
   static constexpr int kStageBytes = kKBytes + kVBytes;
   static constexpr int kQOff = 0;
   static constexpr int kPOff = kQOff + kQBytes;
-  static constexpr int kStageOff = kPOff + 2 * kPBytes;
+  static constexpr int kStageOff = kPOff + 2 * kPBufs * kPBytes;
   static constexpr int kBarOff = kStageOff + kStages * kStageBytes;
   static constexpr int kTotal = kBarOff + 512 + 1024;
   static_assert(kStages * kStageBytes >= 66 * 128 * 4, "merge buffer aliases the stage area");
@@ -72,6 +108,31 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x on the FMA and integer pipes, for the share of the exponentials that the special-function unit
+// has no time for: x = n + f with n = round(x) taken from the low mantissa bits of x + 1.5 * 2^23, a
+// minimax polynomial for 2^f on [-0.5, 0.5] (degree 2: 1.7e-3 relative error, below what an e4m3
+// probability resolves; degree 3: 7.5e-5, below a bf16 ulp), n added to the exponent field.
+template <int kDegree>
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -120.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float p;
+  if (kDegree == 2) {
+    p = fmaf(0.23842892f, f, 0.70344800f);
+    p = fmaf(p, f, 1.0004431f);
+  } else {
+    p = fmaf(0.055171669f, f, 0.24261113f);
+    p = fmaf(p, f, 0.69326097f);
+    p = fmaf(p, f, 0.99992806f);
+  }
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+// Element q of a chunk goes to the polynomial when (q mod 8) < kPolyOf8.
+template <bool kFp8, int kPolyOf8>
+__device__ __forceinline__ float p_exp(int q, float x) {
+  return (q & 7) < kPolyOf8 ? ex2_poly<kFp8 ? 2 : 3>(x) : ex2_approx(x);
 }
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float d;
@@ -90,51 +151,46 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
 }
 
 // Which 128-key tile is the j-th valid one?  Returns its first cache row and how many of its
-// keys are valid.  Segments are (start, length) pairs; zero-length entries are legal.
-__device__ __forceinline__ void locate_tile(const int (&seg)[6], int nseg, int j, int& row, int& valid) {
+// keys are valid.  Segments are (start, length) pairs; zero-length entries are legal.  Fully
+// unrolled so the table stays in registers.
+__device__ __forceinline__ void locate_tile(const int (&seg)[6], int j, int& row, int& valid) {
   row = 0;
   valid = 0;
-  for (int i = 0; i < nseg; ++i) {
+  bool found = false;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
     const int nt = (seg[2 * i + 1] + kKeyTile - 1) / kKeyTile;
-    if (j < nt) {
+    if (!found && j < nt) {
       row = seg[2 * i] + j * kKeyTile;
       valid = min(kKeyTile, seg[2 * i + 1] - j * kKeyTile);
-      return;
+      found = true;
     }
     j -= nt;
   }
 }
 
-// 32 columns of one score row -> probabilities -> the P tile in shared memory (layout of a TMA tile).
-template <bool kFp8, bool kMasked>
-__device__ __forceinline__ void p_chunk(uint32_t tmem_s, int c, int valid, float sl2, float nshift, uint8_t* p_s, int r) {
-  uint32_t rr[32];
-  tmem_ld32(tmem_s + c * 32, rr);
-  tmem_wait_ld();
-  float e[32];
-#pragma unroll
-  for (int q = 0; q < 32; ++q) {
-    float x = fmaf(__uint_as_float(rr[q]), sl2, nshift);
-    if (kMasked && c * 32 + q >= valid) x = -INFINITY;
-    e[q] = ex2_approx(x);
-  }
+// 32 scores of one row (registers) -> probabilities -> the P tile in shared memory (layout of a TMA tile).
+template <bool kFp8, int kPolyOf8>
+__device__ __forceinline__ void p_chunk(const uint32_t (&sc)[32], int c, float sl2, float nshift, uint8_t* p_s, int r) {
   const int sw = r & 7;
+  auto pr = [&](int q) { return p_exp<kFp8, kPolyOf8>(q, fmaf(__uint_as_float(sc[q]), sl2, nshift)); };
   if (kFp8) {
     uint32_t w[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) w[q] = pack_e4m3x4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
+    for (int q = 0; q < 8; ++q) w[q] = pack_e4m3x4(pr(4 * q), pr(4 * q + 1), pr(4 * q + 2), pr(4 * q + 3));
     uint8_t* rowp = p_s + r * 128;
     *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
   } else {
     // keys 0..63 in the first half of the P buffer, 64..127 in the second; 128-byte rows
-    uint32_t w[16];
-#pragma unroll
-    for (int q = 0; q < 16; ++q) w[q] = pack_bf16x2(e[2 * q], e[2 * q + 1]);
     uint8_t* rowp = p_s + (c >> 1) * (kQTile * kKeyTile) + r * 128;
 #pragma unroll
-    for (int h = 0; h < 4; ++h)
-      *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + h) ^ sw) << 4)) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+    for (int h = 0; h < 4; ++h) {
+      uint32_t w[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(pr(8 * h + 2 * q), pr(8 * h + 2 * q + 1));
+      *reinterpret_cast<uint4*>(rowp + ((((c & 1) * 4 + h) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
   }
 }
 
@@ -146,7 +202,13 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdescS = kFp8 ? umma_idesc(0, 0, 128, 128) : umma_idesc(1, 1, 128, 128);
   constexpr uint32_t kIdescPV = kFp8 ? umma_idesc(0, 0, 128, kVRows) : umma_idesc(1, 1, 128, kVRows);
-  constexpr float kPShift = kFp8 ? 8.0f : 0.0f;
+  // P = 2^(kPShift + score - m) with m the row maximum the group last rescaled to; m is raised (and O
+  // rescaled) only when a tile's maximum exceeds it by more than kSlack, so P <= 2^(kPShift + kSlack):
+  // 256 for e4m3 (largest finite value 448), 256 for bf16.
+  constexpr float kPShift = kFp8 ? 5.0f : 0.0f;
+  constexpr float kSlack = kFp8 ? 3.0f : 8.0f;
+  constexpr uint32_t kGroupCols = 256;  // TMEM columns per softmax group: S at 0..127, O (80 columns) at 128
+  constexpr uint32_t kOCol = 128;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -154,11 +216,12 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* kv_full = bars;                  // [stages]
   uint64_t* kv_empty = bars + kStages;       // [stages]
-  uint64_t* s_full = bars + 2 * kStages;     // [group][buffer]
-  uint64_t* s_free = s_full + 4;             // [group][buffer]
-  uint64_t* p_full = s_free + 4;             // [group]
-  uint64_t* pv_full = p_full + 2;            // [group]
-  uint64_t* q_ready = pv_full + 2;
+  uint64_t* s_full = bars + 2 * kStages;     // [group] S(i) is in TMEM
+  uint64_t* s_free = s_full + 2;             // [group] the group holds S(i) in registers
+  uint64_t* p_full = s_free + 2;             // [group] P(i) is in shared memory, O is rescaled
+  uint64_t* pv_done = p_full + 2;            // [group] O += P(i) V(i) has finished
+  uint64_t* turn = pv_done + 2;              // [group] the other group has issued its exponentials
+  uint64_t* q_ready = turn + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* drain_flag = abort_flag + 1;
@@ -166,6 +229,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (warp == 4) QB_TR(4, 0, 0);
   const int q0 = blockIdx.x * kQTile;
   const int qh = blockIdx.y;
   const int kvh = qh / a.gqa;
@@ -175,11 +239,18 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   int nseg = min(__ldg(a.n_segments), min(a.max_segments, 3));
   bool seg_ok = true;
   int n_tiles = 0;
-  for (int i = 0; i < nseg; ++i) {
-    seg[2 * i] = __ldg(a.segments + 2 * i);
-    seg[2 * i + 1] = __ldg(a.segments + 2 * i + 1);
-    if (seg[2 * i] < 0 || seg[2 * i + 1] < 0 || (seg[2 * i] & 15) != 0 || seg[2 * i] + seg[2 * i + 1] > a.capacity) seg_ok = false;
-    n_tiles += (seg[2 * i + 1] + kKeyTile - 1) / kKeyTile;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    if (i < nseg) {
+      seg[2 * i] = __ldg(a.segments + 2 * i);
+      seg[2 * i + 1] = __ldg(a.segments + 2 * i + 1);
+      if (seg[2 * i] < 0 || seg[2 * i + 1] < 0 || (seg[2 * i] & 15) != 0 || seg[2 * i] + seg[2 * i + 1] > a.capacity) seg_ok = false;
+      n_tiles += (seg[2 * i + 1] + kKeyTile - 1) / kKeyTile;
+    }
+  }
+  if (!seg_ok) {
+#pragma unroll
+    for (int i = 0; i < 6; ++i) seg[i] = 0;
   }
   if (!seg_ok) {  // malformed table: report and attend to nothing (output rows become 0)
     n_tiles = 0;
@@ -194,12 +265,11 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       mbar_init(smem_u32(&kv_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&s_full[2 * b]), 1);
-      mbar_init(smem_u32(&s_full[2 * b + 1]), 1);
-      mbar_init(smem_u32(&s_free[2 * b]), 128);
-      mbar_init(smem_u32(&s_free[2 * b + 1]), 128);
+      mbar_init(smem_u32(&s_full[b]), 1);
+      mbar_init(smem_u32(&s_free[b]), 128);
       mbar_init(smem_u32(&p_full[b]), 128);
-      mbar_init(smem_u32(&pv_full[b]), 1);
+      mbar_init(smem_u32(&pv_done[b]), 1);
+      mbar_init(smem_u32(&turn[b]), 128);
     }
     mbar_init(smem_u32(q_ready), 256);
     *abort_flag = 0;
@@ -226,7 +296,11 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (warp == 4) QB_TR(4, 0, 1);
 
+  // Registers move from the four control warps to the softmax warps, which hold a whole score row each.
+  if (warp < 4) {
+  setmaxnreg_dec<kCtrlRegs>();
   if (warp == 0) {
     // ---------------- TMA producer
     if (elect_one()) {
@@ -236,7 +310,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         const uint32_t ph = (j / kStages) & 1;
         if (!mbar_wait(smem_u32(&kv_empty[s]), ph ^ 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN)) break;
         int row, valid;
-        locate_tile(seg, nseg, j, row, valid);
+        locate_tile(seg, j, row, valid);
         const uint32_t fb = smem_u32(&kv_full[s]);
         mbar_arrive_expect_tx(fb, L::kKBytes + (kFp8 ? 1 : 2) * 64 * 128);
         uint8_t* st = smem + L::kStageOff + s * L::kStageBytes;
@@ -257,28 +331,29 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     }
   } else if (warp == 1 || warp == 2) {
     // ---------------- MMA issuers: warp 1 serves softmax group 0 (even tiles), warp 2 group 1 (odd tiles).
-    // Per group: S(i) goes to TMEM buffer i & 1 of the group; once the group has turned S(i) into P(i),
-    // PV(i) is written over the first 80 columns of the same buffer; the buffer is free for S(i + 2)
-    // when the group has folded PV(i) into its registers.  S(i + 1) is issued ahead of PV(i).
+    // Per group: S(i) goes to the group's S columns as soon as the group has copied S(i - 1) into its
+    // registers; once the group has written P(i) (and rescaled O if a row maximum jumped), O += P(i) V(i)
+    // accumulates in the group's O columns.  S(i + 1) is issued ahead of PV(i).
     const int g = warp - 1;
     const int n_g = n_tiles > g ? (n_tiles - g + 1) / 2 : 0;
     if (elect_one() && n_g > 0) {
       const uint32_t q_addr = smem_u32(q_s);
-      const uint32_t p_addr = smem_u32(smem + L::kPOff + g * L::kPBytes);
+      const uint32_t p_base = smem_u32(smem + L::kPOff + g * L::kPBufs * L::kPBytes);
+      const uint32_t tmem_sg = tmem_base + g * kGroupCols;
+      const uint32_t tmem_og = tmem_sg + kOCol;
       auto stage_addr = [&](int j) { return smem_u32(smem + L::kStageOff + (j % kStages) * L::kStageBytes); };
       auto issue_s = [&](int i) {
         const uint32_t k_addr = stage_addr(2 * i + g);
-        const uint32_t d = tmem_base + g * 256 + (i & 1) * 128;
         if (kFp8) {
           const uint64_t qd = umma_desc_k_sw64(q_addr), kd = umma_desc_k_sw64(k_addr);
 #pragma unroll
-          for (int k = 0; k < 2; ++k) umma_f8(d, qd + 2 * k, kd + 2 * k, kIdescS, k > 0);
+          for (int k = 0; k < 2; ++k) umma_f8(tmem_sg, qd + 2 * k, kd + 2 * k, kIdescS, k > 0);
         } else {
           const uint64_t qd = umma_desc_k_sw128(q_addr), kd = umma_desc_k_sw128(k_addr);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f16(d, qd + 2 * k, kd + 2 * k, kIdescS, k > 0);
+          for (int k = 0; k < 4; ++k) umma_f16(tmem_sg, qd + 2 * k, kd + 2 * k, kIdescS, k > 0);
         }
-        umma_commit(smem_u32(&s_full[2 * g + (i & 1)]));
+        umma_commit(smem_u32(&s_full[g]));
       };
       auto wait_tile = [&](int j) {
         return mbar_wait(smem_u32(&kv_full[j % kStages]), (j / kStages) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
@@ -290,37 +365,43 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         issue_s(0);
       }
       for (int i = 0; i < n_g && ok; ++i) {
+        QB_TR(2 + g, i, 0);
         if (i + 1 < n_g) {
-          const int in = i + 1;
-          ok = wait_tile(2 * in + g);
-          if (ok && in >= 2)
-            ok = mbar_wait(smem_u32(&s_free[2 * g + (in & 1)]), ((in >> 1) - 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
+          ok = wait_tile(2 * (i + 1) + g);
+          QB_TR(2 + g, i, 1);
+          ok = ok && mbar_wait(smem_u32(&s_free[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
           if (!ok) break;
+          QB_TR(2 + g, i, 2);
           tc_fence_after();
-          issue_s(in);
+          issue_s(i + 1);
         }
+        QB_TR(2 + g, i, 3);
         ok = mbar_wait(smem_u32(&p_full[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
         if (!ok) break;
+        QB_TR(2 + g, i, 4);
         tc_fence_after();
         const uint32_t v_addr = stage_addr(2 * i + g) + L::kKBytes;
-        const uint32_t d = tmem_base + g * 256 + (i & 1) * 128;
+        const uint32_t p_addr = p_base + (i % L::kPBufs) * L::kPBytes;
         if (kFp8) {
           const uint64_t pd = umma_desc_k_sw128(p_addr), vd = umma_desc_k_sw128(v_addr);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f8(d, pd + 2 * k, vd + 2 * k, kIdescPV, k > 0);
+          for (int k = 0; k < 4; ++k) umma_f8(tmem_og, pd + 2 * k, vd + 2 * k, kIdescPV, (i | k) > 0);
         } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t pd = umma_desc_k_sw128(p_addr + (k >> 2) * (L::kPBytes / 2));
             const uint64_t vd = umma_desc_k_sw128(v_addr + (k >> 2) * L::kVTile);
-            umma_f16(d, pd + 2 * (k & 3), vd + 2 * (k & 3), kIdescPV, k > 0);
+            umma_f16(tmem_og, pd + 2 * (k & 3), vd + 2 * (k & 3), kIdescPV, (i | k) > 0);
           }
         }
-        umma_commit(smem_u32(&pv_full[g]));
+        umma_commit(smem_u32(&pv_done[g]));
         umma_commit(smem_u32(&kv_empty[(2 * i + g) % kStages]));
+        QB_TR(2 + g, i, 5);
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    setmaxnreg_inc<kSoftmaxRegs>();
     // ---------------- softmax groups: one query row per thread, group g takes tiles j = 2 i + g
     const int g = (warp - 4) >> 2;
     const int lane_grp = warp & 3;
@@ -328,7 +409,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const int t = q0 + r;
     const bool row_ok = t < a.tpf;
     const uint32_t lane_addr = static_cast<uint32_t>(lane_grp * 32) << 16;
-    uint8_t* p_s = smem + L::kPOff + g * L::kPBytes;
+    uint8_t* p_g = smem + L::kPOff + g * L::kPBufs * L::kPBytes;
 
     // Q row -> RoPE -> shared memory (K-major, swizzled like a TMA tile).  Group 0 rotates pairs
     // 0..15 (spatial angles), group 1 pairs 16..31 (temporal angles).
@@ -390,106 +471,140 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       }
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(q_ready));
+      if (warp == 4) QB_TR(4, 0, 2);
     }
 
     const float ks = a.k_scale ? __ldg(a.k_scale + kvh) : 1.0f;
     const float sl2 = ks * 0.125f * 1.4426950408889634f;  // scores -> log2 domain, 1/sqrt(64) folded in
-    const uint32_t tmem_g = tmem_base + g * 256 + lane_addr;  // this group's two S / PV buffers
-    float m_run = -1.0e30f, alpha_prev = 0.f, l_run = 0.f;
-    float2 o2[32];
-#pragma unroll
-    for (int d = 0; d < 32; ++d) o2[d] = make_float2(0.f, 0.f);
+    const uint32_t tmem_s = tmem_base + g * kGroupCols + lane_addr;  // this thread's row of the group's S
+    const uint32_t tmem_o = tmem_s + kOCol;                          // ... and of its O accumulator
+    float m_run = -1.0e30f;
     bool ok = true;
     const int my_tiles = n_tiles > g ? (n_tiles - g + 1) / 2 : 0;
 
-    auto fold_pv = [&](int i) {  // o = o * alpha + PV(tile i of this group); column 64 carries the row sum
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&pv_full[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
-      if (!ok) return;
-      tc_fence_after();
-      const uint32_t tmem_pv = tmem_g + (i & 1) * 128;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_pv + c * 32, rr);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q = 0; q < 16; ++q)
-          {
-            o2[c * 16 + q].x = fmaf(o2[c * 16 + q].x, alpha_prev, __uint_as_float(rr[2 * q]));
-            o2[c * 16 + q].y = fmaf(o2[c * 16 + q].y, alpha_prev, __uint_as_float(rr[2 * q + 1]));
-          }
-      }
-      uint32_t r16[16];
-      tmem_ld16(tmem_pv + 64, r16);
-      tmem_wait_ld();
-      l_run = fmaf(l_run, alpha_prev, __uint_as_float(r16[0]));
-      tc_fence_before();
-      mbar_arrive(smem_u32(&s_free[2 * g + (i & 1)]));  // the buffer may take S(i + 2) now
-    };
-
     for (int i = 0; i < my_tiles && ok; ++i) {
+      if (lane_grp == 0) QB_TR(g, i, 0);
       int row, valid;
-      locate_tile(seg, nseg, 2 * i + g, row, valid);
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[2 * g + (i & 1)]), (i >> 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
+      locate_tile(seg, 2 * i + g, row, valid);
+      if (lane_grp == 0) QB_TR(g, i, 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tmem_s = tmem_g + (i & 1) * 128;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_s + c * 32, rr);
-        tmem_wait_ld();
-        if (valid == kKeyTile) {
-          float m0 = mx, m1 = -INFINITY;  // two chains of 3-input max: 16 instructions for 32 values
+      if (lane_grp == 0) QB_TR(g, i, 2);
+      // the whole score row into registers; the S columns are then free for the next tile
+      uint32_t sc[4][32];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            m0 = max3f(m0, __uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]));
-            m1 = max3f(m1, __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
-          }
-          mx = fmaxf(m0, m1);
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + c * 32, sc[c]);
+      tmem_wait_ld();
+      if (lane_grp == 0) QB_TR(g, i, 3);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&s_free[g]));
+      if (valid != kKeyTile) {  // last tile of a segment whose length is not a multiple of 128
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int q = 0; q < 32; ++q)
-            if (c * 32 + q < valid) mx = fmaxf(mx, __uint_as_float(rr[q]));
+            if (c * 32 + q >= valid) sc[c][q] = 0xff800000u;  // -inf
+      }
+      float mx[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float m0 = __uint_as_float(sc[c][0]), m1 = __uint_as_float(sc[c][1]);
+#pragma unroll
+        for (int q = 0; q < 15; ++q) {  // two chains of 3-input max
+          if (q & 1) m1 = max3f(m1, __uint_as_float(sc[c][2 + 2 * q]), __uint_as_float(sc[c][3 + 2 * q]));
+          else m0 = max3f(m0, __uint_as_float(sc[c][2 + 2 * q]), __uint_as_float(sc[c][3 + 2 * q]));
+        }
+        mx[c] = fmaxf(m0, m1);
+      }
+      const float m_tile = max3f(max3f(mx[0], mx[1], mx[2]), mx[3], -1.0e30f) * sl2;
+      if (lane_grp == 0) QB_TR(g, i, 4);
+      if (i == 0) {
+        m_run = m_tile;
+      } else {
+        const bool jump = m_tile > m_run + kSlack;
+        const bool any_jump = __any_sync(0xffffffffu, jump);
+        // O may be rescaled only when PV(i - 1) has finished.  The P tile written below was last read
+        // by PV(i - 1) when the group has one P tile; with two it was PV(i - 2), which finished before
+        // S(i) did (the MMA warp issued it earlier, and s_full covers everything issued before it).
+        if (L::kPBufs == 1 || any_jump) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&pv_done[g]), (i - 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
+          if (!ok) break;
+        }
+        if (any_jump) {
+          const float alpha = jump ? ex2_approx(m_run - m_tile) : 1.0f;
+          if (jump) m_run = m_tile;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t oo[32];
+            tmem_ld32(tmem_o + c * 32, oo);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 32; ++q) oo[q] = __float_as_uint(__uint_as_float(oo[q]) * alpha);
+            tmem_st32(tmem_o + c * 32, oo);
+          }
+          const uint32_t lsum = tmem_ld1(tmem_o + 64);
+          tmem_wait_ld();
+          tmem_st1(tmem_o + 64, __float_as_uint(__uint_as_float(lsum) * alpha));
+          tmem_wait_st();
         }
       }
-      const float m_new = fmaxf(m_run, mx * sl2);
-      const float alpha = ex2_approx(m_run - m_new);
-      if (i > 0) {
-        fold_pv(i - 1);
+      const float nshift = kPShift - m_run;
+      if (lane_grp == 0) QB_TR(g, i, 5);
+      // The two groups take turns on the exponentials (the special-function unit is the scarcest
+      // resource of this kernel): order G0(0) G1(0) G0(1) G1(1) ...  While one group runs its
+      // exponentials the other loads its next score row, finds the maximum and talks to the MMA warps.
+      if (g == 0 ? i > 0 : true) {
+        const uint32_t par = g == 0 ? (i - 1) & 1 : i & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&turn[g]), par, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
         if (!ok) break;
       }
-      // pass 2: probabilities -> shared memory.  Full tiles (all but the last tile of a segment whose
-      // length is not a multiple of 128) take the path without per-element masking.
-      const float nshift = kPShift - m_new;
-      if (valid == kKeyTile) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) p_chunk<kFp8, false>(tmem_s, c, valid, sl2, nshift, p_s, r);
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) p_chunk<kFp8, true>(tmem_s, c, valid, sl2, nshift, p_s, r);
+      if (lane_grp == 0) QB_TR(g, i, 6);
+      uint8_t* p_s = p_g + (i % L::kPBufs) * L::kPBytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        // handed over before the last chunks: the other group needs a while to wake up, and two warps
+        // per scheduler keep the special-function unit busier than one
+        if (c == kHandoffChunk) mbar_arrive(smem_u32(&turn[1 - g]));
+        p_chunk<kFp8, kPolyOf8>(sc[c], c, sl2, nshift, p_s, r);
       }
-      m_run = m_new;
-      alpha_prev = alpha;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&p_full[g]));
+      if (lane_grp == 0) QB_TR(g, i, 7);
     }
-    if (ok && my_tiles > 0) fold_pv(my_tiles - 1);
+    if (warp == 4) QB_TR(4, 0, 3);
+    // the group's result: 64 outputs and the row sum, still scaled by 2^(kPShift - m_run)
+    float o[64];
+    float l_run = 0.f;
+#pragma unroll
+    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    if (ok && my_tiles > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&pv_done[g]), (my_tiles - 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
+      if (ok) {
+        tc_fence_after();
+        uint32_t oo[2][32];
+        tmem_ld32(tmem_o, oo[0]);
+        tmem_ld32(tmem_o + 32, oo[1]);
+        const uint32_t lsum = tmem_ld1(tmem_o + 64);
+        tmem_wait_ld();
+#pragma unroll
+        for (int d = 0; d < 64; ++d) o[d] = __uint_as_float(oo[d >> 5][d & 31]);
+        l_run = __uint_as_float(lsum);
+      }
+    }
 
+    if (warp == 4) QB_TR(4, 0, 4);
     // ---------------- merge the two groups (tensor work and TMA traffic are finished for both after the barrier)
     asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (warp == 4) QB_TR(4, 0, 5);
     float* comb = reinterpret_cast<float*>(smem + L::kStageOff);  // [66][128]
     if (g == 1) {
       comb[0 * 128 + r] = m_run;
       comb[1 * 128 + r] = l_run;
 #pragma unroll
-      for (int d = 0; d < 32; ++d) {
-        comb[(2 + 2 * d) * 128 + r] = o2[d].x;
-        comb[(3 + 2 * d) * 128 + r] = o2[d].y;
-      }
+      for (int d = 0; d < 64; ++d) comb[(2 + d) * 128 + r] = o[d];
     }
     asm volatile("bar.sync 2, 256;" ::: "memory");
     if (g == 0 && ok && row_ok && *abort_flag == 0) {
@@ -507,8 +622,8 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int d = 4 * v + q;
-          const float e0 = o2[d].x * s0 + comb[(2 + 2 * d) * 128 + r] * s1;
-          const float e1 = o2[d].y * s0 + comb[(3 + 2 * d) * 128 + r] * s1;
+          const float e0 = o[2 * d] * s0 + comb[(2 + 2 * d) * 128 + r] * s1;
+          const float e1 = o[2 * d + 1] * s0 + comb[(3 + 2 * d) * 128 + r] * s1;
           w[q] = pack_bf16x2(e0, e1);
         }
         dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -521,8 +636,10 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     }
   }
 
+  if (warp == 4) QB_TR(4, 0, 6);
   tc_fence_before();
   __syncthreads();
+  if (warp == 4) QB_TR(4, 0, 7);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -532,6 +649,12 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 }  // namespace qb
 
 using namespace qb;
+
+#ifdef QB_ATTN_TRACE
+extern "C" int32_t qb_debug_attn_trace(void* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(g_attn_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p) {
   (void)p;

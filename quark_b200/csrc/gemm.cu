@@ -1,7 +1,7 @@
 // C[M,N] = epilogue(A[M,K] . B[N,K]^T) on the sm_100a tensor cores.
 //
 // One CTA computes one 128 x BN output tile over one K slice.  Warp 0 feeds a ring of
-// shared-memory stages with TMA (128-byte swizzle, no multicast), one thread of warp 1 issues
+// shared-memory stages with TMA (128-byte swizzle), one thread of warp 1 issues
 // tcgen05.mma into a TMEM accumulator, warps 2-5 read the accumulator back (one row per
 // thread) and run the epilogue.  bf16 operands use kind::f16 (K = 16 per instruction), e4m3
 // operands kind::f8f6f4 (K = 32); both move 128 bytes of K per stage row, so the two paths share

@@ -394,6 +394,33 @@ def test_owl_attn_model_geometry(qb, kv_dt, H, W, pd, ft):
     _attn_check(got, want, f"attn {H}x{W} pd={pd} ft={ft} {kv_dt}", kv_dt == "e4m3")
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("direction", ["rising", "falling"])
+def test_owl_attn_score_scale_drifts_along_the_cache(qb, kv_dt, direction):
+    """Key magnitude ramps along the cache rows, so the row maxima jump from tile to tile (rising: the
+    running maximum has to be raised again and again; falling: it stays at the first tile's)."""
+    r = util.rng(41)
+    Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 16, 8, 1, 20
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 8 * 64)), n_q_heads=4, n_kv_heads=2)
+    ramp = np.linspace(0.25, 14.0, cap, dtype=np.float32)
+    if direction == "falling":
+        ramp = ramp[::-1]
+    Kf = r.standard_normal((Hk, cap, 64), dtype=np.float32) * ramp[None, :, None]
+    Vf = r.standard_normal((Hk, 64, cap), dtype=np.float32)
+    to = codec.f32_to_bf16 if kv_dt == "bf16" else codec.f32_to_e4m3
+    Kc, Vc = to(Kf.reshape(Hk * cap, 64)), to(Vf.reshape(Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    got = _attn_run(qb, qkv, Kc, Vc, segs, [n], ft, Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=pd, kv_dt=kv_dt)
+    # scores reach +-60 here, so one bf16 ulp on a rotated query moves a probability by 20 %: the
+    # oracle is fed the rotated query narrowed the way the kernel narrows it for its MMAs (bf16 or
+    # e4m3, nearest even), which the reference oracle keeps in f32
+    with codec.bf16_rounding("rne"):
+        want = ops.owl_attn(qkv, Kc, Vc, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                            q_quant=kv_dt)  # fmt: skip
+    _attn_check(got, want, f"attn drifting scale {direction} {kv_dt}", kv_dt == "e4m3")
+
+
 def test_owl_attn_e4m3_side_output_is_the_narrowed_bf16_output(qb):
     r = util.rng(31)
     Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 8, 4, 1, 9
