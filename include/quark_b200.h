@@ -59,6 +59,12 @@ int32_t qb_device_status(uint32_t* status_host);
 /* Number of kernels this library has launched since it was loaded (launches recorded into a CUDA
  * graph during capture count once, replays do not count). */
 uint64_t qb_kernel_launch_count(void);
+/* The hot-path kernels are launched so that each may begin its set-up (barriers, TMEM, weight prefetch)
+ * while the kernel before it in the stream is still running (programmatic dependent launch); each waits
+ * for that kernel to complete before it reads its results or writes global memory, so results do not
+ * change.  enabled = 0 turns this off (as does QB_DEPENDENT_LAUNCH=0 in the environment when the library
+ * is loaded).  Returns the previous setting.  No counterpart in the reference. */
+int32_t qb_set_dependent_launch(int32_t enabled);
 
 /* ------------------------------------------------------------------ memory / streams / graphs
  * Replaces the ctypes libcuda subset the reference's tensor class uses
@@ -108,8 +114,10 @@ typedef struct {
   int32_t gate_groups;               /* G: gate is [G, N], each row covers M/G rows */
   int32_t split_k;                   /* 0 = choose; >= 1 forces the number of K slices */
   int32_t tile_n;                    /* 0 = choose; 64, 128 or 256 */
-  int32_t reserved;                  /* slice mode: 0 = sum K slices inside a thread-block cluster when there are 2, 4 or 8
-                                        of them (no workspace traffic); 1 = always through the workspace */
+  int32_t reserved;                  /* flags.  bit 0, slice mode: 0 = sum K slices inside a thread-block cluster when there
+                                        are 2, 4 or 8 of them (no workspace traffic); 1 = always through the workspace.
+                                        bit 1: B is constant (weights; no kernel in flight writes it), so its first tiles
+                                        may be fetched before the kernels ahead of this one in the stream have finished */
   const float* a_scale; /* [1]  optional */
   const float* w_scale; /* [N]  optional */
 } qb_gemm_params;

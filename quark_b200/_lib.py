@@ -81,6 +81,7 @@ SIGNATURES = {
     "qb_set_device": (_I, [_I]),
     "qb_device_status": (_I, [C.POINTER(_U)]),
     "qb_kernel_launch_count": (C.c_uint64, []),
+    "qb_set_dependent_launch": (C.c_int32, [C.c_int32]),
     "qb_malloc": (_I, [C.POINTER(_P), _Z]),
     "qb_free": (_I, [_P]),
     "qb_host_alloc": (_I, [C.POINTER(_P), _Z]),
@@ -169,6 +170,11 @@ def require_device(device: int = 0) -> None:
 
 def kernel_launch_count() -> int:
     return int(load().qb_kernel_launch_count())
+
+
+def set_dependent_launch(enabled: bool) -> bool:
+    """Turns the overlap of a kernel's set-up with its predecessor's tail on or off; returns the old setting."""
+    return bool(load().qb_set_dependent_launch(1 if enabled else 0))
 
 
 def device_status() -> int:

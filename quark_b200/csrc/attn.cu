@@ -234,6 +234,51 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   const int qh = blockIdx.y;
   const int kvh = qh / a.gqa;
 
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&kv_full[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&s_full[b]), 1);
+      mbar_init(smem_u32(&s_free[b]), 128);
+      mbar_init(smem_u32(&p_full[b]), 128);
+      mbar_init(smem_u32(&pv_done[b]), 1);
+      mbar_init(smem_u32(&turn[b]), 128);
+    }
+    mbar_init(smem_u32(q_ready), 256);
+    *abort_flag = 0;
+    *drain_flag = 0;
+    fence_barrier_init();
+  }
+  // rows of ones under every V^T tile (16 rows x 128 bytes each): the tensor core then returns the row sum of P
+  {
+    constexpr uint32_t kOnes = kFp8 ? 0x38383838u : 0x3F803F80u;
+    constexpr int kTilesPerStage = kFp8 ? 1 : 2;
+    for (int i = threadIdx.x; i < kStages * kTilesPerStage * 128; i += kAttnThreads) {  // 128 x 16 bytes per tile
+      const int tile = i >> 7, v = i & 127;
+      uint8_t* base = smem + L::kStageOff + (tile / kTilesPerStage) * L::kStageBytes + L::kKBytes + (tile % kTilesPerStage) * L::kVTile;
+      *reinterpret_cast<uint4*>(base + 64 * 128 + v * 16) = make_uint4(kOnes, kOnes, kOnes, kOnes);
+    }
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (warp == 4) QB_TR(4, 0, 1);
+
+  // Everything above touched only this CTA's shared memory and TMEM, so it may run while the kernels
+  // before this one in the stream are still at work; everything below reads what they wrote.
+  grid_dep_launch();
+  grid_dep_wait();
+
   // segment table -> number of key tiles (same in every thread)
   int seg[6] = {0, 0, 0, 0, 0, 0};
   int nseg = min(__ldg(a.n_segments), min(a.max_segments, 3));
@@ -257,46 +302,9 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     if (threadIdx.x == 0) atomicOr(a.status, QB_DEV_BAD_SEGMENT);
   }
 
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmV);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&s_full[b]), 1);
-      mbar_init(smem_u32(&s_free[b]), 128);
-      mbar_init(smem_u32(&p_full[b]), 128);
-      mbar_init(smem_u32(&pv_done[b]), 1);
-      mbar_init(smem_u32(&turn[b]), 128);
-    }
-    mbar_init(smem_u32(q_ready), 256);
-    *abort_flag = 0;
-    *drain_flag = 0;
-    fence_barrier_init();
-  }
   if (threadIdx.x >= 96 && threadIdx.x < 104) temporal_cos_sin(__ldg(a.frame_t), threadIdx.x - 96, tm);
-  // rows of ones under every V^T tile (16 rows x 128 bytes each): the tensor core then returns the row sum of P
-  {
-    constexpr uint32_t kOnes = kFp8 ? 0x38383838u : 0x3F803F80u;
-    constexpr int kTilesPerStage = kFp8 ? 1 : 2;
-    for (int i = threadIdx.x; i < kStages * kTilesPerStage * 128; i += kAttnThreads) {  // 128 x 16 bytes per tile
-      const int tile = i >> 7, v = i & 127;
-      uint8_t* base = smem + L::kStageOff + (tile / kTilesPerStage) * L::kStageBytes + L::kKBytes + (tile % kTilesPerStage) * L::kVTile;
-      *reinterpret_cast<uint4*>(base + 64 * 128 + v * 16) = make_uint4(kOnes, kOnes, kOnes, kOnes);
-    }
-    fence_proxy_async_smem();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  if (warp == 4) QB_TR(4, 0, 1);
+
 
   // Registers move from the four control warps to the softmax warps, which hold a whole score row each.
   if (warp < 4) {
@@ -708,10 +716,8 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (fp8) {
     QB_CUDA_OK(cudaFuncSetAttribute(owl_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<true>::kTotal));
-    owl_attn_kernel<true><<<grid, kAttnThreads, AttnSmem<true>::kTotal, st>>>(tmK, tmV, a);
-  } else {
-    QB_CUDA_OK(cudaFuncSetAttribute(owl_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<false>::kTotal));
-    owl_attn_kernel<false><<<grid, kAttnThreads, AttnSmem<false>::kTotal, st>>>(tmK, tmV, a);
+    return launch_dep("owl_attn kernel", owl_attn_kernel<true>, grid, dim3(kAttnThreads), AttnSmem<true>::kTotal, st, tmK, tmV, a);
   }
-  return check_launch("owl_attn kernel");
+  QB_CUDA_OK(cudaFuncSetAttribute(owl_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<false>::kTotal));
+  return launch_dep("owl_attn kernel", owl_attn_kernel<false>, grid, dim3(kAttnThreads), AttnSmem<false>::kTotal, st, tmK, tmV, a);
 }

@@ -40,6 +40,36 @@ inline int32_t check_launch(const char* what) {
   return QB_OK;
 }
 
+// Programmatic dependent launch: a kernel launched through launch_dep() may start while the kernel
+// before it in the stream is still running, so that its set-up (barrier init, TMEM allocation,
+// descriptor and weight prefetch) overlaps that kernel's tail.  Every such kernel executes
+// grid_dep_wait() before it reads anything an earlier kernel wrote and before it writes global
+// memory; the wait returns when all earlier kernels have completed and their writes are visible.
+// qb_set_dependent_launch(0) (or QB_DEPENDENT_LAUNCH=0 in the environment) turns the attribute off;
+// the device-side calls are then no-ops.
+extern int g_dependent_launch;
+
+template <typename... KArgs, typename... Args>
+inline int32_t launch_dep(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_dependent_launch ? 1 : 0;
+  ++g_launch_count;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return fail(QB_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return QB_OK;
+}
+
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t dtype_size(int32_t dt) { return dt == QB_BF16 ? 2 : dt == QB_E4M3 ? 1 : 4; }
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -68,14 +98,23 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 // x * sigmoid(x) with the exact exponential (the reference oracle uses exp, not an approximation).
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
-// The same with the hardware approximations (2^x and 1/x, ~2^-22 relative error each), which is what
-// the reference's GEMM epilogue uses (ref: src/quark/lang/epilogue.py:43-69): a handful of
-// instructions instead of ~50, for epilogues that sit on the critical path of a tensor-core kernel.
+// The same with a hardware approximation (tanh.approx.f32, 2^-11 relative error: a quarter of a bf16
+// ulp) for epilogues on the critical path of a tensor-core kernel, where the special-function unit is
+// the bound: 3 instructions, one of them on that unit.  The reference's GEMM epilogue uses approximate
+// exp2 and reciprocal for the same reason (ref: src/quark/lang/epilogue.py:43-69).
 __device__ __forceinline__ float silu_fast(float x) {
-  float e, r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-  return x * r;
+  // x * sigmoid(x) = h + h * tanh(h) with h = x / 2: one special-function instruction per element
+  const float h = 0.5f * x;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+  return fmaf(h, t, h);
+}
+
+// 32-byte global stores (one full sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
 }
 
 }  // namespace qb

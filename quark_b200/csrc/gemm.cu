@@ -23,10 +23,19 @@ constexpr int kRowBytes = 128;    // bytes of K per stage row = one swizzle atom
 constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
 constexpr int kSmemBudget = 200 * 1024;
 
+#ifdef QB_GEMM_TRACE
+__device__ long long g_gemm_trace[148 * 4][8];  // [CTA][point]: globaltimer ns
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define QB_GT(pt) do { const int cta_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; if (cta_ < 148 * 4) g_gemm_trace[cta_][pt] = gtime(); } while (0)
+#else
+#define QB_GT(pt) do { } while (0)
+#endif
+
 struct GemmArgs {
   int M, N, K;
   int kb_total, kb_per_split, splits;
   int cluster;  // K slices are the CTAs of one thread-block cluster and are summed through distributed shared memory
+  int b_const;  // no kernel still in flight writes B (weights): its first tiles are fetched ahead of the grid dependency
   int c_dtype, activation, rows_per_gate;
   const float* a_scale;
   const float* w_scale;
@@ -44,7 +53,8 @@ struct GemmSmem {
   static constexpr int kStageBytes = kBM * kRowBytes + BN * kRowBytes;
   static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
   static constexpr int kBarOffset = kStages * kStageBytes;
-  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+  static constexpr int kColOffset = kBarOffset + 256;            // per-column scale, bias, gate of this tile as f32
+  static constexpr int kTotal = kColOffset + 3 * BN * 4 + 1024;  // + alignment slack
 };
 
 // Applies the epilogue to 8 consecutive columns of one row and stores them.
@@ -139,6 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) QB_GT(0);
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
   const int split = blockIdx.z;
@@ -169,12 +180,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dep_launch();  // set-up is done: the next kernel in the stream may begin its own
+  if (threadIdx.x == 0) QB_GT(1);
 
   if (warp == 0) {
     // ---------------- TMA producer
     if (elect_one()) {
-      int issued = 0;
-      for (int it = 0; it < n_iter; ++it) {
+      // The weight tiles of the first stages do not depend on the kernels before this one, so they are
+      // already on their way while those kernels finish; A follows once they have.
+      const int ahead = g.b_const ? min(kStages, n_iter) : 0;
+      for (int it = 0; it < ahead; ++it) {
+        const uint32_t fb = smem_u32(&full_bar[it]);
+        mbar_arrive_expect_tx(fb, L::kStageBytes);
+        tma_load_2d(smem_u32(smem + it * L::kStageBytes + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, n0);
+      }
+      grid_dep_wait();
+      QB_GT(2);
+      for (int it = 0; it < ahead; ++it)
+        tma_load_2d(smem_u32(smem + it * L::kStageBytes), &tmA, smem_u32(&full_bar[it]), (kb0 + it) * kKElems, m0);
+      int issued = ahead;
+      for (int it = ahead; it < n_iter; ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
         if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM)) break;
@@ -205,6 +230,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint32_t ph = (it / kStages) & 1;
         ok = mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM);
         if (!ok) break;
+        if (it == 0) QB_GT(3);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
         const uint64_t a_desc = umma_desc_k_sw128(a_addr);
@@ -220,16 +246,129 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         umma_commit(smem_u32(&empty_bar[s]));
       }
       umma_commit(smem_u32(acc_bar));
+      QB_GT(4);
     }
   } else {
     // ---------------- epilogue, part 1: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
     const int m = m0 + row;
+    grid_dep_wait();  // bias / gate / residual are read and C is written only after the earlier kernels are done
+    // The fast epilogue needs whole 32-column chunks inside N, 32-byte aligned rows of C, and one gate row
+    // for the whole tile; anything else takes the general path below.
+    const int m_last = min(m0 + kBM, g.M) - 1;
+    const bool fast = g.splits == 1 && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(g.C) & 31u) == 0 &&
+                      (g.gate == nullptr || m0 / g.rows_per_gate == m_last / g.rows_per_gate);
+    constexpr int kResInRegs = BN <= 128 ? 1 : 0;
+    uint32_t res[kResInRegs ? BN / 2 : 1];
+    if (fast) {
+      // while the main loop runs: per-column vectors of this tile to shared memory, this row's residual to registers
+      float* col = reinterpret_cast<float*>(smem + L::kColOffset);
+      const int et = threadIdx.x - 64;  // 0 .. 127
+      const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+      const size_t grow = g.gate ? static_cast<size_t>(m0 / g.rows_per_gate) * g.N : 0;
+      for (int j = et; j < BN; j += 128) {
+        const int n = n0 + j;
+        const bool in = n < g.N;
+        col[j] = (in && g.w_scale) ? sa * __ldg(g.w_scale + n) : sa;
+        col[BN + j] = (in && g.bias) ? bf16_bits_to_f32(__ldg(g.bias + n)) : 0.f;
+        col[2 * BN + j] = (in && g.gate) ? bf16_bits_to_f32(__ldg(g.gate + grow + n)) : 0.f;
+      }
+      if (kResInRegs && g.gate != nullptr && m < g.M) {
+#pragma unroll
+        for (int q = 0; q < BN / 8; ++q) {
+          const int n = n0 + q * 8;
+          uint4 x = make_uint4(0u, 0u, 0u, 0u);
+          if (n < g.N) x = __ldg(reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n));
+          res[(kResInRegs ? q : 0) * 4 + 0] = x.x;
+          res[(kResInRegs ? q : 0) * 4 + 1] = x.y;
+          res[(kResInRegs ? q : 0) * 4 + 2] = x.z;
+          res[(kResInRegs ? q : 0) * 4 + 3] = x.w;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_bar), 0, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM));
+    if (threadIdx.x == 64) QB_GT(5);
     tc_fence_after();
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
-    if (ok && g.splits == 1) {
+    if (ok && fast) {
+      // One accumulator row per thread, 32 columns at a time.  Per-column vectors come from shared
+      // memory and the residual row from registers, both fetched during the main loop, so no global
+      // load sits between the accumulator and the stores; every store writes whole 32-byte sectors.
+      const float* col = reinterpret_cast<const float*>(smem + L::kColOffset);
+      const bool has_gate = g.gate != nullptr;
+      const bool has_scale = g.a_scale != nullptr || g.w_scale != nullptr;
+      const bool has_bias = g.bias != nullptr;
+      uint32_t rbuf[2][32];  // chunk c + 1 is on its way from TMEM while chunk c is processed
+      tmem_ld32(taddr, rbuf[0]);
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        tmem_wait_ld();
+        if (c + 1 < BN / 32) tmem_ld32(taddr + (c + 1) * 32, rbuf[(c + 1) & 1]);
+        const uint32_t(&r)[32] = rbuf[c & 1];
+        const int n = n0 + c * 32;
+        if (m < g.M && n < g.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (has_scale) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= col[c * 32 + j];
+          }
+          if (has_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += col[BN + c * 32 + j];
+          }
+          if (g.activation == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_fast(v[j]);
+          }
+          if (has_gate) {
+            uint32_t rw[16];
+            if (kResInRegs) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) rw[j] = res[kResInRegs ? c * 16 + j : 0];
+            } else {  // 256-column tiles: the row does not fit in registers beside the accumulator chunk
+              const uint4* rp = reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 x = __ldg(rp + q);
+                rw[4 * q] = x.x; rw[4 * q + 1] = x.y; rw[4 * q + 2] = x.z; rw[4 * q + 3] = x.w;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              v[2 * j] = __fadd_rn(bf16lo(rw[j]), __fmul_rn(col[2 * BN + c * 32 + 2 * j], v[2 * j]));
+              v[2 * j + 1] = __fadd_rn(bf16hi(rw[j]), __fmul_rn(col[2 * BN + c * 32 + 2 * j + 1], v[2 * j + 1]));
+            }
+          }
+          const size_t off = static_cast<size_t>(m) * g.N + n;
+          if (g.c_dtype == QB_BF16) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[16 * h + 2 * j], v[16 * h + 2 * j + 1]);
+              st_global_v8(static_cast<uint16_t*>(g.C) + off + 16 * h, w);
+            }
+          } else if (g.c_dtype == QB_E4M3) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = pack_e4m3x4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            st_global_v8(static_cast<uint8_t*>(g.C) + off, w);
+          } else {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[8 * h + j]);
+              st_global_v8(static_cast<float*>(g.C) + off + 8 * h, w);
+            }
+          }
+        }
+      }
+    } else if (ok && g.splits == 1) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -353,6 +492,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (clustered) cluster_sync();  // nobody leaves while a peer may still read its staging tile
 
   __syncthreads();
+  if (threadIdx.x == 0) QB_GT(6);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -449,7 +589,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       // measured: a K slice costs far more than its arithmetic share (row-per-thread f32 partial
       // stores, a second pass by the last CTA): ~12 us at 512 x 2048 x 8192, so slices only pay
       // when they multiply the number of busy SMs
-      const bool cl = p.reserved != 1 && (s == 2 || s == 4 || s == 8);
+      const bool cl = (p.reserved & 1) == 0 && (s == 2 || s == 4 || s == 8);
       // measured at 512 x 2048 x 8192: 4 workspace slices +12 us, 4 cluster slices +7 us over one slice
       if (s > 1) cta += (cl ? 12000.0 : 20000.0) + bn * 8.0 + s * bn * 4.0;
       const double cost = waves * cta;
@@ -492,7 +632,7 @@ static int32_t validate_gemm(const qb_gemm_params* p) {
   QB_REQUIRE(p->activation == 0 || p->activation == 1, QB_ERR_INVALID_ARG, "gemm: activation %d", p->activation);
   QB_REQUIRE(p->tile_n == 0 || p->tile_n == 64 || p->tile_n == 128 || p->tile_n == 256, QB_ERR_INVALID_ARG, "gemm: tile_n %d", p->tile_n);
   QB_REQUIRE(p->split_k >= 0 && p->split_k <= 16, QB_ERR_INVALID_ARG, "gemm: split_k %d", p->split_k);
-  QB_REQUIRE(p->reserved == 0 || p->reserved == 1, QB_ERR_INVALID_ARG, "gemm: slice_mode %d", p->reserved);
+  QB_REQUIRE(p->reserved >= 0 && p->reserved <= 3, QB_ERR_INVALID_ARG, "gemm: flags %d", p->reserved);
   return QB_OK;
 }
 
@@ -506,20 +646,21 @@ static int32_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = L::kTotal;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = static_cast<unsigned>(args.splits);
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_dependent_launch ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, FP8>, tmA, tmB, args);
     ++g_launch_count;
     if (e != cudaSuccess) return fail(QB_ERR_LAUNCH, "gemm kernel (cluster of %d): %s", args.splits, cudaGetErrorString(e));
     return QB_OK;
   }
-  gemm_kernel<BN, FP8><<<grid, kGemmThreads, L::kTotal, st>>>(tmA, tmB, args);
-  return check_launch("gemm kernel");
+  return launch_dep("gemm kernel", gemm_kernel<BN, FP8>, grid, dim3(kGemmThreads), L::kTotal, st, tmA, tmB, args);
 }
 
 int32_t quantize_e4m3_launch(const void* X, void* out, size_t n, int32_t src_dtype, cudaStream_t st);
@@ -527,6 +668,12 @@ int32_t quantize_e4m3_launch(const void* X, void* out, size_t n, int32_t src_dty
 }  // namespace qb
 
 using namespace qb;
+
+#ifdef QB_GEMM_TRACE
+extern "C" int32_t qb_debug_gemm_trace(void* host_out) {
+  return cudaMemcpyFromSymbol(host_out, qb::g_gemm_trace, sizeof(qb::g_gemm_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" size_t qb_gemm_workspace_bytes(const qb_gemm_params* p) {
   if (validate_gemm(p) != QB_OK) return 0;
@@ -577,6 +724,7 @@ extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bi
   g.M = p->M; g.N = p->N; g.K = p->K;
   g.kb_total = pl.kb_total; g.kb_per_split = pl.kb_per_split; g.splits = pl.splits;
   g.cluster = pl.cluster;
+  g.b_const = (p->reserved & 2) != 0;
   g.c_dtype = p->c_dtype; g.activation = p->activation; g.rows_per_gate = rows_per_gate;
   g.a_scale = p->a_scale; g.w_scale = p->w_scale;
   g.bias = static_cast<const uint16_t*>(bias);

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* _
                                                                 const uint16_t* __restrict__ bias, uint16_t* __restrict__ out,
                                                                 uint8_t* __restrict__ out_q, int D, int rows_per_group, float eps,
                                                                 int activation) {
+  grid_dep_wait();    // inputs come from the kernels before this one
+  grid_dep_launch();  // the next kernel may begin its set-up
   const int row = blockIdx.x;
   const uint16_t* x = X + static_cast<size_t>(row) * D;
   const size_t goff = static_cast<size_t>(row / rows_per_group) * D;
@@ -176,6 +178,8 @@ __global__ void __launch_bounds__(256) silu_kernel(const uint16_t* __restrict__ 
 
 __global__ void __launch_bounds__(256) euler_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ V,
                                                      const float* __restrict__ dsig, uint16_t* __restrict__ out, size_t n) {
+  grid_dep_wait();    // inputs come from the kernels before this one
+  grid_dep_launch();  // the next kernel may begin its set-up
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
   const float d = __ldg(dsig);
   if (i8 + 8 <= n) {
@@ -213,7 +217,11 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
   }
 }
 
-__global__ void increment_kernel(int32_t* c) { c[0] += 1; }
+__global__ void increment_kernel(int32_t* c) {
+  grid_dep_wait();    // inputs come from the kernels before this one
+  grid_dep_launch();  // the next kernel may begin its set-up
+  c[0] += 1;
+}
 
 // ---------------------------------------------------------------- patchify / unpatchify
 // Both are thin GEMMs (K = C*ph*pw = 128 in, N = 128 out for the model) run once per NFE.
@@ -309,6 +317,8 @@ __global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* __restr
 template <bool kToTokens>
 __global__ void __launch_bounds__(256) patch_move_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C, int H, int Wd,
                                                           int ph, int pw, int tokens) {
+  grid_dep_wait();    // inputs come from the kernels before this one
+  grid_dep_launch();  // the next kernel may begin its set-up
   const int K = C * ph * pw;
   const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (i >= static_cast<size_t>(tokens) * K) return;
@@ -357,10 +367,9 @@ int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void*
   QB_REQUIRE(activation == 0 || activation == 1, QB_ERR_INVALID_ARG, "ada_rmsnorm: activation %d", activation);
   QB_REQUIRE(aligned16(X) && aligned16(scale) && aligned16(bias) && aligned16(out) && aligned16(out_q), QB_ERR_ALIGN,
              "ada_rmsnorm: pointers must be 16-byte aligned");
-  ada_rmsnorm_kernel<256><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(scale), static_cast<const uint16_t*>(bias),
-      static_cast<uint16_t*>(out), static_cast<uint8_t*>(out_q), D, rows / groups, eps, activation);
-  return check_launch("ada_rmsnorm");
+  return launch_dep("ada_rmsnorm", ada_rmsnorm_kernel<256>, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(scale), static_cast<const uint16_t*>(bias),
+                    static_cast<uint16_t*>(out), static_cast<uint8_t*>(out_q), D, rows / groups, eps, activation);
 }
 
 int32_t qb_head_rmsnorm(const void* X, void* out, int32_t rows, int32_t n_q_heads, int32_t n_kv_heads, int32_t Dh, float eps,
@@ -414,15 +423,13 @@ int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out
   QB_REQUIRE(X && V && dsig && out, QB_ERR_INVALID_ARG, "euler_step: NULL pointer");
   QB_REQUIRE(aligned16(X) && aligned16(V) && aligned16(out), QB_ERR_ALIGN, "euler_step: pointers must be 16-byte aligned");
   if (n == 0) return QB_OK;
-  euler_kernel<<<blocks_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(V),
-                                                                             dsig, static_cast<uint16_t*>(out), n);
-  return check_launch("euler_step");
+  return launch_dep("euler_step", euler_kernel, dim3(blocks_for(n)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(V), dsig, static_cast<uint16_t*>(out), n);
 }
 
 int32_t qb_increment(int32_t* counter, void* stream) {
   QB_REQUIRE(counter != nullptr, QB_ERR_INVALID_ARG, "increment: NULL pointer");
-  increment_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter);
-  return check_launch("increment");
+  return launch_dep("increment", increment_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(stream), counter);
 }
 
 static int32_t check_patch_geometry(const char* who, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, int32_t d_model) {
@@ -453,9 +460,9 @@ int32_t qb_patch_gather(const void* latent, void* tokens_out, int32_t C, int32_t
   QB_REQUIRE(C > 0 && H > 0 && Wd > 0 && ph > 0 && pw > 0 && H % ph == 0 && Wd % pw == 0, QB_ERR_INVALID_ARG, "patch_gather: bad geometry");
   const int tokens = (H / ph) * (Wd / pw);
   const size_t n = static_cast<size_t>(tokens) * C * ph * pw;
-  patch_move_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(latent), static_cast<uint16_t*>(tokens_out), C, H, Wd, ph, pw, tokens);
-  return check_launch("patch_gather");
+  return launch_dep("patch_gather", patch_move_kernel<true>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(latent), static_cast<uint16_t*>(tokens_out), C, H, Wd, ph,
+                    pw, tokens);
 }
 
 int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream) {
@@ -463,9 +470,9 @@ int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int
   QB_REQUIRE(C > 0 && H > 0 && Wd > 0 && ph > 0 && pw > 0 && H % ph == 0 && Wd % pw == 0, QB_ERR_INVALID_ARG, "patch_scatter: bad geometry");
   const int tokens = (H / ph) * (Wd / pw);
   const size_t n = static_cast<size_t>(tokens) * C * ph * pw;
-  patch_move_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(tokens_in), static_cast<uint16_t*>(latent_out), C, H, Wd, ph, pw, tokens);
-  return check_launch("patch_scatter");
+  return launch_dep("patch_scatter", patch_move_kernel<false>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(tokens_in), static_cast<uint16_t*>(latent_out), C, H, Wd,
+                    ph, pw, tokens);
 }
 
 int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out, int32_t C, int32_t H, int32_t Wd, int32_t ph,

@@ -62,6 +62,8 @@ __device__ __forceinline__ void head_norm16(float (&f)[16], float eps, uint4& o0
 
 template <bool kFp8>
 __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArgs a) {
+  grid_dep_wait();    // inputs come from the kernels before this one
+  grid_dep_launch();  // the next kernel may begin its set-up
   constexpr int kEs = kFp8 ? 1 : 2;
   __shared__ float tm[16];
   __shared__ __align__(16) uint16_t vt[kPostTile * kPostVPitch];
@@ -253,8 +255,6 @@ extern "C" int32_t qb_qkv_post(const void* qkv_in, const void* qkv_first, const 
   a.eps = eps;
   dim3 grid(tpf / kPostTile, p->n_kv_heads);
   if (p->kv_dtype == QB_E4M3)
-    qkv_post_kernel<true><<<grid, kPostThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
-  else
-    qkv_post_kernel<false><<<grid, kPostThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
-  return check_launch("qkv_post");
+    return launch_dep("qkv_post", qkv_post_kernel<true>, grid, dim3(kPostThreads), 0, static_cast<cudaStream_t>(stream), a);
+  return launch_dep("qkv_post", qkv_post_kernel<false>, grid, dim3(kPostThreads), 0, static_cast<cudaStream_t>(stream), a);
 }

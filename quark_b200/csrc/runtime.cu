@@ -7,6 +7,11 @@ namespace qb {
 
 __device__ unsigned int g_qb_status = 0;
 unsigned long long g_launch_count = 0;
+static int dependent_launch_default() {
+  const char* e = getenv("QB_DEPENDENT_LAUNCH");
+  return (e != nullptr && e[0] == '0') ? 0 : 1;
+}
+int g_dependent_launch = dependent_launch_default();
 
 // Device address of the status word for the current device (one copy of the symbol per device).
 unsigned int* status_word() {
@@ -80,6 +85,11 @@ int32_t qb_device_status(uint32_t* status_host) {
 }
 
 uint64_t qb_kernel_launch_count(void) { return g_launch_count; }
+int32_t qb_set_dependent_launch(int32_t enabled) {
+  const int prev = g_dependent_launch;
+  g_dependent_launch = enabled != 0;
+  return prev;
+}
 
 int32_t qb_malloc(void** ptr_host, size_t bytes) {
   QB_REQUIRE(ptr_host != nullptr, QB_ERR_INVALID_ARG, "ptr_host is NULL");

@@ -118,11 +118,14 @@ def rope_table(H: int, W: int) -> QuarkTensor:
 
 
 def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=None, bias=None, gate=None,
-         residual=None, gate_groups=1, out=None, *, a_scale=None, w_scale=None, split_k=0, tile_n=0, slice_mode=0):  # fmt: skip
+         residual=None, gate_groups=1, out=None, *, a_scale=None, w_scale=None, split_k=0, tile_n=0, slice_mode=0,
+         b_constant=False):  # fmt: skip
     """``C = A @ B.T`` (+ bias, SiLU, ``residual + gate * C``); ``src/quark/functional/gemm.py:597-635``.
 
     ``a_scale`` / ``w_scale`` (f32 device tensors) and ``split_k`` / ``tile_n`` / ``slice_mode`` are extensions; left
-    at their defaults the call is the reference's.
+    at their defaults the call is the reference's.  ``b_constant=True`` promises that no kernel still in
+    flight writes ``B`` (a weight matrix): the kernel then fetches its first ``B`` tiles while the kernels
+    before it in the stream are still finishing.
     """
     if b_shuffled:
         raise NotImplementedError("qf.gemm: b_shuffled=True is not supported (disabled upstream as well)")
@@ -160,7 +163,7 @@ def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=
     p = _lib.GemmParams(
         M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code(od, "bf16"),
         compute_dtype=_code(cd, "bf16"), activation=1 if activation == "silu" else 0, gate_groups=int(gate_groups),
-        split_k=int(split_k), tile_n=int(tile_n), reserved=int(slice_mode),
+        split_k=int(split_k), tile_n=int(tile_n), reserved=int(slice_mode) | (2 if b_constant else 0),
         a_scale=a_scale.data_ptr() if a_scale is not None else None,
         w_scale=w_scale.data_ptr() if w_scale is not None else None,
     )  # fmt: skip
@@ -486,7 +489,7 @@ def patchify(X, W, *, B: int, C: int, H: int, W_spatial: int, ph: int = 2, pw: i
     if K % 16 == 0 and d_model % 8 == 0:  # tensor-core route: gather the patches, then one GEMM
         tmp = _scratch("patchify", (tokens, K), "bf16")
         _lib.check(_lib.load().qb_patch_gather(_p(X), _p(tmp), C, H, W_spatial, ph, pw, _s()))
-        return gemm(tmp, W, out_dtype="bf16", out=out.reshape(tokens, d_model))
+        return gemm(tmp, W, out_dtype="bf16", out=out.reshape(tokens, d_model), b_constant=True)
     _lib.check(_lib.load().qb_patchify(_p(X), _p(W), _p(out), C, H, W_spatial, ph, pw, d_model, _s()))
     return out
 
@@ -511,7 +514,7 @@ def unpatchify(X, weight, bias, *, B: int, C: int, H: int, W: int, ph: int = 2, 
     n_out = C * ph * pw
     if d_model % 16 == 0 and n_out % 8 == 0:  # tensor-core route: one GEMM (bias in its epilogue), then scatter
         tmp = _scratch("unpatchify", (tokens, n_out), "bf16")
-        gemm(X.reshape(tokens, d_model), weight, out_dtype="bf16", bias=bias, out=tmp)
+        gemm(X.reshape(tokens, d_model), weight, out_dtype="bf16", bias=bias, out=tmp, b_constant=True)
         _lib.check(_lib.load().qb_patch_scatter(_p(tmp), _p(out), C, H, W, ph, pw, _s()))
         return out
     _lib.check(_lib.load().qb_unpatchify(_p(X), _p(weight), _p(bias), _p(out), C, H, W, ph, pw, d_model, _s()))

@@ -153,6 +153,7 @@ class Linear(Module):
         return qf.gemm(
             x, self.weight.data, out_dtype=od, compute_dtype=b_dt if b_dt == "e4m3" else None, activation=activation,
             bias=self.bias.data if self._has_bias else bias, gate=gate, residual=residual, gate_groups=gate_groups, out=out,
+            b_constant=True,  # a Parameter: written by load_params only, never by a kernel of the forward pass
         )  # fmt: skip
 
 

@@ -139,6 +139,30 @@ def test_graph_replay_equals_eager(qb, quant):
         np.testing.assert_array_equal(a, b)
 
 
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_dependent_launch_changes_no_bit(qb, quant, use_graph):
+    """Kernels that start their set-up under the tail of the kernel before them must produce the frames
+    of fully serialised launches, eagerly and when replayed from a CUDA graph."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, quant)
+    params = make_params(cfg, seed=6, weight_std=0.08)
+    r = util.rng(13)
+    lats = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(5)]
+    outs = []
+    try:
+        for dependent in (False, True):
+            qb._lib.set_dependent_launch(dependent)
+            eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=use_graph)
+            eng.append_frame(lats[0])
+            outs.append([eng.gen_frame(noise=lats[1 + k]) for k in range(4)])
+    finally:
+        qb._lib.set_dependent_launch(True)
+    for a, b in zip(*outs):
+        np.testing.assert_array_equal(a, b)
+
+
 def test_config1_block_360p_bf16(qb):
     """BASELINE config 1: one local block at 360p (128 tokens, d_model 2048), cache pre-filled with 16 frames."""
     from quark_b200.models import QuantConfig, Waypoint15Config, make_params
