@@ -42,13 +42,15 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* _
   const uint16_t* x = X + static_cast<size_t>(row) * D;
   const size_t goff = static_cast<size_t>(row / rows_per_group) * D;
   constexpr int kMaxVec = 4;  // D <= 8 * kThreads * kMaxVec
-  uint4 xv[kMaxVec];
+  uint4 xv[kMaxVec], sv[kMaxVec], bv[kMaxVec];  // scale and bias are fetched with the row, not after the reduction
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     const int c = (i * kThreads + threadIdx.x) * 8;
     if (c < D) {
       xv[i] = *reinterpret_cast<const uint4*>(x + c);
+      sv[i] = __ldg(reinterpret_cast<const uint4*>(scale + goff + c));
+      bv[i] = __ldg(reinterpret_cast<const uint4*>(bias + goff + c));
       float f[8];
       unpack8(xv[i], f);
 #pragma unroll
@@ -69,8 +71,8 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* _
     if (c < D) {
       float f[8], s[8], b[8];
       unpack8(xv[i], f);
-      unpack8(__ldg(reinterpret_cast<const uint4*>(scale + goff + c)), s);
-      unpack8(__ldg(reinterpret_cast<const uint4*>(bias + goff + c)), b);
+      unpack8(sv[i], s);
+      unpack8(bv[i], b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float y = __fmul_rn(f[j], inv);

@@ -101,6 +101,34 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
     a.n_segments[0] = n;
   }
 
+  // Every global load of this thread is issued before the first result is needed: the kernel is a chain
+  // of short phases, and one memory latency per phase would dominate its run time.
+  const int tt = threadIdx.x >> 2, q = threadIdx.x & 3;
+  const int t = t0 + tt;
+  const size_t row = static_cast<size_t>(t) * a.qkv_dim;
+  constexpr int kMaxGqa = 4;
+  uint4 qa[kMaxGqa], qb4[kMaxGqa];
+#pragma unroll
+  for (int h = 0; h < kMaxGqa; ++h) {
+    if (h < a.gqa) {
+      const size_t off = row + (head * a.gqa + h) * 64 + q * 16;
+      qa[h] = *reinterpret_cast<const uint4*>(a.qkv_in + off);
+      qb4[h] = *reinterpret_cast<const uint4*>(a.qkv_in + off + 8);
+    }
+  }
+  const size_t koff = row + k_off + head * 64 + q * 16;
+  const uint4 ka = *reinterpret_cast<const uint4*>(a.qkv_in + koff);
+  const uint4 kb = *reinterpret_cast<const uint4*>(a.qkv_in + koff + 8);
+  float xy[16];
+  {
+    const float4* rp = reinterpret_cast<const float4*>(a.rope_xy + static_cast<size_t>(t) * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(rp + i);
+      xy[4 * i] = v.x; xy[4 * i + 1] = v.y; xy[4 * i + 2] = v.z; xy[4 * i + 3] = v.w;
+    }
+  }
+
   // ---- V: value residual, round, keep a copy for the transpose, write the packed output
   const float lam = a.qkv_first != nullptr ? __ldg(a.lamb) : 0.f;
   for (int v = threadIdx.x; v < kPostTile * 8; v += kPostThreads) {
@@ -125,10 +153,19 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
   __syncthreads();
 
   // ---- Q heads that share this KV head, then K: 4 lanes per token, 16 elements per lane
-  const int tt = threadIdx.x >> 2, q = threadIdx.x & 3;
-  const int t = t0 + tt;
-  const size_t row = static_cast<size_t>(t) * a.qkv_dim;
-  for (int h = 0; h < a.gqa; ++h) {
+#pragma unroll
+  for (int h = 0; h < kMaxGqa; ++h) {
+    if (h < a.gqa) {
+      const size_t off = row + (head * a.gqa + h) * 64 + q * 16;
+      float f[16];
+      unpack16(qa[h], qb4[h], f);
+      uint4 o0, o1;
+      head_norm16(f, a.eps, o0, o1);
+      *reinterpret_cast<uint4*>(a.qkv_out + off) = o0;
+      *reinterpret_cast<uint4*>(a.qkv_out + off + 8) = o1;
+    }
+  }
+  for (int h = kMaxGqa; h < a.gqa; ++h) {  // more Q heads per KV head than were fetched ahead
     const size_t off = row + (head * a.gqa + h) * 64 + q * 16;
     float f[16];
     unpack16(*reinterpret_cast<const uint4*>(a.qkv_in + off), *reinterpret_cast<const uint4*>(a.qkv_in + off + 8), f);
@@ -138,21 +175,14 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
     *reinterpret_cast<uint4*>(a.qkv_out + off + 8) = o1;
   }
   {
-    const size_t off = row + k_off + head * 64 + q * 16;
+    const size_t off = koff;
     float f[16];
-    unpack16(*reinterpret_cast<const uint4*>(a.qkv_in + off), *reinterpret_cast<const uint4*>(a.qkv_in + off + 8), f);
+    unpack16(ka, kb, f);
     uint4 o0, o1;
     head_norm16(f, a.eps, o0, o1);
     *reinterpret_cast<uint4*>(a.qkv_out + off) = o0;
     *reinterpret_cast<uint4*>(a.qkv_out + off + 8) = o1;
     unpack16(o0, o1, f);  // rotate what the stand-alone append would read back: the bf16-rounded values
-    float xy[16];
-    const float4* rp = reinterpret_cast<const float4*>(a.rope_xy + static_cast<size_t>(t) * 16);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 v = __ldg(rp + i);
-      xy[4 * i] = v.x; xy[4 * i + 1] = v.y; xy[4 * i + 2] = v.z; xy[4 * i + 3] = v.w;
-    }
     float y0[8], y1[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
