@@ -180,6 +180,14 @@ def time_kernels(qb, eng, peaks):
     return res
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the hot kernels at this
+# workload's shapes, from the ncu captures summarised in profiles/owl_attn_720p_fp8.md and
+# profiles/gemm_720p_fp8.md (6-layer model, same per-launch shapes as the 24-layer one).
+NCU_DRAM_BYTES_PER_LAUNCH = {"owl_attn": 18.96e6, "gemm_fc2": 23.1e6, "gemm_fc1": 17.9e6, "gemm_qkv": 9.5e6, "gemm_out": 7.4e6}
+SFU_EXP_PER_CLK_PER_SM = 16  # ex2.approx.f32: one warp instruction per 8 cycles and scheduler (measured)
+N_SMS = 148
+
+
 def max_over_ranks(values, dist, device="cpu"):
     """Element-wise maximum of a list of floats over all ranks (identity without a process group)."""
     if dist is None:
@@ -261,6 +269,13 @@ def run_ours(args):
         dom = max(("owl_attn", "gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"), key=lambda k: kernels[k]["us_per_launch"])
         gemm_us = sum(kernels[k]["us_per_launch"] for k in ("gemm_qkv", "gemm_out", "gemm_fc1", "gemm_fc2"))
         dk = kernels[dom]
+        # head_dim 64 leaves 256 tensor flops per exponential: the attention kernel is bound by the
+        # special-function unit long before the tensor pipe; report that roofline beside the contract's one
+        exps = cfg.tpf * cfg.n_heads * kernels["owl_attn"]["keys_attended_mean"]
+        sm_hz = (clocks.summary().get("sm_mhz") or 1965.0) * 1e6
+        floor_us = exps / (SFU_EXP_PER_CLK_PER_SM * N_SMS * sm_hz) * 1e6
+        sfu = {"exponentials_per_launch": int(exps), "floor_us": round(floor_us, 2),
+               "frac": round(floor_us / kernels["owl_attn"]["us_per_launch"], 3)}
         fp8_peak = 2.0 * peaks["bf16_tflops"]
         line = {
             "metric": "latent_fps_720p_fp8",
@@ -301,10 +316,11 @@ def run_ours(args):
                 "peak": round(fp8_peak, 1),
                 "unit": "TFLOP/s",
                 "frac": dk["frac_of_peak"],
-                "traffic": None,
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dom),
                 "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s (no e4m3 peak was measured)",
             },
             "kernels": kernels,
+            "owl_attn_sfu_bound": sfu,
             "gemm_us_per_layer": round(gemm_us, 2),
             "clocks": clocks.summary(),
             "device_status": status,
