@@ -103,12 +103,12 @@ def gemm_flops(M, N, K):
 # --------------------------------------------------------------------------- our arm
 
 
-def build_engine(seed: int, device: int, n_layers: int = 24):
+def build_engine(seed: int, device: int, n_layers: int = 24, *, tp_rank: int = 0, tp_world: int = 1, comm=None):
     import quark_b200 as qb
     from quark_b200.models import QuantConfig, Waypoint15Config
 
-    cfg = Waypoint15Config(height=HEIGHT, width=WIDTH, n_layers=n_layers, quant=QuantConfig.all_fp8())
-    eng = qb.Engine(cfg=cfg, quant=cfg.quant, seed=seed, device=device)
+    cfg = Waypoint15Config(height=HEIGHT, width=WIDTH, n_layers=n_layers, quant=QuantConfig.all_fp8(), tp_rank=tp_rank, tp_world=tp_world)
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, seed=seed, device=device, comm=comm)
     # pre-fill every layer's cache with seeded N(0,1) -> e4m3 K/V, as after 128 appended frames
     r = np.random.default_rng([seed, 99])
     for blk in eng.model.blocks:
@@ -332,6 +332,81 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- one session sharded over the GPUs
+
+
+def run_tp(args):
+    """One 720p fp8 session sharded by KV-head group over all ranks (strong scaling): QKV / fc1 column-parallel,
+    out-proj / fc2 row-parallel, an NCCL sum all-reduce of the [512, 2048] bf16 partial after each of the two.
+    Every rank sees only its own GPU; no torch in the process."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ["CUDA_VISIBLE_DEVICES"] = str(local)
+    import quark_b200 as qb
+    from quark_b200.runtime.nccl import LocalComm, NcclComm
+
+    qb._lib.require_device(0)
+    id_path = f"/tmp/qb_nccl_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}.id"
+    comm = NcclComm(rank, world, id_path) if world > 1 else LocalComm()
+    _, eng = build_engine(seed=0, device=0, tp_rank=rank, tp_world=world, comm=comm)  # same weights and noise on every rank
+    n = eng.cfg.latent_numel
+    noises = [np.random.default_rng([1234, i]).standard_normal(n, dtype=np.float32) for i in range(4)]
+    for i in range(max(args.warmup, 3)):
+        eng.gen_frame(noise=noises[i % 4])
+    eng.set_frame_t(FRAME_T0 + 1)
+    flag = qb.QuarkTensor.zeros(1, dtype="f32")
+
+    def barrier():
+        comm.all_reduce_max(flag)
+        qb.runtime.synchronize()
+
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+        e0.record()
+        for _ in range(args.steps):
+            eng.gen(eng._noise_dev)
+        e1.record()
+        e1.synchronize()
+        barrier()
+        dev_ms = e0.elapsed_ms(e1)
+        t0 = time.perf_counter()
+        e2, e3 = qb.runtime.Event(), qb.runtime.Event()
+        e2.record()
+        for i in range(args.steps):
+            eng.gen_frame(noise=noises[i % 4])
+        e3.record()
+        e3.synchronize()
+        e2e_ms = max(e2.elapsed_ms(e3), (time.perf_counter() - t0) * 1e3)
+        barrier()
+    times = qb.QuarkTensor.from_numpy(np.array([dev_ms, e2e_ms], dtype=np.float32))
+    comm.all_reduce_max(times)
+    qb.runtime.synchronize()
+    dev_ms, e2e_ms = (float(v) for v in times.to_numpy())
+    status = qb._lib.device_status()
+    launches_per_frame, h2d, d2h = eng.launches_per_frame, eng.h2d_bytes_per_frame, eng.d2h_bytes_per_frame
+    eng.close()  # the frame graph holds the communicator's collectives: it goes first
+    comm.destroy()
+    if rank == 0:
+        ms_per_step = dev_ms / args.steps
+        fps = args.steps * 1000.0 / dev_ms
+        print(json.dumps({
+            "metric": "latent_fps_720p_fp8", "value": round(fps, 3), "unit": "frames/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "ms_per_nfe": round(ms_per_step / 5.0, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": round(fps / PUBLISHED_LATENT_FPS_720P_FP8, 3),
+            "dtype": "e4m3", "data": "synthetic", "impl": "ours",
+            "config": {"workload": "gen_frame 720p fp8, ONE session sharded over the GPUs (BASELINE configs[4])",
+                       "parallelism": f"tp{world} by KV-head group: {16 // world} KV heads per GPU, QKV / fc1 column-parallel, out-proj / fc2 "
+                                      "row-parallel, 2 NCCL all-reduces of [512, 2048] bf16 per block (48 per NFE) inside the CUDA graph",
+                       "frame_t": FRAME_T0 + 1, "l2": "inputs larger than L2"},
+            "e2e": {"value": round(args.steps * 1000.0 / e2e_ms, 3), "unit": "frames/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches_per_frame * args.steps), "launches_per_frame": int(launches_per_frame),
+            "clocks": clocks.summary(), "device_status": status,
+        }), flush=True)  # fmt: skip
+
+
 # --------------------------------------------------------------------------- CPU oracle arm
 
 
@@ -434,12 +509,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="sessions", choices=["sessions", "tp"],
+                    help="N > 1: 'sessions' = one independent session per GPU (weak scaling, the default); "
+                         "'tp' = one session sharded by KV-head group with NCCL all-reduces (strong scaling)")
     ap.add_argument("--layers", type=int, default=24, help="model depth for --profile-nfe (smaller = less device memory under a profiler)")
     args = ap.parse_args()
     if args.profile_nfe:
         run_profile_nfe(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.mode == "tp":
+        run_tp(args)
     else:
         run_ours(args)
 

@@ -137,11 +137,17 @@ def _linear(x, w, quant: Quant, **epi):
     return ops.gemm(x, w, **epi)
 
 
-def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame_t: int, *, qkv_first, frozen: bool, quant: Quant):
-    """One transformer block; returns ``(x, qkv)`` (waypoint_15.py:389-440, ctrl_emb=None)."""
+def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame_t: int, *, qkv_first, frozen: bool, quant: Quant,
+                  tp_world: int = 1, reduce=None):  # fmt: skip
+    """One transformer block; returns ``(x, qkv)`` (waypoint_15.py:389-440, ctrl_emb=None).
+
+    ``tp_world > 1`` restates one rank of the sharding by KV-head group: ``blk`` holds that rank's weight
+    slices, ``st`` its heads' caches, and ``reduce(partial_bf16) -> summed_bf16`` stands for the sum over
+    the ranks after each row-parallel GEMM; gate and residual are applied once, after the sum.
+    """
     s0, b0, g0, s1, b1, g1 = blk["lut"][sigma_idx]
-    Hq, Hk = cfg.n_heads, cfg.n_kv_heads
-    Dh = cfg.d_model // Hq
+    Hq, Hk = cfg.n_heads // tp_world, cfg.n_kv_heads // tp_world
+    Dh = cfg.d_model // cfg.n_heads
     kv_dtype = "e4m3" if quant.kv_cache == "fp8" else "bf16"
     geo = dict(H_spatial=cfg.height, W_spatial=cfg.width)
 
@@ -180,10 +186,16 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         q_quant="e4m3" if (quant.attn_compute == "fp8" and quant.mirror_operand_rounding) else None,
         **geo,
     )
-    x = _linear(attn, blk["out.weight"], quant, gate=g0, residual=x)
+    if reduce is None:
+        x = _linear(attn, blk["out.weight"], quant, gate=g0, residual=x)
+    else:
+        x = ops.ada_gate_residual(x, reduce(_linear(attn, blk["out.weight"], quant)), g0)
     h = ops.ada_rmsnorm(x, s1, b1)
     h = ops.silu(_linear(h, blk["fc1.weight"], quant))
-    x = _linear(h, blk["fc2.weight"], quant, gate=g1, residual=x)
+    if reduce is None:
+        x = _linear(h, blk["fc2.weight"], quant, gate=g1, residual=x)
+    else:
+        x = ops.ada_gate_residual(x, reduce(_linear(h, blk["fc2.weight"], quant)), g1)
     return x, qkv
 
 

@@ -39,7 +39,7 @@ class _Pinned:
 
 class Engine:
     def __init__(self, model_uri=None, *, cfg: Waypoint15Config | None = None, quant="fp8", load_weights=True, seed: int = 0,
-                 params: dict | None = None, device: int = 0, use_graph: bool = True):  # fmt: skip
+                 params: dict | None = None, device: int = 0, use_graph: bool = True, comm=None):  # fmt: skip
         if isinstance(model_uri, Waypoint15Config):
             cfg, model_uri = model_uri, None
         if model_uri is not None:
@@ -55,7 +55,7 @@ class Engine:
                 raise ValueError("Engine: quant must be 'fp8', 'bf16' or a QuantConfig")
         base = cfg or Waypoint15Config()
         self.cfg = cfg = Waypoint15Config(**{**base.__dict__, "quant": quant})
-        self.model = Waypoint15(cfg)
+        self.model = Waypoint15(cfg, comm)
         if load_weights:
             self.model.load_params(params if params is not None else make_params(cfg, seed))
             self.model.prepare()
@@ -96,6 +96,16 @@ class Engine:
     def launches_per_frame(self) -> int:
         """Kernels in the captured frame graph (0 before the first ``gen_frame``)."""
         return int(self.gen.launches_per_frame)
+
+    def close(self) -> None:
+        """Drops the captured frame graph (a communicator whose collectives it holds cannot be destroyed
+        before); the engine runs eagerly afterwards unless a new graph is captured."""
+        self.gen._graph = None
+        self._use_graph = False
+        import gc
+
+        gc.collect()
+        _stream.synchronize()
 
     # ---- session API
     def reset(self) -> None:

@@ -77,6 +77,11 @@ class Waypoint15Config:
     fuse_silu: bool = True
     # head_rmsnorm + value residual + KV append as one launch (bit-identical to the three).
     fuse_qkv_post: bool = True
+    # Tensor parallelism by KV-head group: rank `tp_rank` of `tp_world` owns n_kv_heads / tp_world KV heads
+    # with their Q heads (QKV and fc1 column-parallel, out-proj and fc2 row-parallel, partial outputs summed
+    # over the ranks).  The reference is single-GPU; tp_world = 1 is its wiring.
+    tp_world: int = 1
+    tp_rank: int = 0
 
     def __post_init__(self):
         if self.ctrl_conditioning:
@@ -85,6 +90,10 @@ class Waypoint15Config:
             raise NotImplementedError("Waypoint15Config: MoE and quilt are not implemented")
         if self.d_model // self.n_heads != 64:
             raise NotImplementedError("Waypoint15Config: only head_dim 64 is supported")
+        if self.tp_world < 1 or not (0 <= self.tp_rank < self.tp_world):
+            raise ValueError(f"Waypoint15Config: tp_rank {self.tp_rank} of tp_world {self.tp_world}")
+        if self.n_kv_heads % self.tp_world or (self.d_model * self.mlp_ratio) % (128 * self.tp_world):
+            raise ValueError(f"Waypoint15Config: {self.n_kv_heads} KV heads / MLP width do not divide over {self.tp_world} ranks")
 
     @property
     def Dh(self):
@@ -113,6 +122,23 @@ class Waypoint15Config:
     @property
     def v_width(self):
         return self.n_kv_heads * self.Dh
+
+    # ---- this rank's share (everything when tp_world == 1)
+    @property
+    def n_heads_local(self):
+        return self.n_heads // self.tp_world
+
+    @property
+    def n_kv_heads_local(self):
+        return self.n_kv_heads // self.tp_world
+
+    @property
+    def qkv_dim_local(self):
+        return (self.n_heads_local + 2 * self.n_kv_heads_local) * self.Dh
+
+    @property
+    def mlp_dim_local(self):
+        return self.mlp_dim // self.tp_world
 
     @property
     def latent_numel(self):
@@ -183,30 +209,57 @@ def make_params(cfg: Waypoint15Config, seed: int = 0, *, weight_std: float = 0.0
     return params
 
 
+def shard_block_params(cfg: Waypoint15Config, blk: dict) -> dict:
+    """The slices of one block's weights that rank ``cfg.tp_rank`` owns.
+
+    QKV rows are regrouped as ``[Q heads | K heads | V heads]`` of the rank's KV-head group, so the
+    packed layout (and with it every kernel) is the single-GPU one with fewer heads; out-proj keeps the
+    columns of the rank's Q heads, fc1 a row block, fc2 the matching column block.  Conditioning rows,
+    ``lamb`` and everything outside the blocks are replicated.
+    """
+    G, r, Dh = cfg.tp_world, cfg.tp_rank, cfg.Dh
+    if G == 1:
+        return blk
+    nq, nk = cfg.n_heads_local * Dh, cfg.n_kv_heads_local * Dh
+    k0, v0 = cfg.n_heads * Dh, (cfg.n_heads + cfg.n_kv_heads) * Dh
+    w = np.asarray(blk["qkv.weight"])
+    out = dict(blk)
+    out["qkv.weight"] = np.ascontiguousarray(np.concatenate([w[r * nq : (r + 1) * nq], w[k0 + r * nk : k0 + (r + 1) * nk], w[v0 + r * nk : v0 + (r + 1) * nk]]))
+    out["out.weight"] = np.ascontiguousarray(np.asarray(blk["out.weight"])[:, r * nq : (r + 1) * nq])
+    m = cfg.mlp_dim_local
+    out["fc1.weight"] = np.ascontiguousarray(np.asarray(blk["fc1.weight"])[r * m : (r + 1) * m])
+    out["fc2.weight"] = np.ascontiguousarray(np.asarray(blk["fc2.weight"])[:, r * m : (r + 1) * m])
+    return out
+
+
 # ---------------------------------------------------------------------------
 # model
 # ---------------------------------------------------------------------------
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, cfg: Waypoint15Config, layer_idx: int):
+    def __init__(self, cfg: Waypoint15Config, layer_idx: int, comm=None):
         d = cfg.d_model
         self._cfg = cfg
+        self._comm = comm
+        if cfg.tp_world > 1 and (comm is None or comm.world != cfg.tp_world or comm.rank != cfg.tp_rank):
+            raise ValueError("TransformerBlock: tp_world > 1 needs a communicator of that size and rank")
         self._cond_lut: list[tuple] = []
+        nq, nk = cfg.n_heads_local, cfg.n_kv_heads_local  # heads of this rank
         self.pre_attn_norm = nn.AdaRMSNorm()
-        self.qkv_proj = nn.Linear(d, cfg.qkv_dim, out_dtype="bf16")
-        self.head_norm = nn.HeadRMSNorm(cfg.n_heads, cfg.n_kv_heads, cfg.Dh)
+        self.qkv_proj = nn.Linear(d, cfg.qkv_dim_local, out_dtype="bf16")
+        self.head_norm = nn.HeadRMSNorm(nq, nk, cfg.Dh)
         if cfg.value_residual:
-            self.v_residual = nn.ValueResidualPacked(cfg.v_col_offset, cfg.v_width)
+            self.v_residual = nn.ValueResidualPacked((nq + nk) * cfg.Dh, nk * cfg.Dh)
         kv_dt = "e4m3" if cfg.quant.kv_cache == "fp8" else "bf16"
-        geo = dict(B=1, n_kv_heads=cfg.n_kv_heads, H_spatial=cfg.height, W_spatial=cfg.width, num_buckets=cfg.num_buckets(layer_idx),
+        geo = dict(B=1, n_kv_heads=nk, H_spatial=cfg.height, W_spatial=cfg.width, num_buckets=cfg.num_buckets(layer_idx),
                    pinned_dilation=cfg.pinned_dilation(layer_idx), packed_qkv=True)  # fmt: skip
-        self.kv_cache = nn.KVCacheUpdate(n_q_heads=cfg.n_heads, Dh=cfg.Dh, dtype=kv_dt, **geo)
+        self.kv_cache = nn.KVCacheUpdate(n_q_heads=nq, Dh=cfg.Dh, dtype=kv_dt, **geo)
         self.attn = nn.OwlAttn(gqa_ratio=cfg.gqa_ratio, compute_dtype="e4m3" if cfg.quant.attn_compute == "fp8" else None, **geo)
-        self.out_proj = nn.Linear(cfg.n_heads * cfg.Dh, d, out_dtype="bf16")
+        self.out_proj = nn.Linear(nq * cfg.Dh, d, out_dtype="bf16")
         self.attn_gate = nn.AdaGateResidual()
         self.pre_mlp_norm = nn.AdaRMSNorm()
-        self.mlp = nn.MLP(d, cfg.mlp_dim, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
+        self.mlp = nn.MLP(d, cfg.mlp_dim_local, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
         self.mlp_gate = nn.AdaGateResidual()
 
     def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None):
@@ -215,7 +268,9 @@ class TransformerBlock(nn.Module):
             raise NotImplementedError("controller conditioning is not implemented")
         s0, b0, g0, s1, b1, g1 = self._cond_lut[sigma_idx]
         fp8 = self.qkv_proj.weight.data.dtype == "e4m3"
-        fuse = self._cfg.fuse_gate_residual
+        tp = self._cfg.tp_world > 1
+        # row-parallel partial outputs are summed over the ranks before gate and residual are applied (once)
+        fuse = self._cfg.fuse_gate_residual and not tp
 
         qkv = self.qkv_proj(self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8))
         use_first = hasattr(self, "v_residual") and qkv_first is not None
@@ -224,7 +279,7 @@ class TransformerBlock(nn.Module):
             qkv = qf.qkv_post(
                 qkv, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
                 frame_t if frame_t is not None else kc.frame_t, kc._frozen[1 if frozen else 0], kc.Vt_cache, kc.segments, kc.n_segments,
-                kc.K_cache, n_q_heads=self._cfg.n_heads, n_kv_heads=self._cfg.n_kv_heads, H_spatial=self._cfg.height,
+                kc.K_cache, n_q_heads=self._cfg.n_heads_local, n_kv_heads=self._cfg.n_kv_heads_local, H_spatial=self._cfg.height,
                 W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
                 out=nn._cached(self, "qkv_post", qkv.shape, "bf16"),
             )  # fmt: skip
@@ -237,21 +292,28 @@ class TransformerBlock(nn.Module):
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
         else:
-            x = self.attn_gate(x, self.out_proj(attn_out), g0)
+            y = self.out_proj(attn_out)
+            if tp:
+                self._comm.all_reduce_sum(y)
+            x = self.attn_gate(x, y, g0)
         h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8)
         if fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
         else:
-            x = self.mlp_gate(x, self.mlp(h), g1)
+            y = self.mlp(h)
+            if tp:
+                self._comm.all_reduce_sum(y)
+            x = self.mlp_gate(x, y, g1)
         return x, qkv
 
 
 class Waypoint15(nn.Module):
-    def __init__(self, cfg: Waypoint15Config | None = None):
+    def __init__(self, cfg: Waypoint15Config | None = None, comm=None):
         self.cfg = cfg = cfg or Waypoint15Config()
+        self.comm = comm
         ph, pw = cfg.patch
         self.patchify = nn.Patchify(cfg.channels, cfg.d_model, cfg.height * ph, cfg.width * pw, ph, pw)
-        self.blocks = nn.ModuleList([TransformerBlock(cfg, i) for i in range(cfg.n_layers)])
+        self.blocks = nn.ModuleList([TransformerBlock(cfg, i, comm) for i in range(cfg.n_layers)])
         self.out_norm = nn.AdaRMSNorm()
         self.unpatchify = nn.Unpatchify(cfg.d_model, cfg.channels, cfg.height * ph, cfg.width * pw, ph, pw)
         self._out_norm_luts: list[tuple] = []
@@ -260,13 +322,15 @@ class Waypoint15(nn.Module):
         self._x_bufs = None
 
     def load_params(self, params: dict) -> "Waypoint15":
-        """Upload a ``make_params``-style dict; call ``prepare()`` afterwards."""
+        """Upload a ``make_params``-style dict (full-size weights; a tensor-parallel rank keeps its slices);
+        call ``prepare()`` afterwards."""
         up = lambda a: QuarkTensor.from_numpy(np.asarray(a), dtype="bf16")  # noqa: E731
         self.patchify.weight.data = up(params["patchify.weight"])
         self.unpatchify.weight.data = up(params["unpatchify.weight"])
         self.unpatchify.bias.data = up(params["unpatchify.bias"])
         self._out_norm_luts = [tuple(up(r) for r in rows) for rows in params["out_norm.lut"]]
         for blk, p in zip(self.blocks, params["blocks"]):
+            p = shard_block_params(self.cfg, p)
             blk.qkv_proj.weight.data = up(p["qkv.weight"])
             blk.out_proj.weight.data = up(p["out.weight"])
             blk.mlp.fc1.weight.data = up(p["fc1.weight"])

@@ -1,0 +1,160 @@
+"""Sum all-reduce across the GPUs of one node for the tensor-parallel mode, through ``libnccl.so.2`` with ctypes.
+
+The reference is single-GPU; its sharding by KV-head group needs one exchange step per row-parallel
+GEMM: the ``[tpf, d_model]`` bf16 partial outputs are summed over the ranks.  NCCL does that here
+(ring / NVLS over NVLink, chosen by NCCL).  The call goes to the active stream, so it is captured into
+the frame's CUDA graph like any kernel.
+
+One process per GPU.  The ranks of one node agree on the communicator through a file: rank 0 writes
+the 128-byte unique id, the others wait for it (bounded).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import importlib.util
+import os
+import time
+
+from . import stream as _stream
+
+_NCCL_BF16, _NCCL_F32, _NCCL_SUM, _NCCL_MAX = 9, 7, 0, 2
+_DT = {"bf16": _NCCL_BF16, "f32": _NCCL_F32}
+
+
+class NcclError(RuntimeError):
+    pass
+
+
+class _UniqueId(C.Structure):
+    _fields_ = [("internal", C.c_char * 128)]
+
+
+def _find_library() -> str:
+    env = os.environ.get("QB_NCCL_PATH")
+    if env:
+        return env
+    spec = importlib.util.find_spec("nvidia.nccl")  # the wheel torch depends on; found without importing torch
+    if spec is not None and spec.submodule_search_locations:
+        for base in spec.submodule_search_locations:
+            cand = os.path.join(base, "lib", "libnccl.so.2")
+            if os.path.exists(cand):
+                return cand
+    return "libnccl.so.2"
+
+
+def _write_id(path: str, uid: "_UniqueId") -> None:
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "wb") as f:
+        f.write(C.string_at(C.byref(uid), 128))  # all 128 bytes (a c_char array would stop at the first NUL)
+    os.replace(tmp, path)  # atomic: a reader never sees a partial id
+
+
+def _read_id(path: str, timeout_s: float, rank: int) -> "_UniqueId":
+    t0 = time.monotonic()
+    while not os.path.exists(path):
+        if time.monotonic() - t0 > timeout_s:
+            raise NcclError(f"NcclComm: rank {rank} waited {timeout_s:.0f} s for {path}")
+        time.sleep(0.01)
+    with open(path, "rb") as f:
+        raw = f.read()
+    if len(raw) != 128:
+        raise NcclError(f"NcclComm: {path} holds {len(raw)} bytes, expected 128")
+    uid = _UniqueId()
+    C.memmove(C.byref(uid), raw, 128)
+    return uid
+
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        path = _find_library()
+        try:
+            lib = C.CDLL(path)
+        except OSError as e:
+            raise NcclError(f"cannot load NCCL ({path}): {e}; set QB_NCCL_PATH") from e
+        lib.ncclGetErrorString.restype = C.c_char_p
+        lib.ncclGetErrorString.argtypes = [C.c_int]
+        lib.ncclGetUniqueId.argtypes = [C.POINTER(_UniqueId)]
+        lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, _UniqueId, C.c_int]
+        lib.ncclAllReduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        lib.ncclCommDestroy.argtypes = [C.c_void_p]
+        lib.ncclCommAbort.argtypes = [C.c_void_p]
+        _lib = lib
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NcclError(f"{what}: {load().ncclGetErrorString(rc).decode()} ({rc})")
+
+
+class LocalComm:
+    """World of one: nothing to exchange."""
+
+    rank, world = 0, 1
+
+    def all_reduce_sum(self, t):
+        return t
+
+    def all_reduce_max(self, t):
+        return t
+
+    def destroy(self):
+        pass
+
+
+class NcclComm:
+    """``NcclComm(rank, world, id_path)``: the calling process must already have selected its GPU."""
+
+    def __init__(self, rank: int, world: int, id_path: str, *, timeout_s: float = 120.0):
+        if not (0 <= rank < world):
+            raise ValueError(f"NcclComm: rank {rank} of {world}")
+        self.rank, self.world = int(rank), int(world)
+        lib = load()
+        uid = _UniqueId()
+        if rank == 0:
+            _check(lib.ncclGetUniqueId(C.byref(uid)), "ncclGetUniqueId")
+            _write_id(id_path, uid)
+        else:
+            uid = _read_id(id_path, timeout_s, rank)
+        comm = C.c_void_p()
+        _check(lib.ncclCommInitRank(C.byref(comm), self.world, uid, self.rank), "ncclCommInitRank")
+        self._comm = comm
+
+    def _all_reduce(self, t, op):
+        if t.dtype not in _DT:
+            raise TypeError(f"all_reduce: dtype {t.dtype}")
+        p = C.c_void_p(t.data_ptr())
+        _check(load().ncclAllReduce(p, p, t.numel, _DT[t.dtype], op, self._comm, C.c_void_p(_stream.active_stream())), "ncclAllReduce")
+        return t
+
+    def all_reduce_sum(self, t):
+        """In-place sum of a bf16 or f32 device tensor over all ranks, on the active stream."""
+        return self._all_reduce(t, _NCCL_SUM)
+
+    def all_reduce_max(self, t):
+        return self._all_reduce(t, _NCCL_MAX)
+
+    def abort(self):
+        if self._comm is not None:
+            load().ncclCommAbort(self._comm)
+            self._comm = None
+
+    def destroy(self, timeout_s: float = 10.0) -> bool:
+        """Releases the communicator.  NCCL keeps a communicator alive while a CUDA graph that captured one
+        of its collectives exists, and ``ncclCommDestroy`` then blocks: destroy such graphs first
+        (``Engine.close()``).  The call runs in a helper thread and is given ``timeout_s``; if it has not
+        returned by then the communicator is left to process exit and False is returned."""
+        if self._comm is None:
+            return True
+        import threading
+
+        comm, self._comm = self._comm, None
+        th = threading.Thread(target=lambda: load().ncclCommDestroy(comm), daemon=True)
+        th.start()
+        th.join(timeout_s)
+        return not th.is_alive()
