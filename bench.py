@@ -332,6 +332,114 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- 360p bf16 NFE (BASELINE configs[1])
+
+
+def run_nfe_360p_bf16(args):
+    """The full 24-layer model at 360p (128 tokens, grid 16 x 8), all bf16, caches pre-filled with seeded
+    N(0, 1) K / V as after 128 frames: ms per NFE from graph replays of gen_frame (5 NFE).  At M = 128 the
+    GEMMs stream their weights (92 MB of bf16 per layer) and are HBM bound."""
+    import quark_b200 as qb
+    from quark_b200.models import QuantConfig, Waypoint15Config
+
+    cfg = Waypoint15Config(height=16, width=8, quant=QuantConfig.all_bf16())
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, seed=0, device=0)
+    r = np.random.default_rng([0, 99])
+    for blk in eng.model.blocks:
+        for t in (blk.kv_cache.K_cache, blk.kv_cache.Vt_cache):
+            t.copy_from(qb.QuarkTensor.from_numpy(r.standard_normal(t.numel, dtype=np.float32).reshape(t.shape), dtype="bf16"))
+    eng.set_frame_t(FRAME_T0)
+    noise = r.standard_normal(cfg.latent_numel, dtype=np.float32)
+    for _ in range(max(args.warmup, 3)):
+        eng.gen_frame(noise=noise)
+    eng.set_frame_t(FRAME_T0 + 1)
+    qb.runtime.synchronize()
+    e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+    e0.record()
+    for _ in range(args.steps):
+        eng.gen(eng._noise_dev)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_ms(e1) / args.steps
+    peaks = measured_peaks()
+    weight_bytes = 24 * 46_137_344 * 2
+    print(json.dumps({"workload": "gen_frame 360p bf16, 24 layers, 128 tokens (BASELINE configs[1])", "ms_per_frame": round(ms, 4),
+                      "ms_per_nfe": round(ms / 5, 4), "latent_fps": round(1000.0 / ms, 2),
+                      "weight_stream_gbs": round(weight_bytes / (ms / 5) / 1e6, 1), "hbm_frac": round(weight_bytes / (ms / 5) / 1e6 / peaks["hbm_gbs"], 3),
+                      "launches_per_frame": eng.launches_per_frame, "device_status": qb._lib.device_status()}), flush=True)  # fmt: skip
+
+
+# --------------------------------------------------------------------------- isolated attention sweep (BASELINE configs[3])
+
+
+def run_attn_sweep(args):
+    """owl_attn alone at 720p (512 queries, GQA 32/16 x 64) over KV histories of 16 / 64 / 128 / 256 buckets
+    of 512 tokens, bf16 and e4m3, on a write frame (3 segments, one bucket masked) and the frame after
+    (2 segments); prints one JSON line with a row per point.  K / V are seeded N(0, 1)."""
+    import quark_b200 as qb
+
+    qb._lib.require_device(0)
+    peaks = measured_peaks()
+    H, W, Hk, gqa, pd = HEIGHT, WIDTH, 16, 2, 8
+    tpf = H * W
+    r = np.random.default_rng(7)
+    qkv = qb.QuarkTensor.from_numpy(r.standard_normal((tpf, 4096), dtype=np.float32), dtype="bf16")
+
+    def randn_dev(shape, dt):
+        a = r.standard_normal(shape, dtype=np.float32)
+        if dt == "bf16":
+            return qb.QuarkTensor.from_numpy(a, dtype="bf16")
+        return qb.qf.quantize_e4m3(qb.QuarkTensor.from_numpy(a))
+
+    def segment_table(ft, nb):
+        """(start, length) pairs of the valid key ranges at frame ft: ring buckets plus the tail slot; on a
+        write frame after the ring has wrapped, the bucket about to be overwritten is left out."""
+        L = nb * tpf
+        bucket = (ft + pd - 1) // pd
+        slot = bucket % nb
+        if ft % pd == 0 and bucket >= nb:
+            return [0, slot * tpf, (slot + 1) * tpf, (nb - slot - 1) * tpf, L, tpf], 3
+        return [0, min(bucket, nb) * tpf, L, tpf, 0, 0], 2
+
+    rows = []
+    for kv_dt in ("bf16", "e4m3"):
+        es = 2 if kv_dt == "bf16" else 1
+        for nb in (16, 64, 128, 256):
+            cap = (nb + 1) * tpf
+            Kc, Vc = randn_dev((Hk * cap, 64), kv_dt), randn_dev((Hk * 64, cap), kv_dt)
+            out = qb.QuarkTensor.empty(tpf, 2048, dtype="bf16")
+            for ft in (nb * pd, nb * pd + 1):
+                segs, n = segment_table(ft, nb)
+                S = int(sum(segs[1::2][:n]))
+                sg = qb.QuarkTensor.from_numpy(np.asarray(segs, np.int32))
+                ns = qb.QuarkTensor.from_numpy(np.array([n], np.int32))
+                ftt = qb.QuarkTensor.from_numpy(np.array([ft], np.int32))
+                call = lambda: qb.qf.owl_attn(qkv, Kc, Vc, sg, ns, 1, Hk, gqa, H, W, nb, pd, compute_dtype="e4m3" if kv_dt == "e4m3" else None,
+                                              packed_qkv=True, frame_t=ftt, out=out)  # noqa: E731
+                call()
+                reps = max(3, min(20, int(2e5 / max(S, 1))))
+                with qb.runtime.capture_graph() as cap_:
+                    for _ in range(reps):
+                        call()
+                cap_.graph.launch()
+                e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+                e0.record()
+                cap_.graph.launch()
+                e1.record()
+                e1.synchronize()
+                us = e0.elapsed_ms(e1) * 1e3 / reps
+                del cap_  # the graph must be gone before the next capture begins (destroying it is not capturable)
+                flops = attn_flops(tpf, float(S))
+                byts = 2 * Hk * S * 64 * es + 2 * tpf * 32 * 64 * 2
+                tensor_peak = peaks["bf16_tflops"] * (2.0 if kv_dt == "e4m3" else 1.0)
+                rows.append({"kv": kv_dt, "buckets": nb, "frame_t": ft, "segments": int(n), "keys": S, "us": round(us, 1),
+                             "tflops": round(flops / us / 1e6, 1), "tensor_frac": round(flops / us / 1e6 / tensor_peak, 3),
+                             "gbs": round(byts / us / 1e3, 1), "hbm_frac": round(byts / us / 1e3 / peaks["hbm_gbs"], 3),
+                             "sfu_frac": round(tpf * 32 * S / (SFU_EXP_PER_CLK_PER_SM * N_SMS * 1.965e9) * 1e6 / us, 3)})  # fmt: skip
+            del Kc, Vc
+    print(json.dumps({"attn_sweep_720p": rows, "device_status": qb._lib.device_status(), "peaks": peaks}), flush=True)
+
+
 # --------------------------------------------------------------------------- one session sharded over the GPUs
 
 
@@ -509,6 +617,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--attn-sweep", action="store_true", help="time owl_attn alone over KV histories of 16 .. 256 buckets and exit")
+    ap.add_argument("--nfe-360p-bf16", action="store_true", help="time the 24-layer model at 360p in bf16 and exit")
     ap.add_argument("--mode", default="sessions", choices=["sessions", "tp"],
                     help="N > 1: 'sessions' = one independent session per GPU (weak scaling, the default); "
                          "'tp' = one session sharded by KV-head group with NCCL all-reduces (strong scaling)")
@@ -518,6 +628,10 @@ def main():
         run_profile_nfe(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.attn_sweep:
+        run_attn_sweep(args)
+    elif args.nfe_360p_bf16:
+        run_nfe_360p_bf16(args)
     elif args.mode == "tp":
         run_tp(args)
     else:

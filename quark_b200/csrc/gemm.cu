@@ -20,7 +20,7 @@ namespace qb {
 
 constexpr int kBM = 128;          // rows of A per tile = TMEM lanes
 constexpr int kRowBytes = 128;    // bytes of K per stage row = one swizzle atom
-constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
+constexpr int kGemmThreads = 320; // 10 warps: TMA, MMA, 2 x 4 epilogue (two warps per TMEM lane quarter)
 constexpr int kSmemBudget = 200 * 1024;
 
 #ifdef QB_GEMM_TRACE
@@ -259,15 +259,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int m_last = min(m0 + kBM, g.M) - 1;
     const bool fast = g.splits == 1 && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(g.C) & 31u) == 0 &&
                       (g.gate == nullptr || m0 / g.rows_per_gate == m_last / g.rows_per_gate);
+    // Two warps share each TMEM lane quarter (w and w + 4 see the same 32 rows): in the fast epilogue the
+    // first takes the even 32-column chunks of the row, the second the odd ones.  The other epilogue paths
+    // are run by the first four warps alone.
+    const int half = (warp - 2) >> 2;
+    constexpr int kMyChunks = BN / 64;  // 32-column chunks per warp
     constexpr int kResInRegs = BN <= 128 ? 1 : 0;
-    uint32_t res[kResInRegs ? BN / 2 : 1];
+    uint32_t res[kResInRegs ? kMyChunks * 16 : 1];
     if (fast) {
       // while the main loop runs: per-column vectors of this tile to shared memory, this row's residual to registers
       float* col = reinterpret_cast<float*>(smem + L::kColOffset);
-      const int et = threadIdx.x - 64;  // 0 .. 127
+      const int et = threadIdx.x - 64;  // 0 .. 255
       const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
       const size_t grow = g.gate ? static_cast<size_t>(m0 / g.rows_per_gate) * g.N : 0;
-      for (int j = et; j < BN; j += 128) {
+      for (int j = et; j < BN; j += 256) {
         const int n = n0 + j;
         const bool in = n < g.N;
         col[j] = (in && g.w_scale) ? sa * __ldg(g.w_scale + n) : sa;
@@ -276,8 +281,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (kResInRegs && g.gate != nullptr && m < g.M) {
 #pragma unroll
-        for (int q = 0; q < BN / 8; ++q) {
-          const int n = n0 + q * 8;
+        for (int q = 0; q < kMyChunks * 4; ++q) {
+          const int n = n0 + (2 * (q >> 2) + half) * 32 + (q & 3) * 8;  // chunk 2 * (q / 4) + half, 8 columns at a time
           uint4 x = make_uint4(0u, 0u, 0u, 0u);
           if (n < g.N) x = __ldg(reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n));
           res[(kResInRegs ? q : 0) * 4 + 0] = x.x;
@@ -286,7 +291,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           res[(kResInRegs ? q : 0) * 4 + 3] = x.w;
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 2, 256;" ::: "memory");
     }
     const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_bar), 0, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM));
     if (threadIdx.x == 64) QB_GT(5);
@@ -300,13 +305,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool has_gate = g.gate != nullptr;
       const bool has_scale = g.a_scale != nullptr || g.w_scale != nullptr;
       const bool has_bias = g.bias != nullptr;
-      uint32_t rbuf[2][32];  // chunk c + 1 is on its way from TMEM while chunk c is processed
-      tmem_ld32(taddr, rbuf[0]);
+      uint32_t rbuf[2][32];  // this warp's next chunk is on its way from TMEM while the current one is processed
+      tmem_ld32(taddr + half * 32, rbuf[0]);
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int lc = 0; lc < kMyChunks; ++lc) {
+        const int c = 2 * lc + half;
         tmem_wait_ld();
-        if (c + 1 < BN / 32) tmem_ld32(taddr + (c + 1) * 32, rbuf[(c + 1) & 1]);
-        const uint32_t(&r)[32] = rbuf[c & 1];
+        if (lc + 1 < kMyChunks) tmem_ld32(taddr + (c + 2) * 32, rbuf[(lc + 1) & 1]);
+        const uint32_t(&r)[32] = rbuf[lc & 1];
         const int n = n0 + c * 32;
         if (m < g.M && n < g.N) {
           float v[32];
@@ -328,7 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t rw[16];
             if (kResInRegs) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) rw[j] = res[kResInRegs ? c * 16 + j : 0];
+              for (int j = 0; j < 16; ++j) rw[j] = res[kResInRegs ? lc * 16 + j : 0];
             } else {  // 256-column tiles: the row does not fit in registers beside the accumulator chunk
               const uint4* rp = reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n);
 #pragma unroll
@@ -368,6 +374,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
+    } else if (half == 1) {
+      // the general paths below are written for the first four epilogue warps
     } else if (ok && g.splits == 1) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -456,7 +464,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     __syncthreads();
   }
-  if (use_staging && warp >= 2 && *abort_flag == 0) {
+  if (use_staging && warp >= 2 && warp < 6 && *abort_flag == 0) {
     // Rows are dealt out to the CTAs of the cluster; each sums its rows over all slices, in slice order,
     // reading the peers' staging tiles through distributed shared memory.  Consecutive threads take
     // consecutive groups of 8 columns, so global loads and stores are coalesced.
