@@ -188,6 +188,18 @@ int32_t qb_qkv_post(const void* qkv_in, const void* qkv_first, const float* lamb
                     const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments, int32_t* n_segments,
                     const float* rope_xy, const qb_kv_params* p, float eps, void* stream);
 
+/* The QKV projection with qb_qkv_post as its epilogue: qkv_out = post(A @ B^T), caches and segment table
+ * updated, in one launch; the projection's raw output never goes to memory.  Same bytes as qb_gemm
+ * followed by qb_qkv_post (ref: qkv_proj then the three calls of TransformerBlock.forward,
+ * src/quark/models/waypoint_15.py:396-407).  gp describes the GEMM (M = H*W tokens, N = (n_q_heads +
+ * 2 n_kv_heads) * 64, bf16 output, no activation, no scales; tile_n and split_k are overridden: 128-column
+ * tiles hold two whole heads, one K slice).  qkv_out and K_cache must be 32-byte aligned.  Workspace as
+ * for qb_gemm with tile_n = 128, split_k = 1. */
+int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out, const void* qkv_first, const float* lamb,
+                         const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments,
+                         int32_t* n_segments, const float* rope_xy, const qb_gemm_params* gp, const qb_kv_params* kp, float eps,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* Fills rope_xy [H*W, 16] on the device: token t -> (h, w) = (t / W, t % W).  The angles follow
  * ref: src/quark/kernels/kv_cache_update/reference.py:61-106 (f64 position x frequency, narrowed
  * to f32); cos/sin are the CUDA single-precision functions. */

@@ -14,6 +14,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 #include "sm100.cuh"
 
 namespace qb {
@@ -31,6 +32,23 @@ __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u6
 #define QB_GT(pt) do { } while (0)
 #endif
 
+// What the QKV projection's fused epilogue needs beyond the GEMM: per-head RMS norm of Q and K, value
+// residual on V, RoPE(K) and the KV-cache append happen on the accumulator tile, before anything is
+// written (the stand-alone kernels are in qkv_post.cu and kv.cu; results are bit-identical to them).
+struct QkvTail {
+  const uint16_t* qkv_first;  // may be null: no value residual
+  const float* lamb;
+  const int32_t* frame_t;
+  const int32_t* frozen;
+  void* K_cache;
+  void* Vt_cache;
+  int32_t* segments;
+  int32_t* n_segments;
+  const float* rope_xy;
+  int n_q_heads, n_kv_heads, tpf, nb, pd, max_segments, kv_fp8;
+  float eps;
+};
+
 struct GemmArgs {
   int M, N, K;
   int kb_total, kb_per_split, splits;
@@ -46,6 +64,8 @@ struct GemmArgs {
   float* partials;
   int* counters;
   unsigned int* status;
+  int qkv_mode;  // the fused QKV epilogue below replaces the plain one (128-column tiles only)
+  QkvTail qkv;
 };
 
 template <int BN>
@@ -123,6 +143,222 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
+}
+
+// ---------------------------------------------------------------- fused epilogue of the QKV projection
+// Tile = 128 tokens x 2 heads (128 columns).  Epilogue warp w owns the 32 tokens of TMEM lane quarter
+// w % 4 and head (w - 2) / 4 of the tile, so every thread holds one whole head of one token: the head's
+// RMS norm, the value residual and the K rotation need no exchange between threads.  Arithmetic, rounding
+// points and summation order are those of qkv_post.cu (and through it of head_rmsnorm, value_residual_packed
+// and kv_cache_update), so the bytes written are the same.  V is transposed through the idle stage memory.
+constexpr int kQkvVPitch = 72;  // 16-bit words per token row of the V staging tile
+
+template <bool kCacheFp8>
+__device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* smem, float* tm, uint64_t* acc_bar, volatile int* abort_flag,
+                                                  uint32_t tmem_base, int warp, int lane, int m0, int n0) {
+  constexpr int kEs = kCacheFp8 ? 1 : 2;
+  const QkvTail& q = g.qkv;
+  const int half = (warp - 2) >> 2, lane_grp = warp & 3;
+  const int row = lane_grp * 32 + lane;
+  const int t = m0 + row;  // token
+  const bool valid = t < g.M;
+  const int et = threadIdx.x - 64;  // 0 .. 255
+  const int col0 = n0 + half * 64;  // first column of this thread's head
+  const int k_off = q.n_q_heads * 64, v_off = (q.n_q_heads + q.n_kv_heads) * 64;
+  const int kind = col0 < k_off ? 0 : col0 < v_off ? 1 : 2;  // Q, K or V head (uniform over the warp)
+  const bool in_n = col0 < g.N;
+  const int ft = __ldg(q.frame_t);
+  const int frozen = __ldg(q.frozen);
+  const int L = q.nb * q.tpf;
+  const int cap = L + q.tpf;
+  const int bucket = (ft + q.pd - 1) / q.pd;
+  const int slot = bucket % q.nb;
+  const bool is_write = (ft % q.pd) == 0;
+  const bool ring = is_write && frozen == 0;
+
+  if (et < 8) temporal_cos_sin(ft, et, tm);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && et == 32) {  // segment table: one thread of the grid
+    int sg[6] = {0, 0, 0, 0, 0, 0};
+    int n;
+    if (is_write && bucket >= q.nb) {
+      sg[1] = slot * q.tpf;
+      sg[2] = (slot + 1) * q.tpf;
+      sg[3] = (q.nb - slot - 1) * q.tpf;
+      sg[4] = L;
+      sg[5] = q.tpf;
+      n = 3;
+    } else {
+      sg[1] = min(bucket, q.nb) * q.tpf;
+      sg[2] = L;
+      sg[3] = q.tpf;
+      n = 2;
+    }
+#pragma unroll
+    for (int i = 0; i < 6; ++i)
+      if (i < 2 * q.max_segments) q.segments[i] = sg[i];
+    for (int i = 6; i < 2 * q.max_segments; ++i) q.segments[i] = 0;
+    q.n_segments[0] = n;
+  }
+  // while the main loop runs: what this thread's head needs from global memory
+  float xy[16];
+  uint32_t vf[32];
+  const bool mix = kind == 2 && q.qkv_first != nullptr;
+  const float lam = mix ? __ldg(q.lamb) : 0.f;
+  if (kind == 1 && valid && in_n) {
+    const float4* rp = reinterpret_cast<const float4*>(q.rope_xy + static_cast<size_t>(t) * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(rp + i);
+      xy[4 * i] = v.x; xy[4 * i + 1] = v.y; xy[4 * i + 2] = v.z; xy[4 * i + 3] = v.w;
+    }
+  }
+  if (mix && valid && in_n) {
+    const uint4* fp = reinterpret_cast<const uint4*>(q.qkv_first + static_cast<size_t>(t) * g.N + col0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 v = __ldg(fp + i);
+      vf[4 * i] = v.x; vf[4 * i + 1] = v.y; vf[4 * i + 2] = v.z; vf[4 * i + 3] = v.w;
+    }
+  }
+  asm volatile("bar.sync 2, 256;" ::: "memory");  // temporal cos / sin visible
+
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_bar), 0, abort_flag, g.status, QB_DEV_WAIT_TIMEOUT_GEMM));
+  tc_fence_after();
+  uint16_t* vt = reinterpret_cast<uint16_t*>(smem);  // [2 heads][128 tokens][kQkvVPitch], over the stage memory (idle now)
+  if (ok) {
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + half * 64;
+    uint32_t r0[32], r1[32];
+    tmem_ld32(taddr, r0);
+    tmem_ld32(taddr + 32, r1);
+    tmem_wait_ld();
+    // the projection's output as the unfused path would store and re-read it: rounded to bf16
+    float f[64];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      f[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r0[j])));
+      f[32 + j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r1[j])));
+    }
+    uint32_t o[32];  // the head as it goes to qkv_out: 64 bf16
+    if (kind < 2) {
+      // sum of squares in the order of the 4-lanes-per-head kernel: per 16 elements 8 + 8, then pairs of sixteenths
+      float sq[4];
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sa += f[16 * l + j] * f[16 * l + j];
+#pragma unroll
+        for (int j = 8; j < 16; ++j) sb += f[16 * l + j] * f[16 * l + j];
+        sq[l] = sa + sb;
+      }
+      const float ss = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+      const float inv = 1.0f / sqrtf(ss * (1.0f / 64.0f) + q.eps);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = pack_bf16x2(__fmul_rn(f[2 * j], inv), __fmul_rn(f[2 * j + 1], inv));
+    } else if (mix) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float c0 = f[2 * j], c1 = f[2 * j + 1];
+        o[j] = pack_bf16x2(__fadd_rn(c0, __fmul_rn(lam, __fsub_rn(bf16lo(vf[j]), c0))),
+                           __fadd_rn(c1, __fmul_rn(lam, __fsub_rn(bf16hi(vf[j]), c1))));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+    }
+    if (valid && in_n) {
+      uint16_t* dst = static_cast<uint16_t*>(g.C) + static_cast<size_t>(t) * g.N + col0;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const uint32_t w[8] = {o[8 * h], o[8 * h + 1], o[8 * h + 2], o[8 * h + 3], o[8 * h + 4], o[8 * h + 5], o[8 * h + 6], o[8 * h + 7]};
+        st_global_v8(dst + 16 * h, w);
+      }
+    }
+    if (kind == 1 && valid && in_n) {
+      // rotate what the stand-alone append would read back (the bf16-rounded normalised K): y0 = pairs' first
+      // outputs, y1 = their second outputs; a cache row is y0[0..31] followed by y1[0..31]
+      const int head = (col0 - k_off) >> 6;
+      float y0[32], y1[32];
+#pragma unroll
+      for (int pr = 0; pr < 32; ++pr) {
+        float c, sn;
+        pair_cos_sin(pr, xy, tm, c, sn);
+        const float x0 = bf16lo(o[pr]), x1 = bf16hi(o[pr]);
+        y0[pr] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+        y1[pr] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn));
+      }
+      uint8_t* kc = static_cast<uint8_t*>(q.K_cache);
+      const size_t row_bytes = 64 * kEs;
+      uint8_t* tail = kc + (static_cast<size_t>(head) * cap + L + t) * row_bytes;
+      uint8_t* rr = kc + (static_cast<size_t>(head) * cap + static_cast<size_t>(slot) * q.tpf + t) * row_bytes;
+      if (kCacheFp8) {
+        uint32_t w0[8], w1[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          w0[j] = pack_e4m3x4(y0[4 * j], y0[4 * j + 1], y0[4 * j + 2], y0[4 * j + 3]);
+          w1[j] = pack_e4m3x4(y1[4 * j], y1[4 * j + 1], y1[4 * j + 2], y1[4 * j + 3]);
+        }
+        st_global_v8(tail, w0);
+        st_global_v8(tail + 32, w1);
+        if (ring) {
+          st_global_v8(rr, w0);
+          st_global_v8(rr + 32, w1);
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int e = 16 * (h & 1) + 2 * j;  // 16 values per 32-byte store; h < 2: y0, h >= 2: y1
+            w[j] = h < 2 ? pack_bf16x2(y0[e], y0[e + 1]) : pack_bf16x2(y1[e], y1[e + 1]);
+          }
+          st_global_v8(tail + 32 * h, w);
+          if (ring) st_global_v8(rr + 32 * h, w);
+        }
+      }
+    }
+    if (kind == 2) {  // the mixed V head of this token into the staging tile, 16-byte rows of 8 channels
+      uint16_t* vrow = vt + (half * 128 + row) * kQkvVPitch;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8)
+        *reinterpret_cast<uint4*>(vrow + c8 * 8) = make_uint4(o[4 * c8], o[4 * c8 + 1], o[4 * c8 + 2], o[4 * c8 + 3]);
+    }
+  }
+  asm volatile("bar.sync 2, 256;" ::: "memory");  // V staging complete
+  if (ok) {
+    // transposed 16-byte stores: one channel x (8 | 16) consecutive tokens each, for the V heads of this tile
+    constexpr int kTokPerVec = 16 / kEs;
+    constexpr int kVecPerCh = 128 / kTokPerVec;
+    uint8_t* vc = static_cast<uint8_t*>(q.Vt_cache);
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+      const int hcol = n0 + hh * 64;
+      if (hcol < v_off || hcol >= g.N) continue;
+      const int head = (hcol - v_off) >> 6;
+      const uint16_t* src = vt + hh * 128 * kQkvVPitch;
+      for (int v = et; v < 64 * kVecPerCh; v += 256) {
+        const int d = v / kVecPerCh, j = v % kVecPerCh;
+        const int t1 = j * kTokPerVec;
+        if (m0 + t1 + kTokPerVec > q.tpf) continue;
+        uint32_t w[4];
+        if (kCacheFp8) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            w[i] = pack_e4m3x4(bf16_bits_to_f32(src[(t1 + 4 * i) * kQkvVPitch + d]), bf16_bits_to_f32(src[(t1 + 4 * i + 1) * kQkvVPitch + d]),
+                               bf16_bits_to_f32(src[(t1 + 4 * i + 2) * kQkvVPitch + d]), bf16_bits_to_f32(src[(t1 + 4 * i + 3) * kQkvVPitch + d]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            w[i] = static_cast<uint32_t>(src[(t1 + 2 * i) * kQkvVPitch + d]) | (static_cast<uint32_t>(src[(t1 + 2 * i + 1) * kQkvVPitch + d]) << 16);
+        }
+        const uint4 ov = make_uint4(w[0], w[1], w[2], w[3]);
+        const size_t ch = (static_cast<size_t>(head) * 64 + d) * cap;
+        *reinterpret_cast<uint4*>(vc + (ch + L + m0 + t1) * kEs) = ov;
+        if (ring) *reinterpret_cast<uint4*>(vc + (ch + static_cast<size_t>(slot) * q.tpf + m0 + t1) * kEs) = ov;
+      }
+    }
+  }
 }
 
 template <int BN, bool FP8>
@@ -254,10 +490,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int row = lane_grp * 32 + lane;
     const int m = m0 + row;
     grid_dep_wait();  // bias / gate / residual are read and C is written only after the earlier kernels are done
+    bool qkv_done = false;
+    if constexpr (BN == 128) {
+      if (g.qkv_mode) {
+        float* tm = reinterpret_cast<float*>(smem + L::kColOffset);
+        if (g.qkv.kv_fp8)
+          qkv_tail_epilogue<true>(g, smem, tm, acc_bar, abort_flag, tmem_base, warp, lane, m0, n0);
+        else
+          qkv_tail_epilogue<false>(g, smem, tm, acc_bar, abort_flag, tmem_base, warp, lane, m0, n0);
+        qkv_done = true;
+      }
+    }
     // The fast epilogue needs whole 32-column chunks inside N, 32-byte aligned rows of C, and one gate row
     // for the whole tile; anything else takes the general path below.
     const int m_last = min(m0 + kBM, g.M) - 1;
-    const bool fast = g.splits == 1 && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(g.C) & 31u) == 0 &&
+    const bool fast = !qkv_done && g.splits == 1 && g.N % 32 == 0 && (reinterpret_cast<uintptr_t>(g.C) & 31u) == 0 &&
                       (g.gate == nullptr || m0 / g.rows_per_gate == m_last / g.rows_per_gate);
     // Two warps share each TMEM lane quarter (w and w + 4 see the same 32 rows): in the fast epilogue the
     // first takes the even 32-column chunks of the row, the second the odd ones.  The other epilogue paths
@@ -374,7 +621,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
-    } else if (half == 1) {
+    } else if (half == 1 || qkv_done) {
       // the general paths below are written for the first four epilogue warps
     } else if (ok && g.splits == 1) {
 #pragma unroll 1
@@ -689,8 +936,8 @@ extern "C" size_t qb_gemm_workspace_bytes(const qb_gemm_params* p) {
   return pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
 }
 
-extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
-                           const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                        const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail) {
   int32_t rc = validate_gemm(p);
   if (rc != QB_OK) return rc;
   QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
@@ -743,6 +990,11 @@ extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bi
   g.partials = pl.partial_bytes ? reinterpret_cast<float*>(ws + pl.counters_bytes + pl.aq_bytes) : nullptr;
   g.status = status_word();
   QB_REQUIRE(g.status != nullptr, QB_ERR_CUDA, "gemm: device status word unavailable");
+  if (tail != nullptr) {
+    QB_REQUIRE(pl.bn == 128 && pl.splits == 1, QB_ERR_INVALID_ARG, "gemm_qkv_post: needs 128-column tiles and one K slice");
+    g.qkv_mode = 1;
+    g.qkv = *tail;
+  }
 
   dim3 grid((p->N + pl.bn - 1) / pl.bn, (p->M + kBM - 1) / kBM, pl.splits);
   if (fp8) {
@@ -753,6 +1005,48 @@ extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bi
   if (pl.bn == 256) return launch_gemm<256, false>(tmA, tmB, g, grid, st);
   if (pl.bn == 128) return launch_gemm<128, false>(tmA, tmB, g, grid, st);
   return launch_gemm<64, false>(tmA, tmB, g, grid, st);
+}
+
+extern "C" int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                           const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_run(A, B, C, bias, gate, residual, p, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out, const void* qkv_first, const float* lamb,
+                                    const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments,
+                                    int32_t* n_segments, const float* rope_xy, const qb_gemm_params* gp, const qb_kv_params* kp, float eps,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(gp != nullptr && kp != nullptr, QB_ERR_INVALID_ARG, "gemm_qkv_post: params are NULL");
+  QB_REQUIRE(qkv_out && frame_t && frozen && K_cache && Vt_cache && segments && n_segments && rope_xy, QB_ERR_INVALID_ARG,
+             "gemm_qkv_post: NULL pointer");
+  QB_REQUIRE((qkv_first == nullptr) == (lamb == nullptr), QB_ERR_INVALID_ARG, "gemm_qkv_post: qkv_first and lamb come together");
+  QB_REQUIRE(kp->quilt_factor == 1 && kp->packed_qkv == 1, QB_ERR_UNSUPPORTED, "gemm_qkv_post: packed QKV without quilting only");
+  QB_REQUIRE(kp->n_kv_heads > 0 && kp->n_q_heads > 0 && kp->n_q_heads % kp->n_kv_heads == 0, QB_ERR_INVALID_ARG,
+             "gemm_qkv_post: %d Q heads over %d KV heads", kp->n_q_heads, kp->n_kv_heads);
+  QB_REQUIRE(kp->H_spatial > 0 && kp->W_spatial > 0 && kp->num_buckets > 0 && kp->pinned_dilation > 0, QB_ERR_INVALID_ARG,
+             "gemm_qkv_post: sizes must be positive");
+  QB_REQUIRE(kp->kv_dtype == QB_BF16 || kp->kv_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "gemm_qkv_post: kv_dtype %d", kp->kv_dtype);
+  QB_REQUIRE(kp->max_segments >= 3, QB_ERR_INVALID_ARG, "gemm_qkv_post: max_segments %d < 3", kp->max_segments);
+  const int tpf = kp->H_spatial * kp->W_spatial;
+  QB_REQUIRE(gp->M == tpf && gp->N == (kp->n_q_heads + 2 * kp->n_kv_heads) * 64, QB_ERR_INVALID_ARG,
+             "gemm_qkv_post: the projection is [%d, %d] but the geometry needs [%d, %d]", gp->M, gp->N, tpf,
+             (kp->n_q_heads + 2 * kp->n_kv_heads) * 64);
+  QB_REQUIRE(tpf % 16 == 0, QB_ERR_UNSUPPORTED, "gemm_qkv_post: H*W = %d must be a multiple of 16", tpf);
+  QB_REQUIRE(gp->c_dtype == QB_BF16 && gp->activation == 0 && gp->a_scale == nullptr && gp->w_scale == nullptr, QB_ERR_INVALID_ARG,
+             "gemm_qkv_post: bf16 output without activation or scales");
+  QB_REQUIRE((reinterpret_cast<uintptr_t>(qkv_out) & 31u) == 0 && (reinterpret_cast<uintptr_t>(K_cache) & 31u) == 0 && aligned16(Vt_cache) &&
+                 aligned16(qkv_first) && aligned16(rope_xy),
+             QB_ERR_ALIGN, "gemm_qkv_post: qkv_out and K_cache must be 32-byte aligned, the other pointers 16-byte aligned");
+  qb_gemm_params p = *gp;
+  p.tile_n = 128;
+  p.split_k = 1;
+  QkvTail t{};
+  t.qkv_first = static_cast<const uint16_t*>(qkv_first);
+  t.lamb = lamb; t.frame_t = frame_t; t.frozen = frozen;
+  t.K_cache = K_cache; t.Vt_cache = Vt_cache; t.segments = segments; t.n_segments = n_segments; t.rope_xy = rope_xy;
+  t.n_q_heads = kp->n_q_heads; t.n_kv_heads = kp->n_kv_heads; t.tpf = tpf; t.nb = kp->num_buckets; t.pd = kp->pinned_dilation;
+  t.max_segments = kp->max_segments; t.kv_fp8 = kp->kv_dtype == QB_E4M3; t.eps = eps;
+  return gemm_run(A, B, qkv_out, nullptr, nullptr, nullptr, &p, workspace, workspace_bytes, stream, &t);
 }
 
 // ---------------------------------------------------------------- GEMM on built-in scratch memory

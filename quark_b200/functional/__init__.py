@@ -291,6 +291,54 @@ def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segmen
     return out
 
 
+def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, n_q_heads, n_kv_heads,
+                  H_spatial, W_spatial, num_buckets, pinned_dilation, compute_dtype=None, eps: float = 1e-6, max_segments=3, out=None):  # fmt: skip
+    """``qkv_post(gemm(A, B))`` in one launch: the QKV projection whose epilogue normalises the Q and K heads,
+    mixes V with the first block's, rotates K and appends K / V to the caches (same bytes as the two calls;
+    no reference counterpart as a single call).  Returns the packed QKV that ``owl_attn`` reads."""
+    K = int(A.shape[-1])
+    M = A.numel // K
+    N = int(B.shape[0])
+    tpf = int(H_spatial) * int(W_spatial)
+    if M != tpf or N != (n_q_heads + 2 * n_kv_heads) * 64 or int(B.shape[1]) != K:
+        raise ValueError(f"qf.gemm_qkv_post: A {tuple(A.shape)} x B {tuple(B.shape)} is not the [{tpf}, {(n_q_heads + 2 * n_kv_heads) * 64}] projection")
+    a_dt, b_dt = _dt(A), _dt(B)
+    cd = compute_dtype or (b_dt if b_dt == "e4m3" else a_dt)
+    if (QKV_first is None) != (lamb is None):
+        raise ValueError("qf.gemm_qkv_post: QKV_first and lamb must be given together")
+    if QKV_first is not None and (tuple(QKV_first.shape) != (M, N) or _dt(QKV_first) != "bf16" or _dt(lamb) != "f32"):
+        raise ValueError("qf.gemm_qkv_post: QKV_first must be the packed bf16 QKV of the first block and lamb an f32 tensor")
+    cap = num_buckets * tpf + tpf
+    if tuple(K_cache.shape) != (n_kv_heads * cap, 64) or tuple(Vt_cache.shape) != (n_kv_heads * 64, cap):
+        raise ValueError(f"qf.gemm_qkv_post: cache shapes {tuple(K_cache.shape)} / {tuple(Vt_cache.shape)} do not match capacity {cap}")
+    if int(segments.shape[0]) != max_segments * 2 or int(n_segments.shape[0]) != 1:
+        raise ValueError("qf.gemm_qkv_post: segments / n_segments shapes")
+    kvd = _dt(K_cache)
+    if _dt(Vt_cache) != kvd or kvd not in ("bf16", "e4m3"):
+        raise TypeError(f"qf.gemm_qkv_post: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
+    if out is None:
+        out = QuarkTensor.empty(M, N, dtype="bf16")
+    elif out.numel != M * N or out.dtype != "bf16":
+        raise ValueError(f"qf.gemm_qkv_post: out is {out.shape} {out.dtype}, expected ({M}, {N}) bf16")
+    gp = _lib.GemmParams(
+        M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code("bf16", "bf16"),
+        compute_dtype=_code(cd, "bf16"), activation=0, gate_groups=1, split_k=1, tile_n=128, reserved=2, a_scale=None, w_scale=None,
+    )  # fmt: skip
+    kp = _lib.KvParams(
+        n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+    )  # fmt: skip
+    lib = _lib.load()
+    ws = _workspace(int(lib.qb_gemm_workspace_bytes(C.byref(gp))))
+    _lib.check(
+        lib.qb_gemm_qkv_post(
+            _p(A), _p(B), _p(out), _p(QKV_first), _p(lamb), _p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments),
+            _p(rope_table(H_spatial, W_spatial)), C.byref(gp), C.byref(kp), float(eps), _p(ws), ws.nbytes if ws is not None else 0, _s(),
+        )
+    )  # fmt: skip
+    return out
+
+
 _DUMMY_FRAME_T: QuarkTensor | None = None
 
 

@@ -77,6 +77,8 @@ class Waypoint15Config:
     fuse_silu: bool = True
     # head_rmsnorm + value residual + KV append as one launch (bit-identical to the three).
     fuse_qkv_post: bool = True
+    # ... and that launch folded into the QKV projection's epilogue (same bytes again); needs fuse_qkv_post.
+    fuse_qkv_gemm: bool = True
     # Tensor parallelism by KV-head group: rank `tp_rank` of `tp_world` owns n_kv_heads / tp_world KV heads
     # with their Q heads (QKV and fc1 column-parallel, out-proj and fc2 row-parallel, partial outputs summed
     # over the ranks).  The reference is single-GPU; tp_world = 1 is its wiring.
@@ -272,9 +274,19 @@ class TransformerBlock(nn.Module):
         # row-parallel partial outputs are summed over the ranks before gate and residual are applied (once)
         fuse = self._cfg.fuse_gate_residual and not tp
 
-        qkv = self.qkv_proj(self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8))
+        h0 = self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)
         use_first = hasattr(self, "v_residual") and qkv_first is not None
-        if self._cfg.fuse_qkv_post:
+        if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm:
+            kc = self.kv_cache
+            qkv = qf.gemm_qkv_post(
+                h0, self.qkv_proj.weight.data, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
+                frame_t if frame_t is not None else kc.frame_t, kc._frozen[1 if frozen else 0], kc.Vt_cache, kc.segments, kc.n_segments,
+                kc.K_cache, n_q_heads=self._cfg.n_heads_local, n_kv_heads=self._cfg.n_kv_heads_local, H_spatial=self._cfg.height,
+                W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
+                out=nn._cached(self, "qkv_post", (h0.numel // int(h0.shape[-1]), self._cfg.qkv_dim_local), "bf16"),
+            )  # fmt: skip
+        elif self._cfg.fuse_qkv_post:
+            qkv = self.qkv_proj(h0)
             kc = self.kv_cache
             qkv = qf.qkv_post(
                 qkv, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
@@ -284,7 +296,7 @@ class TransformerBlock(nn.Module):
                 out=nn._cached(self, "qkv_post", qkv.shape, "bf16"),
             )  # fmt: skip
         else:
-            qkv = self.head_norm(qkv)
+            qkv = self.head_norm(self.qkv_proj(h0))
             if use_first:
                 qkv = self.v_residual(qkv, qkv_first)
             self.kv_cache(qkv, frame_t, frozen=frozen)

@@ -245,6 +245,45 @@ def test_qkv_post_is_bit_identical_to_the_three_kernels(qb, kv_dt, H, W, Hq, Hk,
     np.testing.assert_array_equal(nb_.to_numpy(), na.to_numpy())
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("lin", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,Hq,Hk,nb,pd,ft,frozen,with_first", [(8, 8, 4, 2, 4, 1, 6, 0, True), (8, 8, 2, 1, 4, 2, 9, 0, True),
+                                                                  (16, 8, 32, 16, 16, 8, 128, 0, True), (32, 16, 32, 16, 16, 1, 129, 1, True),
+                                                                  (8, 16, 32, 16, 16, 8, 64, 0, False)])  # fmt: skip
+def test_gemm_qkv_post_is_bit_identical_to_gemm_then_qkv_post(qb, kv_dt, lin, H, W, Hq, Hk, nb, pd, ft, frozen, with_first):
+    """The QKV projection with the fused epilogue writes the bytes of the projection followed by qkv_post
+    (itself pinned to the three reference ops above): packed QKV, both caches, the segment table."""
+    r = util.rng(H * W + ft + 1)
+    qf = qb.qf
+    tpf, cap, D, Kd = H * W, (nb + 1) * H * W, (Hq + 2 * Hk) * 64, 256
+    x = bf16_randn(r, (tpf, Kd))
+    first = bf16_randn(r, (tpf, D))
+    if lin == "e4m3":
+        A, Wt = T(qb, codec.f32_to_e4m3(f32(x, "bf16")), "e4m3"), T(qb, e4m3_randn(r, (D, Kd), 0.5), "e4m3")
+    else:
+        A, Wt = T(qb, x, "bf16"), T(qb, bf16_randn(r, (D, Kd), 0.1), "bf16")
+    lam = T(qb, np.array([0.37], np.float32))
+
+    def state():
+        carrier = np.uint16 if kv_dt == "bf16" else np.uint8
+        return (T(qb, np.full((Hk * cap, 64), 0x11, carrier), kv_dt), T(qb, np.full((Hk * 64, cap), 0x22, carrier), kv_dt),
+                T(qb, np.full(6, -7, np.int32)), T(qb, np.array([-7], np.int32)))  # fmt: skip
+
+    ftt, frz = T(qb, np.array([ft], np.int32)), T(qb, np.array([frozen], np.int32))
+    kw = dict(n_q_heads=Hq, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd)
+    fa, la = (T(qb, first, "bf16"), lam) if with_first else (None, None)
+    Ka, Va, sa, na = state()
+    raw = qf.gemm(A, Wt, out_dtype="bf16", compute_dtype="e4m3" if lin == "e4m3" else None, tile_n=128)
+    q1 = qf.qkv_post(raw, fa, la, ftt, frz, Va, sa, na, Ka, **kw)
+    Kb, Vb, sb, nb_ = state()
+    q2 = qf.gemm_qkv_post(A, Wt, fa, la, ftt, frz, Vb, sb, nb_, Kb, **kw)
+    np.testing.assert_array_equal(q2.to_numpy(), q1.to_numpy())
+    np.testing.assert_array_equal(Kb.to_numpy(), Ka.to_numpy())
+    np.testing.assert_array_equal(Vb.to_numpy(), Va.to_numpy())
+    np.testing.assert_array_equal(sb.to_numpy(), sa.to_numpy())
+    np.testing.assert_array_equal(nb_.to_numpy(), na.to_numpy())
+
+
 # --------------------------------------------------------------------------- GEMM
 
 
