@@ -836,17 +836,20 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       if (s_eff != s) continue;
       const long ctas = static_cast<long>(tiles) * s;
       const long waves = (ctas + sms - 1) / sms;
-      // cycles per 128 bytes of K, fitted to measured steady-state rates of this kernel on B200
-      // (1045 / 620 cycles at BN = 256 / 128), a fixed launch + prologue cost, the epilogue, and for
-      // K slices the partial-tile store plus the last CTA's pass over all slices
-      const double per_kb = 300.0 + 2.6 * bn;
-      double cta = kbps * per_kb + 3000.0 + bn * 12.0;
-      // measured: a K slice costs far more than its arithmetic share (row-per-thread f32 partial
-      // stores, a second pass by the last CTA): ~12 us at 512 x 2048 x 8192, so slices only pay
-      // when they multiply the number of busy SMs
+      // Cycles per 128 bytes of K: the slower of what one SM can take in (150 + 2.3 BN, fitted at M = 128 where
+      // few CTAs run) and its share of the L2's aggregate delivery when a whole wave pulls at once (about
+      // 9000 bytes per clock over the chip: 19 TB/s measured at M = 512).  Fixed cost: launch, set-up, first
+      // tile, epilogue (2.8 us at BN = 64).  K slices add the staging, the cluster barrier and the reduction
+      // through distributed shared memory (3.5 - 5.7 us measured for 2 - 4 slices), or the far slower trip
+      // through the workspace (12 - 14 us), so slices pay only when they multiply the number of busy SMs or
+      // K is long.  Measured at M = 128, bf16, 2048 x 8192: 22 us in one slice, 12 us in 4 cluster slices.
+      const long in_wave = ctas < sms ? ctas : sms;
+      const double stage_bytes = 128.0 * (kBM + bn);
+      const double per_sm = 150.0 + 2.3 * bn, shared = in_wave * stage_bytes / 9000.0;
+      const double per_kb = per_sm > shared ? per_sm : shared;
+      double cta = kbps * per_kb + 5000.0 + bn * 12.0;
       const bool cl = (p.reserved & 1) == 0 && (s == 2 || s == 4 || s == 8);
-      // measured at 512 x 2048 x 8192: 4 workspace slices +12 us, 4 cluster slices +7 us over one slice
-      if (s > 1) cta += (cl ? 12000.0 : 20000.0) + bn * 8.0 + s * bn * 4.0;
+      if (s > 1) cta += cl ? 7500.0 + bn * 20.0 + s * bn * 4.0 : 26000.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
         best_cost = cost;
