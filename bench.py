@@ -183,7 +183,7 @@ def time_kernels(qb, eng, peaks):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the hot kernels at this
 # workload's shapes, from the ncu captures summarised in profiles/owl_attn_720p_fp8.md and
 # profiles/gemm_720p_fp8.md (6-layer model, same per-launch shapes as the 24-layer one).
-NCU_DRAM_BYTES_PER_LAUNCH = {"owl_attn": 18.96e6, "gemm_fc2": 23.1e6, "gemm_fc1": 17.9e6, "gemm_qkv": 9.5e6, "gemm_out": 7.4e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"owl_attn": 18.96e6, "gemm_fc2": 23.1e6, "gemm_fc1": 17.9e6, "gemm_qkv": 10.6e6, "gemm_out": 7.4e6}
 SFU_EXP_PER_CLK_PER_SM = 16  # ex2.approx.f32: one warp instruction per 8 cycles and scheduler (measured)
 N_SMS = 148
 
