@@ -228,6 +228,11 @@ typedef struct {
   const float* v_scale;
 } qb_attn_params;
 
+/* Bytes of workspace qb_owl_attn needs for `p`: 0 unless the keys of one (query tile, head) are shared by
+ * several CTAs, which is chosen when query tiles x heads would leave most SMs idle (360p; a tensor-parallel
+ * rank with few heads) or forced with kv_splits.  The workspace starts with one ticket per (query tile,
+ * head), which must be zero before the first use (the kernel leaves them zero), followed by the CTAs'
+ * partial results; it must not be the workspace of qb_gemm.  Shares are summed in a fixed order. */
 size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p);
 int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
                     const int32_t* n_segments, const int32_t* frame_t, void* out, void* out_q, const float* rope_xy,

@@ -83,6 +83,11 @@ struct AttnArgs {
   const float* v_scale;
   unsigned int* status;
   int tpf, qkv_dim, n_q_heads, gqa, capacity, max_segments;
+  // Key splits (gridDim.z > 1): CTA z walks its share of the key tiles and leaves (m, row sum, 64 outputs)
+  // per query row in `partials`; the CTA that draws the last ticket of a (query tile, head) sums the
+  // shares in order of z and writes the output.
+  float* partials;  // [heads][query tiles][splits][66][128]
+  int* tickets;     // [heads][query tiles], zero between launches
 };
 
 template <bool kFp8>
@@ -194,7 +199,9 @@ __device__ __forceinline__ void p_chunk(const uint32_t (&sc)[32], int c, float s
   }
 }
 
-template <bool kFp8>
+// kSplit: the keys of a (query tile, head) are shared by gridDim.z CTAs (see AttnArgs::partials).  The
+// unsplit kernel is an instantiation of its own so that none of this reaches its instruction stream.
+template <bool kFp8, bool kSplit>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
   using L = AttnSmem<kFp8>;
@@ -301,6 +308,13 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     n_tiles = 0;
     if (threadIdx.x == 0) atomicOr(a.status, QB_DEV_BAD_SEGMENT);
   }
+  // this CTA's share of the key tiles: tiles tile0 .. tile0 + n_tiles - 1 of the list
+  const int n_splits = kSplit ? static_cast<int>(gridDim.z) : 1;
+  int tile0 = 0;
+  if (kSplit) {
+    tile0 = static_cast<int>(blockIdx.z) * n_tiles / n_splits;
+    n_tiles = static_cast<int>(blockIdx.z + 1) * n_tiles / n_splits - tile0;
+  }
 
   if (threadIdx.x >= 96 && threadIdx.x < 104) temporal_cos_sin(__ldg(a.frame_t), threadIdx.x - 96, tm);
   __syncthreads();
@@ -318,7 +332,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         const uint32_t ph = (j / kStages) & 1;
         if (!mbar_wait(smem_u32(&kv_empty[s]), ph ^ 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN)) break;
         int row, valid;
-        locate_tile(seg, j, row, valid);
+        locate_tile(seg, tile0 + j, row, valid);
         const uint32_t fb = smem_u32(&kv_full[s]);
         mbar_arrive_expect_tx(fb, L::kKBytes + (kFp8 ? 1 : 2) * 64 * 128);
         uint8_t* st = smem + L::kStageOff + s * L::kStageBytes;
@@ -493,7 +507,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     for (int i = 0; i < my_tiles && ok; ++i) {
       if (lane_grp == 0) QB_TR(g, i, 0);
       int row, valid;
-      locate_tile(seg, 2 * i + g, row, valid);
+      locate_tile(seg, tile0 + 2 * i + g, row, valid);
       if (lane_grp == 0) QB_TR(g, i, 1);
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
       if (!ok) break;
@@ -615,30 +629,93 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       for (int d = 0; d < 64; ++d) comb[(2 + d) * 128 + r] = o[d];
     }
     asm volatile("bar.sync 2, 256;" ::: "memory");
-    if (g == 0 && ok && row_ok && *abort_flag == 0) {
-      const float m1 = comb[r], l1 = comb[128 + r];
-      const float m = fmaxf(m_run, m1);
-      const float a0 = ex2_approx(m_run - m), a1 = ex2_approx(m1 - m);
-      const float l = l_run * a0 + l1 * a1;
-      const float vs = a.v_scale ? __ldg(a.v_scale + kvh) : 1.0f;
-      const float inv = l > 0.f ? vs / l : 0.f;
-      const float s0 = a0 * inv, s1 = a1 * inv;
-      uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64);
+    if (g == 0 && !kSplit) {
+      if (ok && row_ok && *abort_flag == 0) {
+        const float m1 = comb[r], l1 = comb[128 + r];
+        const float m = fmaxf(m_run, m1);
+        const float a0 = ex2_approx(m_run - m), a1 = ex2_approx(m1 - m);
+        const float l = l_run * a0 + l1 * a1;
+        const float vs = a.v_scale ? __ldg(a.v_scale + kvh) : 1.0f;
+        const float inv = l > 0.f ? vs / l : 0.f;
+        const float s0 = a0 * inv, s1 = a1 * inv;
+        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64);
 #pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        uint32_t w[4];
+        for (int v = 0; v < 8; ++v) {
+          uint32_t w[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int d = 4 * v + q;
-          const float e0 = o[2 * d] * s0 + comb[(2 + 2 * d) * 128 + r] * s1;
-          const float e1 = o[2 * d + 1] * s0 + comb[(3 + 2 * d) * 128 + r] * s1;
-          w[q] = pack_bf16x2(e0, e1);
+          for (int q = 0; q < 4; ++q) {
+            const int d = 4 * v + q;
+            const float e0 = o[2 * d] * s0 + comb[(2 + 2 * d) * 128 + r] * s1;
+            const float e1 = o[2 * d + 1] * s0 + comb[(3 + 2 * d) * 128 + r] * s1;
+            w[q] = pack_bf16x2(e0, e1);
+          }
+          dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
+            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
+                make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
+                           pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
+          }
         }
-        dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
-        if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
-          *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
-              make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
-                         pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
+      }
+    } else if (kSplit && g == 0) {
+      // keys shared with other CTAs.  This CTA's result for the row: both groups brought to a common maximum,
+      // not yet divided by the row sum
+      const bool good = ok && *abort_flag == 0;
+      const float m1 = comb[r], l1 = comb[128 + r];
+      float m = fmaxf(m_run, m1);
+      const float a0 = ex2_approx(m_run - m), a1 = ex2_approx(m1 - m);
+      float l = l_run * a0 + l1 * a1;
+      float e[64];
+#pragma unroll
+      for (int d = 0; d < 64; ++d) e[d] = o[d] * a0 + comb[(2 + d) * 128 + r] * a1;
+      bool writer;  // does this CTA write the output rows?
+      {
+        const int item = qh * gridDim.x + blockIdx.x;  // (head, query tile)
+        float* mine = a.partials + (static_cast<size_t>(item) * n_splits + blockIdx.z) * (66 * 128);
+        mine[r] = m;
+        mine[128 + r] = l;
+#pragma unroll
+        for (int d = 0; d < 64; ++d) mine[(2 + d) * 128 + r] = e[d];
+        __threadfence();
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        int* last = reinterpret_cast<int*>(comb);  // the group's exchange buffer is free again
+        if (r == 0) *last = atomicAdd(a.tickets + item, 1) == n_splits - 1;
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        writer = *last != 0;
+        if (writer) {
+          __threadfence();
+          // sum the shares in order of z: the result does not depend on which CTA came last
+          const float* part = a.partials + static_cast<size_t>(item) * n_splits * (66 * 128);
+          m = -1.0e30f;
+          for (int z = 0; z < n_splits; ++z) m = fmaxf(m, __ldcg(part + z * (66 * 128) + r));
+          l = 0.f;
+#pragma unroll
+          for (int d = 0; d < 64; ++d) e[d] = 0.f;
+          for (int z = 0; z < n_splits; ++z) {
+            const float* pz = part + z * (66 * 128);
+            const float w = ex2_approx(__ldcg(pz + r) - m);
+            l = fmaf(w, __ldcg(pz + 128 + r), l);
+#pragma unroll
+            for (int d = 0; d < 64; ++d) e[d] = fmaf(w, __ldcg(pz + (2 + d) * 128 + r), e[d]);
+          }
+          if (r == 0) a.tickets[item] = 0;  // ready for the next launch
+        }
+      }
+      if (writer && good && row_ok) {
+        const float vs = a.v_scale ? __ldg(a.v_scale + kvh) : 1.0f;
+        const float inv = l > 0.f ? vs / l : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          uint32_t w[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(e[8 * v + 2 * q] * inv, e[8 * v + 2 * q + 1] * inv);
+          dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
+            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
+                make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
+                           pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
+          }
         }
       }
     }
@@ -664,16 +741,39 @@ extern "C" int32_t qb_debug_attn_trace(void* host_out) {
 }
 #endif
 
+// How many CTAs share the keys of one (query tile, head).  One when the grid already fills most of the GPU
+// (720p: 4 query tiles x 32 heads); otherwise as many as it takes to reach the SM count, while every
+// share keeps a few key tiles (360p: 1 x 32 -> 4 shares; a tensor-parallel rank with 2 KV heads: 8).
+static int attn_key_splits(const qb_attn_params* p) {
+  if (p->kv_splits > 0) return p->kv_splits;
+  const int tpf = p->H_spatial * p->W_spatial;
+  const int items = ((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio;
+  const int tiles = ((p->num_buckets + 1) * tpf + kKeyTile - 1) / kKeyTile;  // at most
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  int n = sms / (items > 0 ? items : 1);
+  if (n > tiles / 3) n = tiles / 3;
+  if (n > 8) n = 8;
+  return n < 2 ? 1 : n;
+}
+
+static size_t attn_ticket_bytes(const qb_attn_params* p) {
+  const int tpf = p->H_spatial * p->W_spatial;
+  return round_up(static_cast<size_t>((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio * sizeof(int), 1024);
+}
+
 extern "C" size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p) {
-  (void)p;
-  return 0;
+  if (p == nullptr || p->H_spatial <= 0 || p->W_spatial <= 0 || p->n_kv_heads <= 0 || p->gqa_ratio <= 0 || p->num_buckets <= 0) return 0;
+  const int n = attn_key_splits(p);
+  if (n <= 1) return 0;
+  const int tpf = p->H_spatial * p->W_spatial;
+  const size_t items = static_cast<size_t>((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio;
+  return attn_ticket_bytes(p) + items * n * (66 * 128) * sizeof(float);
 }
 
 extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
                                const int32_t* n_segments, const int32_t* frame_t, void* out, void* out_q, const float* rope_xy,
                                const qb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "owl_attn: params are NULL");
   QB_REQUIRE(qkv && K_cache && Vt_cache && segments && n_segments && frame_t && out && rope_xy, QB_ERR_INVALID_ARG,
              "owl_attn: NULL pointer");
@@ -712,12 +812,22 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   a.qkv_dim = (Hq + 2 * p->n_kv_heads) * 64;
   a.n_q_heads = Hq; a.gqa = p->gqa_ratio; a.capacity = cap; a.max_segments = p->max_segments;
 
-  dim3 grid((tpf + kQTile - 1) / kQTile, Hq);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (fp8) {
-    QB_CUDA_OK(cudaFuncSetAttribute(owl_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<true>::kTotal));
-    return launch_dep("owl_attn kernel", owl_attn_kernel<true>, grid, dim3(kAttnThreads), AttnSmem<true>::kTotal, st, tmK, tmV, a);
+  QB_REQUIRE(p->kv_splits >= 0 && p->kv_splits <= 16, QB_ERR_INVALID_ARG, "owl_attn: kv_splits %d", p->kv_splits);
+  const int splits = attn_key_splits(p);
+  if (splits > 1) {
+    const size_t need = qb_owl_attn_workspace_bytes(p);
+    QB_REQUIRE(workspace != nullptr && workspace_bytes >= need, QB_ERR_WORKSPACE, "owl_attn: %d key splits need a workspace of %zu bytes, %zu given",
+               splits, need, workspace_bytes);
+    QB_REQUIRE(aligned16(workspace), QB_ERR_ALIGN, "owl_attn: workspace must be 16-byte aligned");
+    a.tickets = static_cast<int*>(workspace);
+    a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + attn_ticket_bytes(p));
   }
-  QB_CUDA_OK(cudaFuncSetAttribute(owl_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<false>::kTotal));
-  return launch_dep("owl_attn kernel", owl_attn_kernel<false>, grid, dim3(kAttnThreads), AttnSmem<false>::kTotal, st, tmK, tmV, a);
+  dim3 grid((tpf + kQTile - 1) / kQTile, Hq, splits);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto launch = [&](auto kernel, int smem_bytes) -> int32_t {
+    QB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    return launch_dep("owl_attn kernel", kernel, grid, dim3(kAttnThreads), smem_bytes, st, tmK, tmV, a);
+  };
+  if (fp8) return splits > 1 ? launch(owl_attn_kernel<true, true>, AttnSmem<true>::kTotal) : launch(owl_attn_kernel<true, false>, AttnSmem<true>::kTotal);
+  return splits > 1 ? launch(owl_attn_kernel<false, true>, AttnSmem<false>::kTotal) : launch(owl_attn_kernel<false, false>, AttnSmem<false>::kTotal);
 }

@@ -557,7 +557,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
       for (int lc = 0; lc < kMyChunks; ++lc) {
         const int c = 2 * lc + half;
-        tmem_wait_ld();
+        tmem_wait_ld_into(rbuf[lc & 1]);
         if (lc + 1 < kMyChunks) tmem_ld32(taddr + (c + 2) * 32, rbuf[(lc + 1) & 1]);
         const uint32_t(&r)[32] = rbuf[lc & 1];
         const int n = n0 + c * 32;

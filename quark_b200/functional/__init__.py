@@ -63,6 +63,19 @@ def _workspace(nbytes: int) -> QuarkTensor | None:
     return _WS
 
 
+_ATTN_WS: QuarkTensor | None = None
+
+
+def _attn_workspace(nbytes: int) -> QuarkTensor | None:
+    """The attention kernel's own zero-initialised scratch (tickets first; never shared with the GEMM's)."""
+    global _ATTN_WS
+    if nbytes <= 0:
+        return None
+    if _ATTN_WS is None or _ATTN_WS.nbytes < nbytes:
+        _ATTN_WS = QuarkTensor.zeros(int(nbytes), dtype="e4m3")
+    return _ATTN_WS
+
+
 _SCRATCH: dict = {}
 
 
@@ -344,7 +357,7 @@ _DUMMY_FRAME_T: QuarkTensor | None = None
 
 def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_ratio, H_spatial, W_spatial, num_buckets,
              pinned_dilation, out_dtype=None, compute_dtype=None, max_segments=3, packed_qkv=False, quilt_factor=1,
-             quilt_offset=0, frame_t=None, *, out=None, out_q=None, k_scale=None, v_scale=None):  # fmt: skip
+             quilt_offset=0, frame_t=None, *, out=None, out_q=None, k_scale=None, v_scale=None, kv_splits=0):  # fmt: skip
     """Segment-sparse GQA attention with inline Q RoPE (``src/quark/functional/owl_attn.py:322-394``)."""
     global _DUMMY_FRAME_T
     if Q.ndim != 2:
@@ -394,13 +407,12 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     p = _lib.AttnParams(
         n_kv_heads=n_kv_heads, gqa_ratio=gqa_ratio, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], compute_dtype=_lib.DTYPE_CODE[cd],
-        max_segments=max_segments, packed_qkv=1, quilt_factor=1, kv_splits=0,
+        max_segments=max_segments, packed_qkv=1, quilt_factor=1, kv_splits=int(kv_splits),
         k_scale=k_scale.data_ptr() if k_scale is not None else None,
         v_scale=v_scale.data_ptr() if v_scale is not None else None,
     )  # fmt: skip
     lib = _lib.load()
-    need = int(lib.qb_owl_attn_workspace_bytes(C.byref(p)))
-    ws = _workspace(need) if need else None
+    ws = _attn_workspace(int(lib.qb_owl_attn_workspace_bytes(C.byref(p))))
     _lib.check(
         lib.qb_owl_attn(
             _p(Q), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(frame_t), _p(out), _p(out_q),

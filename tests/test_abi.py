@@ -63,3 +63,26 @@ def test_argument_validation_needs_no_gpu():
     assert lib.qb_owl_attn(one, one, one, one, one, one, one, None, one, C.byref(ap), None, 0, None) == -2  # mixed dtypes
     assert lib.qb_rope_table_build(one, 0, 8, None) == -1
     assert lib.qb_device_check(9999) == -5
+
+
+def test_attention_key_split_choice_and_workspace_size_need_no_gpu():
+    """How many CTAs share the keys of one (query tile, head) follows from the geometry alone: none at 720p
+    (4 x 32 items fill the GPU), four at 360p (32 items), eight for a tensor-parallel rank with two KV heads;
+    the workspace is one ticket per item (rounded to 1 KiB) plus 66 x 128 floats per item and share."""
+    import ctypes as C
+
+    from quark_b200 import _lib
+
+    lib = _lib.load()
+
+    def ws(H, W, Hk, splits=0):
+        ap = _lib.AttnParams(n_kv_heads=Hk, gqa_ratio=2, H_spatial=H, W_spatial=W, num_buckets=16, pinned_dilation=1, kv_dtype=1,
+                             compute_dtype=1, max_segments=3, packed_qkv=1, quilt_factor=1, kv_splits=splits)  # fmt: skip
+        return int(lib.qb_owl_attn_workspace_bytes(C.byref(ap)))
+
+    per = 66 * 128 * 4
+    assert ws(32, 16, 16) == 0
+    assert ws(16, 8, 16) == 1024 + 32 * 4 * per
+    assert ws(32, 16, 2) == 1024 + 16 * 8 * per
+    assert ws(32, 16, 16, splits=1) == 0
+    assert ws(32, 16, 16, splits=2) == 1024 + 128 * 2 * per

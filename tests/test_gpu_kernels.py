@@ -460,6 +460,35 @@ def test_owl_attn_score_scale_drifts_along_the_cache(qb, kv_dt, direction):
     _attn_check(got, want, f"attn drifting scale {direction} {kv_dt}", kv_dt == "e4m3")
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,pd,ft,splits", [(16, 8, 1, 16, 0), (16, 8, 8, 129, 3), (8, 8, 1, 5, 8), (32, 16, 1, 129, 2)])
+def test_owl_attn_keys_shared_by_several_ctas(qb, kv_dt, H, W, pd, ft, splits):
+    """Key splits (chosen at 360p, where 32 CTAs would leave most SMs idle; forced otherwise, also to more
+    shares than there are key tiles): same result as one CTA per (query tile, head) up to the order of the
+    sums, the same bytes on every call, and the oracle's result within the usual tolerance."""
+    r = util.rng(300 + ft)
+    Hk, gqa, nb = 16, 2, 16
+    tpf, cap = H * W, 17 * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 4096)), n_q_heads=32, n_kv_heads=16)
+    if kv_dt == "bf16":
+        Kc, Vc = bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap))
+    else:
+        Kc, Vc = e4m3_randn(r, (Hk * cap, 64)), e4m3_randn(r, (Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    args = (T(qb, qkv, "bf16"), T(qb, Kc, kv_dt), T(qb, Vc, kv_dt), T(qb, np.asarray(segs, np.int32)), T(qb, np.array([n], np.int32)), 1, Hk, gqa, H, W, nb, pd)
+    kw = dict(compute_dtype="e4m3" if kv_dt == "e4m3" else None, packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32)))
+    one = qb.qf.owl_attn(*args, kv_splits=1, **kw).to_numpy()
+    got = qb.qf.owl_attn(*args, kv_splits=splits, **kw).to_numpy()
+    again = qb.qf.owl_attn(*args, kv_splits=splits, **kw).to_numpy()
+    np.testing.assert_array_equal(got, again)
+    g, w = f32(got, "bf16"), f32(one, "bf16")
+    # e4m3 probabilities are rounded relative to each share's own running maximum
+    assert util.cosine(g, w) >= (0.9995 if kv_dt == "e4m3" else 0.99999) and (kv_dt == "e4m3" or util.max_rel(g, w) <= 1e-2)
+    want = ops.owl_attn(qkv, Kc, Vc, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                        q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
+    _attn_check(got, want, f"attn split {splits} {H}x{W} pd={pd} ft={ft} {kv_dt}", kv_dt == "e4m3")
+
+
 def test_owl_attn_e4m3_side_output_is_the_narrowed_bf16_output(qb):
     r = util.rng(31)
     Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 8, 4, 1, 9
