@@ -67,13 +67,23 @@ def compare(got_u16, want_u16, what, fp8, max_rel=util.BF16_MAX_REL, cos_min=uti
         assert cs >= cos_min and mr <= max_rel, f"{what}: cosine={cs:.6f} max_rel={mr:.3e}"
 
 
+WIRINGS = {
+    # everything folded into GEMM epilogues (the default)
+    "fused": dict(),
+    # the QKV post-processing as a kernel of its own after the projection
+    "qkv_post_kernel": dict(fuse_qkv_gemm=False),
+    # the reference's launch sequence: every op its own kernel
+    "reference": dict(fuse_gate_residual=False, fuse_silu=False, fuse_qkv_post=False, fuse_qkv_gemm=False),
+}
+
+
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
-@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("fused", list(WIRINGS))
 def test_small_model_session_matches_oracle(qb, quant, fused):
     """append 5 frames (the rings wrap), then generate 2 frames; compare latents and cache bytes."""
     from quark_b200.models import make_params
 
-    cfg = small_cfg(qb, quant, fuse_gate_residual=fused, fuse_silu=fused)
+    cfg = small_cfg(qb, quant, **WIRINGS[fused])
     params = make_params(cfg, seed=3, weight_std=0.08)
     eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=False)
     op, oq = oracle_params(params, quant), oquant(quant)
