@@ -30,7 +30,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PUBLISHED_LATENT_FPS_720P_FP8 = 20.0  # RTX 4090, the reference's README table
+PUBLISHED_LATENT_FPS_720P_FP8 = 20.0  # RTX 4090, from the table in the reference project's README
 HEIGHT, WIDTH = 32, 16  # 720p token grid in the orientation BASELINE.json states (32 x 16 = 512 tokens)
 FRAME_T0 = 128  # caches pre-filled as if 128 frames had been appended
 
