@@ -151,7 +151,7 @@ def time_kernels(qb, eng, peaks):
     xq = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="e4m3")
     hq = qb.QuarkTensor.zeros(tpf, cfg.mlp_dim, dtype="e4m3")
     xr = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="bf16")
-    aq = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="bf16")
+    aq = qb.QuarkTensor.zeros(tpf, cfg.d_model, dtype="e4m3")  # the e4m3 copy of its output that attention emits
     g = eng.model.blocks[0]._cond_lut[0][2]
     qkv = qb.QuarkTensor.zeros(tpf, cfg.qkv_dim, dtype="bf16")
     fp8_peak = 2.0 * peaks["bf16_tflops"]
