@@ -260,6 +260,11 @@ int32_t qb_ada_gate_residual(const void* X, const void* Y, const void* gate, voi
                              void* stream);
 /* out = x * sigmoid(x).  ref: src/quark/kernels/silu/reference.py:10-18. */
 int32_t qb_silu(const void* X, void* out, void* out_q, size_t n, void* stream);
+/* out = x * rsqrt(mean(x^2 over the last dimension) + eps), bf16 [rows, D], no gain.
+ * ref: src/quark/kernels/rmsnorm/reference.py:10-22 (qf.rmsnorm, src/quark/functional/rmsnorm.py:29-45). */
+int32_t qb_rmsnorm(const void* X, void* out, int32_t rows, int32_t D, float eps, void* stream);
+/* out = x + y, bf16, n elements.  ref: src/quark/kernels/elementwise/reference.py:10-19 (op "add"; nn.Add). */
+int32_t qb_add(const void* X, const void* Y, void* out, size_t n, void* stream);
 /* out = x + dsig[0] * v; dsig f32[1] on the device.  ref: src/quark/functional/euler_step.py:36-41. */
 int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out, size_t n, void* stream);
 /* counter[0] += 1.  ref: src/quark/kernels/increment/kernel.py:1-7. */

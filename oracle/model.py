@@ -138,7 +138,7 @@ def _linear(x, w, quant: Quant, **epi):
 
 
 def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame_t: int, *, qkv_first, frozen: bool, quant: Quant,
-                  tp_world: int = 1, reduce=None):  # fmt: skip
+                  tp_world: int = 1, reduce=None, ctrl_emb=None):  # fmt: skip
     """One transformer block; returns ``(x, qkv)`` (waypoint_15.py:389-440, ctrl_emb=None).
 
     ``tp_world > 1`` restates one rank of the sharding by KV-head group: ``blk`` holds that rank's weight
@@ -190,6 +190,10 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         x = _linear(attn, blk["out.weight"], quant, gate=g0, residual=x)
     else:
         x = ops.ada_gate_residual(x, reduce(_linear(attn, blk["out.weight"], quant)), g0)
+    if ctrl_emb is not None and "ctrl.fc1_x.weight" in blk:
+        # controller conditioning on every ctrl_conditioning_period-th block (waypoint_15.py:419-424); bf16 throughout
+        x = ops.add(x, ops.mlp_fusion(ops.rmsnorm(x), ops.rmsnorm(ctrl_emb), blk["ctrl.fc1_x.weight"], blk["ctrl.fc1_c.weight"],
+                                      blk["ctrl.fc2.weight"]))  # fmt: skip
     h = ops.ada_rmsnorm(x, s1, b1)
     h = ops.silu(_linear(h, blk["fc1.weight"], quant))
     if reduce is None:
@@ -199,14 +203,15 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
     return x, qkv
 
 
-def nfe_forward(cfg, params: dict, state: list, latent, sigma_idx: int, frame_t: int, *, frozen: bool, quant: Quant):
+def nfe_forward(cfg, params: dict, state: list, latent, sigma_idx: int, frame_t: int, *, frozen: bool, quant: Quant, ctrl_emb=None):
     """One network evaluation on a ``[1, C*2H*2W]`` bf16 latent (waypoint_15.py:626-661)."""
     ph, pw = cfg.patch
     H2, W2 = cfg.height * ph, cfg.width * pw
     x = ops.patchify(latent, params["patchify.weight"], C=cfg.channels, H=H2, Wd=W2, ph=ph, pw=pw)
     qkv_first = None
     for li in range(cfg.n_layers):
-        x, qkv = block_forward(cfg, li, params["blocks"][li], state[li], x, sigma_idx, frame_t, qkv_first=qkv_first, frozen=frozen, quant=quant)
+        x, qkv = block_forward(cfg, li, params["blocks"][li], state[li], x, sigma_idx, frame_t, qkv_first=qkv_first, frozen=frozen, quant=quant,
+                               ctrl_emb=ctrl_emb)  # fmt: skip
         if li == 0 and getattr(cfg, "value_residual", True):
             qkv_first = qkv
     s_on, b_on = params["out_norm.lut"][sigma_idx]
@@ -214,13 +219,17 @@ def nfe_forward(cfg, params: dict, state: list, latent, sigma_idx: int, frame_t:
     return ops.unpatchify(x, params["unpatchify.weight"], params["unpatchify.bias"], C=cfg.channels, H=H2, Wd=W2, ph=ph, pw=pw)
 
 
-def gen_frame(cfg, params: dict, state: list, noise_latent, frame_t: int, *, quant: Quant):
-    """Four Euler denoise steps plus the commit pass; returns ``(latent, frame_t + 1)``."""
+def gen_frame(cfg, params: dict, state: list, noise_latent, frame_t: int, *, quant: Quant, ctrl_input=None):
+    """Four Euler denoise steps plus the commit pass; returns ``(latent, frame_t + 1)``.  ``ctrl_input`` is the
+    padded controller row; it is embedded once per frame (waypoint_15.py:597-611, :755-766)."""
     sig = cfg.scheduler_sigmas
     x = noise_latent
     n = len(sig) - 1
+    ctrl_emb = None
+    if ctrl_input is not None and "ctrl_emb.fc1.weight" in params:
+        ctrl_emb = ops.controller_embedding(ctrl_input, params["ctrl_emb.fc1.weight"], params["ctrl_emb.fc2.weight"])
     for si in range(n):
-        v = nfe_forward(cfg, params, state, x, si, frame_t, frozen=True, quant=quant)
+        v = nfe_forward(cfg, params, state, x, si, frame_t, frozen=True, quant=quant, ctrl_emb=ctrl_emb)
         x = ops.euler_step(x, v, float(sig[si + 1] - sig[si]))
-    nfe_forward(cfg, params, state, x, n, frame_t, frozen=False, quant=quant)
+    nfe_forward(cfg, params, state, x, n, frame_t, frozen=False, quant=quant, ctrl_emb=ctrl_emb)
     return x, frame_t + 1

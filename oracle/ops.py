@@ -312,6 +312,33 @@ def ada_rmsnorm(X, scale, bias, *, eps: float = 1e-6, activation: str | None = N
     return y if return_f32 else from_f32(y, dtype)
 
 
+def rmsnorm(X, *, eps: float = 1e-6, dtype: str = "bf16"):
+    """``x * rsqrt(mean(x^2, last dim) + eps)``, no gain (src/quark/kernels/rmsnorm/reference.py:10-22; the
+    model calls it with eps = 1e-6, src/quark/functional/rmsnorm.py:29)."""
+    x = to_f32(X, dtype)
+    inv = 1.0 / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
+    return from_f32((x * inv).astype(np.float32), dtype)
+
+
+def add(X, Y, *, dtype: str = "bf16"):
+    """``x + y`` (src/quark/kernels/elementwise/reference.py:10-19, op "add")."""
+    return from_f32(to_f32(X, dtype) + to_f32(Y, dtype), dtype)
+
+
+def mlp_fusion(X, cond, w_x, w_c, w_2):
+    """``fc2(silu(x @ Wx.T + cond @ Wc.T))`` the way the reference runs it (src/quark/nn/layers.py:797-822):
+    the cond projection is a GEMM of its own whose bf16 result is fc1_x's bias row, SiLU is a separate op
+    on the bf16 GEMM output.  All bf16."""
+    h_c = gemm(cond, w_c).reshape(-1)
+    h = silu(gemm(X, w_x, bias=h_c))
+    return gemm(h, w_2)
+
+
+def controller_embedding(ctrl_input, w1, w2):
+    """``fc2(silu(fc1(ctrl_input)))`` on the padded controller row (src/quark/nn/layers.py:760-794)."""
+    return gemm(silu(gemm(ctrl_input, w1)), w2)
+
+
 def head_rmsnorm(X, *, n_q_heads: int, n_kv_heads: int, Dh: int = 64, eps: float = 1e-6, dtype: str = "bf16"):
     """Per-head RMS norm of the Q and K columns, V copied (head_rmsnorm/reference.py:10-26)."""
     x = to_f32(X, dtype).copy()

@@ -10,14 +10,14 @@ from . import functional  # noqa: F401
 from . import functional as qf  # noqa: F401
 from .runtime.tensor import QuarkTensor  # noqa: F401
 
-__all__ = ["QuarkTensor", "qf", "functional", "runtime", "Engine", "Waypoint15", "Waypoint15Config", "QuantConfig"]
+__all__ = ["QuarkTensor", "qf", "functional", "runtime", "Engine", "CtrlInput", "Waypoint15", "Waypoint15Config", "QuantConfig"]
 
 
 def __getattr__(name):
-    if name in ("Engine",):
-        from .engine import Engine
+    if name in ("Engine", "CtrlInput"):
+        from . import engine
 
-        return Engine
+        return getattr(engine, name)
     if name in ("Waypoint15", "Waypoint15Config", "QuantConfig", "GenerateFrame"):
         from .models import waypoint_15 as m
 

@@ -114,6 +114,8 @@ SIGNATURES = {
     "qb_owl_attn_workspace_bytes": (_Z, [C.POINTER(AttnParams)]),
     "qb_owl_attn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(AttnParams), _P, _Z, _P]),
     "qb_ada_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P]),
+    "qb_rmsnorm": (_I, [_P, _P, _I, _I, _F, _P]),
+    "qb_add": (_I, [_P, _P, _P, _Z, _P]),
     "qb_head_rmsnorm": (_I, [_P, _P, _I, _I, _I, _I, _F, _P]),
     "qb_value_residual_packed": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "qb_ada_gate_residual": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),

@@ -178,6 +178,70 @@ __global__ void __launch_bounds__(256) silu_kernel(const uint16_t* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------- plain RMSNorm and elementwise add
+// (the controller-conditioning path: src/quark/kernels/rmsnorm/reference.py:10-22, elementwise add)
+// One CTA per row, like ada_rmsnorm without the affine step.
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, int D, float eps) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int row = blockIdx.x;
+  const uint16_t* x = X + static_cast<size_t>(row) * D;
+  constexpr int kMaxVec = 4;  // D <= 8 * kThreads * kMaxVec
+  uint4 xv[kMaxVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * kThreads + threadIdx.x) * 8;
+    if (c < D) {
+      xv[i] = *reinterpret_cast<const uint4*>(x + c);
+      float f[8];
+      unpack8(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+  __shared__ float red[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) tot += red[w];
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(D) + eps);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * kThreads + threadIdx.x) * 8;
+    if (c < D) {
+      float f[8];
+      unpack8(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(f[j], inv);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * D + c) = pack8(f);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) add_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ Y, uint16_t* __restrict__ out,
+                                                   size_t n) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i8 + 8 <= n) {
+    float x[8], y[8];
+    unpack8(*reinterpret_cast<const uint4*>(X + i8), x);
+    unpack8(*reinterpret_cast<const uint4*>(Y + i8), y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __fadd_rn(x[j], y[j]);
+    *reinterpret_cast<uint4*>(out + i8) = pack8(x);
+  } else {
+    for (size_t i = i8; i < n; ++i) {
+      const __nv_bfloat16 r = __float2bfloat16_rn(__fadd_rn(bf16_bits_to_f32(X[i]), bf16_bits_to_f32(Y[i])));
+      out[i] = *reinterpret_cast<const uint16_t*>(&r);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) euler_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ V,
                                                      const float* __restrict__ dsig, uint16_t* __restrict__ out, size_t n) {
   grid_dep_wait();    // inputs come from the kernels before this one
@@ -419,6 +483,24 @@ int32_t qb_silu(const void* X, void* out, void* out_q, size_t n, void* stream) {
   silu_kernel<<<blocks_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<uint16_t*>(out),
                                                                             static_cast<uint8_t*>(out_q), n);
   return check_launch("silu");
+}
+
+int32_t qb_rmsnorm(const void* X, void* out, int32_t rows, int32_t D, float eps, void* stream) {
+  QB_REQUIRE(X && out, QB_ERR_INVALID_ARG, "rmsnorm: NULL pointer");
+  QB_REQUIRE(rows > 0 && D > 0, QB_ERR_INVALID_ARG, "rmsnorm: rows %d, D %d", rows, D);
+  QB_REQUIRE(D % 8 == 0 && D <= 8192, QB_ERR_UNSUPPORTED, "rmsnorm: D = %d must be a multiple of 8 and at most 8192", D);
+  QB_REQUIRE(eps > 0.f, QB_ERR_INVALID_ARG, "rmsnorm: eps must be positive");
+  QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "rmsnorm: pointers must be 16-byte aligned");
+  return launch_dep("rmsnorm", rmsnorm_kernel<256>, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(X), static_cast<uint16_t*>(out), D, eps);
+}
+
+int32_t qb_add(const void* X, const void* Y, void* out, size_t n, void* stream) {
+  QB_REQUIRE(X && Y && out, QB_ERR_INVALID_ARG, "add: NULL pointer");
+  QB_REQUIRE(aligned16(X) && aligned16(Y) && aligned16(out), QB_ERR_ALIGN, "add: pointers must be 16-byte aligned");
+  if (n == 0) return QB_OK;
+  return launch_dep("add", add_kernel, dim3(blocks_for(n)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(Y), static_cast<uint16_t*>(out), n);
 }
 
 int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out, size_t n, void* stream) {

@@ -12,6 +12,7 @@ result back: those copies are the only host <-> device traffic per frame.
 from __future__ import annotations
 
 import ctypes as C
+from dataclasses import dataclass, field
 
 import numpy as np
 
@@ -35,6 +36,15 @@ class _Pinned:
             _lib.load().qb_host_free(C.c_void_p(self.ptr))
         except Exception:
             pass
+
+
+@dataclass
+class CtrlInput:
+    """Controller input for one frame (``src/quark/models/waypoint_15.py:38-43``)."""
+
+    button: set = field(default_factory=set)
+    mouse: tuple = (0.0, 0.0)
+    scroll_wheel: int = 0
 
 
 class Engine:
@@ -70,6 +80,14 @@ class Engine:
         self._rng = np.random.default_rng([seed, 7])
         self.h2d_bytes_per_frame = n * 2
         self.d2h_bytes_per_frame = n * 2
+        # persistent controller row (device) and its pinned staging copy; refilled per frame, so the captured
+        # graph always reads the same address (src/quark/engine/cuda.py:115-116, models/_waypoint_15_io.py:225-322)
+        self._ctrl_dev = self._ctrl_host = None
+        if cfg.ctrl_conditioning:
+            w = cfg.ctrl_input_width
+            self._ctrl_dev = QuarkTensor.zeros(1, w, dtype="bf16")
+            self._ctrl_host = _Pinned(w * 2, np.uint16)
+            self.h2d_bytes_per_frame += w * 2
 
     # ---- helpers
     def _latent_shape(self):
@@ -85,6 +103,26 @@ class Engine:
         if out.size != self.cfg.latent_numel:
             raise ValueError(f"Engine: latent has {out.size} elements, expected {self._latent_shape()}")
         return out.reshape(-1)
+
+    def _encode_ctrl(self, ctrl):
+        """Packs ``[mouse x, mouse y, one flag per pressed button, scroll wheel]`` (bf16, zero padded) and copies it
+        to the persistent device row; None when the model has no controller path.  ``ctrl=None`` is the idle
+        controller (all zeros), as upstream."""
+        if self._ctrl_dev is None:
+            if ctrl is not None:
+                raise ValueError("Engine: ctrl given but the model was built with ctrl_conditioning=False")
+            return None
+        ctrl = ctrl or CtrlInput()
+        nb = self.cfg.n_buttons
+        row = np.zeros(self.cfg.ctrl_input_width, np.float32)
+        row[0], row[1] = float(ctrl.mouse[0]), float(ctrl.mouse[1])
+        for b in ctrl.button:
+            if 0 <= b < nb:
+                row[2 + b] = 1.0
+        row[2 + nb] = float(ctrl.scroll_wheel)
+        self._ctrl_host.array[:] = (row.view(np.uint32) >> np.uint32(16)).astype(np.uint16)
+        self._h2d(self._ctrl_dev, self._ctrl_host.ptr, row.size * 2)
+        return self._ctrl_dev
 
     def _h2d(self, dev: QuarkTensor, host_ptr: int, nbytes: int):
         _lib.check(_lib.load().qb_memcpy_async(C.c_void_p(dev.data_ptr()), C.c_void_p(host_ptr), nbytes, 0, C.c_void_p(_stream.active_stream())))
@@ -116,12 +154,13 @@ class Engine:
         self.gen.set_frame_t(value)
         self._frame = int(value)
 
-    def append_frame(self, latent):
+    def append_frame(self, latent, ctrl=None):
         """Commit a given latent frame to the KV caches (one NFE at the last sigma, ring writes on) and
         advance the frame counter (``src/quark/engine/cuda.py:177-195`` without the VAE)."""
         self._noise_host.array[:] = self._to_bf16(latent)
         self._h2d(self._append_dev, self._noise_host.ptr, self.cfg.latent_numel * 2)
-        self.model(self._append_dev, sigma_idx=self.gen.n_denoise, frame_t=self.gen.frame_t, frozen=False)
+        ctrl_emb = self.model.encode_ctrl(self._encode_ctrl(ctrl))
+        self.model(self._append_dev, sigma_idx=self.gen.n_denoise, frame_t=self.gen.frame_t, ctrl_emb=ctrl_emb, frozen=False)
         from . import functional as qf
 
         qf.increment(self.gen.frame_t)
@@ -136,8 +175,7 @@ class Engine:
         noise.  Returns the latent as a bf16-carrier ``uint16`` array ``[1, C, 2H, 2W]`` when
         ``return_img`` is true (there is no VAE to make pixels), else None.
         """
-        if ctrl is not None:
-            raise NotImplementedError("Engine.gen_frame: controller input is not implemented")
+        ctrl_dev = self._encode_ctrl(ctrl)
         n = self.cfg.latent_numel
         if noise is None:
             noise = self._rng.standard_normal(n, dtype=np.float32)
@@ -145,7 +183,7 @@ class Engine:
         self._h2d(self._noise_dev, self._noise_host.ptr, n * 2)
         if self._use_graph and self.gen._graph is None:
             self._capture()
-        out = self.gen(self._noise_dev)
+        out = self.gen(self._noise_dev, ctrl_dev)
         self._frame += 1
         if not return_img:
             return None
@@ -160,7 +198,7 @@ class Engine:
         for blk in self.model.blocks:
             kc = blk.kv_cache
             saved.append([(t, t.to_numpy()) for t in (kc.K_cache, kc.Vt_cache, kc.segments, kc.n_segments)])
-        self.gen.prepare_graph(self._noise_dev, start_frame_t=self._frame)
+        self.gen.prepare_graph(self._noise_dev, self._ctrl_dev, start_frame_t=self._frame)
         for items in saved:
             for t, host in items:
                 t.copy_from_numpy(host)

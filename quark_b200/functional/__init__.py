@@ -511,6 +511,25 @@ def silu(X, *, out=None, out_q=None):
     return out
 
 
+def rmsnorm(X, eps: float = 1e-6, *, out=None):
+    """``x * rsqrt(mean(x^2, last dim) + eps)``, no gain (``src/quark/functional/rmsnorm.py:29-45``)."""
+    _bf16_only("qf.rmsnorm", X)
+    D = int(X.shape[-1])
+    out = _like(X, out, "qf.rmsnorm")
+    _lib.check(_lib.load().qb_rmsnorm(_p(X), _p(out), X.numel // D, D, float(eps), _s()))
+    return out
+
+
+def add(X, Y, *, out=None):
+    """``x + y`` on same-shape bf16 tensors (the reference's ``elemwise_binary("add")``, ``src/quark/nn/layers.py:655-669``)."""
+    _bf16_only("qf.add", X, Y)
+    if Y.numel != X.numel:
+        raise ValueError(f"qf.add: X {X.shape} and Y {Y.shape}")
+    out = _like(X, out, "qf.add")
+    _lib.check(_lib.load().qb_add(_p(X), _p(Y), _p(out), X.numel, _s()))
+    return out
+
+
 def euler_step(X, V, Dsig, *, out=None):
     """``cast(f32(X) + f32(Dsig[0]) * f32(V), X.dtype)`` (``src/quark/functional/euler_step.py:36-41``)."""
     _bf16_only("qf.euler_step", X, V)

@@ -67,7 +67,12 @@ class Waypoint15Config:
     value_residual: bool = True
     fourier_dim: int = 512
     scheduler_sigmas: tuple[float, ...] = (1.0, 0.9, 0.75, 0.3, 0.0)
+    # Controller conditioning (mouse / buttons / scroll folded into every ctrl_conditioning_period-th block,
+    # ref: src/quark/models/waypoint_15.py:98-100, :349-366).  The reference's default is on; random-init
+    # benchmark configurations run with ctrl_emb = None, so the default here is off.
     ctrl_conditioning: bool = False
+    ctrl_conditioning_period: int = 3
+    n_buttons: int = 256
     quant: QuantConfig = field(default_factory=QuantConfig.all_bf16)
     quilt_factor: int = 1
     moe: bool = False
@@ -86,8 +91,8 @@ class Waypoint15Config:
     tp_rank: int = 0
 
     def __post_init__(self):
-        if self.ctrl_conditioning:
-            raise NotImplementedError("Waypoint15Config: controller conditioning is not implemented")
+        if self.ctrl_conditioning and (self.ctrl_conditioning_period < 1 or self.n_buttons < 0):
+            raise ValueError("Waypoint15Config: ctrl_conditioning_period must be positive and n_buttons non-negative")
         if self.moe or self.quilt_factor != 1:
             raise NotImplementedError("Waypoint15Config: MoE and quilt are not implemented")
         if self.d_model // self.n_heads != 64:
@@ -141,6 +146,14 @@ class Waypoint15Config:
     @property
     def mlp_dim_local(self):
         return self.mlp_dim // self.tp_world
+
+    @property
+    def ctrl_input_width(self):
+        """Controller row: mouse x, mouse y, one flag per button, scroll wheel, padded to a multiple of 16."""
+        return (self.n_buttons + 3 + 15) // 16 * 16
+
+    def has_ctrl(self, layer):
+        return self.ctrl_conditioning and layer % self.ctrl_conditioning_period == 0
 
     @property
     def latent_numel(self):
@@ -204,8 +217,16 @@ def make_params(cfg: Waypoint15Config, seed: int = 0, *, weight_std: float = 0.0
         mb = _cond.bf16_to_f32(_randn_bf16(r, (d,), weight_std))
         projs = [_cond.bf16_to_f32(_randn_bf16(r, (d, d), weight_std)) for _ in range(6)]
         blk["lut"] = [_cond.block_rows(emb[si], ab, mb, projs) for si in range(ns)]
+        if cfg.has_ctrl(i):  # a generator of its own: the weights above do not depend on this switch
+            rc = np.random.default_rng([seed, i, 7])
+            for k in ("ctrl.fc1_x.weight", "ctrl.fc1_c.weight", "ctrl.fc2.weight"):
+                blk[k] = _randn_bf16(rc, (d, d), weight_std)
         return blk
 
+    if cfg.ctrl_conditioning:
+        rc = np.random.default_rng([seed, 2_000_000])
+        params["ctrl_emb.fc1.weight"] = _randn_bf16(rc, (cfg.mlp_dim, cfg.ctrl_input_width), weight_std)
+        params["ctrl_emb.fc2.weight"] = _randn_bf16(rc, (d, cfg.mlp_dim), weight_std)
     with ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
         params["blocks"] = list(ex.map(one_layer, range(cfg.n_layers)))
     return params
@@ -260,14 +281,20 @@ class TransformerBlock(nn.Module):
         self.attn = nn.OwlAttn(gqa_ratio=cfg.gqa_ratio, compute_dtype="e4m3" if cfg.quant.attn_compute == "fp8" else None, **geo)
         self.out_proj = nn.Linear(nq * cfg.Dh, d, out_dtype="bf16")
         self.attn_gate = nn.AdaGateResidual()
+        if cfg.has_ctrl(layer_idx):
+            if cfg.tp_world > 1:
+                raise NotImplementedError("TransformerBlock: controller conditioning with tp_world > 1 is not implemented")
+            # bf16 end to end, also under fp8 (src/quark/models/waypoint_15.py:349-366)
+            self.ctrl_fusion = nn.MLPFusion(d, out_dtype="bf16")
+            self.ctrl_x_norm = nn.RMSNorm()
+            self.ctrl_emb_norm = nn.RMSNorm()
+            self.ctrl_residual = nn.Add()
         self.pre_mlp_norm = nn.AdaRMSNorm()
         self.mlp = nn.MLP(d, cfg.mlp_dim_local, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
         self.mlp_gate = nn.AdaGateResidual()
 
     def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None):
         """Returns ``(x, qkv)`` (``src/quark/models/waypoint_15.py:389-440``)."""
-        if ctrl_emb is not None:
-            raise NotImplementedError("controller conditioning is not implemented")
         s0, b0, g0, s1, b1, g1 = self._cond_lut[sigma_idx]
         fp8 = self.qkv_proj.weight.data.dtype == "e4m3"
         tp = self._cfg.tp_world > 1
@@ -308,6 +335,8 @@ class TransformerBlock(nn.Module):
             if tp:
                 self._comm.all_reduce_sum(y)
             x = self.attn_gate(x, y, g0)
+        if ctrl_emb is not None and hasattr(self, "ctrl_fusion"):
+            x = self.ctrl_residual(x, self.ctrl_fusion(self.ctrl_x_norm(x), self.ctrl_emb_norm(ctrl_emb)))
         h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8)
         if fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
@@ -328,6 +357,8 @@ class Waypoint15(nn.Module):
         self.blocks = nn.ModuleList([TransformerBlock(cfg, i, comm) for i in range(cfg.n_layers)])
         self.out_norm = nn.AdaRMSNorm()
         self.unpatchify = nn.Unpatchify(cfg.d_model, cfg.channels, cfg.height * ph, cfg.width * pw, ph, pw)
+        if cfg.ctrl_conditioning:
+            self.ctrl_emb = nn.ControllerInputEmbedding(cfg.n_buttons, cfg.d_model, cfg.mlp_ratio, out_dtype="bf16")
         self._out_norm_luts: list[tuple] = []
         # Two residual-stream buffers used alternately by consecutive blocks when the gate/residual
         # epilogue is fused: a GEMM must not write the tensor it reads its residual from.
@@ -341,12 +372,19 @@ class Waypoint15(nn.Module):
         self.unpatchify.weight.data = up(params["unpatchify.weight"])
         self.unpatchify.bias.data = up(params["unpatchify.bias"])
         self._out_norm_luts = [tuple(up(r) for r in rows) for rows in params["out_norm.lut"]]
+        if hasattr(self, "ctrl_emb"):
+            self.ctrl_emb.fc1.weight.data = up(params["ctrl_emb.fc1.weight"])
+            self.ctrl_emb.fc2.weight.data = up(params["ctrl_emb.fc2.weight"])
         for blk, p in zip(self.blocks, params["blocks"]):
             p = shard_block_params(self.cfg, p)
             blk.qkv_proj.weight.data = up(p["qkv.weight"])
             blk.out_proj.weight.data = up(p["out.weight"])
             blk.mlp.fc1.weight.data = up(p["fc1.weight"])
             blk.mlp.fc2.weight.data = up(p["fc2.weight"])
+            if hasattr(blk, "ctrl_fusion"):
+                blk.ctrl_fusion.fc1_x.weight.data = up(p["ctrl.fc1_x.weight"])
+                blk.ctrl_fusion.fc1_c.weight.data = up(p["ctrl.fc1_c.weight"])
+                blk.ctrl_fusion.fc2.weight.data = up(p["ctrl.fc2.weight"])
             if hasattr(blk, "v_residual"):
                 blk.v_residual.lamb.data = QuarkTensor.from_numpy(np.array([p["lamb"]], dtype=np.float32))
             blk._cond_lut = [tuple(up(r) for r in rows) for rows in p["lut"]]
@@ -359,6 +397,15 @@ class Waypoint15(nn.Module):
             for lin in (blk.qkv_proj, blk.out_proj, blk.mlp.fc1, blk.mlp.fc2):
                 lin.prepare(**kwargs)
         _stream.synchronize()
+
+    def encode_ctrl(self, ctrl_input):
+        """The padded controller row ``[1, ctrl_input_width]`` (bf16) -> ``ctrl_emb [1, d_model]``, once per frame;
+        None without controller conditioning or without an input (``src/quark/models/waypoint_15.py:597-611``)."""
+        if ctrl_input is None or not hasattr(self, "ctrl_emb"):
+            return None
+        if ctrl_input.dtype != "bf16" or tuple(ctrl_input.shape) != (1, self.cfg.ctrl_input_width):
+            raise TypeError(f"encode_ctrl: expected a bf16 [1, {self.cfg.ctrl_input_width}] row, got {ctrl_input.dtype} {ctrl_input.shape}")
+        return self.ctrl_emb(ctrl_input)
 
     def set_frame_t(self, value: int) -> None:
         for blk in self.blocks:
@@ -401,6 +448,7 @@ class GenerateFrame(nn.Module):
         self.euler_steps = nn.ModuleList([nn.EulerStep() for _ in range(self.n_denoise)])
         self.frame_t = QuarkTensor.zeros(1, dtype="s32")
         self._graph = None
+        self._ctrl_in = None
         self._in = None
         self._out = None
         self.launches_per_frame = 0  # kernels in the captured frame graph
@@ -413,14 +461,13 @@ class GenerateFrame(nn.Module):
         self.set_frame_t(0)
 
     def forward(self, latent, ctrl_input=None):
-        if ctrl_input is not None:
-            raise NotImplementedError("controller conditioning is not implemented")
         ft = self.frame_t
         x = latent
+        ctrl_emb = self.model.encode_ctrl(ctrl_input)
         for si in range(self.n_denoise):
-            v = self.model(x, sigma_idx=si, frame_t=ft, frozen=True)
+            v = self.model(x, sigma_idx=si, frame_t=ft, ctrl_emb=ctrl_emb, frozen=True)
             x = self.euler_steps[si](x, v, self.dsig_tensors[si])
-        self.model(x, sigma_idx=self.n_denoise, frame_t=ft)
+        self.model(x, sigma_idx=self.n_denoise, frame_t=ft, ctrl_emb=ctrl_emb)
         qf.increment(ft)
         return x
 
@@ -430,15 +477,16 @@ class GenerateFrame(nn.Module):
         restore or reset the caches afterwards."""
         self._in = QuarkTensor.empty(*example_latent.shape, dtype="bf16")
         self._in.copy_from(example_latent)
+        self._ctrl_in = example_ctrl_input  # a persistent device row the caller refills per frame
         self.set_frame_t(start_frame_t)
-        self.forward(self._in)
+        self.forward(self._in, self._ctrl_in)
         _stream.synchronize()
         self.set_frame_t(start_frame_t)
         from .. import _lib
 
         n0 = _lib.kernel_launch_count()
         with _stream.capture_graph() as cap:
-            self._out = self.forward(self._in)
+            self._out = self.forward(self._in, self._ctrl_in)
         self.launches_per_frame = _lib.kernel_launch_count() - n0
         self._graph = cap.graph
         self.set_frame_t(start_frame_t)
@@ -447,6 +495,8 @@ class GenerateFrame(nn.Module):
     def __call__(self, latent, ctrl_input=None):
         if self._graph is None:
             return self.forward(latent, ctrl_input)
+        if ctrl_input is not None and ctrl_input is not self._ctrl_in:
+            raise ValueError("GenerateFrame: the captured graph reads the controller row given to prepare_graph; refill that tensor")
         self._in.copy_from(latent)
         self._graph.launch()
         return self._out

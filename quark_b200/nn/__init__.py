@@ -198,6 +198,48 @@ class AdaRMSNorm(Module):
         return out_q if emit_e4m3 else out
 
 
+class RMSNorm(Module):
+    """Plain RMSNorm, no gain; caches its output (``layers.py:645-652``)."""
+
+    def forward(self, x):
+        return qf.rmsnorm(x, out=_cached(self, "out", x.shape, x.dtype))
+
+
+class Add(Module):
+    """``x + y`` into a cached buffer (``layers.py:655-669``)."""
+
+    def forward(self, x, y):
+        return qf.add(x, y, out=_cached(self, "out", x.shape, x.dtype))
+
+
+class MLPFusion(Module):
+    """``y = fc2(silu(x @ Wx.T + cond @ Wc.T))``: the cond projection enters fc1_x as its bias row
+    (``layers.py:797-822``).  bf16 throughout, also when the model's other linears are e4m3."""
+
+    def __init__(self, d_model: int, out_dtype: str = "bf16"):
+        self.fc1_x = Linear(d_model, d_model, out_dtype=out_dtype)
+        self.fc1_c = Linear(d_model, d_model, out_dtype=out_dtype)
+        self.fc2 = Linear(d_model, d_model, out_dtype=out_dtype)
+
+    def forward(self, x, cond):
+        h_c = self.fc1_c(cond).reshape(-1)
+        return self.fc2(self.fc1_x(x, bias=h_c, activation="silu"))
+
+
+class ControllerInputEmbedding(Module):
+    """``[mouse(2) | buttons one-hot | scroll]`` padded to a multiple of 16 -> fc1 -> SiLU -> fc2 -> ``[1, d_model]``
+    (``layers.py:760-794``).  bf16 throughout."""
+
+    def __init__(self, n_buttons: int, d_model: int, mlp_ratio: int = 4, out_dtype: str = "bf16"):
+        self._raw_in = n_buttons + 3
+        self._padded_in = (self._raw_in + 15) // 16 * 16
+        self.fc1 = Linear(self._padded_in, d_model * mlp_ratio, out_dtype=out_dtype)
+        self.fc2 = Linear(d_model * mlp_ratio, d_model, out_dtype=out_dtype)
+
+    def forward(self, ctrl_input):
+        return self.fc2(self.fc1(ctrl_input, activation="silu"))
+
+
 class AdaGateResidual(Module):
     def forward(self, x, y, gate):
         return qf.ada_gate_residual(x, y, gate, out=_cached(self, "out", x.shape, x.dtype))

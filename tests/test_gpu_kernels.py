@@ -123,6 +123,36 @@ def test_glue_ops_at_model_size(qb):
     assert c.to_numpy().tolist() == [42]
 
 
+def test_controller_conditioning_ops_against_golden_and_oracle(qb):
+    """Plain RMSNorm, add, MLPFusion and the controller embedding: against the fixtures made from the reference's
+    oracles, and at model width against the oracle."""
+    from quark_b200 import nn
+
+    z = np.load(G / "ctrl.npz")
+    qf = qb.qf
+    X, Y, cond = T(qb, z["X"], "bf16"), T(qb, z["Y"], "bf16"), T(qb, z["cond"], "bf16")
+    assert_close_bf16(qf.rmsnorm(X).to_numpy(), z["rmsnorm"], "rmsnorm")
+    assert np.percentile(util.bf16_ulp_diff(qf.rmsnorm(X).to_numpy(), z["rmsnorm"]), 99.9) <= 1
+    assert_close_bf16(qf.rmsnorm(cond).to_numpy(), z["rmsnorm_row"], "rmsnorm row")
+    got_add = qf.add(X, Y).to_numpy()
+    assert util.bf16_ulp_diff(got_add, z["add"]).max() <= 1  # the reference's oracle truncates to bf16, the kernel rounds to nearest
+    with codec.bf16_rounding("rne"):
+        np.testing.assert_array_equal(got_add, ops.add(z["X"], z["Y"]))
+    fus = nn.MLPFusion(256)
+    fus.fc1_x.weight.data, fus.fc1_c.weight.data, fus.fc2.weight.data = T(qb, z["Wx"], "bf16"), T(qb, z["Wc"], "bf16"), T(qb, z["W2"], "bf16")
+    assert_close_bf16(fus(X, cond).to_numpy(), z["mlp_fusion"], "MLPFusion")
+    emb = nn.ControllerInputEmbedding(29, 64)
+    emb.fc1.weight.data, emb.fc2.weight.data = T(qb, z["We1"], "bf16"), T(qb, z["We2"], "bf16")
+    assert_close_bf16(emb(T(qb, z["ctrl_input"], "bf16")).to_numpy(), z["ctrl_emb"], "ControllerInputEmbedding")
+    # model width: 512 tokens x 2048, ragged tail for add
+    r = util.rng(17)
+    x = bf16_randn(r, (512, 2048), 3.0)
+    assert_close_bf16(qf.rmsnorm(T(qb, x, "bf16")).to_numpy(), ops.rmsnorm(x), "rmsnorm 512 x 2048")
+    a, b = bf16_randn(r, (1, 8 * 1000 + 5)), bf16_randn(r, (1, 8 * 1000 + 5))
+    with codec.bf16_rounding("rne"):
+        np.testing.assert_array_equal(qf.add(T(qb, a, "bf16"), T(qb, b, "bf16")).to_numpy(), ops.add(a, b))
+
+
 def test_rope_table_device_builder_matches_numpy(qb):
     import ctypes as C
 

@@ -13,6 +13,7 @@ import pytest
 
 from oracle import codec
 from oracle import model as omodel
+from oracle import ops as oracle_ops
 from tests import util
 from tests.util import f32
 
@@ -128,6 +129,55 @@ def test_small_model_session_matches_oracle(qb, quant, fused):
         compare(got.reshape(-1), want_trunc[k].reshape(-1), f"gen_frame {k} {quant} fused={fused} vs truncating oracle", quant == "fp8", max_rel=5e-2)
         compare(got.reshape(-1), want_rne[k].reshape(-1), f"gen_frame {k} {quant} fused={fused} vs round-to-nearest oracle", quant == "fp8")
     assert int(eng.gen.frame_t.to_numpy()[0]) == ft == 7
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_controller_conditioning_session_matches_oracle(qb, quant, use_graph):
+    """Controller conditioning on (every 3rd block of a 4-block model: blocks 0 and 3): frames appended and
+    generated under changing controller input against the chained oracle; and the input must matter."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, quant, ctrl_conditioning=True, n_buttons=13)
+    assert cfg.ctrl_input_width == 16 and [cfg.has_ctrl(i) for i in range(4)] == [True, False, False, True]
+    params = make_params(cfg, seed=4, weight_std=0.08)
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=use_graph)
+    op, oq = oracle_params(params, quant), oquant(quant)
+    r = util.rng(14)
+    lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(2)]
+    noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(3)]
+    ctrls = [qb.CtrlInput(button={1, 7}, mouse=(0.5, -0.25), scroll_wheel=1), None, qb.CtrlInput(button={12, 99}, mouse=(-1.0, 2.0))]
+
+    def row(c):
+        c = c or qb.CtrlInput()
+        v = np.zeros((1, 16), np.float32)
+        v[0, 0], v[0, 1] = c.mouse
+        for b in c.button:
+            if b < 13:
+                v[0, 2 + b] = 1.0
+        v[0, 15] = c.scroll_wheel
+        return codec.f32_to_bf16(v)
+
+    with codec.bf16_rounding("rne"):
+        state, ft, want = omodel.new_state(cfg, oq), 0, []
+        for lat in lats:
+            emb = oracle_ops.controller_embedding(row(ctrls[0]), op["ctrl_emb.fc1.weight"], op["ctrl_emb.fc2.weight"])
+            omodel.nfe_forward(cfg, op, state, lat, len(cfg.scheduler_sigmas) - 1, ft, frozen=False, quant=oq, ctrl_emb=emb)
+            ft += 1
+        for nz, c in zip(noises, ctrls):
+            w, ft = omodel.gen_frame(cfg, op, state, codec.f32_to_bf16(nz), ft, quant=oq, ctrl_input=row(c))
+            want.append(w)
+    for lat in lats:
+        eng.append_frame(lat, ctrl=ctrls[0])
+    got = [eng.gen_frame(ctrl=c, noise=nz) for nz, c in zip(noises, ctrls)]
+    for k in range(3):
+        compare(got[k].reshape(-1), want[k].reshape(-1), f"ctrl gen_frame {k} {quant} graph={use_graph}", quant == "fp8")
+    # the same noise under another controller input gives another frame
+    eng2 = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, use_graph=use_graph)
+    for lat in lats:
+        eng2.append_frame(lat, ctrl=ctrls[0])
+    other = eng2.gen_frame(ctrl=qb.CtrlInput(button={3}), noise=noises[0])
+    assert np.any(other != got[0])
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])

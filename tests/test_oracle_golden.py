@@ -172,3 +172,14 @@ def test_rope_orientation_matters(H, W):
     c1, _ = ops.rope_tables(H, W, 5)
     c2, _ = ops.rope_tables(W, H, 5)
     assert not np.array_equal(c1, c2)
+
+
+def test_controller_conditioning_ops():
+    """Plain RMSNorm, elementwise add, MLPFusion and the controller embedding against the reference's numpy
+    oracles composed in the order its modules launch them (``tests/golden/make_golden_ctrl.py``)."""
+    z = load("ctrl.npz")
+    np.testing.assert_array_equal(ops.rmsnorm(z["X"]), z["rmsnorm"])
+    np.testing.assert_array_equal(ops.rmsnorm(z["cond"]), z["rmsnorm_row"])
+    np.testing.assert_array_equal(ops.add(z["X"], z["Y"]), z["add"])
+    assert_bf16_close(ops.mlp_fusion(z["X"], z["cond"], z["Wx"], z["Wc"], z["W2"]), z["mlp_fusion"])
+    assert_bf16_close(ops.controller_embedding(z["ctrl_input"], z["We1"], z["We2"]), z["ctrl_emb"])
