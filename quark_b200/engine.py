@@ -53,10 +53,14 @@ class Engine:
         if isinstance(model_uri, Waypoint15Config):
             cfg, model_uri = model_uri, None
         if model_uri is not None:
-            raise NotImplementedError(
-                "Engine: loading a checkpoint by URI (safetensors / YAML / hub download) is not implemented; "
-                "pass cfg=Waypoint15Config(...) and optionally params=<dict of host arrays>"
-            )
+            # a local directory with config.yaml and model.safetensors (src/quark/engine/cuda.py:77, :105-108);
+            # only the transformer is read: the autoencoder and the prompt encoder sit outside this package
+            from .models.checkpoint import load_checkpoint
+
+            if cfg is None:
+                cfg = Waypoint15Config.from_yaml(model_uri)
+            if load_weights and params is None:
+                params = load_checkpoint(model_uri, cfg)
         _lib.require_device(device)
         _lib.check(_lib.load().qb_set_device(device))
         if isinstance(quant, str):

@@ -168,6 +168,33 @@ class Waypoint15Config:
     def pinned_dilation(self, layer):
         return self.global_pinned_dilation if self.is_global(layer) else 1
 
+    _YAML_SCALARS = ("d_model", "n_layers", "n_heads", "n_kv_heads", "mlp_ratio", "channels", "height", "width", "local_window",
+                     "global_window", "global_pinned_dilation", "global_attn_period", "global_attn_offset", "value_residual",
+                     "fourier_dim", "n_buttons", "ctrl_conditioning_period", "moe", "quilt_factor")  # fmt: skip
+
+    @classmethod
+    def from_dict(cls, raw: dict, **overrides) -> "Waypoint15Config":
+        """From the mapping of a training ``config.yaml`` (``src/quark/models/waypoint_15.py:173-219``): known
+        fields are taken, the rest (autoencoder URI, prompt conditioning, frame rate ...) is the caller's concern;
+        ``ctrl_conditioning`` there is the controller specification, and only whether it is present matters."""
+        kw = {k: raw[k] for k in cls._YAML_SCALARS if k in raw}
+        if "patch" in raw:
+            kw["patch"] = tuple(raw["patch"])
+        if "scheduler_sigmas" in raw:
+            kw["scheduler_sigmas"] = tuple(float(s) for s in raw["scheduler_sigmas"])
+        if "ctrl_conditioning" in raw:
+            kw["ctrl_conditioning"] = raw["ctrl_conditioning"] is not None
+        kw.update(overrides)
+        return cls(**kw)
+
+    @classmethod
+    def from_yaml(cls, model_uri, **overrides) -> "Waypoint15Config":
+        """``model_uri``: a ``config.yaml`` or a directory holding one.  A hub repository id cannot be resolved
+        (no download client here) and raises ``FileNotFoundError``."""
+        from .checkpoint import load_yaml_config
+
+        return cls.from_dict(load_yaml_config(model_uri), **overrides)
+
 
 # ---------------------------------------------------------------------------
 # seeded random-init parameters (host numpy, bf16 carriers)

@@ -181,6 +181,47 @@ def test_controller_conditioning_session_matches_oracle(qb, quant, use_graph):
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_engine_from_checkpoint_directory_matches_oracle(qb, quant, tmp_path):
+    """``Engine(model_uri)`` on a directory with ``config.yaml`` and an upstream-layout ``model.safetensors``
+    (split Q/K/V, shared and separate cond heads, 4-D patch weights, both controller layouts): the session
+    equals the chained oracle run on the remapped parameters, and an engine handed those parameters directly."""
+    from quark_b200.models import checkpoint as ck
+    from tests.test_checkpoint import tiny_cfg, write_model_dir
+
+    write_model_dir(tiny_cfg(n_buttons=13), tmp_path, seed=6)
+    eng = qb.Engine(str(tmp_path), quant=quant)
+    cfg = eng.cfg
+    assert (cfg.d_model, cfg.n_layers, cfg.ctrl_conditioning, cfg.ctrl_input_width) == (128, 4, True, 16)
+    params = ck.load_checkpoint(tmp_path, cfg)
+    assert [b["lamb"] for b in params["blocks"]] == [0.625, 0.25, 0.5, 0.5]
+    op, oq = oracle_params(params, quant), oquant(quant)
+    r = util.rng(21)
+    lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(2)]
+    noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(2)]
+    ctrl = qb.CtrlInput(button={0, 5}, mouse=(0.25, -0.5), scroll_wheel=-1)
+    v = np.zeros((1, 16), np.float32)
+    v[0, 0], v[0, 1], v[0, 2], v[0, 7], v[0, 15] = 0.25, -0.5, 1.0, 1.0, -1.0
+    row = codec.f32_to_bf16(v)
+    with codec.bf16_rounding("rne"):
+        state, ft, want = omodel.new_state(cfg, oq), 0, []
+        emb = oracle_ops.controller_embedding(row, op["ctrl_emb.fc1.weight"], op["ctrl_emb.fc2.weight"])
+        for lat in lats:
+            omodel.nfe_forward(cfg, op, state, lat, len(cfg.scheduler_sigmas) - 1, ft, frozen=False, quant=oq, ctrl_emb=emb)
+            ft += 1
+        for nz in noises:
+            w, ft = omodel.gen_frame(cfg, op, state, codec.f32_to_bf16(nz), ft, quant=oq, ctrl_input=row)
+            want.append(w)
+    direct = qb.Engine(cfg=cfg, quant=cfg.quant, params=params)
+    for e in (eng, direct):
+        for lat in lats:
+            e.append_frame(lat, ctrl=ctrl)
+    for k, nz in enumerate(noises):
+        got = eng.gen_frame(ctrl=ctrl, noise=nz)
+        compare(got.reshape(-1), want[k].reshape(-1), f"checkpoint gen_frame {k} {quant}", quant == "fp8")
+        np.testing.assert_array_equal(got, direct.gen_frame(ctrl=ctrl, noise=nz))
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
 def test_graph_replay_equals_eager(qb, quant):
     from quark_b200.models import make_params
 
