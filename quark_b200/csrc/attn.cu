@@ -25,7 +25,13 @@
 // groups fall into lock step and leave the unit idle half of the time (73 us); strict alternation 60 us;
 // alternation with the half-tile overlap 54 us.  A polynomial 2^x on the FMA pipe for part of the elements
 // (QB_POLY_OF8 > 0) is slower here, because the softmax warps are issue bound as well: 57 / 61 / 63 us for
-// 1 / 2 / 3 of every 8 elements.
+// 1 / 2 / 3 of every 8 elements.  Also measured and not kept (52 us as it stands): two threads per query row
+// (16 softmax warps of 64 keys each, row maxima exchanged through shared memory) 58 us; row maxima taken
+// during the exponentials instead of before them, with the rare row that outgrows its maximum written twice,
+// 57 us (the instructions moved into the exponential phase lengthen it by what the phase before it saves).
+// Every mbarrier wait on a softmax warp's path costs about 100 cycles per tile even when it succeeds at once
+// (2 us per launch), which is why each warp arrives once (lane 0, after __syncwarp) and waits as rarely as
+// the data flow allows.
 //
 // The row sum of P comes out of the tensor core: 16 rows of ones follow the 64 V^T rows of every
 // stage, so PV has 80 columns and column 64 is sum_k P[q, k] of exactly the rounded P that is
@@ -139,6 +145,12 @@ template <bool kFp8, int kPolyOf8>
 __device__ __forceinline__ float p_exp(int q, float x) {
   return (q & 7) < kPolyOf8 ? ex2_poly<kFp8 ? 2 : 3>(x) : ex2_approx(x);
 }
+// One arrival for the whole warp: an mbarrier arrival is an atomic on shared memory.  __syncwarp orders the
+// lanes' earlier writes (and fences) before lane 0's arrival, which releases them to the waiting thread.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -225,10 +237,15 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   uint64_t* kv_empty = bars + kStages;       // [stages]
   uint64_t* s_full = bars + 2 * kStages;     // [group] S(i) is in TMEM
   uint64_t* s_free = s_full + 2;             // [group] the group holds S(i) in registers
-  uint64_t* p_full = s_free + 2;             // [group] P(i) is in shared memory, O is rescaled
-  uint64_t* pv_done = p_full + 2;            // [group] O += P(i) V(i) has finished
+  // p_full counts warps' arrivals, and a warp that had to rescale can be late: were there one barrier per group,
+  // an early warp's arrival for tile i + 1 could complete tile i's phase in the late warp's place.  Even and odd
+  // tiles therefore have barriers of their own (no warp can be two tiles ahead: S(i + 2) is not computed before
+  // all four have copied S(i + 1), which they do after finishing tile i).
+  uint64_t* p_full = s_free + 2;             // [group][tile parity] P(i) is in shared memory, O is rescaled
+  uint64_t* pv_done = p_full + 4;            // [group] O += P(i) V(i) has finished
   uint64_t* turn = pv_done + 2;              // [group] the other group has issued its exponentials
-  uint64_t* q_ready = turn + 2;
+  uint64_t* o_final = turn + 2;              // [group] every PV of the group has finished
+  uint64_t* q_ready = o_final + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* drain_flag = abort_flag + 1;
@@ -250,12 +267,14 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&s_full[b]), 1);
-      mbar_init(smem_u32(&s_free[b]), 128);
-      mbar_init(smem_u32(&p_full[b]), 128);
+      mbar_init(smem_u32(&s_free[b]), 4);
+      mbar_init(smem_u32(&p_full[2 * b]), 4);
+      mbar_init(smem_u32(&p_full[2 * b + 1]), 4);
       mbar_init(smem_u32(&pv_done[b]), 1);
-      mbar_init(smem_u32(&turn[b]), 128);
+      mbar_init(smem_u32(&turn[b]), 4);
+      mbar_init(smem_u32(&o_final[b]), 1);
     }
-    mbar_init(smem_u32(q_ready), 256);
+    mbar_init(smem_u32(q_ready), 8);
     *abort_flag = 0;
     *drain_flag = 0;
     fence_barrier_init();
@@ -398,7 +417,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           issue_s(i + 1);
         }
         QB_TR(2 + g, i, 3);
-        ok = mbar_wait(smem_u32(&p_full[g]), i & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
+        ok = mbar_wait(smem_u32(&p_full[2 * g + (i & 1)]), (i >> 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN);
         if (!ok) break;
         QB_TR(2 + g, i, 4);
         tc_fence_after();
@@ -420,6 +439,9 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         umma_commit(smem_u32(&kv_empty[(2 * i + g) % kStages]));
         QB_TR(2 + g, i, 5);
       }
+      // pv_done flips once per tile and the fp8 softmax warps rarely look at it, so its parity cannot tell
+      // "all finished" from "two still in flight"; the end of the accumulation has a barrier of its own
+      if (ok) umma_commit(smem_u32(&o_final[g]));
     }
   }
   } else {
@@ -492,7 +514,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(smem_u32(q_ready));
+      warp_arrive(smem_u32(q_ready), lane);
       if (warp == 4) QB_TR(4, 0, 2);
     }
 
@@ -517,10 +539,15 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       uint32_t sc[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + c * 32, sc[c]);
-      tmem_wait_ld();
+      // the wait names the loaded registers, so that nothing the compiler does with them (a move, a spill)
+      // can be placed between a load and the wait, where they do not hold the scores yet
+      tmem_wait_ld_into(sc[0]);
+      tmem_loaded(sc[1]);
+      tmem_loaded(sc[2]);
+      tmem_loaded(sc[3]);
       if (lane_grp == 0) QB_TR(g, i, 3);
       tc_fence_before();
-      mbar_arrive(smem_u32(&s_free[g]));
+      warp_arrive(smem_u32(&s_free[g]), lane);
       if (valid != kKeyTile) {  // last tile of a segment whose length is not a multiple of 128
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -561,13 +588,14 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           for (int c = 0; c < 2; ++c) {
             uint32_t oo[32];
             tmem_ld32(tmem_o + c * 32, oo);
-            tmem_wait_ld();
+            tmem_wait_ld_into(oo);
 #pragma unroll
             for (int q = 0; q < 32; ++q) oo[q] = __float_as_uint(__uint_as_float(oo[q]) * alpha);
             tmem_st32(tmem_o + c * 32, oo);
           }
-          const uint32_t lsum = tmem_ld1(tmem_o + 64);
+          uint32_t lsum = tmem_ld1(tmem_o + 64);
           tmem_wait_ld();
+          tmem_loaded(lsum);
           tmem_st1(tmem_o + 64, __float_as_uint(__uint_as_float(lsum) * alpha));
           tmem_wait_st();
         }
@@ -588,12 +616,12 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       for (int c = 0; c < 4; ++c) {
         // handed over before the last chunks: the other group needs a while to wake up, and two warps
         // per scheduler keep the special-function unit busier than one
-        if (c == kHandoffChunk) mbar_arrive(smem_u32(&turn[1 - g]));
+        if (c == kHandoffChunk && lane == 0) mbar_arrive(smem_u32(&turn[1 - g]));
         p_chunk<kFp8, kPolyOf8>(sc[c], c, sl2, nshift, p_s, r);
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&p_full[g]));
+      warp_arrive(smem_u32(&p_full[2 * g + (i & 1)]), lane);
       if (lane_grp == 0) QB_TR(g, i, 7);
     }
     if (warp == 4) QB_TR(4, 0, 3);
@@ -603,14 +631,16 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
     for (int d = 0; d < 64; ++d) o[d] = 0.f;
     if (ok && my_tiles > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&pv_done[g]), (my_tiles - 1) & 1, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&o_final[g]), 0, abort_flag, a.status, QB_DEV_WAIT_TIMEOUT_ATTN));
       if (ok) {
         tc_fence_after();
         uint32_t oo[2][32];
         tmem_ld32(tmem_o, oo[0]);
         tmem_ld32(tmem_o + 32, oo[1]);
-        const uint32_t lsum = tmem_ld1(tmem_o + 64);
-        tmem_wait_ld();
+        uint32_t lsum = tmem_ld1(tmem_o + 64);
+        tmem_wait_ld_into(oo[0]);
+        tmem_loaded(oo[1]);
+        tmem_loaded(lsum);
 #pragma unroll
         for (int d = 0; d < 64; ++d) o[d] = __uint_as_float(oo[d >> 5][d & 31]);
         l_run = __uint_as_float(lsum);

@@ -230,7 +230,8 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
     uint32_t r0[32], r1[32];
     tmem_ld32(taddr, r0);
     tmem_ld32(taddr + 32, r1);
-    tmem_wait_ld();
+    tmem_wait_ld_into(r0);
+    tmem_loaded(r1);
     // the projection's output as the unfused path would store and re-read it: rounded to bf16
     float f[64];
 #pragma unroll
@@ -628,7 +629,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
+        tmem_wait_ld_into(r);
         if (m < g.M) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -649,7 +650,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
+        tmem_wait_ld_into(r);
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           *reinterpret_cast<float4*>(dst + c * 32 + q * 4) = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
@@ -662,7 +663,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
+        tmem_wait_ld_into(r);
         if (m < g.M) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) {

@@ -175,6 +175,20 @@ __device__ __forceinline__ void tmem_wait_ld_into(uint32_t (&r)[32]) {
       : "memory");
 }
 
+// For further register arrays that were loaded before the same wait: no instruction, only the same read-write
+// operands, placed right after tmem_wait_ld_into, so these values too exist for the compiler only from here on.
+__device__ __forceinline__ void tmem_loaded(uint32_t (&r)[32]) {
+  asm volatile(
+      ""
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+        "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+        "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+__device__ __forceinline__ void tmem_loaded(uint32_t& r) { asm volatile("" : "+r"(r) : : "memory"); }
+
 // Same, 16 consecutive columns.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
