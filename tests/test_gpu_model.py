@@ -180,6 +180,38 @@ def test_controller_conditioning_session_matches_oracle(qb, quant, use_graph):
     assert np.any(other != got[0])
 
 
+@pytest.mark.parametrize("linear,kv", [("fp8", "bf16"), ("bf16", "fp8")])
+def test_mixed_quant_session_matches_oracle(qb, linear, kv):
+    """``QuantConfig`` switches the linears and the cache / attention separately (``waypoint_15.py:46-76``):
+    e4m3 GEMMs over a bf16 cache, and bf16 GEMMs over an e4m3 cache, each against the chained oracle."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    q = QuantConfig(linear=linear, kv_cache=kv, attn_compute=kv)
+    cfg = Waypoint15Config(**{**small_cfg(qb, "bf16").__dict__, "quant": q})
+    params = make_params(cfg, seed=5, weight_std=0.08)
+    eng = qb.Engine(cfg=cfg, quant=q, params=params)
+    op = oracle_params(params, linear)
+    oq = omodel.Quant(linear=linear, kv_cache=kv, attn_compute=kv)
+    r = util.rng(31)
+    lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(3)]
+    noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(2)]
+    with codec.bf16_rounding("rne"):
+        state, ft, want = omodel.new_state(cfg, oq), 0, []
+        for lat in lats:
+            omodel.nfe_forward(cfg, op, state, lat, len(cfg.scheduler_sigmas) - 1, ft, frozen=False, quant=oq)
+            ft += 1
+        for nz in noises:
+            w, ft = omodel.gen_frame(cfg, op, state, codec.f32_to_bf16(nz), ft, quant=oq)
+            want.append(w)
+    for lat in lats:
+        eng.append_frame(lat)
+    kd = "e4m3" if kv == "fp8" else "bf16"
+    assert eng.model.blocks[0].kv_cache.K_cache.dtype == kd
+    for k, nz in enumerate(noises):
+        got = eng.gen_frame(noise=nz)
+        compare(got.reshape(-1), want[k].reshape(-1), f"mixed linear={linear} kv={kv} frame {k}", True)
+
+
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
 def test_engine_from_checkpoint_directory_matches_oracle(qb, quant, tmp_path):
     """``Engine(model_uri)`` on a directory with ``config.yaml`` and an upstream-layout ``model.safetensors``
