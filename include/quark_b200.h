@@ -267,6 +267,14 @@ int32_t qb_rmsnorm(const void* X, void* out, int32_t rows, int32_t D, float eps,
 int32_t qb_add(const void* X, const void* Y, void* out, size_t n, void* stream);
 /* out = x + dsig[0] * v; dsig f32[1] on the device.  ref: src/quark/functional/euler_step.py:36-41. */
 int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out, size_t n, void* stream);
+/* out[0..n) = standard normals (bf16 or f32) from Philox4x32-10 + Box-Muller; stateless: the draw is a function
+ * of (counter[0] * counter_stride, seed0, seed1) alone, so the call can sit in a captured graph and a caller that
+ * advances counter[0] by one per draw with counter_stride >= ceil(n / 4) never reuses a Philox counter.
+ * counter is a u32 on the device.  ref: src/quark/functional/randn.py:33-82, src/quark/kernels/randn/kernel.py:200-254
+ * (same counters, key, uniform mapping and output layout as its default tile; counter_stride = 1 is its meaning of
+ * counter_offset). */
+int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,
+                 void* stream);
 /* counter[0] += 1.  ref: src/quark/kernels/increment/kernel.py:1-7. */
 int32_t qb_increment(int32_t* counter, void* stream);
 /* latent [1, C*H*W] -> tokens [(H/ph)*(W/pw), d_model] = patches . W[d_model, C*ph*pw]^T.

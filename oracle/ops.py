@@ -393,3 +393,59 @@ def unpatchify(X, W, bias, *, C: int, H: int, Wd: int, ph: int = 2, pw: int = 2,
     Hp, Wp = H // ph, Wd // pw
     h = h.reshape(1, Hp, Wp, C, ph, pw).transpose(0, 3, 1, 4, 2, 5)
     return from_f32(np.ascontiguousarray(h).reshape(1, C * H * Wd), dtype)
+
+
+# ---------------------------------------------------------------------------
+# randn: Philox4x32-10 + Box-Muller
+# ---------------------------------------------------------------------------
+
+
+def philox4x32_10(counter, key):
+    """Philox4x32 with 10 rounds (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11).
+
+    ``counter``: ``uint32 [..., 4]``, ``key``: ``uint32 [..., 2]`` (broadcast together); returns ``uint32 [..., 4]``.
+    The round, multipliers and key schedule are those of the reference's kernel
+    (``src/quark/kernels/randn/kernel.py:44-48, 130-147``), which are the published ones."""
+    c = np.array(np.broadcast_arrays(*[np.asarray(counter, np.uint64)[..., i] for i in range(4)]))
+    k = np.array(np.broadcast_arrays(*[np.asarray(key, np.uint64)[..., i] for i in range(2)]), dtype=np.uint64)
+    k = [np.broadcast_to(k[0], c[0].shape).copy(), np.broadcast_to(k[1], c[0].shape).copy()]
+    c = [x.copy() for x in c]
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c[0]
+        p1 = np.uint64(0xCD9E8D57) * c[2]
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k[0], lo1, hi0 ^ c[3] ^ k[1], lo0]
+        k = [(k[0] + np.uint64(0x9E3779B9)) & mask, (k[1] + np.uint64(0xBB67AE85)) & mask]
+    return np.stack(c, axis=-1).astype(np.uint32)
+
+
+def randn(n: int, counter_offset: int = 0, *, seed0: int = 0xDEADBEEF, seed1: int = 0xBADC0FFE, counter_stride: int = 1, dtype: str = "f32"):
+    """``n`` standard normals in the order the device kernel writes them.
+
+    Restates ``src/quark/kernels/randn/kernel.py:149-254`` at its default tile (128 threads, 2048 outputs per
+    block, ``config.py:11-20``): thread ``t`` of block ``b``, pass ``g`` draws Philox counter
+    ``(b * 512 + g * 128 + t + offset, 0, seed0, seed1)`` under the key ``(seed0, seed1)``; word ``x`` becomes the
+    uniform ``(x >> 8) * 2^-24 + 2^-25``; words (0, 1) and (2, 3) become two normals each,
+    ``sqrt(-2 ln u1) * (cos, sin)(2 pi u2)``; the four land at ``b * 2048 + (4 g + k) * 128 + t``.  The reference has
+    no value oracle for this op (``reference.py`` returns zeros: "statistical, not bitwise"), and its kernel uses
+    approximate log2 / sqrt / sin / cos, so agreement with any implementation is to a tolerance, not bitwise;
+    the integers (Philox words) are exact.  ``counter_stride`` multiplies the offset (1 = the reference)."""
+    blocks = (n + 2047) // 2048
+    b = np.arange(blocks, dtype=np.uint64)[:, None, None]
+    g = np.arange(4, dtype=np.uint64)[None, :, None]
+    t = np.arange(128, dtype=np.uint64)[None, None, :]
+    off = (int(counter_offset) * int(counter_stride)) & 0xFFFFFFFF
+    c0 = ((b * np.uint64(512) + g * np.uint64(128) + t + np.uint64(off)) & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+    ctr = np.stack([c0, np.zeros_like(c0), np.full_like(c0, seed0 & 0xFFFFFFFF), np.full_like(c0, seed1 & 0xFFFFFFFF)], axis=-1)
+    w = philox4x32_10(ctr, np.array([seed0 & 0xFFFFFFFF, seed1 & 0xFFFFFFFF], np.uint32))  # [blocks, 4, 128, 4]
+    u = (w >> np.uint32(8)).astype(np.float32) * np.float32(2.0**-24) + np.float32(2.0**-25)
+    z = np.empty(u.shape, np.float32)
+    for h in range(2):
+        r = np.sqrt(np.float32(-2.0) * np.log(u[..., 2 * h].astype(np.float64))).astype(np.float32)
+        th = (np.float32(2.0 * np.pi) * u[..., 2 * h + 1]).astype(np.float64)
+        z[..., 2 * h] = r * np.cos(th).astype(np.float32)
+        z[..., 2 * h + 1] = r * np.sin(th).astype(np.float32)
+    # [block, g, t, k] -> position block * 2048 + (4 g + k) * 128 + t
+    flat = z.transpose(0, 1, 3, 2).reshape(-1)[:n]
+    return from_f32(flat, "bf16") if dtype == "bf16" else flat

@@ -289,6 +289,69 @@ __global__ void increment_kernel(int32_t* c) {
   c[0] += 1;
 }
 
+// ---------------------------------------------------------------- randn
+// Standard normals from a counter: Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3")
+// on the counter (group, 0, seed0, seed1) with the key (seed0, seed1), the four words turned into uniforms
+// (top 24 bits) * 2^-24 + 2^-25 and pairwise into normals by Box-Muller.  A block of 128 threads fills 2048
+// consecutive outputs: thread t, pass g (0..3) draws group block * 512 + g * 128 + t + offset and writes its four
+// normals to positions block * 2048 + (4 g + k) * 128 + t, k = 0..3, so that every store is coalesced.  This
+// is the layout of the reference's kernel at its default tile (src/quark/kernels/randn/kernel.py:200-254,
+// config.py:11-20), which has no oracle of its own (reference.py: "statistical, not bitwise").
+constexpr int kRandnThreads = 128;
+constexpr int kRandnPerBlock = 2048;
+
+__device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    c[0] = hi1 ^ c[1] ^ k0;
+    c[1] = lo1;
+    c[2] = hi0 ^ c[3] ^ k1;
+    c[3] = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+__device__ __forceinline__ float randn_uniform(uint32_t x) { return fmaf(static_cast<float>(x >> 8), 5.9604644775390625e-8f, 2.98023223876953125e-8f); }
+
+template <typename Out>
+__global__ void __launch_bounds__(kRandnThreads) randn_kernel(const uint32_t* __restrict__ counter, Out* __restrict__ out, size_t n,
+                                                              uint32_t stride, uint32_t seed0, uint32_t seed1) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const uint32_t offset = counter[0] * stride;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kRandnPerBlock;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t c[4] = {static_cast<uint32_t>(blockIdx.x) * (kRandnPerBlock / 4) + g * kRandnThreads + threadIdx.x + offset, 0u, seed0, seed1};
+    philox4x32_10(c, seed0, seed1);
+    float z[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float u1 = randn_uniform(c[2 * h]), u2 = randn_uniform(c[2 * h + 1]);
+      const float r = sqrtf(-1.3862943611198906f * log2f(u1));  // sqrt(-2 ln u1)
+      float sn, cs;
+      sincosf(6.283185307179586f * u2, &sn, &cs);
+      z[2 * h] = r * cs;
+      z[2 * h + 1] = r * sn;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const size_t i = base + (4 * g + k) * kRandnThreads + threadIdx.x;
+      if (i < n) {
+        if constexpr (sizeof(Out) == 4) {
+          out[i] = z[k];
+        } else {
+          const __nv_bfloat16 b = __float2bfloat16_rn(z[k]);
+          out[i] = *reinterpret_cast<const uint16_t*>(&b);
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- patchify / unpatchify
 // Both are thin GEMMs (K = C*ph*pw = 128 in, N = 128 out for the model) run once per NFE.
 // A CTA stages kTok token rows in shared memory as f32; each thread owns one output feature and
@@ -509,6 +572,20 @@ int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out
   if (n == 0) return QB_OK;
   return launch_dep("euler_step", euler_kernel, dim3(blocks_for(n)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(V), dsig, static_cast<uint16_t*>(out), n);
+}
+
+int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,
+                 void* stream) {
+  QB_REQUIRE(counter && out, QB_ERR_INVALID_ARG, "randn: NULL pointer");
+  QB_REQUIRE(out_dtype == QB_BF16 || out_dtype == QB_F32, QB_ERR_INVALID_ARG, "randn: out_dtype %d (bf16 or f32)", out_dtype);
+  QB_REQUIRE(n <= (static_cast<size_t>(1) << 33), QB_ERR_INVALID_ARG, "randn: %zu samples exceed one 32-bit counter range", n);
+  if (n == 0) return QB_OK;
+  const dim3 grid(static_cast<unsigned>((n + kRandnPerBlock - 1) / kRandnPerBlock));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == QB_F32)
+    return launch_dep("randn", randn_kernel<float>, grid, dim3(kRandnThreads), 0, st, counter, static_cast<float*>(out), n, counter_stride, seed0, seed1);
+  return launch_dep("randn", randn_kernel<uint16_t>, grid, dim3(kRandnThreads), 0, st, counter, static_cast<uint16_t*>(out), n, counter_stride, seed0,
+                    seed1);
 }
 
 int32_t qb_increment(int32_t* counter, void* stream) {

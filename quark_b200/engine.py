@@ -49,7 +49,7 @@ class CtrlInput:
 
 class Engine:
     def __init__(self, model_uri=None, *, cfg: Waypoint15Config | None = None, quant="fp8", load_weights=True, seed: int = 0,
-                 params: dict | None = None, device: int = 0, use_graph: bool = True, comm=None):  # fmt: skip
+                 params: dict | None = None, device: int = 0, use_graph: bool = True, comm=None, device_noise: bool = False):  # fmt: skip
         if isinstance(model_uri, Waypoint15Config):
             cfg, model_uri = model_uri, None
         if model_uri is not None:
@@ -82,6 +82,10 @@ class Engine:
         self._noise_dev = QuarkTensor.empty(1, n, dtype="bf16")
         self._append_dev = QuarkTensor.empty(1, n, dtype="bf16")
         self._rng = np.random.default_rng([seed, 7])
+        # device_noise: the frame's starting noise is drawn on the device (qf.randn keyed by the frame counter)
+        # instead of on the host, so a frame needs no host-to-device copy (src/quark/functional/randn.py:1-17)
+        self._device_noise = bool(device_noise)
+        self._noise_seeds = (0xDEADBEEF, (0xBADC0FFE + int(seed)) & 0xFFFFFFFF)
         self.h2d_bytes_per_frame = n * 2
         self.d2h_bytes_per_frame = n * 2
         # persistent controller row (device) and its pinned staging copy; refilled per frame, so the captured
@@ -158,6 +162,31 @@ class Engine:
         self.gen.set_frame_t(value)
         self._frame = int(value)
 
+    def snapshot(self) -> dict:
+        """The session's state as host arrays: every layer's caches and segment table, the frame counter and
+        the host noise generator.  ``restore`` brings a session (of the same configuration) back to it, so a
+        continuation can be replayed or branched.  The reference has no counterpart (its engine can only
+        ``reset``, ``src/quark/engine/base.py:187-195``)."""
+        _stream.synchronize()
+        layers = []
+        for blk in self.model.blocks:
+            kc = blk.kv_cache
+            layers.append({k: getattr(kc, k).to_numpy().copy() for k in ("K_cache", "Vt_cache", "segments", "n_segments")})
+        return {"layers": layers, "frame_t": int(self.gen.frame_t.to_numpy()[0]), "frame": self._frame,
+                "rng": self._rng.bit_generator.state, "geometry": (self.cfg.n_layers, self.cfg.tpf, str(self.cfg.quant.kv_cache))}  # fmt: skip
+
+    def restore(self, snap: dict) -> None:
+        if snap.get("geometry") != (self.cfg.n_layers, self.cfg.tpf, str(self.cfg.quant.kv_cache)):
+            raise ValueError(f"Engine.restore: snapshot of {snap.get('geometry')} does not fit this engine")
+        _stream.synchronize()
+        for blk, saved in zip(self.model.blocks, snap["layers"]):
+            for k, host in saved.items():
+                getattr(blk.kv_cache, k).copy_from_numpy(host)
+        self.gen.set_frame_t(snap["frame_t"])
+        self._frame = snap["frame"]
+        self._rng.bit_generator.state = snap["rng"]
+        _stream.synchronize()
+
     def append_frame(self, latent, ctrl=None):
         """Commit a given latent frame to the KV caches (one NFE at the last sigma, ring writes on) and
         advance the frame counter (``src/quark/engine/cuda.py:177-195`` without the VAE)."""
@@ -181,10 +210,17 @@ class Engine:
         """
         ctrl_dev = self._encode_ctrl(ctrl)
         n = self.cfg.latent_numel
-        if noise is None:
-            noise = self._rng.standard_normal(n, dtype=np.float32)
-        self._noise_host.array[:] = self._to_bf16(noise)
-        self._h2d(self._noise_dev, self._noise_host.ptr, n * 2)
+        if noise is None and self._device_noise:
+            from . import functional as qf
+
+            # one draw per frame: frame f uses the Philox counters [f * stride, f * stride + n / 4)
+            qf.randn(shape=(1, n), dtype="bf16", counter_offset=self.gen.frame_t, out=self._noise_dev, counter_stride=(n + 3) // 4,
+                     seed0=self._noise_seeds[0], seed1=self._noise_seeds[1])  # fmt: skip
+        else:
+            if noise is None:
+                noise = self._rng.standard_normal(n, dtype=np.float32)
+            self._noise_host.array[:] = self._to_bf16(noise)
+            self._h2d(self._noise_dev, self._noise_host.ptr, n * 2)
         if self._use_graph and self.gen._graph is None:
             self._capture()
         out = self.gen(self._noise_dev, ctrl_dev)

@@ -542,6 +542,34 @@ def euler_step(X, V, Dsig, *, out=None):
     return out
 
 
+def randn(*, shape, dtype: str = "bf16", counter_offset, out=None, seed0: int = 0xDEADBEEF, seed1: int = 0xBADC0FFE, counter_stride: int = 1):
+    """Standard normals of ``shape`` made on the device: Philox4x32-10 + Box-Muller, a pure function of
+    ``(counter_offset[0] * counter_stride, seed0, seed1)`` (``src/quark/functional/randn.py:33-82``).
+
+    ``counter_offset`` is a one-element device tensor (four bytes: ``s32`` here, read as unsigned).  The reference
+    leaves it to the caller to move it far enough between draws; ``counter_stride`` (an addition) multiplies it on
+    the device, so a counter that goes up by one per draw (the frame counter, say) with
+    ``counter_stride >= ceil(n / 4)`` gives disjoint Philox counters.  ``out`` makes the call allocation-free."""
+    if isinstance(shape, int):
+        shape = (shape,)
+    n = 1
+    for d in shape:
+        n *= int(d)
+    if n <= 0:
+        raise ValueError(f"qf.randn: shape {shape}")
+    if dtype not in ("bf16", "f32"):
+        raise ValueError(f"qf.randn: dtype must be 'bf16' or 'f32', got {dtype!r}")
+    if _dt(counter_offset) not in ("s32", "u32") or counter_offset.numel != 1:
+        raise TypeError("qf.randn: counter_offset must be a one-element 32-bit integer tensor")
+    if out is None:
+        out = QuarkTensor.empty(*shape, dtype=dtype)
+    elif out.numel != n or _dt(out) != dtype:
+        raise ValueError(f"qf.randn: out is {out.shape} {_dt(out)}, expected {n} elements of {dtype}")
+    _lib.check(_lib.load().qb_randn(_p(counter_offset), _p(out), n, _lib.DTYPE_CODE[dtype], int(counter_stride) & 0xFFFFFFFF, seed0 & 0xFFFFFFFF,
+                                    seed1 & 0xFFFFFFFF, _s()))  # fmt: skip
+    return out
+
+
 def increment(counter):
     if _dt(counter) != "s32":
         raise TypeError("qf.increment: counter must be an s32 tensor")

@@ -556,3 +556,47 @@ def test_owl_attn_empty_segments_give_zero(qb):
     got = _attn_run(qb, bf16_randn(r, (tpf, 512)), bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap)), [0, 0, 0, 0, 0, 0], [2], 0,
                     Hk=Hk, gqa=gqa, H=H, W=W, nb=nb, pd=1, kv_dt="bf16")  # fmt: skip
     assert not got.any()
+
+
+# --------------------------------------------------------------------------- randn
+
+
+@pytest.mark.parametrize("n", [2048, 1000, 3 * 2048 + 40, 65536])
+def test_randn_against_oracle(qb, n):
+    """Philox words are integers and exact; the Box-Muller transcendentals differ in the last bits between numpy
+    and the device library, so f32 normals are held to 2e-5 (|z| < 5.9) and bf16 ones to one unit in the last place,
+    with at least 99.5 % of them bit-equal."""
+    ctr = T(qb, np.array([5], np.int32))
+    got = qb.qf.randn(shape=(n,), dtype="f32", counter_offset=ctr).to_numpy()
+    want = ops.randn(n, 5)
+    assert got.shape == (n,) and np.all(np.isfinite(got))
+    assert float(np.abs(got - want).max()) <= 2e-5
+    gb = qb.qf.randn(shape=(1, n), dtype="bf16", counter_offset=ctr).to_numpy().reshape(-1)
+    with codec.bf16_rounding("rne"):
+        wb = ops.randn(n, 5, dtype="bf16")
+    gf, wf = f32(gb, "bf16"), f32(wb, "bf16")
+    assert np.all(np.abs(gf - wf) <= np.abs(wf) * 2.0**-7 + 2e-5)
+    assert float((gb == wb).mean()) >= 0.995
+
+
+def test_randn_is_a_function_of_counter_stride_and_seeds(qb):
+    n = 4096
+    draw = lambda c, **kw: qb.qf.randn(shape=(n,), dtype="bf16", counter_offset=T(qb, np.array([c], np.int32)), **kw).to_numpy()  # noqa: E731
+    a = draw(3)
+    np.testing.assert_array_equal(a, draw(3))  # stateless: same counter, same draw
+    assert not np.array_equal(a, draw(4))
+    np.testing.assert_array_equal(draw(3, counter_stride=256), draw(768))
+    np.testing.assert_array_equal(draw(512)[:2048], draw(0)[2048:])  # 512 counters per block of 2048
+    assert not np.array_equal(a, draw(3, seed0=1))
+    assert not np.array_equal(a, draw(3, seed1=1))
+    # writes into a caller's buffer, and only n elements of it
+    buf = T(qb, np.full(n + 16, 0x7FC0, np.uint16), "bf16")
+    view = qb.QuarkTensor(buf._storage, (n,), "bf16", 0)
+    qb.qf.randn(shape=(n,), dtype="bf16", counter_offset=T(qb, np.array([3], np.int32)), out=view)
+    back = buf.to_numpy()
+    np.testing.assert_array_equal(back[:n], a)
+    assert np.all(back[n:] == 0x7FC0)
+    with pytest.raises(ValueError):
+        qb.qf.randn(shape=(n,), dtype="e4m3", counter_offset=T(qb, np.array([3], np.int32)))
+    with pytest.raises(TypeError):
+        qb.qf.randn(shape=(n,), counter_offset=T(qb, np.zeros(2, np.int32)))

@@ -14,6 +14,7 @@ import pytest
 from oracle import codec
 from oracle import model as omodel
 from oracle import ops as oracle_ops
+from oracle.ops import randn as ops_randn
 from tests import util
 from tests.util import f32
 
@@ -251,6 +252,54 @@ def test_engine_from_checkpoint_directory_matches_oracle(qb, quant, tmp_path):
         got = eng.gen_frame(ctrl=ctrl, noise=nz)
         compare(got.reshape(-1), want[k].reshape(-1), f"checkpoint gen_frame {k} {quant}", quant == "fp8")
         np.testing.assert_array_equal(got, direct.gen_frame(ctrl=ctrl, noise=nz))
+
+
+def test_snapshot_restore_replays_the_session(qb):
+    """A session restored to a snapshot continues exactly as it did the first time (caches, segment tables,
+    frame counter and host noise generator all come back), also when other frames were generated in between."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, "fp8")
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=make_params(cfg, seed=8, weight_std=0.08), seed=3)
+    r = util.rng(5)
+    for _ in range(3):
+        eng.append_frame(codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)))
+    snap = eng.snapshot()
+    assert snap["frame_t"] == 3 and len(snap["layers"]) == cfg.n_layers
+    first = [eng.gen_frame() for _ in range(3)]  # the ring of 2 local buckets wraps in here
+    assert int(eng.gen.frame_t.to_numpy()[0]) == 6
+    eng.restore(snap)
+    assert int(eng.gen.frame_t.to_numpy()[0]) == 3
+    again = [eng.gen_frame() for _ in range(3)]
+    for a, b in zip(first, again):
+        np.testing.assert_array_equal(a, b)
+    other = qb.Engine(cfg=small_cfg(qb, "fp8", n_layers=2), quant=cfg.quant, load_weights=True)
+    with pytest.raises(ValueError, match="does not fit"):
+        other.restore(snap)
+
+
+def test_device_noise_is_the_randn_stream_of_the_frame_counter(qb):
+    """``device_noise=True``: frame f starts from qf.randn at counter f (stride = latent / 4): the same frame as
+    the engine gives when handed that noise from the host, and no two frames share noise."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, "bf16")
+    params = make_params(cfg, seed=9, weight_std=0.08)
+    dev = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, seed=4, device_noise=True)
+    host = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, seed=4)
+    n = cfg.latent_numel
+    lat = codec.f32_to_bf16(util.rng(6).standard_normal((1, n)).astype(np.float32))
+    for e in (dev, host):
+        e.append_frame(lat)
+    frames = []
+    for f in (1, 2):
+        got = dev.gen_frame()
+        with codec.bf16_rounding("rne"):
+            noise = ops_randn(n, f, counter_stride=(n + 3) // 4, seed1=(0xBADC0FFE + 4) & 0xFFFFFFFF, dtype="bf16")
+        want = host.gen_frame(noise=noise)
+        compare(got.reshape(-1), want.reshape(-1), f"device-noise frame {f}", False)
+        frames.append(got)
+    assert np.any(frames[0] != frames[1])
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
