@@ -152,6 +152,10 @@ int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void
  * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
  * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */
 int32_t qb_quantize_e4m3(const void* X, void* out, size_t n, int32_t src_dtype, void* stream);
+/* out[0..n) (bf16) = X[0..n) (e4m3), exact (every e4m3 value is a bf16 value; NaN stays NaN).  The widening half
+ * of the reference's cast-on-load for a cache whose dtype differs from the attention's compute dtype
+ * (ref: src/quark/kernels/owl_attn/kernel.py:342-348), here as a pass of its own. */
+int32_t qb_dequantize_e4m3(const void* X, void* out, size_t n, void* stream);
 
 /* ------------------------------------------------------------------ KV-cache append
  * Reads the K and V columns of packed qkv [tpf, (Hq + 2 Hk) * 64] bf16, applies ortho-RoPE to K

@@ -172,16 +172,21 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
     )
     st["segments"][:] = segs
     st["n_segments"][:] = nseg
+    Kc, Vc, attn_kv_dtype = st["K_cache"], st["Vt_cache"], kv_dtype
+    if quant.kv_cache == "bf16" and quant.attn_compute == "fp8" and quant.mirror_operand_rounding:
+        # e4m3 arithmetic over a bf16 cache: K and V are narrowed as they are loaded (kernels/owl_attn/kernel.py:342-348).
+        # The opposite mix (e4m3 cache, bf16 arithmetic) needs nothing here: widening e4m3 is exact.
+        Kc, Vc, attn_kv_dtype = from_f32(to_f32(Kc, "bf16"), "e4m3"), from_f32(to_f32(Vc, "bf16"), "e4m3"), "e4m3"
     attn = ops.owl_attn(
         qkv,
-        st["K_cache"],
-        st["Vt_cache"],
+        Kc,
+        Vc,
         st["segments"],
         st["n_segments"],
         frame_t,
         n_kv_heads=Hk,
         gqa_ratio=Hq // Hk,
-        kv_dtype=kv_dtype,
+        kv_dtype=attn_kv_dtype,
         Dh=Dh,
         q_quant="e4m3" if (quant.attn_compute == "fp8" and quant.mirror_operand_rounding) else None,
         **geo,

@@ -107,6 +107,7 @@ SIGNATURES = {
     "qb_gemm_static_scratch_capacity": (_Z, []),
     "qb_gemm_static_scratch": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(GemmParams), _P]),
     "qb_quantize_e4m3": (_I, [_P, _P, _Z, _I, _P]),
+    "qb_dequantize_e4m3": (_I, [_P, _P, _Z, _P]),
     "qb_kv_cache_update": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
     "qb_qkv_post": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _F, _P]),
     "qb_gemm_qkv_post": (_I, [_P] * 12 + [C.POINTER(GemmParams), C.POINTER(KvParams), _F, _P, _Z, _P]),

@@ -2,6 +2,8 @@
 // AdaRMSNorm, per-head RMSNorm, value residual, gate + residual, SiLU, Euler step, e4m3 narrowing,
 // patchify / unpatchify and the frame counter.  bf16 in and out, f32 arithmetic written as
 // separate multiplies and adds where the CPU oracle does so, 16-byte accesses throughout.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace qb {
@@ -289,6 +291,36 @@ __global__ void increment_kernel(int32_t* c) {
   c[0] += 1;
 }
 
+// ---------------------------------------------------------------- e4m3 -> bf16
+// Every e4m3 value is a bf16 value (3 mantissa bits, exponents -9 .. 8), so the widening is exact; NaN stays NaN.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint16_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
+  const __half2 h = *reinterpret_cast<const __half2*>(&h2);
+  const __nv_bfloat162 b = __floats2bfloat162_rn(__low2float(h), __high2float(h));
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ X, uint16_t* __restrict__ out, size_t n) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const size_t i16 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 16;
+  if (i16 + 16 <= n) {
+    const uint4 v = *reinterpret_cast<const uint4*>(X + i16);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = e4m3x2_to_bf16x2(static_cast<uint16_t>(w[j] & 0xFFFF));
+      o[2 * j + 1] = e4m3x2_to_bf16x2(static_cast<uint16_t>(w[j] >> 16));
+    }
+    *reinterpret_cast<uint4*>(out + i16) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(out + i16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {
+    for (size_t i = i16; i < n; ++i) out[i] = static_cast<uint16_t>(e4m3x2_to_bf16x2(X[i]) & 0xFFFF);
+  }
+}
+
 // ---------------------------------------------------------------- randn
 // Standard normals from a counter: Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3")
 // on the counter (group, 0, seed0, seed1) with the key (seed0, seed1), the four words turned into uniforms
@@ -572,6 +604,15 @@ int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out
   if (n == 0) return QB_OK;
   return launch_dep("euler_step", euler_kernel, dim3(blocks_for(n)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(V), dsig, static_cast<uint16_t*>(out), n);
+}
+
+int32_t qb_dequantize_e4m3(const void* X, void* out, size_t n, void* stream) {
+  QB_REQUIRE(n == 0 || (X && out), QB_ERR_INVALID_ARG, "dequantize_e4m3: NULL pointer");
+  QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "dequantize_e4m3: pointers must be 16-byte aligned");
+  if (n == 0) return QB_OK;
+  const size_t blocks = (n + 256 * 16 - 1) / (256 * 16);
+  return launch_dep("dequantize_e4m3", dequantize_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint8_t*>(X), static_cast<uint16_t*>(out), n);
 }
 
 int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,

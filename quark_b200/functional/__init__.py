@@ -202,6 +202,18 @@ def quantize_e4m3(X, *, out=None):
     return out
 
 
+def dequantize_e4m3(X, *, out=None):
+    """e4m3 -> bf16, exact (every e4m3 value is a bf16 value)."""
+    if _dt(X) != "e4m3":
+        raise TypeError(f"qf.dequantize_e4m3: source dtype {_dt(X)!r} (expected e4m3)")
+    if out is None:
+        out = QuarkTensor.empty(*X.shape, dtype="bf16")
+    elif out.numel != X.numel or out.dtype != "bf16":
+        raise ValueError("qf.dequantize_e4m3: out must be a bf16 tensor of the same size")
+    _lib.check(_lib.load().qb_dequantize_e4m3(_p(X), _p(out), X.numel, _s()))
+    return out
+
+
 # ---------------------------------------------------------------------------
 # KV cache append and attention
 # ---------------------------------------------------------------------------
@@ -355,6 +367,16 @@ def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_
 _DUMMY_FRAME_T: QuarkTensor | None = None
 
 
+_CAST_SCRATCH: dict = {}
+
+
+def _cast_scratch(t, dtype: str, which: int):
+    key = (tuple(t.shape), dtype, which)
+    if key not in _CAST_SCRATCH:
+        _CAST_SCRATCH[key] = QuarkTensor.empty(*t.shape, dtype=dtype)
+    return _CAST_SCRATCH[key]
+
+
 def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_ratio, H_spatial, W_spatial, num_buckets,
              pinned_dilation, out_dtype=None, compute_dtype=None, max_segments=3, packed_qkv=False, quilt_factor=1,
              quilt_offset=0, frame_t=None, *, out=None, out_q=None, k_scale=None, v_scale=None, kv_splits=0):  # fmt: skip
@@ -387,10 +409,18 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     cd = compute_dtype.value if hasattr(compute_dtype, "value") else compute_dtype
     if cd is None:
         cd = "bf16"
+    if cd not in ("bf16", "e4m3") or kvd not in ("bf16", "e4m3"):
+        raise NotImplementedError(f"qf.owl_attn: compute_dtype={cd!r} with a {kvd!r} cache (bf16 and e4m3 only)")
     if cd != kvd:
-        raise NotImplementedError(
-            f"qf.owl_attn: compute_dtype={cd!r} with a {kvd!r} cache; supported pairs are bf16/bf16 and e4m3/e4m3"
-        )
+        # The reference casts K and V to the compute dtype as it loads them (src/quark/kernels/owl_attn/kernel.py:
+        # 342-348).  Here the cast is a pass of its own into a scratch copy of the two caches (one pair per shape,
+        # reused by every layer: calls on one stream run in order), after which the kernel for that dtype runs.
+        # Same values as casting on load; a cache's worth of extra traffic per call, so not the fast path.
+        conv = quantize_e4m3 if cd == "e4m3" else dequantize_e4m3
+        Ks, Vs = _cast_scratch(K_cache, cd, 0), _cast_scratch(Vt_cache, cd, 1)
+        conv(K_cache, out=Ks)
+        conv(Vt_cache, out=Vs)
+        K_cache, Vt_cache, kvd = Ks, Vs, cd
     od = out_dtype.value if hasattr(out_dtype, "value") else out_dtype
     if od not in (None, "bf16"):
         raise NotImplementedError(f"qf.owl_attn: out_dtype {od!r} (only bf16)")

@@ -2,10 +2,10 @@
 
 Mirrors ``src/quark/models/waypoint_15.py``: ``QuantConfig`` (``:46-76``), ``Waypoint15Config``
 (``:79-171``), ``TransformerBlock`` (``:259-440``), ``Waypoint15`` (``:448-661``) and
-``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: the
-controller-conditioning branch (``ctrl_emb`` is always None here), MoE, quilt, checkpoint
-download.  Weights come from ``make_params`` (seeded random init, the stand-in for the real
-checkpoint) or any dict of the same layout via ``Waypoint15.load_params``.
+``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: MoE,
+quilt, checkpoint download from a hub.  Weights come from ``make_params`` (seeded random init),
+from a local checkpoint (``checkpoint.load_checkpoint``) or any dict of the same layout, through
+``Waypoint15.load_params``.
 """
 
 from __future__ import annotations
@@ -36,8 +36,6 @@ class QuantConfig:
             v = getattr(self, name)
             if v not in ("fp8", "bf16"):
                 raise ValueError(f"QuantConfig.{name}: must be 'fp8' or 'bf16', got {v!r}")
-        if self.kv_cache != self.attn_compute:
-            raise NotImplementedError("QuantConfig: kv_cache and attn_compute must match (cast-on-load is not implemented)")
 
     @classmethod
     def all_bf16(cls) -> "QuantConfig":

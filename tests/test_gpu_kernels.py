@@ -600,3 +600,40 @@ def test_randn_is_a_function_of_counter_stride_and_seeds(qb):
         qb.qf.randn(shape=(n,), dtype="e4m3", counter_offset=T(qb, np.array([3], np.int32)))
     with pytest.raises(TypeError):
         qb.qf.randn(shape=(n,), counter_offset=T(qb, np.zeros(2, np.int32)))
+
+
+# --------------------------------------------------------------------------- cache dtype != compute dtype
+
+
+def test_dequantize_e4m3_is_exact_for_every_code(qb):
+    codes = np.tile(np.arange(256, dtype=np.uint8), 5)[:1275]  # ragged length: tail path too
+    got = qb.qf.dequantize_e4m3(T(qb, codes, "e4m3")).to_numpy()
+    want = codec.f32_to_bf16(codec.e4m3_to_f32(codes))
+    nan = np.isnan(codec.e4m3_to_f32(codes))
+    np.testing.assert_array_equal(got[~nan], want[~nan])
+    assert np.all(np.isnan(f32(got[nan], "bf16"))) and nan.sum() == int(np.isin(codes, [0x7F, 0xFF]).sum()) == 9
+
+
+@pytest.mark.parametrize("kv_dt,compute", [("e4m3", "bf16"), ("bf16", "e4m3")])
+def test_owl_attn_cache_dtype_differs_from_compute_dtype(qb, kv_dt, compute):
+    """Cast on load (``src/quark/kernels/owl_attn/kernel.py:342-348``): the result equals attention over a cache
+    that already holds the cast values, bit for bit, and the oracle's within the usual bound."""
+    r = util.rng(91)
+    Hk, gqa, H, W, nb, pd, ft = 2, 2, 16, 8, 4, 1, 6
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 8 * 64)), n_q_heads=4, n_kv_heads=2)
+    if kv_dt == "e4m3":
+        Kc, Vc = e4m3_randn(r, (Hk * cap, 64)), e4m3_randn(r, (Hk * 64, cap))
+        Kx, Vx = codec.f32_to_bf16(codec.e4m3_to_f32(Kc)), codec.f32_to_bf16(codec.e4m3_to_f32(Vc))
+    else:
+        Kc, Vc = bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap))
+        Kx, Vx = codec.f32_to_e4m3(codec.bf16_to_f32(Kc)), codec.f32_to_e4m3(codec.bf16_to_f32(Vc))
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    common = (T(qb, np.asarray(segs, np.int32)), T(qb, np.array([n], np.int32)), 1, Hk, gqa, H, W, nb, pd)
+    kw = dict(compute_dtype=compute, packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32)))
+    got = qb.qf.owl_attn(T(qb, qkv, "bf16"), T(qb, Kc, kv_dt), T(qb, Vc, kv_dt), *common, **kw).to_numpy()
+    direct = qb.qf.owl_attn(T(qb, qkv, "bf16"), T(qb, Kx, compute), T(qb, Vx, compute), *common, **kw).to_numpy()
+    np.testing.assert_array_equal(got, direct)
+    want = ops.owl_attn(qkv, Kx, Vx, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=compute,
+                        q_quant="e4m3" if compute == "e4m3" else None)  # fmt: skip
+    _attn_check(got, want, f"attn cache={kv_dt} compute={compute}", compute == "e4m3")

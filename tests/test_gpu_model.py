@@ -181,18 +181,19 @@ def test_controller_conditioning_session_matches_oracle(qb, quant, use_graph):
     assert np.any(other != got[0])
 
 
-@pytest.mark.parametrize("linear,kv", [("fp8", "bf16"), ("bf16", "fp8")])
-def test_mixed_quant_session_matches_oracle(qb, linear, kv):
-    """``QuantConfig`` switches the linears and the cache / attention separately (``waypoint_15.py:46-76``):
-    e4m3 GEMMs over a bf16 cache, and bf16 GEMMs over an e4m3 cache, each against the chained oracle."""
+@pytest.mark.parametrize("linear,kv,attn", [("fp8", "bf16", "bf16"), ("bf16", "fp8", "fp8"), ("fp8", "fp8", "bf16"), ("bf16", "bf16", "fp8")])
+def test_mixed_quant_session_matches_oracle(qb, linear, kv, attn):
+    """``QuantConfig`` switches the linears, the cache and the attention arithmetic separately
+    (``waypoint_15.py:46-76``): e4m3 GEMMs over a bf16 cache, bf16 GEMMs over an e4m3 cache, an e4m3 cache widened
+    for bf16 attention and a bf16 cache narrowed for e4m3 attention, each against the chained oracle."""
     from quark_b200.models import QuantConfig, Waypoint15Config, make_params
 
-    q = QuantConfig(linear=linear, kv_cache=kv, attn_compute=kv)
+    q = QuantConfig(linear=linear, kv_cache=kv, attn_compute=attn)
     cfg = Waypoint15Config(**{**small_cfg(qb, "bf16").__dict__, "quant": q})
     params = make_params(cfg, seed=5, weight_std=0.08)
     eng = qb.Engine(cfg=cfg, quant=q, params=params)
     op = oracle_params(params, linear)
-    oq = omodel.Quant(linear=linear, kv_cache=kv, attn_compute=kv)
+    oq = omodel.Quant(linear=linear, kv_cache=kv, attn_compute=attn)
     r = util.rng(31)
     lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(3)]
     noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(2)]
@@ -210,7 +211,7 @@ def test_mixed_quant_session_matches_oracle(qb, linear, kv):
     assert eng.model.blocks[0].kv_cache.K_cache.dtype == kd
     for k, nz in enumerate(noises):
         got = eng.gen_frame(noise=nz)
-        compare(got.reshape(-1), want[k].reshape(-1), f"mixed linear={linear} kv={kv} frame {k}", True)
+        compare(got.reshape(-1), want[k].reshape(-1), f"mixed linear={linear} kv={kv} attn={attn} frame {k}", True)
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
