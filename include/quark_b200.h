@@ -176,11 +176,15 @@ typedef struct {
   int32_t kv_dtype;     /* QB_BF16 or QB_E4M3 */
   int32_t max_segments; /* 3 */
   int32_t quilt_factor; /* must be 1 */
-  int32_t packed_qkv;   /* must be 1 */
+  int32_t packed_qkv;   /* 1: qb_kv_cache_update (packed projection); 0: qb_kv_cache_update_kv (separate K, V) */
 } qb_kv_params;
 
 int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
                            int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p, void* stream);
+/* The same with K and V as tensors of their own, head-major [Hk * tpf, 64] bf16 each (the reference's
+ * packed_qkv=False layout, src/quark/kernels/kv_cache_update/reference.py:183-186); p->packed_qkv must be 0. */
+int32_t qb_kv_cache_update_kv(const void* K, const void* V, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
+                              int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p, void* stream);
 
 /* head_rmsnorm + value_residual_packed + kv_cache_update in one pass over the packed QKV projection
  * (ref: the three calls of TransformerBlock.forward, src/quark/models/waypoint_15.py:398-407).
@@ -225,7 +229,8 @@ typedef struct {
   int32_t kv_dtype;      /* QB_BF16 or QB_E4M3 */
   int32_t compute_dtype; /* QB_BF16 or QB_E4M3 */
   int32_t max_segments;  /* 3 */
-  int32_t packed_qkv;    /* must be 1 */
+  int32_t packed_qkv;    /* 1: qkv is the packed projection, out is [tpf, Hq * 64]; 0: qkv is Q alone, head-major
+                          * [Hq * tpf, 64], and so is out (src/quark/kernels/owl_attn/reference.py:62-69, :106-110) */
   int32_t quilt_factor;  /* must be 1 */
   int32_t kv_splits;     /* 0 = choose; > 1 splits the keys over CTAs (needs workspace) */
   const float* k_scale;

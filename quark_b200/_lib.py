@@ -109,6 +109,7 @@ SIGNATURES = {
     "qb_quantize_e4m3": (_I, [_P, _P, _Z, _I, _P]),
     "qb_dequantize_e4m3": (_I, [_P, _P, _Z, _P]),
     "qb_kv_cache_update": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
+    "qb_kv_cache_update_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
     "qb_qkv_post": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _F, _P]),
     "qb_gemm_qkv_post": (_I, [_P] * 12 + [C.POINTER(GemmParams), C.POINTER(KvParams), _F, _P, _Z, _P]),
     "qb_rope_table_build": (_I, [_P, _I, _I, _P]),

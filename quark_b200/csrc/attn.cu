@@ -88,7 +88,11 @@ struct AttnArgs {
   const float* k_scale;
   const float* v_scale;
   unsigned int* status;
-  int tpf, qkv_dim, n_q_heads, gqa, capacity, max_segments;
+  int tpf, n_q_heads, gqa, capacity, max_segments;
+  // Q of token t, head h starts at qkv + t * q_row + h * q_head (16-bit words), its output row at out + t * o_row +
+  // h * o_head: the packed projection has q_row = qkv_dim, q_head = 64, o_row = Hq * 64, o_head = 64; the head-major
+  // layout [Hq * tpf, 64] of Q and of the output has 64 and tpf * 64 for both
+  int q_row, q_head, o_row, o_head;
   // Key splits (gridDim.z > 1): CTA z walks its share of the key tiles and leaves (m, row sum, 64 outputs)
   // per query row in `partials`; the CTA that draws the last ticket of a (query tile, head) sums the
   // shares in order of z and writes the output.
@@ -469,7 +473,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
             xy[4 * i] = v.x; xy[4 * i + 1] = v.y; xy[4 * i + 2] = v.z; xy[4 * i + 3] = v.w;
           }
         }
-        const uint4* src = reinterpret_cast<const uint4*>(a.qkv + static_cast<size_t>(t) * a.qkv_dim + qh * 64 + g * 32);
+        const uint4* src = reinterpret_cast<const uint4*>(a.qkv + static_cast<size_t>(t) * a.q_row + static_cast<size_t>(qh) * a.q_head + g * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           const uint4 x = __ldg(src + v);
@@ -668,7 +672,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         const float vs = a.v_scale ? __ldg(a.v_scale + kvh) : 1.0f;
         const float inv = l > 0.f ? vs / l : 0.f;
         const float s0 = a0 * inv, s1 = a1 * inv;
-        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64);
+        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * a.o_row + static_cast<size_t>(qh) * a.o_head);
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           uint32_t w[4];
@@ -681,7 +685,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           }
           dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
-            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
+            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * a.o_row + static_cast<size_t>(qh) * a.o_head + v * 8) =
                 make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
                            pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
           }
@@ -734,7 +738,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       if (writer && good && row_ok) {
         const float vs = a.v_scale ? __ldg(a.v_scale + kvh) : 1.0f;
         const float inv = l > 0.f ? vs / l : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64);
+        uint4* dst = reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * a.o_row + static_cast<size_t>(qh) * a.o_head);
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           uint32_t w[4];
@@ -742,7 +746,7 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(e[8 * v + 2 * q] * inv, e[8 * v + 2 * q + 1] * inv);
           dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           if (a.out_q != nullptr) {  // narrowed from the bf16-rounded values: equals a separate bf16 -> e4m3 cast
-            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * (a.n_q_heads * 64) + qh * 64 + v * 8) =
+            *reinterpret_cast<uint2*>(a.out_q + static_cast<size_t>(t) * a.o_row + static_cast<size_t>(qh) * a.o_head + v * 8) =
                 make_uint2(pack_e4m3x4(bf16lo(w[0]), bf16hi(w[0]), bf16lo(w[1]), bf16hi(w[1])),
                            pack_e4m3x4(bf16lo(w[2]), bf16hi(w[2]), bf16lo(w[3]), bf16hi(w[3])));
           }
@@ -808,7 +812,7 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   QB_REQUIRE(qkv && K_cache && Vt_cache && segments && n_segments && frame_t && out && rope_xy, QB_ERR_INVALID_ARG,
              "owl_attn: NULL pointer");
   QB_REQUIRE(p->quilt_factor == 1, QB_ERR_UNSUPPORTED, "owl_attn: quilt_factor %d is not supported (only 1)", p->quilt_factor);
-  QB_REQUIRE(p->packed_qkv == 1, QB_ERR_UNSUPPORTED, "owl_attn: only the packed-QKV layout is supported");
+  QB_REQUIRE(p->packed_qkv == 0 || p->packed_qkv == 1, QB_ERR_INVALID_ARG, "owl_attn: packed_qkv %d", p->packed_qkv);
   QB_REQUIRE(p->n_kv_heads > 0 && p->gqa_ratio > 0 && p->H_spatial > 0 && p->W_spatial > 0 && p->num_buckets > 0,
              QB_ERR_INVALID_ARG, "owl_attn: sizes must be positive");
   QB_REQUIRE(p->kv_dtype == QB_BF16 || p->kv_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "owl_attn: kv_dtype %d", p->kv_dtype);
@@ -839,7 +843,11 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   a.status = status_word();
   QB_REQUIRE(a.status != nullptr, QB_ERR_CUDA, "owl_attn: device status word unavailable");
   a.tpf = tpf;
-  a.qkv_dim = (Hq + 2 * p->n_kv_heads) * 64;
+  if (p->packed_qkv) {
+    a.q_row = (Hq + 2 * p->n_kv_heads) * 64; a.q_head = 64; a.o_row = Hq * 64; a.o_head = 64;
+  } else {
+    a.q_row = 64; a.q_head = tpf * 64; a.o_row = 64; a.o_head = tpf * 64;
+  }
   a.n_q_heads = Hq; a.gqa = p->gqa_ratio; a.capacity = cap; a.max_segments = p->max_segments;
 
   QB_REQUIRE(p->kv_splits >= 0 && p->kv_splits <= 16, QB_ERR_INVALID_ARG, "owl_attn: kv_splits %d", p->kv_splits);

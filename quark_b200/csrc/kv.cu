@@ -15,7 +15,11 @@ constexpr int kKvThreads = 256;
 constexpr int kVPitch = 72;      // smem row pitch of the V tile in 16-bit words
 
 struct KvArgs {
-  const uint16_t* qkv;
+  // K and V of token t, head h start at k_src / v_src + t * row_stride + h * head_stride (16-bit words): the packed
+  // projection has row_stride = qkv_dim, head_stride = 64; separate [Hk * tpf, 64] tensors have 64 and tpf * 64
+  const uint16_t* k_src;
+  const uint16_t* v_src;
+  size_t row_stride, head_stride;
   const int32_t* frame_t;
   const int32_t* frozen;
   void* K_cache;
@@ -23,7 +27,6 @@ struct KvArgs {
   int32_t* segments;
   int32_t* n_segments;
   const float* rope_xy;
-  int qkv_dim, k_off, v_off;
   int tpf, nb, pd, max_segments;
 };
 
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
   // stage V (raw bf16) for the transpose
   for (int v = threadIdx.x; v < kKvTile * 8; v += kKvThreads) {
     const int tt = v >> 3, c = v & 7;
-    const uint4 x = *reinterpret_cast<const uint4*>(a.qkv + static_cast<size_t>(t0 + tt) * a.qkv_dim + a.v_off + head * 64 + c * 8);
+    const uint4 x = *reinterpret_cast<const uint4*>(a.v_src + static_cast<size_t>(t0 + tt) * a.row_stride + head * a.head_stride + c * 8);
     *reinterpret_cast<uint4*>(&vt[tt * kVPitch + c * 8]) = x;
   }
   __syncthreads();
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
     const int tt = threadIdx.x / kThreadsPerTok;
     const int q = threadIdx.x % kThreadsPerTok;
     const int t = t0 + tt;
-    const uint16_t* src = a.qkv + static_cast<size_t>(t) * a.qkv_dim + a.k_off + head * 64 + q * kPairs * 2;
+    const uint16_t* src = a.k_src + static_cast<size_t>(t) * a.row_stride + head * a.head_stride + q * kPairs * 2;
     float xy[16];
     {
       const float4* r = reinterpret_cast<const float4*>(a.rope_xy + static_cast<size_t>(t) * 16);
@@ -200,14 +203,12 @@ extern "C" int32_t qb_rope_table_build(float* rope_xy, int32_t H_spatial, int32_
   return check_launch("rope_table_build");
 }
 
-extern "C" int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
-                                      int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p,
-                                      void* stream) {
-  QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "kv_cache_update: params are NULL");
-  QB_REQUIRE(qkv && frame_t && frozen && K_cache && Vt_cache && segments && n_segments && rope_xy, QB_ERR_INVALID_ARG,
+static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride, size_t head_stride, const int32_t* frame_t,
+                         const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments, int32_t* n_segments, const float* rope_xy,
+                         const qb_kv_params* p, void* stream) {
+  QB_REQUIRE(k_src && v_src && frame_t && frozen && K_cache && Vt_cache && segments && n_segments && rope_xy, QB_ERR_INVALID_ARG,
              "kv_cache_update: NULL pointer");
   QB_REQUIRE(p->quilt_factor == 1, QB_ERR_UNSUPPORTED, "kv_cache_update: quilt_factor %d is not supported (only 1)", p->quilt_factor);
-  QB_REQUIRE(p->packed_qkv == 1, QB_ERR_UNSUPPORTED, "kv_cache_update: only the packed-QKV layout is supported");
   QB_REQUIRE(p->n_kv_heads > 0 && p->n_q_heads >= 0 && p->H_spatial > 0 && p->W_spatial > 0 && p->num_buckets > 0 &&
                  p->pinned_dilation > 0,
              QB_ERR_INVALID_ARG, "kv_cache_update: sizes must be positive");
@@ -215,17 +216,16 @@ extern "C" int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, c
   QB_REQUIRE(p->max_segments >= 3, QB_ERR_INVALID_ARG, "kv_cache_update: max_segments %d < 3", p->max_segments);
   const int tpf = p->H_spatial * p->W_spatial;
   QB_REQUIRE(tpf % kKvTile == 0, QB_ERR_UNSUPPORTED, "kv_cache_update: H*W = %d must be a multiple of %d", tpf, kKvTile);
-  QB_REQUIRE(aligned16(qkv) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(rope_xy), QB_ERR_ALIGN,
+  QB_REQUIRE(aligned16(k_src) && aligned16(v_src) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(rope_xy), QB_ERR_ALIGN,
              "kv_cache_update: pointers must be 16-byte aligned");
   KvArgs a{};
-  a.qkv = static_cast<const uint16_t*>(qkv);
+  a.k_src = static_cast<const uint16_t*>(k_src);
+  a.v_src = static_cast<const uint16_t*>(v_src);
+  a.row_stride = row_stride; a.head_stride = head_stride;
   a.frame_t = frame_t; a.frozen = frozen;
   a.K_cache = K_cache; a.Vt_cache = Vt_cache;
   a.segments = segments; a.n_segments = n_segments;
   a.rope_xy = rope_xy;
-  a.qkv_dim = (p->n_q_heads + 2 * p->n_kv_heads) * 64;
-  a.k_off = p->n_q_heads * 64;
-  a.v_off = (p->n_q_heads + p->n_kv_heads) * 64;
   a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation; a.max_segments = p->max_segments;
   dim3 grid(tpf / kKvTile, p->n_kv_heads);
   if (p->kv_dtype == QB_E4M3)
@@ -233,4 +233,25 @@ extern "C" int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, c
   else
     kv_append_kernel<false><<<grid, kKvThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("kv_cache_update");
+}
+
+extern "C" int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
+                                      int32_t* segments, int32_t* n_segments, const float* rope_xy, const qb_kv_params* p,
+                                      void* stream) {
+  QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "kv_cache_update: params are NULL");
+  QB_REQUIRE(qkv != nullptr, QB_ERR_INVALID_ARG, "kv_cache_update: NULL pointer");
+  QB_REQUIRE(p->packed_qkv == 1, QB_ERR_INVALID_ARG, "kv_cache_update: separate K and V go through qb_kv_cache_update_kv");
+  const uint16_t* base = static_cast<const uint16_t*>(qkv);
+  return kv_append(base + p->n_q_heads * 64, base + (p->n_q_heads + p->n_kv_heads) * 64,
+                   static_cast<size_t>(p->n_q_heads + 2 * p->n_kv_heads) * 64, 64, frame_t, frozen, K_cache, Vt_cache, segments, n_segments,
+                   rope_xy, p, stream);
+}
+
+extern "C" int32_t qb_kv_cache_update_kv(const void* K, const void* V, const int32_t* frame_t, const int32_t* frozen, void* K_cache,
+                                         void* Vt_cache, int32_t* segments, int32_t* n_segments, const float* rope_xy,
+                                         const qb_kv_params* p, void* stream) {
+  QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "kv_cache_update: params are NULL");
+  QB_REQUIRE(p->packed_qkv == 0, QB_ERR_INVALID_ARG, "kv_cache_update: the packed projection goes through qb_kv_cache_update");
+  const size_t tpf = static_cast<size_t>(p->H_spatial) * p->W_spatial;
+  return kv_append(K, V, 64, tpf * 64, frame_t, frozen, K_cache, Vt_cache, segments, n_segments, rope_xy, p, stream);
 }

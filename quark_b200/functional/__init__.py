@@ -235,20 +235,27 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
                     n_q_heads=0, rope_n_frames=1, quilt_factor=1, quilt_offset=0):  # fmt: skip
     """In-place RoPE + cache append (``src/quark/functional/kv_cache_update.py:187-265``).
 
-    ``K`` is the packed QKV tensor when ``packed_qkv=True`` (``V`` is then ignored, as upstream).
+    ``K`` is the packed QKV tensor when ``packed_qkv=True`` (``V`` is then ignored, as upstream); otherwise ``K`` and
+    ``V`` are head-major ``[B * n_kv_heads * tpf, 64]`` tensors of their own.
     Returns ``(K_cache, Vt_cache, segments, n_segments)``, the very tensors that were passed in.
     """
-    del V, rope_n_frames
+    del rope_n_frames
     tpf = int(H_spatial) * int(W_spatial)
     _quilt_checks("qf.kv_cache_update", tpf, quilt_factor, quilt_offset)
     if B != 1:
         raise NotImplementedError("qf.kv_cache_update: only B=1 is supported (the model is batch 1)")
-    if not packed_qkv:
-        raise NotImplementedError("qf.kv_cache_update: only packed_qkv=True is supported")
     Dh = 64
-    qkv_dim = (n_q_heads + 2 * n_kv_heads) * Dh
-    if K.ndim != 2 or tuple(K.shape) != (B * tpf, qkv_dim):
-        raise ValueError(f"qf.kv_cache_update: packed QKV shape {tuple(K.shape)} != ({B * tpf}, {qkv_dim})")
+    if packed_qkv:
+        qkv_dim = (n_q_heads + 2 * n_kv_heads) * Dh
+        if K.ndim != 2 or tuple(K.shape) != (B * tpf, qkv_dim):
+            raise ValueError(f"qf.kv_cache_update: packed QKV shape {tuple(K.shape)} != ({B * tpf}, {qkv_dim})")
+    else:
+        if K.ndim != 2 or tuple(K.shape) != (B * n_kv_heads * tpf, Dh):
+            raise ValueError(f"qf.kv_cache_update: K shape {tuple(K.shape)} != ({B * n_kv_heads * tpf}, {Dh})")
+        if V is None or tuple(V.shape) != tuple(K.shape):
+            raise ValueError(f"qf.kv_cache_update: V shape {None if V is None else tuple(V.shape)} != K shape {tuple(K.shape)}")
+        if _dt(V) != "bf16":
+            raise TypeError(f"qf.kv_cache_update: V dtype {_dt(V)!r} (expected bf16)")
     if _dt(K) != "bf16":
         raise TypeError(f"qf.kv_cache_update: input dtype {_dt(K)!r} (expected bf16)")
     cap = num_buckets * tpf + tpf
@@ -268,14 +275,13 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
         raise TypeError(f"qf.kv_cache_update: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
     p = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
-        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1,
+        packed_qkv=1 if packed_qkv else 0,
     )  # fmt: skip
-    _lib.check(
-        _lib.load().qb_kv_cache_update(
-            _p(K), _p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments),
-            _p(rope_table(H_spatial, W_spatial)), C.byref(p), _s(),
-        )
-    )  # fmt: skip
+    tail = (_p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(rope_table(H_spatial, W_spatial)),
+            C.byref(p), _s())  # fmt: skip
+    lib = _lib.load()
+    _lib.check(lib.qb_kv_cache_update(_p(K), *tail) if packed_qkv else lib.qb_kv_cache_update_kv(_p(K), _p(V), *tail))
     return K_cache, Vt_cache, segments, n_segments
 
 
@@ -388,12 +394,14 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     _quilt_checks("qf.owl_attn", tpf, quilt_factor, quilt_offset)
     if B != 1:
         raise NotImplementedError("qf.owl_attn: only B=1 is supported (the model is batch 1)")
-    if not packed_qkv:
-        raise NotImplementedError("qf.owl_attn: only packed_qkv=True is supported")
     n_q = n_kv_heads * gqa_ratio
-    Dh = int(Q.shape[1]) // (n_q + 2 * n_kv_heads)
-    if Dh != 64 or int(Q.shape[1]) != (n_q + 2 * n_kv_heads) * 64 or int(Q.shape[0]) != B * tpf:
-        raise ValueError(f"qf.owl_attn: packed QKV shape {tuple(Q.shape)} != ({B * tpf}, {(n_q + 2 * n_kv_heads) * 64})")
+    Dh = 64
+    # packed: Q is the QKV projection [tpf, (Hq + 2 Hk) * 64] and the output is [tpf, Hq * 64]; otherwise Q and the
+    # output are head-major [Hq * tpf, 64] (src/quark/kernels/owl_attn/kernel.py:248-288)
+    q_shape = (B * tpf, (n_q + 2 * n_kv_heads) * 64) if packed_qkv else (B * n_q * tpf, Dh)
+    o_shape = (B * tpf, n_q * Dh) if packed_qkv else (B * n_q * tpf, Dh)
+    if tuple(Q.shape) != q_shape:
+        raise ValueError(f"qf.owl_attn: {'packed QKV' if packed_qkv else 'Q'} shape {tuple(Q.shape)} != {q_shape}")
     cap = num_buckets * tpf + tpf
     if tuple(K_cache.shape) != (B * n_kv_heads * cap, Dh):
         raise ValueError(f"qf.owl_attn: K_cache shape {tuple(K_cache.shape)} != ({B * n_kv_heads * cap}, {Dh})")
@@ -425,9 +433,9 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     if od not in (None, "bf16"):
         raise NotImplementedError(f"qf.owl_attn: out_dtype {od!r} (only bf16)")
     if out is None:
-        out = QuarkTensor.empty(B * tpf, n_q * Dh, dtype="bf16")
+        out = QuarkTensor.empty(*o_shape, dtype="bf16")
     elif out.numel != B * tpf * n_q * Dh or out.dtype != "bf16":
-        raise ValueError(f"qf.owl_attn: out is {out.shape} {out.dtype}, expected ({B * tpf}, {n_q * Dh}) bf16")
+        raise ValueError(f"qf.owl_attn: out is {out.shape} {out.dtype}, expected {o_shape} bf16")
     if out_q is not None and (out_q.dtype != "e4m3" or out_q.numel != out.numel):
         raise ValueError("qf.owl_attn: out_q must be an e4m3 tensor of the output's size")
     if frame_t is None:
@@ -437,7 +445,7 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     p = _lib.AttnParams(
         n_kv_heads=n_kv_heads, gqa_ratio=gqa_ratio, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], compute_dtype=_lib.DTYPE_CODE[cd],
-        max_segments=max_segments, packed_qkv=1, quilt_factor=1, kv_splits=int(kv_splits),
+        max_segments=max_segments, packed_qkv=1 if packed_qkv else 0, quilt_factor=1, kv_splits=int(kv_splits),
         k_scale=k_scale.data_ptr() if k_scale is not None else None,
         v_scale=v_scale.data_ptr() if v_scale is not None else None,
     )  # fmt: skip

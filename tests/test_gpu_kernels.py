@@ -637,3 +637,45 @@ def test_owl_attn_cache_dtype_differs_from_compute_dtype(qb, kv_dt, compute):
     want = ops.owl_attn(qkv, Kx, Vx, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=compute,
                         q_quant="e4m3" if compute == "e4m3" else None)  # fmt: skip
     _attn_check(got, want, f"attn cache={kv_dt} compute={compute}", compute == "e4m3")
+
+
+# --------------------------------------------------------------------------- separate Q / K / V (packed_qkv=False)
+
+
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+def test_separate_q_k_v_layout_equals_packed(qb, kv_dt):
+    """``packed_qkv=False`` (the functional default upstream): Q, K, V and the output are head-major ``[heads * tpf,
+    64]`` tensors (``src/quark/kernels/owl_attn/reference.py:62-69, 106-110``; ``kv_cache_update/reference.py:183-186``).
+    Same bytes in the caches and, after regrouping, the same output bits as the packed call, which the oracle covers."""
+    r = util.rng(57)
+    Hq, Hk, H, W, nb, pd, ft = 4, 2, 16, 8, 4, 1, 6
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, (Hq + 2 * Hk) * 64)), n_q_heads=Hq, n_kv_heads=Hk)
+    heads = lambda a, n: np.ascontiguousarray(a.reshape(tpf, n, 64).transpose(1, 0, 2)).reshape(n * tpf, 64)  # noqa: E731
+    Q, K, V = heads(qkv[:, : Hq * 64], Hq), heads(qkv[:, Hq * 64 : (Hq + Hk) * 64], Hk), heads(qkv[:, (Hq + Hk) * 64 :], Hk)
+
+    def state():
+        z = lambda *s: qb.QuarkTensor.zeros(*s, dtype=kv_dt)  # noqa: E731
+        return dict(Vt_cache=z(Hk * 64, cap), segments=T(qb, np.array([0, 0, nb * tpf, tpf, 0, 0], np.int32)),
+                    n_segments=T(qb, np.array([2], np.int32)), K_cache=z(Hk * cap, 64))  # fmt: skip
+
+    geo = dict(B=1, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd)
+    ftt, frz = T(qb, np.array([ft], np.int32)), T(qb, np.array([0], np.int32))
+    a, b = state(), state()
+    qb.qf.kv_cache_update(T(qb, qkv, "bf16"), None, ftt, frz, **a, packed_qkv=True, n_q_heads=Hq, **geo)
+    qb.qf.kv_cache_update(T(qb, K, "bf16"), T(qb, V, "bf16"), ftt, frz, **b, packed_qkv=False, **geo)
+    for k in ("K_cache", "Vt_cache", "segments", "n_segments"):
+        np.testing.assert_array_equal(a[k].to_numpy(), b[k].to_numpy(), err_msg=k)
+    assert a["K_cache"].to_numpy().any()
+
+    cd = "e4m3" if kv_dt == "e4m3" else None
+    att = dict(gqa_ratio=Hq // Hk, compute_dtype=cd, frame_t=ftt)
+    args = (a["K_cache"], a["Vt_cache"], a["segments"], a["n_segments"], 1, Hk)
+    packed = qb.qf.owl_attn(T(qb, qkv, "bf16"), *args, att["gqa_ratio"], H, W, nb, pd, compute_dtype=cd, packed_qkv=True, frame_t=ftt).to_numpy()
+    sep = qb.qf.owl_attn(T(qb, Q, "bf16"), *args, att["gqa_ratio"], H, W, nb, pd, compute_dtype=cd, frame_t=ftt)  # packed_qkv defaults to False
+    assert tuple(sep.shape) == (Hq * tpf, 64)
+    np.testing.assert_array_equal(sep.to_numpy(), heads(packed, Hq))
+    with pytest.raises(ValueError):
+        qb.qf.owl_attn(T(qb, qkv, "bf16"), *args, att["gqa_ratio"], H, W, nb, pd, compute_dtype=cd, frame_t=ftt)
+    with pytest.raises(ValueError):
+        qb.qf.kv_cache_update(T(qb, K, "bf16"), None, ftt, frz, **b, packed_qkv=False, **geo)
