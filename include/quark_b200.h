@@ -34,7 +34,7 @@ extern "C" {
 typedef enum {
   QB_OK = 0,
   QB_ERR_INVALID_ARG = -1, /* bad shape / NULL pointer / inconsistent sizes */
-  QB_ERR_UNSUPPORTED = -2, /* legal in the reference, not implemented here (e.g. quilt_factor > 1) */
+  QB_ERR_UNSUPPORTED = -2, /* legal in the reference, not implemented here (e.g. b_shuffled weights) */
   QB_ERR_ALIGN = -3,       /* pointer or row pitch not 16-byte aligned */
   QB_ERR_LAUNCH = -4,      /* CUDA reported an error at launch */
   QB_ERR_DEVICE = -5,      /* no CUDA device, or not compute capability 10.0 */
@@ -175,8 +175,10 @@ typedef struct {
   int32_t num_buckets, pinned_dilation;
   int32_t kv_dtype;     /* QB_BF16 or QB_E4M3 */
   int32_t max_segments; /* 3 */
-  int32_t quilt_factor; /* must be 1 */
+  int32_t quilt_factor; /* the cache keeps every quilt_factor-th token of a frame (1: all); capacity, slots and
+                         * segments are then those of H*W / quilt_factor tokens per frame */
   int32_t packed_qkv;   /* 1: qb_kv_cache_update (packed projection); 0: qb_kv_cache_update_kv (separate K, V) */
+  int32_t quilt_offset; /* which residue: cached token i is token quilt_offset + i * quilt_factor */
 } qb_kv_params;
 
 int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
@@ -231,7 +233,7 @@ typedef struct {
   int32_t max_segments;  /* 3 */
   int32_t packed_qkv;    /* 1: qkv is the packed projection, out is [tpf, Hq * 64]; 0: qkv is Q alone, head-major
                           * [Hq * tpf, 64], and so is out (src/quark/kernels/owl_attn/reference.py:62-69, :106-110) */
-  int32_t quilt_factor;  /* must be 1 */
+  int32_t quilt_factor;  /* the caches keep H*W / quilt_factor tokens per frame (1: all): capacity = (nb + 1) * that */
   int32_t kv_splits;     /* 0 = choose; > 1 splits the keys over CTAs (needs workspace) */
   const float* k_scale;
   const float* v_scale;

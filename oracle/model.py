@@ -108,7 +108,7 @@ def out_norm_rows(emb_f32, on_w_f32):
 
 def new_state(cfg, quant: Quant):
     """Zeroed caches and the initial segment table (src/quark/nn/layers.py:879-884)."""
-    tpf = cfg.height * cfg.width
+    tpf = cfg.height * cfg.width // getattr(cfg, "quilt_factor", 1)  # tokens of a frame that a cache keeps
     Dh = cfg.d_model // cfg.n_heads
     carrier = np.uint8 if quant.kv_cache == "fp8" else np.uint16
     st = []
@@ -168,6 +168,9 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         Dh=Dh,
         K_cache=st["K_cache"],
         Vt_cache=st["Vt_cache"],
+        # each layer's cache keeps one residue class of the tokens, taking turns over the layers (waypoint_15.py:311-316)
+        quilt_factor=getattr(cfg, "quilt_factor", 1),
+        quilt_offset=layer % getattr(cfg, "quilt_factor", 1),
         **geo,
     )
     st["segments"][:] = segs

@@ -119,6 +119,8 @@ def kv_cache_update(
     Vt_cache=None,
     max_segments: int = 3,
     reference_quirk: bool = False,
+    quilt_factor: int = 1,
+    quilt_offset: int = 0,
 ):
     """Packed-QKV cache append (src/quark/kernels/kv_cache_update/reference.py:148-251), B = 1.
 
@@ -126,20 +128,24 @@ def kv_cache_update(
     they are updated in place (the read-modify-write the GPU kernel does); when they are
     None fresh zero caches are returned, which is what the reference function models.
     Returns ``(K_cache [Hk*capacity, Dh], Vt_cache [Hk*Dh, capacity], segments, n_segments)``.
+    With ``quilt_factor > 1`` the cache keeps tokens ``quilt_offset::quilt_factor`` of the frame (rotated at their
+    own positions first), and capacity, slots and segments are those of ``tpf / quilt_factor`` tokens per frame
+    (``reference.py:201-235``).
     """
-    tpf = H_spatial * W_spatial
+    tpf_all = H_spatial * W_spatial
+    tpf = tpf_all // quilt_factor  # tokens of a frame that the cache keeps
     Hk = n_kv_heads
     L = num_buckets * tpf
     cap = L + tpf
     x = to_f32(qkv, "bf16")
     k0 = n_q_heads * Dh
     v0 = (n_q_heads + n_kv_heads) * Dh
-    K4 = x[:, k0 : k0 + Hk * Dh].reshape(tpf, Hk, Dh).transpose(1, 0, 2)  # [Hk, tpf, Dh]
-    V4 = x[:, v0 : v0 + Hk * Dh].reshape(tpf, Hk, Dh).transpose(1, 0, 2)
+    K4 = x[:, k0 : k0 + Hk * Dh].reshape(tpf_all, Hk, Dh).transpose(1, 0, 2)  # [Hk, tpf, Dh]
+    V4 = x[:, v0 : v0 + Hk * Dh].reshape(tpf_all, Hk, Dh).transpose(1, 0, 2)
     cos, sin = rope_tables(H_spatial, W_spatial, frame_t, Dh)
     k_rot = apply_rope(K4, cos[None], sin[None])
-    k_c = from_f32(k_rot, kv_dtype, reference_quirk=reference_quirk)
-    v_c = from_f32(np.ascontiguousarray(V4), kv_dtype, reference_quirk=reference_quirk)
+    k_c = from_f32(k_rot, kv_dtype, reference_quirk=reference_quirk)[:, quilt_offset::quilt_factor, :]
+    v_c = from_f32(np.ascontiguousarray(V4), kv_dtype, reference_quirk=reference_quirk)[:, quilt_offset::quilt_factor, :]
 
     carrier = np.uint16 if kv_dtype == "bf16" else np.uint8
     if K_cache is None:

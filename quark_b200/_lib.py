@@ -54,7 +54,7 @@ class KvParams(C.Structure):
         ("H_spatial", C.c_int32), ("W_spatial", C.c_int32),
         ("num_buckets", C.c_int32), ("pinned_dilation", C.c_int32),
         ("kv_dtype", C.c_int32), ("max_segments", C.c_int32),
-        ("quilt_factor", C.c_int32), ("packed_qkv", C.c_int32),
+        ("quilt_factor", C.c_int32), ("packed_qkv", C.c_int32), ("quilt_offset", C.c_int32),
     ]  # fmt: skip
 
 

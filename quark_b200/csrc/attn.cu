@@ -782,7 +782,7 @@ static int attn_key_splits(const qb_attn_params* p) {
   if (p->kv_splits > 0) return p->kv_splits;
   const int tpf = p->H_spatial * p->W_spatial;
   const int items = ((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio;
-  const int tiles = ((p->num_buckets + 1) * tpf + kKeyTile - 1) / kKeyTile;  // at most
+  const int tiles = ((p->num_buckets + 1) * (tpf / (p->quilt_factor > 0 ? p->quilt_factor : 1)) + kKeyTile - 1) / kKeyTile;  // at most
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   int n = sms / (items > 0 ? items : 1);
@@ -811,7 +811,8 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "owl_attn: params are NULL");
   QB_REQUIRE(qkv && K_cache && Vt_cache && segments && n_segments && frame_t && out && rope_xy, QB_ERR_INVALID_ARG,
              "owl_attn: NULL pointer");
-  QB_REQUIRE(p->quilt_factor == 1, QB_ERR_UNSUPPORTED, "owl_attn: quilt_factor %d is not supported (only 1)", p->quilt_factor);
+  QB_REQUIRE(p->quilt_factor >= 1 && (p->H_spatial * p->W_spatial) % p->quilt_factor == 0, QB_ERR_INVALID_ARG,
+             "owl_attn: quilt_factor %d does not divide H*W", p->quilt_factor);
   QB_REQUIRE(p->packed_qkv == 0 || p->packed_qkv == 1, QB_ERR_INVALID_ARG, "owl_attn: packed_qkv %d", p->packed_qkv);
   QB_REQUIRE(p->n_kv_heads > 0 && p->gqa_ratio > 0 && p->H_spatial > 0 && p->W_spatial > 0 && p->num_buckets > 0,
              QB_ERR_INVALID_ARG, "owl_attn: sizes must be positive");
@@ -820,7 +821,9 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
              "owl_attn: compute_dtype must equal kv_dtype (bf16 cache + bf16 MMAs, or e4m3 cache + e4m3 MMAs)");
   QB_REQUIRE(p->max_segments >= 1, QB_ERR_INVALID_ARG, "owl_attn: max_segments %d", p->max_segments);
   const int tpf = p->H_spatial * p->W_spatial;
-  const int cap = (p->num_buckets + 1) * tpf;
+  // a quilted cache keeps tpf / quilt_factor tokens per frame (src/quark/kernels/owl_attn/spec.py:79-93); the queries
+  // are all tpf tokens either way, and the segment table already counts cached rows
+  const int cap = (p->num_buckets + 1) * (tpf / p->quilt_factor);
   QB_REQUIRE(cap % 16 == 0, QB_ERR_UNSUPPORTED, "owl_attn: capacity %d must be a multiple of 16", cap);
   QB_REQUIRE(aligned16(qkv) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(out) && aligned16(out_q) && aligned16(rope_xy), QB_ERR_ALIGN,
              "owl_attn: pointers must be 16-byte aligned");

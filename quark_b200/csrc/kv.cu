@@ -27,6 +27,10 @@ struct KvArgs {
   int32_t* segments;
   int32_t* n_segments;
   const float* rope_xy;
+  // Quilt: the cache keeps every quilt-th token of a frame, cached token i being token qoff + i * quilt; tpf below is
+  // the cached count, so slots, capacity and the segment table are those of a frame of tpf tokens
+  // (src/quark/kernels/kv_cache_update/reference.py:201-207, spec.py:66-76).  quilt = 1, qoff = 0: every token.
+  int quilt, qoff;
   int tpf, nb, pd, max_segments;
 };
 
@@ -72,7 +76,7 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
   // stage V (raw bf16) for the transpose
   for (int v = threadIdx.x; v < kKvTile * 8; v += kKvThreads) {
     const int tt = v >> 3, c = v & 7;
-    const uint4 x = *reinterpret_cast<const uint4*>(a.v_src + static_cast<size_t>(t0 + tt) * a.row_stride + head * a.head_stride + c * 8);
+    const uint4 x = *reinterpret_cast<const uint4*>(a.v_src + static_cast<size_t>(a.qoff + (t0 + tt) * a.quilt) * a.row_stride + head * a.head_stride + c * 8);
     *reinterpret_cast<uint4*>(&vt[tt * kVPitch + c * 8]) = x;
   }
   __syncthreads();
@@ -82,10 +86,11 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
     const int tt = threadIdx.x / kThreadsPerTok;
     const int q = threadIdx.x % kThreadsPerTok;
     const int t = t0 + tt;
-    const uint16_t* src = a.k_src + static_cast<size_t>(t) * a.row_stride + head * a.head_stride + q * kPairs * 2;
+    const int ts = a.qoff + t * a.quilt;  // the token this cache row holds: its position sets the rotation
+    const uint16_t* src = a.k_src + static_cast<size_t>(ts) * a.row_stride + head * a.head_stride + q * kPairs * 2;
     float xy[16];
     {
-      const float4* r = reinterpret_cast<const float4*>(a.rope_xy + static_cast<size_t>(t) * 16);
+      const float4* r = reinterpret_cast<const float4*>(a.rope_xy + static_cast<size_t>(ts) * 16);
       const float4 r0 = __ldg(r), r1 = __ldg(r + 1), r2 = __ldg(r + 2), r3 = __ldg(r + 3);
       xy[0] = r0.x; xy[1] = r0.y; xy[2] = r0.z; xy[3] = r0.w; xy[4] = r1.x; xy[5] = r1.y; xy[6] = r1.z; xy[7] = r1.w;
       xy[8] = r2.x; xy[9] = r2.y; xy[10] = r2.z; xy[11] = r2.w; xy[12] = r3.x; xy[13] = r3.y; xy[14] = r3.z; xy[15] = r3.w;
@@ -208,14 +213,17 @@ static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride
                          const qb_kv_params* p, void* stream) {
   QB_REQUIRE(k_src && v_src && frame_t && frozen && K_cache && Vt_cache && segments && n_segments && rope_xy, QB_ERR_INVALID_ARG,
              "kv_cache_update: NULL pointer");
-  QB_REQUIRE(p->quilt_factor == 1, QB_ERR_UNSUPPORTED, "kv_cache_update: quilt_factor %d is not supported (only 1)", p->quilt_factor);
+  QB_REQUIRE(p->quilt_factor >= 1 && p->quilt_offset >= 0 && p->quilt_offset < p->quilt_factor, QB_ERR_INVALID_ARG,
+             "kv_cache_update: quilt_factor %d, quilt_offset %d", p->quilt_factor, p->quilt_offset);
   QB_REQUIRE(p->n_kv_heads > 0 && p->n_q_heads >= 0 && p->H_spatial > 0 && p->W_spatial > 0 && p->num_buckets > 0 &&
                  p->pinned_dilation > 0,
              QB_ERR_INVALID_ARG, "kv_cache_update: sizes must be positive");
   QB_REQUIRE(p->kv_dtype == QB_BF16 || p->kv_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "kv_cache_update: kv_dtype %d", p->kv_dtype);
   QB_REQUIRE(p->max_segments >= 3, QB_ERR_INVALID_ARG, "kv_cache_update: max_segments %d < 3", p->max_segments);
-  const int tpf = p->H_spatial * p->W_spatial;
-  QB_REQUIRE(tpf % kKvTile == 0, QB_ERR_UNSUPPORTED, "kv_cache_update: H*W = %d must be a multiple of %d", tpf, kKvTile);
+  QB_REQUIRE((p->H_spatial * p->W_spatial) % p->quilt_factor == 0, QB_ERR_INVALID_ARG, "kv_cache_update: H*W = %d is not a multiple of quilt_factor %d",
+             p->H_spatial * p->W_spatial, p->quilt_factor);
+  const int tpf = p->H_spatial * p->W_spatial / p->quilt_factor;  // tokens of a frame that the cache keeps
+  QB_REQUIRE(tpf % kKvTile == 0, QB_ERR_UNSUPPORTED, "kv_cache_update: H*W / quilt_factor = %d must be a multiple of %d", tpf, kKvTile);
   QB_REQUIRE(aligned16(k_src) && aligned16(v_src) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(rope_xy), QB_ERR_ALIGN,
              "kv_cache_update: pointers must be 16-byte aligned");
   KvArgs a{};
@@ -226,6 +234,7 @@ static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride
   a.K_cache = K_cache; a.Vt_cache = Vt_cache;
   a.segments = segments; a.n_segments = n_segments;
   a.rope_xy = rope_xy;
+  a.quilt = p->quilt_factor; a.qoff = p->quilt_offset;
   a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation; a.max_segments = p->max_segments;
   dim3 grid(tpf / kKvTile, p->n_kv_heads);
   if (p->kv_dtype == QB_E4M3)
@@ -252,6 +261,6 @@ extern "C" int32_t qb_kv_cache_update_kv(const void* K, const void* V, const int
                                          const qb_kv_params* p, void* stream) {
   QB_REQUIRE(p != nullptr, QB_ERR_INVALID_ARG, "kv_cache_update: params are NULL");
   QB_REQUIRE(p->packed_qkv == 0, QB_ERR_INVALID_ARG, "kv_cache_update: the packed projection goes through qb_kv_cache_update");
-  const size_t tpf = static_cast<size_t>(p->H_spatial) * p->W_spatial;
+  const size_t tpf = static_cast<size_t>(p->H_spatial) * p->W_spatial;  // K and V hold every token, quilt or not
   return kv_append(K, V, 64, tpf * 64, frame_t, frozen, K_cache, Vt_cache, segments, n_segments, rope_xy, p, stream);
 }

@@ -226,8 +226,6 @@ def _quilt_checks(who: str, tpf: int, quilt_factor: int, quilt_offset: int) -> N
         raise ValueError(f"{who}: quilt_offset must be in [0, quilt_factor); got offset={quilt_offset} factor={quilt_factor}")
     if tpf % quilt_factor != 0:
         raise ValueError(f"{who}: H_spatial*W_spatial={tpf} must be divisible by quilt_factor={quilt_factor}")
-    if quilt_factor != 1:
-        raise NotImplementedError(f"{who}: quilt_factor > 1 is not supported")
 
 
 def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, B, n_kv_heads, H_spatial,
@@ -258,7 +256,7 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
             raise TypeError(f"qf.kv_cache_update: V dtype {_dt(V)!r} (expected bf16)")
     if _dt(K) != "bf16":
         raise TypeError(f"qf.kv_cache_update: input dtype {_dt(K)!r} (expected bf16)")
-    cap = num_buckets * tpf + tpf
+    cap = (num_buckets + 1) * (tpf // quilt_factor)  # a quilted cache keeps tpf / quilt_factor tokens per frame
     if tuple(K_cache.shape) != (B * n_kv_heads * cap, Dh):
         raise ValueError(f"qf.kv_cache_update: K_cache shape {tuple(K_cache.shape)} != ({B * n_kv_heads * cap}, {Dh})")
     if tuple(Vt_cache.shape) != (B * n_kv_heads * Dh, cap):
@@ -275,8 +273,8 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
         raise TypeError(f"qf.kv_cache_update: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
     p = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
-        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1,
-        packed_qkv=1 if packed_qkv else 0,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=quilt_factor,
+        packed_qkv=1 if packed_qkv else 0, quilt_offset=quilt_offset,
     )  # fmt: skip
     tail = (_p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(rope_table(H_spatial, W_spatial)),
             C.byref(p), _s())  # fmt: skip
@@ -402,7 +400,7 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     o_shape = (B * tpf, n_q * Dh) if packed_qkv else (B * n_q * tpf, Dh)
     if tuple(Q.shape) != q_shape:
         raise ValueError(f"qf.owl_attn: {'packed QKV' if packed_qkv else 'Q'} shape {tuple(Q.shape)} != {q_shape}")
-    cap = num_buckets * tpf + tpf
+    cap = (num_buckets + 1) * (tpf // quilt_factor)
     if tuple(K_cache.shape) != (B * n_kv_heads * cap, Dh):
         raise ValueError(f"qf.owl_attn: K_cache shape {tuple(K_cache.shape)} != ({B * n_kv_heads * cap}, {Dh})")
     if tuple(Vt_cache.shape) != (B * n_kv_heads * Dh, cap):
@@ -445,7 +443,7 @@ def owl_attn(Q, K_cache, Vt_cache, segments, n_segments, B, n_kv_heads, gqa_rati
     p = _lib.AttnParams(
         n_kv_heads=n_kv_heads, gqa_ratio=gqa_ratio, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], compute_dtype=_lib.DTYPE_CODE[cd],
-        max_segments=max_segments, packed_qkv=1 if packed_qkv else 0, quilt_factor=1, kv_splits=int(kv_splits),
+        max_segments=max_segments, packed_qkv=1 if packed_qkv else 0, quilt_factor=quilt_factor, kv_splits=int(kv_splits),
         k_scale=k_scale.data_ptr() if k_scale is not None else None,
         v_scale=v_scale.data_ptr() if v_scale is not None else None,
     )  # fmt: skip

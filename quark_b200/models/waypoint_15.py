@@ -3,7 +3,7 @@
 Mirrors ``src/quark/models/waypoint_15.py``: ``QuantConfig`` (``:46-76``), ``Waypoint15Config``
 (``:79-171``), ``TransformerBlock`` (``:259-440``), ``Waypoint15`` (``:448-661``) and
 ``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: MoE,
-quilt, checkpoint download from a hub.  Weights come from ``make_params`` (seeded random init),
+checkpoint download from a hub.  Weights come from ``make_params`` (seeded random init),
 from a local checkpoint (``checkpoint.load_checkpoint``) or any dict of the same layout, through
 ``Waypoint15.load_params``.
 """
@@ -91,8 +91,11 @@ class Waypoint15Config:
     def __post_init__(self):
         if self.ctrl_conditioning and (self.ctrl_conditioning_period < 1 or self.n_buttons < 0):
             raise ValueError("Waypoint15Config: ctrl_conditioning_period must be positive and n_buttons non-negative")
-        if self.moe or self.quilt_factor != 1:
-            raise NotImplementedError("Waypoint15Config: MoE and quilt are not implemented")
+        if self.moe:
+            raise NotImplementedError("Waypoint15Config: MoE is not implemented")
+        q = self.quilt_factor
+        if q < 1 or q & (q - 1) or (self.height * self.width) % q:
+            raise ValueError(f"Waypoint15Config: quilt_factor {q} must be a power of two that divides height * width")
         if self.d_model // self.n_heads != 64:
             raise NotImplementedError("Waypoint15Config: only head_dim 64 is supported")
         if self.tp_world < 1 or not (0 <= self.tp_rank < self.tp_world):
@@ -302,6 +305,10 @@ class TransformerBlock(nn.Module):
         kv_dt = "e4m3" if cfg.quant.kv_cache == "fp8" else "bf16"
         geo = dict(B=1, n_kv_heads=nk, H_spatial=cfg.height, W_spatial=cfg.width, num_buckets=cfg.num_buckets(layer_idx),
                    pinned_dilation=cfg.pinned_dilation(layer_idx), packed_qkv=True)  # fmt: skip
+        if cfg.quilt_factor > 1:
+            # each layer's cache keeps one residue class of the frame's tokens, the classes taking turns over the
+            # layers (src/quark/models/waypoint_15.py:311-316)
+            geo.update(quilt_factor=cfg.quilt_factor, quilt_offset=layer_idx % cfg.quilt_factor)
         self.kv_cache = nn.KVCacheUpdate(n_q_heads=nq, Dh=cfg.Dh, dtype=kv_dt, **geo)
         self.attn = nn.OwlAttn(gqa_ratio=cfg.gqa_ratio, compute_dtype="e4m3" if cfg.quant.attn_compute == "fp8" else None, **geo)
         self.out_proj = nn.Linear(nq * cfg.Dh, d, out_dtype="bf16")
@@ -328,7 +335,8 @@ class TransformerBlock(nn.Module):
 
         h0 = self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)
         use_first = hasattr(self, "v_residual") and qkv_first is not None
-        if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm:
+        quilted = self._cfg.quilt_factor > 1  # the fused passes append every token; a quilted cache takes the plain kernels
+        if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm and not quilted:
             kc = self.kv_cache
             qkv = qf.gemm_qkv_post(
                 h0, self.qkv_proj.weight.data, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
@@ -337,7 +345,7 @@ class TransformerBlock(nn.Module):
                 W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
                 out=nn._cached(self, "qkv_post", (h0.numel // int(h0.shape[-1]), self._cfg.qkv_dim_local), "bf16"),
             )  # fmt: skip
-        elif self._cfg.fuse_qkv_post:
+        elif self._cfg.fuse_qkv_post and not quilted:
             qkv = self.qkv_proj(h0)
             kc = self.kv_cache
             qkv = qf.qkv_post(

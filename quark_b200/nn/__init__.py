@@ -303,8 +303,7 @@ class KVCacheUpdate(Module):
         tpf = H_spatial * W_spatial
         if tpf % quilt_factor != 0:
             raise ValueError(f"KVCacheUpdate: tpf={tpf} not divisible by quilt_factor={quilt_factor}")
-        if quilt_factor != 1:
-            raise NotImplementedError("KVCacheUpdate: quilt_factor > 1 is not supported")
+        tpf //= quilt_factor  # tokens of a frame that the cache keeps (src/quark/kernels/kv_cache_update/spec.py:66-76)
         L = num_buckets * tpf
         cap = L + tpf
         self.K_cache = QuarkTensor.zeros(B * n_kv_heads * cap, Dh, dtype=dtype)

@@ -57,7 +57,11 @@ def test_argument_validation_needs_no_gpu():
     kp = _lib.KvParams(n_q_heads=4, n_kv_heads=2, H_spatial=8, W_spatial=8, num_buckets=4, pinned_dilation=1, kv_dtype=0,
                        max_segments=3, quilt_factor=2, packed_qkv=1)  # fmt: skip
     one = C.c_void_p(16)
-    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -2  # quilt unsupported
+    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -2  # 8 * 8 / 2 = 32 cached tokens < one tile of 64
+    kp.quilt_offset = 2
+    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -1  # offset outside [0, quilt_factor)
+    kp.quilt_offset, kp.packed_qkv = 0, 0
+    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -1  # separate K, V have an entry of their own
     ap = _lib.AttnParams(n_kv_heads=2, gqa_ratio=2, H_spatial=8, W_spatial=8, num_buckets=4, pinned_dilation=1, kv_dtype=0,
                          compute_dtype=1, max_segments=3, packed_qkv=1, quilt_factor=1)  # fmt: skip
     assert lib.qb_owl_attn(one, one, one, one, one, one, one, None, one, C.byref(ap), None, 0, None) == -2  # mixed dtypes

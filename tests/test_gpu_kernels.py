@@ -679,3 +679,45 @@ def test_separate_q_k_v_layout_equals_packed(qb, kv_dt):
         qb.qf.owl_attn(T(qb, qkv, "bf16"), *args, att["gqa_ratio"], H, W, nb, pd, compute_dtype=cd, frame_t=ftt)
     with pytest.raises(ValueError):
         qb.qf.kv_cache_update(T(qb, K, "bf16"), None, ftt, frz, **b, packed_qkv=False, **geo)
+
+
+# --------------------------------------------------------------------------- quilt
+
+
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("quilt,qoff,ft", [(2, 1, 3), (4, 2, 9), (2, 0, 6)])
+def test_quilted_cache_append_and_attention(qb, kv_dt, quilt, qoff, ft):
+    """``quilt_factor > 1``: the cache keeps every quilt-th token of a frame (``kv_cache_update/reference.py:201-207``);
+    two appends (one of them a ring write after the wrap) give the oracle's cache bytes and segment table, and
+    attention over the quilted cache (all queries, fewer keys) the oracle's output."""
+    r = util.rng(300 + quilt)
+    Hq, Hk, H, W, nb, pd = 4, 2, 16, 16, 4, 1
+    tpf = H * W
+    tc = tpf // quilt
+    cap = (nb + 1) * tc
+    geo = dict(B=1, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd)
+    Kd, Vd = qb.QuarkTensor.zeros(Hk * cap, 64, dtype=kv_dt), qb.QuarkTensor.zeros(Hk * 64, cap, dtype=kv_dt)
+    segs, nseg = T(qb, np.array([0, 0, nb * tc, tc, 0, 0], np.int32)), T(qb, np.array([2], np.int32))
+    Ko = Vo = None
+    for f in (ft - 1, ft):
+        qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, (Hq + 2 * Hk) * 64)), n_q_heads=Hq, n_kv_heads=Hk)
+        qb.qf.kv_cache_update(T(qb, qkv, "bf16"), None, T(qb, np.array([f], np.int32)), T(qb, np.array([0], np.int32)), Vd, segs, nseg, Kd,
+                              packed_qkv=True, n_q_heads=Hq, quilt_factor=quilt, quilt_offset=qoff, **geo)  # fmt: skip
+        Ko, Vo, so, no = ops.kv_cache_update(qkv, f, 0, n_kv_heads=Hk, n_q_heads=Hq, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd,
+                                             kv_dtype=kv_dt, K_cache=Ko, Vt_cache=Vo, quilt_factor=quilt, quilt_offset=qoff)  # fmt: skip
+    assert Ko.shape == (Hk * cap, 64)
+    np.testing.assert_array_equal(segs.to_numpy(), so)
+    np.testing.assert_array_equal(nseg.to_numpy(), no)
+    np.testing.assert_array_equal(Vd.to_numpy(), Vo)
+    gK, wK = Kd.to_numpy(), Ko
+    if kv_dt == "bf16":
+        assert float(np.abs(f32(gK, "bf16") - f32(wK, "bf16")).max()) <= 2e-2  # rotation in f32, rounded vs truncated
+    else:
+        assert float((gK != wK).mean()) <= 2e-3  # an e4m3 rounding boundary now and then (device vs numpy cos / sin)
+    np.testing.assert_array_equal(gK.any(axis=1), wK.any(axis=1))  # the same cache rows were written
+    cd = "e4m3" if kv_dt == "e4m3" else None
+    got = qb.qf.owl_attn(T(qb, qkv, "bf16"), Kd, Vd, segs, nseg, 1, Hk, Hq // Hk, H, W, nb, pd, compute_dtype=cd, packed_qkv=True,
+                         quilt_factor=quilt, quilt_offset=qoff, frame_t=T(qb, np.array([ft], np.int32))).to_numpy()  # fmt: skip
+    want = ops.owl_attn(qkv, gK, Vd.to_numpy(), so, no, ft, n_kv_heads=Hk, gqa_ratio=Hq // Hk, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                        q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
+    _attn_check(got, want, f"quilt {quilt}/{qoff} {kv_dt}", kv_dt == "e4m3")

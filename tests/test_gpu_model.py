@@ -215,6 +215,40 @@ def test_mixed_quant_session_matches_oracle(qb, linear, kv, attn):
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_quilted_session_matches_oracle(qb, quant):
+    """``quilt_factor = 2``: every layer's cache keeps half of the frame's tokens, even layers the even ones and
+    odd layers the odd ones (``waypoint_15.py:311-316``); frames appended and generated (graph replay) against
+    the chained oracle, and the caches have half the rows."""
+    from quark_b200.models import make_params
+
+    cfg = small_cfg(qb, quant, height=16, width=8, quilt_factor=2)
+    params = make_params(cfg, seed=12, weight_std=0.08)
+    eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params)
+    op, oq = oracle_params(params, quant), oquant(quant)
+    r = util.rng(33)
+    lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(3)]
+    noises = [r.standard_normal((1, cfg.latent_numel)).astype(np.float32) for _ in range(2)]
+    with codec.bf16_rounding("rne"):
+        state, ft, want = omodel.new_state(cfg, oq), 0, []
+        for lat in lats:
+            omodel.nfe_forward(cfg, op, state, lat, len(cfg.scheduler_sigmas) - 1, ft, frozen=False, quant=oq)
+            ft += 1
+        for nz in noises:
+            w, ft = omodel.gen_frame(cfg, op, state, codec.f32_to_bf16(nz), ft, quant=oq)
+            want.append(w)
+    for lat in lats:
+        eng.append_frame(lat)
+    for li, blk in enumerate(eng.model.blocks):
+        nb = cfg.num_buckets(li)
+        assert tuple(blk.kv_cache.K_cache.shape) == (cfg.n_kv_heads * (nb + 1) * 64, 64)
+    for k, nz in enumerate(noises):
+        got = eng.gen_frame(noise=nz)
+        compare(got.reshape(-1), want[k].reshape(-1), f"quilted gen_frame {k} {quant}", quant == "fp8")
+    for li, blk in enumerate(eng.model.blocks):
+        np.testing.assert_array_equal(blk.kv_cache.segments.to_numpy(), state[li]["segments"], err_msg=f"layer {li}")
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
 def test_engine_from_checkpoint_directory_matches_oracle(qb, quant, tmp_path):
     """``Engine(model_uri)`` on a directory with ``config.yaml`` and an upstream-layout ``model.safetensors``
     (split Q/K/V, shared and separate cond heads, 4-D patch weights, both controller layouts): the session
