@@ -76,13 +76,14 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
   // stage V (raw bf16) for the transpose
   for (int v = threadIdx.x; v < kKvTile * 8; v += kKvThreads) {
     const int tt = v >> 3, c = v & 7;
+    if (t0 + tt >= a.tpf) continue;  // a cached frame shorter than the tile (a multiple of 16 tokens)
     const uint4 x = *reinterpret_cast<const uint4*>(a.v_src + static_cast<size_t>(a.qoff + (t0 + tt) * a.quilt) * a.row_stride + head * a.head_stride + c * 8);
     *reinterpret_cast<uint4*>(&vt[tt * kVPitch + c * 8]) = x;
   }
   __syncthreads();
 
   // ---- K: rotate, narrow, store rows
-  if (threadIdx.x < kKvTile * kThreadsPerTok) {
+  if (threadIdx.x < kKvTile * kThreadsPerTok && t0 + threadIdx.x / kThreadsPerTok < a.tpf) {
     const int tt = threadIdx.x / kThreadsPerTok;
     const int q = threadIdx.x % kThreadsPerTok;
     const int t = t0 + tt;
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
   for (int v = threadIdx.x; v < 64 * kVecPerCh; v += kKvThreads) {
     const int d = v / kVecPerCh, j = v % kVecPerCh;
     const int tt = j * kTokPerVec;
+    if (t0 + tt >= a.tpf) continue;
     uint4 o;
     if (kFp8) {
       uint32_t w[4];
@@ -223,7 +225,7 @@ static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride
   QB_REQUIRE((p->H_spatial * p->W_spatial) % p->quilt_factor == 0, QB_ERR_INVALID_ARG, "kv_cache_update: H*W = %d is not a multiple of quilt_factor %d",
              p->H_spatial * p->W_spatial, p->quilt_factor);
   const int tpf = p->H_spatial * p->W_spatial / p->quilt_factor;  // tokens of a frame that the cache keeps
-  QB_REQUIRE(tpf % kKvTile == 0, QB_ERR_UNSUPPORTED, "kv_cache_update: H*W / quilt_factor = %d must be a multiple of %d", tpf, kKvTile);
+  QB_REQUIRE(tpf % 16 == 0, QB_ERR_UNSUPPORTED, "kv_cache_update: H*W / quilt_factor = %d must be a multiple of 16 (one 16-byte vector of V^T)", tpf);
   QB_REQUIRE(aligned16(k_src) && aligned16(v_src) && aligned16(K_cache) && aligned16(Vt_cache) && aligned16(rope_xy), QB_ERR_ALIGN,
              "kv_cache_update: pointers must be 16-byte aligned");
   KvArgs a{};
@@ -236,7 +238,7 @@ static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride
   a.rope_xy = rope_xy;
   a.quilt = p->quilt_factor; a.qoff = p->quilt_offset;
   a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation; a.max_segments = p->max_segments;
-  dim3 grid(tpf / kKvTile, p->n_kv_heads);
+  dim3 grid((tpf + kKvTile - 1) / kKvTile, p->n_kv_heads);
   if (p->kv_dtype == QB_E4M3)
     kv_append_kernel<true><<<grid, kKvThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   else

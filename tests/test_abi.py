@@ -54,11 +54,14 @@ def test_argument_validation_needs_no_gpu():
     p.compute_dtype = 1
     assert lib.qb_gemm(None, None, None, None, None, None, C.byref(p), None, 0, None) == -1  # e4m3 compute needs e4m3 B
     assert lib.qb_gemm_workspace_bytes(C.byref(p)) == 0
+    # every case below fails a check on the host: nothing may reach a launch with these made-up pointers
     kp = _lib.KvParams(n_q_heads=4, n_kv_heads=2, H_spatial=8, W_spatial=8, num_buckets=4, pinned_dilation=1, kv_dtype=0,
-                       max_segments=3, quilt_factor=2, packed_qkv=1)  # fmt: skip
+                       max_segments=3, quilt_factor=3, packed_qkv=1)  # fmt: skip
     one = C.c_void_p(16)
-    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -2  # 8 * 8 / 2 = 32 cached tokens < one tile of 64
-    kp.quilt_offset = 2
+    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -1  # 64 tokens do not split in 3
+    kp.quilt_factor = 8
+    assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -2  # 8 cached tokens: less than one 16-byte vector of V^T
+    kp.quilt_factor, kp.quilt_offset = 2, 2
     assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -1  # offset outside [0, quilt_factor)
     kp.quilt_offset, kp.packed_qkv = 0, 0
     assert lib.qb_kv_cache_update(one, one, one, one, one, one, one, one, C.byref(kp), None) == -1  # separate K, V have an entry of their own

@@ -171,8 +171,8 @@ def test_rope_table_device_builder_matches_numpy(qb):
 # --------------------------------------------------------------------------- KV-cache append
 
 
-def _kv_run(qb, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt, prefill=None):
-    tpf, cap = H * W, (nb + 1) * H * W
+def _kv_run(qb, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt, prefill=None, quilt=1, qoff=0):
+    tpf, cap = H * W, (nb + 1) * (H * W // quilt)
     carrier = np.uint16 if kv_dt == "bf16" else np.uint8
     K0 = np.zeros((Hk * cap, 64), carrier) if prefill is None else np.full((Hk * cap, 64), prefill, carrier)
     V0 = np.zeros((Hk * 64, cap), carrier) if prefill is None else np.full((Hk * 64, cap), prefill, carrier)
@@ -181,15 +181,17 @@ def _kv_run(qb, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt, prefill=None):
     out = qb.qf.kv_cache_update(
         T(qb, qkv, "bf16"), None, T(qb, np.array([ft], np.int32)), T(qb, np.array([frozen], np.int32)), Vc, segs, nseg, Kc,
         B=1, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, packed_qkv=True, n_q_heads=Hq,
+        quilt_factor=quilt, quilt_offset=qoff,
     )  # fmt: skip
     assert out[0] is Kc and out[1] is Vc
     return Kc.to_numpy(), Vc.to_numpy(), segs.to_numpy(), nseg.to_numpy()
 
 
-def _check_kv(K, Vt, segs, nseg, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt):
+def _check_kv(K, Vt, segs, nseg, qkv, ft, frozen, *, Hq, Hk, H, W, nb, pd, kv_dt, quilt=1, qoff=0):
     wK, wV, wsegs, wn = ops.kv_cache_update(
-        qkv, ft, frozen, n_kv_heads=Hk, n_q_heads=Hq, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, kv_dtype=kv_dt
-    )
+        qkv, ft, frozen, n_kv_heads=Hk, n_q_heads=Hq, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd, kv_dtype=kv_dt,
+        quilt_factor=quilt, quilt_offset=qoff,
+    )  # fmt: skip
     np.testing.assert_array_equal(segs, wsegs)
     np.testing.assert_array_equal(nseg, wn)
     np.testing.assert_array_equal(Vt != 0, wV != 0)  # slot indexing: exactly the same cells written
@@ -721,3 +723,63 @@ def test_quilted_cache_append_and_attention(qb, kv_dt, quilt, qoff, ft):
     want = ops.owl_attn(qkv, gK, Vd.to_numpy(), so, no, ft, n_kv_heads=Hk, gqa_ratio=Hq // Hk, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
                         q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
     _attn_check(got, want, f"quilt {quilt}/{qoff} {kv_dt}", kv_dt == "e4m3")
+
+
+# --------------------------------------------------------------------------- the reference's own problem lists
+
+# name, n_kv_heads, H, W, num_buckets, pinned_dilation, kv dtype, quilt_factor, quilt_offset: the thirteen
+# configurations of src/quark/kernels/kv_cache_update/problems.py:17-159 (B = 1, head_dim 64)
+KV_PROBLEMS = [
+    ("smoke_dense", 2, 8, 8, 4, 1, "bf16", 1, 0),
+    ("owl_360p_dense", 16, 16, 8, 16, 1, "bf16", 1, 0),
+    ("owl_360p_dilated", 16, 16, 8, 16, 8, "bf16", 1, 0),
+    ("owl_720p_dense", 16, 32, 16, 16, 1, "bf16", 1, 0),
+    ("owl_720p_dilated", 16, 32, 16, 16, 8, "bf16", 1, 0),
+    ("owl_360p_dense_fp8", 16, 16, 8, 16, 1, "e4m3", 1, 0),
+    ("owl_360p_dilated_fp8", 16, 16, 8, 16, 8, "e4m3", 1, 0),
+    ("owl_720p_dense_fp8", 16, 32, 16, 16, 1, "e4m3", 1, 0),
+    ("owl_720p_dilated_fp8", 16, 32, 16, 16, 8, "e4m3", 1, 0),
+    ("quilt2_off0_360p_dense", 16, 16, 8, 16, 1, "bf16", 2, 0),
+    ("quilt2_off1_360p_dense", 16, 16, 8, 16, 1, "bf16", 2, 1),
+    ("quilt2_off0_360p_dense_fp8", 16, 16, 8, 16, 1, "e4m3", 2, 0),
+    ("quilt4_off2_360p_dense_fp8", 16, 16, 8, 16, 1, "e4m3", 4, 2),
+]
+
+
+@pytest.mark.parametrize("name,Hk,H,W,nb,pd,kv_dt,quilt,qoff", KV_PROBLEMS, ids=[p[0] for p in KV_PROBLEMS])
+def test_kv_cache_update_reference_problem_list(qb, name, Hk, H, W, nb, pd, kv_dt, quilt, qoff):
+    """Every configuration the reference sweeps this kernel over (its ``make fuzz``), each on a ring-write frame
+    after the wrap and on a frozen frame, against the oracle: segment table and V bytes exact, K as in ``_check_kv``."""
+    r = util.rng(len(name) * 31 + H)
+    Hq = 2 * Hk
+    geo = dict(Hq=Hq, Hk=Hk, H=H, W=W, nb=nb, pd=pd, kv_dt=kv_dt, quilt=quilt, qoff=qoff)
+    qkv = ops.head_rmsnorm(bf16_randn(r, (H * W, (Hq + 2 * Hk) * 64)), n_q_heads=Hq, n_kv_heads=Hk)
+    for ft, frozen in ((pd * (nb + 3), 0), (pd * (nb + 3), 1)):
+        K, Vt, segs, nseg = _kv_run(qb, qkv, ft, frozen, **geo)
+        _check_kv(K, Vt, segs, nseg, qkv, ft, frozen, **geo)
+        assert K.shape[0] == Hk * (nb + 1) * (H * W // quilt)
+
+
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("quilt,qoff", [(2, 0), (2, 1), (4, 2)])
+def test_owl_attn_reference_quilt_problems(qb, kv_dt, quilt, qoff):
+    """The three quilted configurations of ``src/quark/kernels/owl_attn/problems.py:26-90`` (360p, 16 buckets, 16 KV
+    heads, GQA 2); its dense and dilated 360p / 720p ones are ``test_owl_attn_model_geometry``.  The cache holds
+    128 / quilt tokens per frame, so key tiles end inside a tile and segments start off tile boundaries."""
+    r = util.rng(500 + quilt + qoff)
+    Hk, gqa, H, W, nb, pd, ft = 16, 2, 16, 8, 16, 1, 21
+    tpf = H * W
+    cap = (nb + 1) * (tpf // quilt)
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 4096)), n_q_heads=32, n_kv_heads=16)
+    if kv_dt == "bf16":
+        Kc, Vc = bf16_randn(r, (Hk * cap, 64)), bf16_randn(r, (Hk * 64, cap))
+    else:
+        Kc, Vc = e4m3_randn(r, (Hk * cap, 64)), e4m3_randn(r, (Hk * 64, cap))
+    segs, n = ops.compute_segments(ft, nb, tpf // quilt, pd)
+    assert n == 3
+    got = qb.qf.owl_attn(T(qb, qkv, "bf16"), T(qb, Kc, kv_dt), T(qb, Vc, kv_dt), T(qb, np.asarray(segs, np.int32)), T(qb, np.array([n], np.int32)),
+                         1, Hk, gqa, H, W, nb, pd, compute_dtype="e4m3" if kv_dt == "e4m3" else None, packed_qkv=True, quilt_factor=quilt,
+                         quilt_offset=qoff, frame_t=T(qb, np.array([ft], np.int32))).to_numpy()  # fmt: skip
+    want = ops.owl_attn(qkv, Kc, Vc, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                        q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
+    _attn_check(got, want, f"attn quilt {quilt}/{qoff} {kv_dt}", kv_dt == "e4m3")
