@@ -286,6 +286,14 @@ int32_t qb_euler_step(const void* X, const void* V, const float* dsig, void* out
  * counter_offset). */
 int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,
                  void* stream);
+/* Mixture-of-experts routing ("correct" mode: every token goes to its own top_k experts, no capacity bound):
+ * weights[e][m] (f32, [E, M]) = softmax over token m's top_k logits at its top_k experts, 0 elsewhere; ties go to
+ * the lower expert index.  logits bf16 [M, E], E <= 32.  ref: src/quark/kernels/moe_router_correct/reference.py:38-49.
+ * The reference's slot tables (token_ids, offsets, work list) have no counterpart: the experts run dense here. */
+int32_t qb_moe_route(const void* logits, float* weights, int32_t M, int32_t E, int32_t top_k, void* stream);
+/* out[m, :] (bf16 [M, D]) = sum over experts with weights[e][m] != 0 of weights[e][m] * partials[e][m][:] (f32
+ * [E, M, D]), summed in f32, narrowed once.  ref: src/quark/kernels/moe_reduce/reference.py:16-33. */
+int32_t qb_moe_combine(const float* partials, const float* weights, void* out, int32_t M, int32_t D, int32_t E, void* stream);
 /* counter[0] += 1.  ref: src/quark/kernels/increment/kernel.py:1-7. */
 int32_t qb_increment(int32_t* counter, void* stream);
 /* latent [1, C*H*W] -> tokens [(H/ph)*(W/pw), d_model] = patches . W[d_model, C*ph*pw]^T.

@@ -203,6 +203,11 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         x = ops.add(x, ops.mlp_fusion(ops.rmsnorm(x), ops.rmsnorm(ctrl_emb), blk["ctrl.fc1_x.weight"], blk["ctrl.fc1_c.weight"],
                                       blk["ctrl.fc2.weight"]))  # fmt: skip
     h = ops.ada_rmsnorm(x, s1, b1)
+    if getattr(cfg, "moe", False):
+        fp8 = getattr(quant, "moe", quant.linear) == "fp8"
+        y = ops.moe(h, blk["moe.router.weight"], blk["moe.expert_in"], blk["moe.expert_out"], top_k=cfg.moe_top_k, fp8=fp8,
+                    a_quant="e4m3" if (fp8 and quant.mirror_operand_rounding) else None)  # fmt: skip
+        return ops.ada_gate_residual(x, y, g1), qkv
     h = ops.silu(_linear(h, blk["fc1.weight"], quant))
     if reduce is None:
         x = _linear(h, blk["fc2.weight"], quant, gate=g1, residual=x)

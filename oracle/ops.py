@@ -455,3 +455,45 @@ def randn(n: int, counter_offset: int = 0, *, seed0: int = 0xDEADBEEF, seed1: in
     # [block, g, t, k] -> position block * 2048 + (4 g + k) * 128 + t
     flat = z.transpose(0, 1, 3, 2).reshape(-1)[:n]
     return from_f32(flat, "bf16") if dtype == "bf16" else flat
+
+
+# ---------------------------------------------------------------------------
+# mixture of experts ("correct" routing)
+# ---------------------------------------------------------------------------
+
+
+def moe_route(logits, top_k: int) -> np.ndarray:
+    """Dense routing weights ``[E, M]`` f32: per token a softmax over its ``top_k`` largest logits at those experts,
+    zero elsewhere; ties to the lower index (``src/quark/kernels/moe_router_correct/reference.py:38-49``)."""
+    L = to_f32(logits, "bf16")
+    M, E = L.shape
+    order = np.argsort(-L, axis=1, kind="stable")[:, :top_k]
+    score = np.take_along_axis(L, order, axis=1)
+    ex = np.exp(score - score.max(axis=-1, keepdims=True))
+    w = ex / ex.sum(axis=-1, keepdims=True)
+    dense = np.zeros((E, M), np.float32)
+    for k in range(top_k):
+        dense[order[:, k], np.arange(M)] = w[:, k]
+    return dense
+
+
+def moe(x, router_w, expert_in, expert_out, *, top_k: int, fp8: bool = False, a_quant: str | None = None):
+    """``out[m] = sum_k w_k * W_out[e_k] silu(W_in[e_k] x_m)`` with the reference's rounding points
+    (``src/quark/nn/moe.py:252-363``): bf16 router logits, bf16 hidden activations, f32 per-expert outputs, one
+    narrowing to bf16 after the weighted sum (``kernels/moe_reduce/reference.py:16-33``).  ``router_w [E, D]`` bf16,
+    ``expert_in [E * H, D]``, ``expert_out [E * D, H]`` (bf16, or e4m3 with ``fp8``)."""
+    E = router_w.shape[0]
+    D = router_w.shape[1]
+    H = expert_in.shape[0] // E
+    wd = "e4m3" if fp8 else "bf16"
+    weights = moe_route(gemm(x, router_w), top_k)
+    xf = to_f32(x, "bf16")
+    acc = np.zeros((xf.shape[0], D), np.float32)
+    for e in range(E):
+        sel = weights[e] != 0
+        if not sel.any():
+            continue
+        h = gemm(x, expert_in[e * H : (e + 1) * H], b_dtype=wd, a_quant=a_quant, activation="silu")
+        y = gemm(h, expert_out[e * D : (e + 1) * D], b_dtype=wd, a_quant=a_quant, return_f32=True)
+        acc[sel] += weights[e][sel, None] * y[sel]
+    return from_f32(acc, "bf16")

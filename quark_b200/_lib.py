@@ -124,6 +124,8 @@ SIGNATURES = {
     "qb_silu": (_I, [_P, _P, _P, _Z, _P]),
     "qb_euler_step": (_I, [_P, _P, _P, _P, _Z, _P]),
     "qb_randn": (_I, [_P, _P, _Z, _I, _U, _U, _U, _P]),
+    "qb_moe_route": (_I, [_P, _P, _I, _I, _I, _P]),
+    "qb_moe_combine": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "qb_increment": (_I, [_P, _P]),
     "qb_patchify": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "qb_unpatchify": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),

@@ -321,6 +321,58 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
   }
 }
 
+// ---------------------------------------------------------------- mixture of experts: routing weights, combination
+// Per token: the top_k experts by logit (ties to the lower index, like a stable descending sort), a softmax over
+// those top_k logits, written as a dense [E][M] f32 table that is zero for the experts a token does not use
+// (ref: src/quark/kernels/moe_router_correct/reference.py:38-49, the "correct" routing).
+constexpr int kMoeMaxExperts = 32;
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const uint16_t* __restrict__ logits, float* __restrict__ weights, int M, int E,
+                                                         int top_k) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float l[kMoeMaxExperts];
+  float w[kMoeMaxExperts];
+  for (int e = 0; e < E; ++e) {
+    l[e] = bf16_bits_to_f32(logits[static_cast<size_t>(m) * E + e]);
+    w[e] = 0.f;
+  }
+  unsigned taken = 0;
+  float top = 0.f, sum = 0.f;
+  for (int k = 0; k < top_k; ++k) {
+    int best = -1;
+    for (int e = 0; e < E; ++e)
+      if (!((taken >> e) & 1u) && (best < 0 || l[e] > l[best])) best = e;
+    taken |= 1u << best;
+    if (k == 0) top = l[best];
+    w[best] = expf(l[best] - top);
+    sum += w[best];
+  }
+  for (int e = 0; e < E; ++e) weights[static_cast<size_t>(e) * M + m] = w[e] / sum;
+}
+
+// out[m, :] = bf16( sum over the experts e with weights[e][m] != 0, in order of e, of weights[e][m] * partials[e][m][:] ),
+// the sum in f32 and one narrowing at the end (ref: src/quark/kernels/moe_reduce/reference.py:16-33).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ partials, const float* __restrict__ weights,
+                                                           uint16_t* __restrict__ out, int M, int D, int E) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int m = blockIdx.x;
+  for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int e = 0; e < E; ++e) {
+      const float w = weights[static_cast<size_t>(e) * M + m];
+      if (w == 0.f) continue;  // an expert the token does not use: its partial is never read
+      const float4 y = *reinterpret_cast<const float4*>(partials + (static_cast<size_t>(e) * M + m) * D + d);
+      acc[0] = fmaf(w, y.x, acc[0]); acc[1] = fmaf(w, y.y, acc[1]); acc[2] = fmaf(w, y.z, acc[2]); acc[3] = fmaf(w, y.w, acc[3]);
+    }
+    const uint2 o = make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]));
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(m) * D + d) = o;
+  }
+}
+
 // ---------------------------------------------------------------- randn
 // Standard normals from a counter: Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3")
 // on the counter (group, 0, seed0, seed1) with the key (seed0, seed1), the four words turned into uniforms
@@ -613,6 +665,22 @@ int32_t qb_dequantize_e4m3(const void* X, void* out, size_t n, void* stream) {
   const size_t blocks = (n + 256 * 16 - 1) / (256 * 16);
   return launch_dep("dequantize_e4m3", dequantize_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint8_t*>(X), static_cast<uint16_t*>(out), n);
+}
+
+int32_t qb_moe_route(const void* logits, float* weights, int32_t M, int32_t E, int32_t top_k, void* stream) {
+  QB_REQUIRE(logits && weights, QB_ERR_INVALID_ARG, "moe_route: NULL pointer");
+  QB_REQUIRE(M > 0 && E > 0 && E <= kMoeMaxExperts && top_k > 0 && top_k <= E, QB_ERR_INVALID_ARG, "moe_route: M %d, E %d (at most %d), top_k %d", M, E,
+             kMoeMaxExperts, top_k);
+  return launch_dep("moe_route", moe_route_kernel, dim3((M + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(logits), weights, M, E, top_k);
+}
+
+int32_t qb_moe_combine(const float* partials, const float* weights, void* out, int32_t M, int32_t D, int32_t E, void* stream) {
+  QB_REQUIRE(partials && weights && out, QB_ERR_INVALID_ARG, "moe_combine: NULL pointer");
+  QB_REQUIRE(M > 0 && D > 0 && D % 4 == 0 && E > 0, QB_ERR_INVALID_ARG, "moe_combine: M %d, D %d (a multiple of 4), E %d", M, D, E);
+  QB_REQUIRE(aligned16(partials) && aligned16(out), QB_ERR_ALIGN, "moe_combine: pointers must be 16-byte aligned");
+  return launch_dep("moe_combine", moe_combine_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), partials, weights,
+                    static_cast<uint16_t*>(out), M, D, E);
 }
 
 int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,

@@ -606,6 +606,37 @@ def randn(*, shape, dtype: str = "bf16", counter_offset, out=None, seed0: int = 
     return out
 
 
+def moe_route(logits, *, top_k: int, out=None):
+    """Dense routing weights ``[E, M]`` f32 of the "correct" mixture-of-experts routing: per token a softmax over its
+    ``top_k`` largest logits, zero elsewhere (``src/quark/kernels/moe_router_correct/reference.py:38-49``)."""
+    if _dt(logits) != "bf16" or logits.ndim != 2:
+        raise TypeError("qf.moe_route: logits must be a bf16 [M, E] tensor")
+    M, E = int(logits.shape[0]), int(logits.shape[1])
+    if out is None:
+        out = QuarkTensor.empty(E, M, dtype="f32")
+    elif out.numel != E * M or _dt(out) != "f32":
+        raise ValueError(f"qf.moe_route: out must be f32 [{E}, {M}]")
+    _lib.check(_lib.load().qb_moe_route(_p(logits), _p(out), M, E, int(top_k), _s()))
+    return out
+
+
+def moe_combine(partials, weights, *, out=None):
+    """``out[m] = sum_e weights[e, m] * partials[e * M + m]`` in f32, narrowed to bf16 once
+    (``src/quark/kernels/moe_reduce/reference.py:16-33``).  ``partials`` f32 ``[E * M, D]``, ``weights`` f32 ``[E, M]``."""
+    if _dt(partials) != "f32" or _dt(weights) != "f32":
+        raise TypeError("qf.moe_combine: partials and weights must be f32")
+    E, M = int(weights.shape[0]), int(weights.shape[1])
+    D = int(partials.shape[-1])
+    if partials.numel != E * M * D:
+        raise ValueError(f"qf.moe_combine: partials {partials.shape} for weights {weights.shape}")
+    if out is None:
+        out = QuarkTensor.empty(M, D, dtype="bf16")
+    elif out.numel != M * D or _dt(out) != "bf16":
+        raise ValueError(f"qf.moe_combine: out must be bf16 [{M}, {D}]")
+    _lib.check(_lib.load().qb_moe_combine(_p(partials), _p(weights), _p(out), M, D, E, _s()))
+    return out
+
+
 def increment(counter):
     if _dt(counter) != "s32":
         raise TypeError("qf.increment: counter must be an s32 tensor")

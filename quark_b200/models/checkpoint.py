@@ -118,14 +118,26 @@ def params_from_state_dict(raw: dict, cfg) -> dict:
             mb = _as_f32(need(p + "mlp_cond_head.bias_in"))
             projs = [_as_f32(need(p + f"attn_cond_head.cond_proj.{j}.weight")) for j in range(3)]
             projs += [_as_f32(need(p + f"mlp_cond_head.cond_proj.{j}.weight")) for j in range(3)]
-        if any((p + pre + "router.weight") in raw for pre in ("mlp.", "dit_mlp.")):
-            raise NotImplementedError(f"block {i} is a mixture-of-experts MLP, which is not implemented")
+        # the checkpoint, not the configuration, says whether a block's MLP is dense or a mixture of experts, so that
+        # dense weights under a MoE configuration (or the reverse) fail here (_waypoint_15_io.py:135-168)
+        moe_pre = next((pre for pre in ("mlp.", "dit_mlp.") if p + pre + "router.weight" in raw), None)
+        if (moe_pre is not None) != bool(cfg.moe):
+            raise ValueError(f"block {i}: the checkpoint's MLP is {'a mixture of experts' if moe_pre else 'dense'}, the configuration says moe={cfg.moe}")
         pre = "mlp." if p + "mlp.fc1.weight" in raw else "dit_mlp."
+        mlp = {}
+        if moe_pre is None:
+            mlp = {"fc1.weight": _as_bf16(need(p + pre + "fc1.weight")), "fc2.weight": _as_bf16(need(p + pre + "fc2.weight"))}
+        else:  # [E, H, D] and [E, D, H] flatten to [E * H, D] and [E * D, H]: the same memory
+            E, Hm = cfg.moe_n_experts, cfg.mlp_dim // cfg.moe_top_k
+            mlp = {"moe.router.weight": _as_bf16(raw[p + moe_pre + "router.weight"]),
+                   "moe.expert_in": _as_bf16(need(p + moe_pre + "expert_in")).reshape(E * Hm, d),
+                   "moe.expert_out": _as_bf16(need(p + moe_pre + "expert_out")).reshape(E * d, Hm)}  # fmt: skip
+            if mlp["moe.router.weight"].shape != (E, d):
+                raise ValueError(f"block {i}: router weight is {mlp['moe.router.weight'].shape}, expected {(E, d)}")
         blk = {
             "qkv.weight": np.concatenate([_as_bf16(need(p + f"attn.{n}_proj.weight")) for n in ("q", "k", "v")], axis=0),
             "out.weight": _as_bf16(need(p + "attn.out_proj.weight")),
-            "fc1.weight": _as_bf16(need(p + pre + "fc1.weight")),
-            "fc2.weight": _as_bf16(need(p + pre + "fc2.weight")),
+            **mlp,
             "lamb": float(_as_f32(raw[p + "attn.v_lamb"]).reshape(-1)[0]) if cfg.value_residual and p + "attn.v_lamb" in raw else 0.5,
             "lut": [_cond.block_rows(emb[si], ab.reshape(-1), mb.reshape(-1), projs) for si in range(ns)],
         }

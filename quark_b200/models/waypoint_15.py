@@ -2,8 +2,8 @@
 
 Mirrors ``src/quark/models/waypoint_15.py``: ``QuantConfig`` (``:46-76``), ``Waypoint15Config``
 (``:79-171``), ``TransformerBlock`` (``:259-440``), ``Waypoint15`` (``:448-661``) and
-``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: MoE,
-checkpoint download from a hub.  Weights come from ``make_params`` (seeded random init),
+``GenerateFrame`` (``:664-766``) with the same field and method names.  Not carried over: the
+capacity-bounded MoE routings, checkpoint download from a hub.  Weights come from ``make_params`` (seeded random init),
 from a local checkpoint (``checkpoint.load_checkpoint``) or any dict of the same layout, through
 ``Waypoint15.load_params``.
 """
@@ -73,7 +73,12 @@ class Waypoint15Config:
     n_buttons: int = 256
     quant: QuantConfig = field(default_factory=QuantConfig.all_bf16)
     quilt_factor: int = 1
+    # Mixture-of-experts MLP (src/quark/models/waypoint_15.py:113-130): moe_n_experts experts of width
+    # mlp_dim / moe_top_k, each token using its top moe_top_k.  Only moe_routing = "correct" is implemented.
     moe: bool = False
+    moe_n_experts: int = 8
+    moe_top_k: int = 2
+    moe_routing: str = "correct"
     # Fold `x + gate * y` into the out-proj / fc2 GEMM epilogue (upstream field, default off there).
     fuse_gate_residual: bool = True
     # Fold SiLU into fc1's epilogue (upstream does on its PTX / Metal GEMMs, not on the cuBLAS route).
@@ -92,7 +97,13 @@ class Waypoint15Config:
         if self.ctrl_conditioning and (self.ctrl_conditioning_period < 1 or self.n_buttons < 0):
             raise ValueError("Waypoint15Config: ctrl_conditioning_period must be positive and n_buttons non-negative")
         if self.moe:
-            raise NotImplementedError("Waypoint15Config: MoE is not implemented")
+            if self.moe_routing != "correct":
+                raise NotImplementedError(f"Waypoint15Config: moe_routing {self.moe_routing!r} is not implemented (only 'correct')")
+            if self.tp_world > 1:
+                raise NotImplementedError("Waypoint15Config: MoE with tp_world > 1 is not implemented")
+            # the router is a GEMM with one output column per expert: a multiple of 8 columns
+            if not (1 <= self.moe_top_k <= self.moe_n_experts <= 32) or self.moe_n_experts % 8 or (self.d_model * self.mlp_ratio) % (8 * self.moe_top_k):
+                raise ValueError(f"Waypoint15Config: moe_top_k {self.moe_top_k} of {self.moe_n_experts} experts over an MLP of {self.d_model * self.mlp_ratio}")
         q = self.quilt_factor
         if q < 1 or q & (q - 1) or (self.height * self.width) % q:
             raise ValueError(f"Waypoint15Config: quilt_factor {q} must be a power of two that divides height * width")
@@ -171,7 +182,8 @@ class Waypoint15Config:
 
     _YAML_SCALARS = ("d_model", "n_layers", "n_heads", "n_kv_heads", "mlp_ratio", "channels", "height", "width", "local_window",
                      "global_window", "global_pinned_dilation", "global_attn_period", "global_attn_offset", "value_residual",
-                     "fourier_dim", "n_buttons", "ctrl_conditioning_period", "moe", "quilt_factor")  # fmt: skip
+                     "fourier_dim", "n_buttons", "ctrl_conditioning_period", "moe", "moe_n_experts", "moe_top_k", "moe_routing",
+                     "quilt_factor")  # fmt: skip
 
     @classmethod
     def from_dict(cls, raw: dict, **overrides) -> "Waypoint15Config":
@@ -241,6 +253,12 @@ def make_params(cfg: Waypoint15Config, seed: int = 0, *, weight_std: float = 0.0
             "fc2.weight": _randn_bf16(r, (d, cfg.mlp_dim), weight_std),
             "lamb": 0.5,
         }
+        if cfg.moe:  # a generator of its own; layouts of src/quark/nn/moe.py:35-38
+            rm = np.random.default_rng([seed, i, 11])
+            E, Hm = cfg.moe_n_experts, cfg.mlp_dim // cfg.moe_top_k
+            blk["moe.router.weight"] = _randn_bf16(rm, (E, d), 10 * weight_std)  # spread logits, so routing is not a coin toss
+            blk["moe.expert_in"] = _randn_bf16(rm, (E * Hm, d), weight_std)
+            blk["moe.expert_out"] = _randn_bf16(rm, (E * d, Hm), weight_std)
         ab = _cond.bf16_to_f32(_randn_bf16(r, (d,), weight_std))
         mb = _cond.bf16_to_f32(_randn_bf16(r, (d,), weight_std))
         projs = [_cond.bf16_to_f32(_randn_bf16(r, (d, d), weight_std)) for _ in range(6)]
@@ -322,7 +340,10 @@ class TransformerBlock(nn.Module):
             self.ctrl_emb_norm = nn.RMSNorm()
             self.ctrl_residual = nn.Add()
         self.pre_mlp_norm = nn.AdaRMSNorm()
-        self.mlp = nn.MLP(d, cfg.mlp_dim_local, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
+        if cfg.moe:
+            self.mlp = nn.MoE(cfg.tpf, d, cfg.mlp_dim // cfg.moe_top_k, cfg.moe_n_experts, cfg.moe_top_k, routing=cfg.moe_routing)
+        else:
+            self.mlp = nn.MLP(d, cfg.mlp_dim_local, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
         self.mlp_gate = nn.AdaGateResidual()
 
     def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None):
@@ -370,8 +391,11 @@ class TransformerBlock(nn.Module):
             x = self.attn_gate(x, y, g0)
         if ctrl_emb is not None and hasattr(self, "ctrl_fusion"):
             x = self.ctrl_residual(x, self.ctrl_fusion(self.ctrl_x_norm(x), self.ctrl_emb_norm(ctrl_emb)))
-        h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8)
-        if fuse:
+        moe = self._cfg.moe
+        h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8 and not moe)  # the router reads bf16; MoE narrows for its experts itself
+        if moe:
+            x = self.mlp_gate(x, self.mlp(h), g1)
+        elif fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
         else:
             y = self.mlp(h)
@@ -412,8 +436,13 @@ class Waypoint15(nn.Module):
             p = shard_block_params(self.cfg, p)
             blk.qkv_proj.weight.data = up(p["qkv.weight"])
             blk.out_proj.weight.data = up(p["out.weight"])
-            blk.mlp.fc1.weight.data = up(p["fc1.weight"])
-            blk.mlp.fc2.weight.data = up(p["fc2.weight"])
+            if self.cfg.moe:
+                blk.mlp.router.weight.data = up(p["moe.router.weight"])
+                blk.mlp.expert_in.data = up(p["moe.expert_in"])
+                blk.mlp.expert_out.data = up(p["moe.expert_out"])
+            else:
+                blk.mlp.fc1.weight.data = up(p["fc1.weight"])
+                blk.mlp.fc2.weight.data = up(p["fc2.weight"])
             if hasattr(blk, "ctrl_fusion"):
                 blk.ctrl_fusion.fc1_x.weight.data = up(p["ctrl.fc1_x.weight"])
                 blk.ctrl_fusion.fc1_c.weight.data = up(p["ctrl.fc1_c.weight"])
@@ -427,8 +456,10 @@ class Waypoint15(nn.Module):
         """Quantise linear weights when ``cfg.quant.linear == "fp8"`` (``waypoint_15.py:502-535``)."""
         kwargs.setdefault("fp8", self.cfg.quant.linear == "fp8")
         for blk in self.blocks:
-            for lin in (blk.qkv_proj, blk.out_proj, blk.mlp.fc1, blk.mlp.fc2):
+            for lin in (blk.qkv_proj, blk.out_proj) + (() if self.cfg.moe else (blk.mlp.fc1, blk.mlp.fc2)):
                 lin.prepare(**kwargs)
+            if self.cfg.moe:  # the experts follow quant.moe, independently of the other linears (waypoint_15.py:505-517)
+                blk.mlp.prepare(moe_fp8=self.cfg.quant.moe == "fp8")
         _stream.synchronize()
 
     def encode_ctrl(self, ctrl_input):

@@ -157,6 +157,51 @@ class Linear(Module):
         )  # fmt: skip
 
 
+class MoE(Module):
+    """Top-k mixture of expert MLPs, ``routing="correct"`` of the reference (``src/quark/nn/moe.py:103-363``): every
+    token goes to its own ``top_k`` experts with a softmax over their logits as weights,
+    ``out = sum_k w_k * W_out[e_k] silu(W_in[e_k] x)``.
+
+    Same parameters and layouts as upstream (``router.weight [E, D]``, ``expert_in [E * H, D]``, ``expert_out
+    [E * D, H]``), same rounding points (bf16 logits, bf16 hidden activations, f32 partial outputs, one narrowing after
+    the weighted sum), so the result is the reference's.  The schedule is not: instead of sorting tokens into
+    per-expert slots and running grouped GEMMs over them, every expert runs over every token and the routing
+    weights, zero outside a token's top k, select what counts.  That costs E / top_k times the flops of the routed
+    form; it needs no data-dependent shapes and no new GEMM kernel.  The capacity-bounded ``"balanced"`` and
+    ``"shared_experts"`` routings change which experts a token reaches and are not implemented."""
+
+    def __init__(self, M: int, d_model: int, d_intermediate: int, n_experts: int, top_k: int, *, routing: str = "correct", out_dtype: str = "bf16"):
+        if routing != "correct":
+            raise NotImplementedError(f"MoE: routing {routing!r} is not implemented (only 'correct')")
+        if not (1 <= top_k <= n_experts <= 32) or n_experts % 8:
+            raise ValueError(f"MoE: top_k {top_k} of {n_experts} experts (8, 16, 24 or 32: the router is a GEMM with one column per expert)")
+        self._M, self._D, self._H, self._E, self._K = M, d_model, d_intermediate, n_experts, top_k
+        self.router = Linear(d_model, n_experts, out_dtype="bf16", fp8_skip=True)  # stays bf16: few columns, precision matters
+        self.expert_in = Parameter(QuarkTensor.zeros(n_experts * d_intermediate, d_model, dtype="bf16"))
+        self.expert_out = Parameter(QuarkTensor.zeros(n_experts * d_model, d_intermediate, dtype="bf16"))
+        self._fp8 = False
+
+    def prepare(self, *, fp8: bool = False, moe_fp8: bool | None = None, **kwargs):
+        use = fp8 if moe_fp8 is None else moe_fp8
+        if use and not self._fp8:
+            self.expert_in.data = qf.quantize_e4m3(self.expert_in.data)
+            self.expert_out.data = qf.quantize_e4m3(self.expert_out.data)
+            self._fp8 = True
+
+    def forward(self, x):
+        M, D, H, E = x.numel // int(x.shape[-1]), self._D, self._H, self._E
+        cd = "e4m3" if self._fp8 else None
+        weights = qf.moe_route(self.router(x), top_k=self._K, out=_cached(self, "weights", (E, M), "f32"))
+        xq = qf.quantize_e4m3(x, out=_cached(self, "xq", (M, D), "e4m3")) if self._fp8 else x  # once, not per expert
+        h = _cached(self, "h", (M, H), "bf16")
+        partials = _cached(self, "partials", (E * M, D), "f32")
+        for e in range(E):
+            qf.gemm(xq, self.expert_in.data.rows(e * H, (e + 1) * H), compute_dtype=cd, activation="silu", out=h, b_constant=True)
+            qf.gemm(h, self.expert_out.data.rows(e * D, (e + 1) * D), out_dtype="f32", compute_dtype=cd, out=partials.rows(e * M, (e + 1) * M),
+                    b_constant=True)  # fmt: skip
+        return qf.moe_combine(partials, weights, out=_cached(self, "out", (M, D), "bf16"))
+
+
 class SiLU(Module):
     def forward(self, x, *, emit_e4m3: bool = False):
         out = _cached(self, "out", x.shape, x.dtype)

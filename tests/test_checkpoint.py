@@ -285,9 +285,11 @@ def test_bad_checkpoints_fail_loudly(tmp_path):
     with pytest.raises(KeyError, match="blocks.2.attn.k_proj"):
         ck.params_from_state_dict(missing, cfg)
     moe = dict(sd)
-    moe["transformer.blocks.1.dit_mlp.router.weight"] = ("BF16", np.zeros((4, cfg.d_model), np.uint16))
-    with pytest.raises(NotImplementedError, match="mixture-of-experts"):
+    moe["transformer.blocks.1.dit_mlp.router.weight"] = ("BF16", np.zeros((8, cfg.d_model), np.uint16))
+    with pytest.raises(ValueError, match="mixture of experts"):  # expert weights under a dense configuration
         ck.params_from_state_dict(moe, cfg)
+    with pytest.raises(ValueError, match="dense"):  # and dense weights under a MoE configuration
+        ck.params_from_state_dict(sd, tiny_cfg(moe=True))
     with pytest.raises(ValueError, match="merged QKV"):
         ck.params_from_state_dict(sd, tiny_cfg(n_kv_heads=2))
     wide = dict(sd)
@@ -296,3 +298,26 @@ def test_bad_checkpoints_fail_loudly(tmp_path):
         ck.params_from_state_dict(wide, cfg)
     with pytest.raises(FileNotFoundError):
         ck.load_checkpoint(tmp_path / "nowhere", cfg)
+
+
+def test_moe_blocks_are_remapped(tmp_path):
+    """Expert weights stored 3-D (``[E, H, D]``, ``[E, D, H]``) come out flattened, the router as it is
+    (``_waypoint_15_io.py:139-163``); the dense keys of those blocks are absent."""
+    cfg = tiny_cfg(moe=True, moe_n_experts=8, moe_top_k=2, ctrl_conditioning=False)
+    sd = synth_upstream(cfg)
+    r = np.random.default_rng(3)
+    E, H, d = 8, cfg.mlp_dim // 2, cfg.d_model
+    for i in range(cfg.n_layers):
+        p = f"transformer.blocks.{i}."
+        pre = "mlp." if i % 2 == 0 else "dit_mlp."
+        del sd[p + pre + "fc1.weight"], sd[p + pre + "fc2.weight"]
+        sd[p + pre + "router.weight"] = ("BF16", _cond._bf16(r.standard_normal((E, d), dtype=np.float32)))
+        sd[p + pre + "expert_in"] = ("BF16", _cond._bf16(r.standard_normal((E, H, d), dtype=np.float32)))
+        sd[p + pre + "expert_out"] = ("F32", r.standard_normal((E, d, H), dtype=np.float32))
+    params = ck.params_from_state_dict(sd, cfg)
+    for i, blk in enumerate(params["blocks"]):
+        p = f"transformer.blocks.{i}." + ("mlp." if i % 2 == 0 else "dit_mlp.")
+        assert "fc1.weight" not in blk and blk["moe.expert_in"].shape == (E * H, d) and blk["moe.expert_out"].shape == (E * d, H)
+        np.testing.assert_array_equal(blk["moe.router.weight"], sd[p + "router.weight"][1])
+        np.testing.assert_array_equal(blk["moe.expert_in"].reshape(E, H, d)[3], sd[p + "expert_in"][1][3])
+        np.testing.assert_array_equal(blk["moe.expert_out"].reshape(E, d, H)[5], trunc_bf16(sd[p + "expert_out"][1][5]))

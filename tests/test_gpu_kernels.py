@@ -783,3 +783,31 @@ def test_owl_attn_reference_quilt_problems(qb, kv_dt, quilt, qoff):
     want = ops.owl_attn(qkv, Kc, Vc, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
                         q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
     _attn_check(got, want, f"attn quilt {quilt}/{qoff} {kv_dt}", kv_dt == "e4m3")
+
+
+# --------------------------------------------------------------------------- mixture of experts
+
+
+def test_moe_route_and_combine(qb):
+    r = util.rng(71)
+    M, E, D, K = 200, 8, 64, 2
+    logits = bf16_randn(r, (M, E))
+    logits[5, :] = logits[5, 0]  # all equal: ties go to the lower index
+    logits[6, 3] = logits[6, 7] = 0x4100  # a tie for the first place
+    w = qb.qf.moe_route(T(qb, logits, "bf16"), top_k=K).to_numpy()
+    want = ops.moe_route(logits, K)
+    np.testing.assert_array_equal(w != 0, want != 0)
+    assert float(np.abs(w - want).max()) <= 1e-6
+    assert np.flatnonzero(w[:, 5]).tolist() == [0, 1] and np.flatnonzero(w[:, 6]).tolist() == [3, 7]
+    np.testing.assert_allclose(w.sum(axis=0), 1.0, atol=1e-6)
+    parts = r.standard_normal((E * M, D)).astype(np.float32)
+    parts[(w == 0).reshape(-1)] = np.nan  # what an unused expert computed must never be read
+    got = qb.qf.moe_combine(T(qb, parts), T(qb, w)).to_numpy()
+    p3 = np.nan_to_num(parts).reshape(E, M, D)
+    ref = np.zeros((M, D), np.float32)
+    for e in range(E):
+        ref = ref + w[e][:, None] * p3[e]
+    with codec.bf16_rounding("rne"):
+        wantb = codec.f32_to_bf16(ref)
+    assert np.all(np.abs(got.astype(np.int32) - wantb.astype(np.int32)) <= 1)
+    assert float((got == wantb).mean()) > 0.99
