@@ -464,7 +464,9 @@ def randn(n: int, counter_offset: int = 0, *, seed0: int = 0xDEADBEEF, seed1: in
 
 def moe_route(logits, top_k: int) -> np.ndarray:
     """Dense routing weights ``[E, M]`` f32: per token a softmax over its ``top_k`` largest logits at those experts,
-    zero elsewhere; ties to the lower index (``src/quark/kernels/moe_router_correct/reference.py:38-49``)."""
+    zero elsewhere (``src/quark/kernels/moe_router_correct/reference.py:38-49``).  Equal logits: the lower index wins, as
+    in the reference's kernel, which inserts with a strict ``>`` (``src/quark/kernels/_moe_router_dsl.py:32-66``); its numpy
+    reference leaves ties to numpy's unstable ``argsort``."""
     L = to_f32(logits, "bf16")
     M, E = L.shape
     order = np.argsort(-L, axis=1, kind="stable")[:, :top_k]

@@ -183,3 +183,31 @@ def test_controller_conditioning_ops():
     np.testing.assert_array_equal(ops.add(z["X"], z["Y"]), z["add"])
     assert_bf16_close(ops.mlp_fusion(z["X"], z["cond"], z["Wx"], z["Wc"], z["W2"]), z["mlp_fusion"])
     assert_bf16_close(ops.controller_embedding(z["ctrl_input"], z["We1"], z["We2"]), z["ctrl_emb"])
+
+
+def test_mixture_of_experts_against_the_reference_oracles():
+    """``ops.moe_route`` / ``ops.moe`` (dense form) against the reference's router, in-projection, out-projection and
+    reduction references chained as ``nn.MoE`` launches them with routing "correct" (``tests/golden/make_golden_moe.py``):
+    the same experts for every token, the same weights, and the same output up to the order of the f32 sums.
+
+    One difference is deliberate.  Where a token's k-th and (k+1)-th logits are equal (bf16 logits: it happens), the
+    reference's numpy oracle takes whichever numpy's unstable ``argsort`` puts first, while its kernel inserts with a
+    strict ``>`` and so keeps the lower expert index (``src/quark/kernels/_moe_router_dsl.py:32-66``).  The oracle here
+    follows the kernel; such tokens are compared for their weights' values only."""
+    z = load("moe.npz")
+    M, D, H, E, K = (int(v) for v in z["geometry"])
+    logits = ops.gemm(z["X"], z["Wr"])
+    np.testing.assert_array_equal(logits, z["logits"])
+    w = ops.moe_route(z["logits"], K)
+    assert w.shape == (E, M)
+    srt = -np.sort(-codec.bf16_to_f32(z["logits"]), axis=1)
+    tie = srt[:, K - 1] == srt[:, K]
+    assert 0 < tie.sum() < M // 8  # the fixture has such tokens, and few
+    np.testing.assert_array_equal((w != 0)[:, ~tie], (z["weights"] != 0)[:, ~tie])
+    np.testing.assert_allclose(w[:, ~tie], z["weights"][:, ~tie], rtol=0, atol=1e-7)
+    np.testing.assert_allclose(np.sort(w[:, tie], axis=0), np.sort(z["weights"][:, tie], axis=0), rtol=0, atol=1e-7)
+    for m in np.flatnonzero(tie):  # ties towards the lower index
+        mine, theirs = np.flatnonzero(w[:, m]), np.flatnonzero(z["weights"][:, m])
+        assert mine.sum() <= theirs.sum()
+    got = ops.moe(z["X"], z["Wr"], z["W_in"], z["W_out"], top_k=K)
+    assert_bf16_close(got[~tie], z["out"][~tie])
