@@ -122,9 +122,11 @@ typedef struct {
   const float* w_scale; /* [N]  optional */
 } qb_gemm_params;
 
-/* Bytes of workspace qb_gemm needs for `p` (K-slice partial sums, tile counters, and the
- * e4m3 copy of a bf16 A).  The counter area must be zero before the first use; qb_gemm leaves
- * it zero.  Calls that share a workspace must not overlap on the GPU. */
+/* Bytes of workspace qb_gemm needs for `p` (tile counters, the e4m3 copy of a bf16 A, K-slice
+ * partial sums); 0 when the call touches no scratch memory.  The counters occupy the first 64 KiB
+ * of the workspace whatever the shape, so calls of different shapes may share one workspace; that
+ * area must be zero before the first use, and qb_gemm leaves it zero.  Calls that share a workspace
+ * must not overlap on the GPU. */
 size_t qb_gemm_workspace_bytes(const qb_gemm_params* p);
 int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                 const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream);
@@ -143,7 +145,10 @@ int32_t qb_gemm(const void* A, const void* B, void* C, const void* bias, const v
  * keeps the previous call's contents (the part that must start at zero is cleared on the stream by
  * every call): two calls that overlap on the GPU (different streams, no ordering) race on it.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
- * that first call before any stream capture begins.  Results are bit-identical to qb_gemm. */
+ * that first call before any stream capture begins.  The address is that of the calling thread's
+ * current device (cudaGetDevice), which must be the device `stream` belongs to; the lookup is safe
+ * against two host threads making their first calls at once, and cudaDeviceReset invalidates it for
+ * that device.  A call that is rejected enqueues nothing.  Results are bit-identical to qb_gemm. */
 size_t qb_gemm_static_scratch_capacity(void);
 int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                                const qb_gemm_params* p, void* stream);
@@ -152,6 +157,11 @@ int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void
  * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
  * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */
 int32_t qb_quantize_e4m3(const void* X, void* out, size_t n, int32_t src_dtype, void* stream);
+/* Per-row scaled narrowing of a bf16 matrix X [rows, cols] (a weight [out, in]): scale[r] = max |X[r, :]| / 448
+ * (1 for an all-zero row), out[r, c] = e4m3(X[r, c] * (1 / scale[r])), every step rounded to nearest in f32.
+ * scale_out receives the f32 [rows] dequantisation scales that qb_gemm takes as w_scale.  An extension: the
+ * reference narrows its weights without a scale (ref: src/quark/nn/layers.py:291-304).  cols % 8 == 0. */
+int32_t qb_quantize_e4m3_rows(const void* X, void* out, float* scale_out, int32_t rows, int32_t cols, void* stream);
 /* out[0..n) (bf16) = X[0..n) (e4m3), exact (every e4m3 value is a bf16 value; NaN stays NaN).  The widening half
  * of the reference's cast-on-load for a cache whose dtype differs from the attention's compute dtype
  * (ref: src/quark/kernels/owl_attn/kernel.py:342-348), here as a pass of its own. */
@@ -179,6 +189,11 @@ typedef struct {
                          * segments are then those of H*W / quilt_factor tokens per frame */
   int32_t packed_qkv;   /* 1: qb_kv_cache_update (packed projection); 0: qb_kv_cache_update_kv (separate K, V) */
   int32_t quilt_offset; /* which residue: cached token i is token quilt_offset + i * quilt_factor */
+  /* Optional per-KV-head quantisation scales, f32 [n_kv_heads] each (NULL = 1, the reference's scale-free caches;
+   * an extension, see qb_attn_params): the cache holds narrow(RoPE(K) * (1 / k_scale[h])) and narrow(V * (1 / v_scale[h])),
+   * the reciprocal and the product both rounded to nearest in f32.  qb_owl_attn given the same scales undoes them. */
+  const float* k_scale;
+  const float* v_scale;
 } qb_kv_params;
 
 int32_t qb_kv_cache_update(const void* qkv, const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache,
@@ -202,8 +217,8 @@ int32_t qb_qkv_post(const void* qkv_in, const void* qkv_first, const float* lamb
  * updated, in one launch; the projection's raw output never goes to memory.  Same bytes as qb_gemm
  * followed by qb_qkv_post (ref: qkv_proj then the three calls of TransformerBlock.forward,
  * src/quark/models/waypoint_15.py:396-407).  gp describes the GEMM (M = H*W tokens, N = (n_q_heads +
- * 2 n_kv_heads) * 64, bf16 output, no activation, no scales; tile_n and split_k are overridden: 128-column
- * tiles hold two whole heads, one K slice).  qkv_out and K_cache must be 32-byte aligned.  Workspace as
+ * 2 n_kv_heads) * 64, bf16 output, no activation; a_scale / w_scale as in qb_gemm; tile_n and split_k are
+ * overridden: 128-column tiles hold two whole heads, one K slice).  qkv_out and K_cache must be 32-byte aligned.  Workspace as
  * for qb_gemm with tile_n = 128, split_k = 1. */
 int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out, const void* qkv_first, const float* lamb,
                          const int32_t* frame_t, const int32_t* frozen, void* K_cache, void* Vt_cache, int32_t* segments,
@@ -242,8 +257,8 @@ typedef struct {
 /* Bytes of workspace qb_owl_attn needs for `p`: 0 unless the keys of one (query tile, head) are shared by
  * several CTAs, which is chosen when query tiles x heads would leave most SMs idle (360p; a tensor-parallel
  * rank with few heads) or forced with kv_splits.  The workspace starts with one ticket per (query tile,
- * head), which must be zero before the first use (the kernel leaves them zero), followed by the CTAs'
- * partial results; it must not be the workspace of qb_gemm.  Shares are summed in a fixed order. */
+ * head) in a fixed 16 KiB area (so calls of different geometries may share a workspace), which must be zero
+ * before the first use (the kernel leaves it zero), followed by the CTAs' partial results; it must not be the workspace of qb_gemm.  Shares are summed in a fixed order. */
 size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p);
 int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, const int32_t* segments,
                     const int32_t* n_segments, const int32_t* frame_t, void* out, void* out_q, const float* rope_xy,

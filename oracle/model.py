@@ -131,9 +131,12 @@ def new_state(cfg, quant: Quant):
 # ---------------------------------------------------------------------------
 
 
-def _linear(x, w, quant: Quant, **epi):
+def _linear(x, blk, name, quant: Quant, **epi):
+    """``blk[name]`` is the weight; ``blk[name + ".scale"]`` (optional) its per-output-channel scales (the scaled-e4m3
+    extension: the reference's weights are narrowed without a scale)."""
+    w = blk[name]
     if quant.linear == "fp8":
-        return ops.gemm(x, w, b_dtype="e4m3", a_quant="e4m3" if quant.mirror_operand_rounding else None, **epi)
+        return ops.gemm(x, w, b_dtype="e4m3", a_quant="e4m3" if quant.mirror_operand_rounding else None, w_scale=blk.get(name + ".scale"), **epi)
     return ops.gemm(x, w, **epi)
 
 
@@ -151,8 +154,10 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
     kv_dtype = "e4m3" if quant.kv_cache == "fp8" else "bf16"
     geo = dict(H_spatial=cfg.height, W_spatial=cfg.width)
 
+    # per-KV-head cache scales of the scaled-e4m3 extension (absent: the reference's scale-free caches)
+    ks, vs = (blk.get("k_scale"), blk.get("v_scale")) if quant.kv_cache == "fp8" else (None, None)
     h = ops.ada_rmsnorm(x, s0, b0)
-    qkv = _linear(h, blk["qkv.weight"], quant)
+    qkv = _linear(h, blk, "qkv.weight", quant)
     qkv = ops.head_rmsnorm(qkv, n_q_heads=Hq, n_kv_heads=Hk, Dh=Dh)
     if getattr(cfg, "value_residual", True) and qkv_first is not None:
         qkv = ops.value_residual_packed(qkv, qkv_first, blk["lamb"], v_col_offset=(Hq + Hk) * Dh, v_width=Hk * Dh)
@@ -171,6 +176,8 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         # each layer's cache keeps one residue class of the tokens, taking turns over the layers (waypoint_15.py:311-316)
         quilt_factor=getattr(cfg, "quilt_factor", 1),
         quilt_offset=layer % getattr(cfg, "quilt_factor", 1),
+        k_scale=ks,
+        v_scale=vs,
         **geo,
     )
     st["segments"][:] = segs
@@ -192,12 +199,14 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         kv_dtype=attn_kv_dtype,
         Dh=Dh,
         q_quant="e4m3" if (quant.attn_compute == "fp8" and quant.mirror_operand_rounding) else None,
+        k_scale=ks,
+        v_scale=vs,
         **geo,
     )
     if reduce is None:
-        x = _linear(attn, blk["out.weight"], quant, gate=g0, residual=x)
+        x = _linear(attn, blk, "out.weight", quant, gate=g0, residual=x)
     else:
-        x = ops.ada_gate_residual(x, reduce(_linear(attn, blk["out.weight"], quant)), g0)
+        x = ops.ada_gate_residual(x, reduce(_linear(attn, blk, "out.weight", quant)), g0)
     if ctrl_emb is not None and "ctrl.fc1_x.weight" in blk:
         # controller conditioning on every ctrl_conditioning_period-th block (waypoint_15.py:419-424); bf16 throughout
         x = ops.add(x, ops.mlp_fusion(ops.rmsnorm(x), ops.rmsnorm(ctrl_emb), blk["ctrl.fc1_x.weight"], blk["ctrl.fc1_c.weight"],
@@ -208,11 +217,11 @@ def block_forward(cfg, layer: int, blk: dict, st: dict, x, sigma_idx: int, frame
         y = ops.moe(h, blk["moe.router.weight"], blk["moe.expert_in"], blk["moe.expert_out"], top_k=cfg.moe_top_k, fp8=fp8,
                     a_quant="e4m3" if (fp8 and quant.mirror_operand_rounding) else None)  # fmt: skip
         return ops.ada_gate_residual(x, y, g1), qkv
-    h = ops.silu(_linear(h, blk["fc1.weight"], quant))
+    h = ops.silu(_linear(h, blk, "fc1.weight", quant))
     if reduce is None:
-        x = _linear(h, blk["fc2.weight"], quant, gate=g1, residual=x)
+        x = _linear(h, blk, "fc2.weight", quant, gate=g1, residual=x)
     else:
-        x = ops.ada_gate_residual(x, reduce(_linear(h, blk["fc2.weight"], quant)), g1)
+        x = ops.ada_gate_residual(x, reduce(_linear(h, blk, "fc2.weight", quant)), g1)
     return x, qkv
 
 

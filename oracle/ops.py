@@ -121,8 +121,13 @@ def kv_cache_update(
     reference_quirk: bool = False,
     quilt_factor: int = 1,
     quilt_offset: int = 0,
+    k_scale=None,
+    v_scale=None,
 ):
     """Packed-QKV cache append (src/quark/kernels/kv_cache_update/reference.py:148-251), B = 1.
+
+    ``k_scale`` / ``v_scale`` (f32 ``[n_kv_heads]``, an extension: the reference is scale free) restate the scaled
+    caches: ``narrow(RoPE(K) * (1 / k_scale[h]))`` and ``narrow(V * (1 / v_scale[h]))``, reciprocal and product in f32.
 
     ``qkv`` is ``[tpf, (Hq + 2 Hk) * Dh]`` bf16.  When ``K_cache`` / ``Vt_cache`` are given
     they are updated in place (the read-modify-write the GPU kernel does); when they are
@@ -144,6 +149,11 @@ def kv_cache_update(
     V4 = x[:, v0 : v0 + Hk * Dh].reshape(tpf_all, Hk, Dh).transpose(1, 0, 2)
     cos, sin = rope_tables(H_spatial, W_spatial, frame_t, Dh)
     k_rot = apply_rope(K4, cos[None], sin[None])
+    V4 = np.ascontiguousarray(V4)
+    if k_scale is not None:
+        k_rot = (k_rot.astype(np.float32) * (np.float32(1.0) / np.asarray(k_scale, np.float32))[:, None, None]).astype(np.float32)
+    if v_scale is not None:
+        V4 = (V4 * (np.float32(1.0) / np.asarray(v_scale, np.float32))[:, None, None]).astype(np.float32)
     k_c = from_f32(k_rot, kv_dtype, reference_quirk=reference_quirk)[:, quilt_offset::quilt_factor, :]
     v_c = from_f32(np.ascontiguousarray(V4), kv_dtype, reference_quirk=reference_quirk)[:, quilt_offset::quilt_factor, :]
 
@@ -199,8 +209,13 @@ def owl_attn(
     out_dtype: str = "bf16",
     q_quant: str | None = None,
     return_f32: bool = False,
+    k_scale=None,
+    v_scale=None,
 ):
     """Segment-masked GQA attention with Q-side RoPE (owl_attn/reference.py:47-111), B = 1.
+
+    ``k_scale`` / ``v_scale`` (f32 ``[n_kv_heads]``, an extension) restate attention over scaled caches:
+    ``S = (Q . Kq^T) * k_scale[h] / sqrt(Dh)``, ``O = (P . Vq) * v_scale[h]``.
 
     Same arithmetic as the reference (f32 scores, exact softmax, f32 ``P @ V``), evaluated one
     Q head at a time over the valid key columns only: masked columns contribute
@@ -233,11 +248,13 @@ def owl_attn(
             kh = h // gqa_ratio
             Ks = Kc[kh][idx]  # [S, Dh]
             Vs = Vc[kh][:, idx]  # [Dh, S]
-            s = (Q_rot[h] @ Ks.T) * scale
+            s = (Q_rot[h] @ Ks.T) * (scale if k_scale is None else scale * np.float32(k_scale[kh]))
             m = s.max(axis=-1, keepdims=True)
             ex = np.exp(s - m)
             den = ex.sum(axis=-1, keepdims=True)
             out[h] = (ex / den) @ Vs.T
+            if v_scale is not None:
+                out[h] *= np.float32(v_scale[kh])
     if packed_qkv:
         res = out.transpose(1, 0, 2).reshape(tpf, Hq * Dh)
     else:
@@ -268,8 +285,13 @@ def gemm(
     gate_groups: int = 1,
     a_quant: str | None = None,
     return_f32: bool = False,
+    a_scale=None,
+    w_scale=None,
 ):
-    """``C = A @ B.T`` with the epilogue order bias -> SiLU -> gate*acc + residual -> cast.
+    """``C = A @ B.T`` with the epilogue order (scales ->) bias -> SiLU -> gate*acc + residual -> cast.
+
+    ``a_scale`` (scalar) / ``w_scale`` (f32 ``[N]``), an extension (the reference's e4m3 GEMM is scale free):
+    ``C = (Aq . Wq^T) * (a_scale * w_scale[n])`` before the rest of the epilogue.
 
     Follows ``src/quark/kernels/gemm/reference.py:18-48``.  The reference keeps A in f32 even
     when the kernel computes in e4m3; ``a_quant="e4m3"`` rounds A through e4m3 first so that a
@@ -280,6 +302,10 @@ def gemm(
         a = to_f32(from_f32(a, a_quant), a_quant)
     b = to_f32(B, b_dtype)
     c = a.reshape(-1, a.shape[-1]) @ b.T
+    if a_scale is not None or w_scale is not None:
+        sa = np.float32(1.0 if a_scale is None else np.asarray(a_scale, np.float32).reshape(-1)[0])
+        col = sa if w_scale is None else (sa * np.asarray(w_scale, np.float32)).reshape(1, -1)
+        c = (c * col).astype(np.float32)
     if bias is not None:
         c = c + to_f32(bias, out_dtype).reshape(1, -1)
     if activation == "silu":
@@ -301,6 +327,16 @@ def quantize_e4m3(X, src_dtype: str = "bf16", *, reference_quirk: bool = False):
 # ---------------------------------------------------------------------------
 # norm / elementwise glue
 # ---------------------------------------------------------------------------
+
+
+def quantize_e4m3_rows(X, src_dtype: str = "bf16"):
+    """Per-row scaled narrowing (an extension; no reference counterpart): ``scale[r] = max|X[r]| / 448`` (1 for an
+    all-zero row), ``q[r] = e4m3(X[r] * (1 / scale[r]))``, every step in f32.  Returns ``(q u8, scale f32[rows])``."""
+    x = to_f32(X, src_dtype)
+    amax = np.max(np.abs(x), axis=1).astype(np.float32)
+    scale = np.where(amax > 0, amax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+    inv = (np.float32(1.0) / scale).astype(np.float32)
+    return from_f32((x * inv[:, None]).astype(np.float32), "e4m3"), scale
 
 
 def ada_rmsnorm(X, scale, bias, *, eps: float = 1e-6, activation: str | None = None, dtype: str = "bf16", return_f32=False):

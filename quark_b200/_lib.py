@@ -55,6 +55,7 @@ class KvParams(C.Structure):
         ("num_buckets", C.c_int32), ("pinned_dilation", C.c_int32),
         ("kv_dtype", C.c_int32), ("max_segments", C.c_int32),
         ("quilt_factor", C.c_int32), ("packed_qkv", C.c_int32), ("quilt_offset", C.c_int32),
+        ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
     ]  # fmt: skip
 
 
@@ -107,6 +108,7 @@ SIGNATURES = {
     "qb_gemm_static_scratch_capacity": (_Z, []),
     "qb_gemm_static_scratch": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(GemmParams), _P]),
     "qb_quantize_e4m3": (_I, [_P, _P, _Z, _I, _P]),
+    "qb_quantize_e4m3_rows": (_I, [_P, _P, _P, _I, _I, _P]),
     "qb_dequantize_e4m3": (_I, [_P, _P, _Z, _P]),
     "qb_kv_cache_update": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
     "qb_kv_cache_update_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),

@@ -791,9 +791,13 @@ static int attn_key_splits(const qb_attn_params* p) {
   return n < 2 ? 1 : n;
 }
 
+// The tickets take a fixed area at the start of the workspace (4096 (query tile, head) items; more only for a
+// geometry that has more), so that calls of different geometries that share a workspace agree on where the
+// tickets end: one call's partial results never land on tickets that another call expects to find zero.
 static size_t attn_ticket_bytes(const qb_attn_params* p) {
   const int tpf = p->H_spatial * p->W_spatial;
-  return round_up(static_cast<size_t>((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio * sizeof(int), 1024);
+  const size_t need = round_up(static_cast<size_t>((tpf + kQTile - 1) / kQTile) * p->n_kv_heads * p->gqa_ratio * sizeof(int), 1024);
+  return need > (16u << 10) ? need : (16u << 10);
 }
 
 extern "C" size_t qb_owl_attn_workspace_bytes(const qb_attn_params* p) {

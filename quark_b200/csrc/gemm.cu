@@ -2,8 +2,8 @@
 //
 // One CTA computes one 128 x BN output tile over one K slice.  Warp 0 feeds a ring of
 // shared-memory stages with TMA (128-byte swizzle), one thread of warp 1 issues
-// tcgen05.mma into a TMEM accumulator, warps 2-5 read the accumulator back (one row per
-// thread) and run the epilogue.  bf16 operands use kind::f16 (K = 16 per instruction), e4m3
+// tcgen05.mma into a TMEM accumulator, warps 2-9 read the accumulator back (one row per thread, two
+// warps per TMEM lane quarter sharing each row's columns) and run the epilogue: 320 threads per CTA.  bf16 operands use kind::f16 (K = 16 per instruction), e4m3
 // operands kind::f8f6f4 (K = 32); both move 128 bytes of K per stage row, so the two paths share
 // every address computation.
 //
@@ -11,6 +11,8 @@
 // workspace, takes a ticket on the tile's counter, and the CTA that draws the last ticket adds
 // the partials in slice order (so the sum does not depend on which CTA came last), applies the
 // epilogue and stores.  No CTA ever waits for another.
+#include <atomic>
+
 #include <cuda.h>
 
 #include "common.cuh"
@@ -45,6 +47,8 @@ struct QkvTail {
   int32_t* segments;
   int32_t* n_segments;
   const float* rope_xy;
+  const float* k_scale;  // optional per-KV-head cache scales (see qb_kv_params)
+  const float* v_scale;
   int n_q_heads, n_kv_heads, tpf, nb, pd, max_segments, kv_fp8;
   float eps;
 };
@@ -232,8 +236,19 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
     tmem_ld32(taddr + 32, r1);
     tmem_wait_ld_into(r0);
     tmem_loaded(r1);
-    // the projection's output as the unfused path would store and re-read it: rounded to bf16
+    // the projection's output as the unfused path would store and re-read it: scaled (acc * (a_scale * w_scale[n]),
+    // as the plain epilogue does) and rounded to bf16
     float f[64];
+    if (g.a_scale != nullptr || g.w_scale != nullptr) {
+      const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float c0 = (g.w_scale && in_n) ? sa * __ldg(g.w_scale + col0 + j) : sa;
+        const float c1 = (g.w_scale && in_n) ? sa * __ldg(g.w_scale + col0 + 32 + j) : sa;
+        r0[j] = __float_as_uint(__uint_as_float(r0[j]) * c0);
+        r1[j] = __float_as_uint(__uint_as_float(r1[j]) * c1);
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       f[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r0[j])));
@@ -279,14 +294,15 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
       // rotate what the stand-alone append would read back (the bf16-rounded normalised K): y0 = pairs' first
       // outputs, y1 = their second outputs; a cache row is y0[0..31] followed by y1[0..31]
       const int head = (col0 - k_off) >> 6;
+      const float inv_k = q.k_scale != nullptr ? __fdiv_rn(1.0f, __ldg(q.k_scale + head)) : 1.0f;  // * 1 changes no bit
       float y0[32], y1[32];
 #pragma unroll
       for (int pr = 0; pr < 32; ++pr) {
         float c, sn;
         pair_cos_sin(pr, xy, tm, c, sn);
         const float x0 = bf16lo(o[pr]), x1 = bf16hi(o[pr]);
-        y0[pr] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
-        y1[pr] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn));
+        y0[pr] = __fmul_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)), inv_k);
+        y1[pr] = __fmul_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn)), inv_k);
       }
       uint8_t* kc = static_cast<uint8_t*>(q.K_cache);
       const size_t row_bytes = 64 * kEs;
@@ -337,6 +353,7 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
       const int hcol = n0 + hh * 64;
       if (hcol < v_off || hcol >= g.N) continue;
       const int head = (hcol - v_off) >> 6;
+      const float inv_v = q.v_scale != nullptr ? __fdiv_rn(1.0f, __ldg(q.v_scale + head)) : 1.0f;
       const uint16_t* src = vt + hh * 128 * kQkvVPitch;
       for (int v = et; v < 64 * kVecPerCh; v += 256) {
         const int d = v / kVecPerCh, j = v % kVecPerCh;
@@ -346,12 +363,15 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
         if (kCacheFp8) {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            w[i] = pack_e4m3x4(bf16_bits_to_f32(src[(t1 + 4 * i) * kQkvVPitch + d]), bf16_bits_to_f32(src[(t1 + 4 * i + 1) * kQkvVPitch + d]),
-                               bf16_bits_to_f32(src[(t1 + 4 * i + 2) * kQkvVPitch + d]), bf16_bits_to_f32(src[(t1 + 4 * i + 3) * kQkvVPitch + d]));
+            w[i] = pack_e4m3x4(__fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i) * kQkvVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 1) * kQkvVPitch + d]), inv_v),
+                               __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 2) * kQkvVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 3) * kQkvVPitch + d]), inv_v));
         } else {
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            w[i] = static_cast<uint32_t>(src[(t1 + 2 * i) * kQkvVPitch + d]) | (static_cast<uint32_t>(src[(t1 + 2 * i + 1) * kQkvVPitch + d]) << 16);
+          for (int i = 0; i < 4; ++i) {
+            const uint16_t lo = src[(t1 + 2 * i) * kQkvVPitch + d], hi = src[(t1 + 2 * i + 1) * kQkvVPitch + d];
+            w[i] = q.v_scale != nullptr ? pack_bf16x2(__fmul_rn(bf16_bits_to_f32(lo), inv_v), __fmul_rn(bf16_bits_to_f32(hi), inv_v))
+                                        : static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+          }
         }
         const uint4 ov = make_uint4(w[0], w[1], w[2], w[3]);
         const size_t ch = (static_cast<size_t>(head) * 64 + d) * cap;
@@ -797,6 +817,12 @@ static int32_t make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, u
   return make_tmap_2d_sw(tm, base, elem_bytes, rows, cols, box_rows, static_cast<uint32_t>(kRowBytes / elem_bytes), 128);
 }
 
+// Tile counters of the workspace K slices live in a fixed area at the start of the workspace, so that calls of
+// different shapes that share one workspace agree on where the counters end and the data begins (a
+// shape-dependent area would let one call's e4m3 copy of A or partial sums land on counters that a later
+// call with more tiles expects to find zero).
+constexpr size_t kCounterBytes = 64u << 10;  // 16384 tiles
+
 struct GemmPlan {
   int bn, splits, kb_total, kb_per_split;
   int cluster;  // slices summed inside a thread-block cluster (2, 4 or 8 slices) instead of through the workspace
@@ -850,6 +876,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       const double per_kb = per_sm > shared ? per_sm : shared;
       double cta = kbps * per_kb + 5000.0 + bn * 12.0;
       const bool cl = (p.reserved & 1) == 0 && (s == 2 || s == 4 || s == 8);
+      if (s > 1 && !cl && static_cast<size_t>(tiles) * sizeof(int) > kCounterBytes) continue;  // more tiles than counters
       if (s > 1) cta += cl ? 7500.0 + bn * 20.0 + s * bn * 4.0 : 26000.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
@@ -868,8 +895,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
     best.kb_total = kb_total;
     best.kb_per_split = kb_total;
   }
-  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + best.bn - 1) / best.bn);
-  best.counters_bytes = round_up(static_cast<size_t>(tiles) * sizeof(int), 1024);
+  best.counters_bytes = kCounterBytes;
   best.aq_bytes = (fp8 && p.a_dtype == QB_BF16) ? round_up(static_cast<size_t>(p.M) * p.K, 1024) : 0;
   best.partial_bytes = (best.splits > 1 && !best.cluster) ? static_cast<size_t>(best.splits) * p.M * p.N * sizeof(float) : 0;
   return best;
@@ -937,11 +963,15 @@ extern "C" int32_t qb_debug_gemm_trace(void* host_out) {
 extern "C" size_t qb_gemm_workspace_bytes(const qb_gemm_params* p) {
   if (validate_gemm(p) != QB_OK) return 0;
   const GemmPlan pl = plan_gemm(*p);
+  if (pl.aq_bytes == 0 && pl.partial_bytes == 0) return 0;  // no scratch memory is touched
   return pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
 }
 
+// clear_counters: the workspace may hold anything (the built-in scratch array keeps the last call's contents), so the
+// tile counters are zeroed on the stream first, after every check has passed and only if this plan reads them.
 static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
-                        const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail) {
+                        const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail,
+                        bool clear_counters = false) {
   int32_t rc = validate_gemm(p);
   if (rc != QB_OK) return rc;
   QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
@@ -965,6 +995,10 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool fp8 = p->compute_dtype == QB_E4M3;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
+  unsigned int* status = status_word();
+  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "gemm: device status word unavailable");
+  if (tail != nullptr) QB_REQUIRE(pl.bn == 128 && pl.splits == 1, QB_ERR_INVALID_ARG, "gemm_qkv_post: needs 128-column tiles and one K slice");
+  if (clear_counters && pl.partial_bytes > 0) QB_CUDA_OK(cudaMemsetAsync(ws, 0, pl.counters_bytes, st));
   const void* a_ptr = A;
   if (pl.aq_bytes > 0) {
     uint8_t* aq = ws + pl.counters_bytes;
@@ -992,10 +1026,8 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
   g.C = C;
   g.counters = reinterpret_cast<int*>(ws);
   g.partials = pl.partial_bytes ? reinterpret_cast<float*>(ws + pl.counters_bytes + pl.aq_bytes) : nullptr;
-  g.status = status_word();
-  QB_REQUIRE(g.status != nullptr, QB_ERR_CUDA, "gemm: device status word unavailable");
+  g.status = status;
   if (tail != nullptr) {
-    QB_REQUIRE(pl.bn == 128 && pl.splits == 1, QB_ERR_INVALID_ARG, "gemm_qkv_post: needs 128-column tiles and one K slice");
     g.qkv_mode = 1;
     g.qkv = *tail;
   }
@@ -1036,8 +1068,7 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
              "gemm_qkv_post: the projection is [%d, %d] but the geometry needs [%d, %d]", gp->M, gp->N, tpf,
              (kp->n_q_heads + 2 * kp->n_kv_heads) * 64);
   QB_REQUIRE(tpf % 16 == 0, QB_ERR_UNSUPPORTED, "gemm_qkv_post: H*W = %d must be a multiple of 16", tpf);
-  QB_REQUIRE(gp->c_dtype == QB_BF16 && gp->activation == 0 && gp->a_scale == nullptr && gp->w_scale == nullptr, QB_ERR_INVALID_ARG,
-             "gemm_qkv_post: bf16 output without activation or scales");
+  QB_REQUIRE(gp->c_dtype == QB_BF16 && gp->activation == 0, QB_ERR_INVALID_ARG, "gemm_qkv_post: bf16 output without activation");
   QB_REQUIRE((reinterpret_cast<uintptr_t>(qkv_out) & 31u) == 0 && (reinterpret_cast<uintptr_t>(K_cache) & 31u) == 0 && aligned16(Vt_cache) &&
                  aligned16(qkv_first) && aligned16(rope_xy),
              QB_ERR_ALIGN, "gemm_qkv_post: qkv_out and K_cache must be 32-byte aligned, the other pointers 16-byte aligned");
@@ -1050,6 +1081,7 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
   t.K_cache = K_cache; t.Vt_cache = Vt_cache; t.segments = segments; t.n_segments = n_segments; t.rope_xy = rope_xy;
   t.n_q_heads = kp->n_q_heads; t.n_kv_heads = kp->n_kv_heads; t.tpf = tpf; t.nb = kp->num_buckets; t.pd = kp->pinned_dilation;
   t.max_segments = kp->max_segments; t.kv_fp8 = kp->kv_dtype == QB_E4M3; t.eps = eps;
+  t.k_scale = kp->k_scale; t.v_scale = kp->v_scale;
   return gemm_run(A, B, qkv_out, nullptr, nullptr, nullptr, &p, workspace, workspace_bytes, stream, &t);
 }
 
@@ -1061,19 +1093,22 @@ namespace qb {
 constexpr size_t kStaticScratchBytes = 8u << 20;
 static __device__ __align__(256) unsigned char g_gemm_static_scratch[kStaticScratchBytes];
 
-// Device address of the scratch array on the current device, looked up once per device.
+// Device address of the scratch array on the calling thread's current device (the device the stream must belong
+// to), looked up once per device and published with a release store, so that two host threads that make their
+// first calls at the same time both end up with the same, fully written entry.  cudaDeviceReset invalidates
+// the entry of that device; a process that resets a device must not call this entry point on it afterwards.
 static int32_t static_scratch_ptr(void** out) {
-  static void* cache[64] = {nullptr};
+  static std::atomic<void*> cache[64];
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
   QB_REQUIRE(dev >= 0 && dev < 64, QB_ERR_DEVICE, "gemm_static_scratch: device ordinal %d out of range", dev);
-  if (cache[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = cache[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     QB_CUDA_OK(cudaGetSymbolAddress(&p, g_gemm_static_scratch));
     QB_REQUIRE(p != nullptr, QB_ERR_CUDA, "gemm_static_scratch: cudaGetSymbolAddress returned a null address");
-    cache[dev] = p;
+    cache[dev].store(p, std::memory_order_release);
   }
-  *out = cache[dev];
+  *out = p;
   return QB_OK;
 }
 }  // namespace qb
@@ -1093,8 +1128,8 @@ extern "C" int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C,
   void* scratch = nullptr;
   rc = static_scratch_ptr(&scratch);
   if (rc != QB_OK) return rc;
-  // The array keeps whatever the previous call left.  Only the tile counters must start at zero;
-  // the e4m3 copy of A and the K-slice partials are fully written before they are read.
-  QB_CUDA_OK(cudaMemsetAsync(scratch, 0, pl.counters_bytes, static_cast<cudaStream_t>(stream)));
-  return qb_gemm(A, B, C, bias, gate, residual, p, scratch, kStaticScratchBytes, stream);
+  // The array keeps whatever the previous call left.  Only the tile counters must start at zero (the e4m3 copy of
+  // A and the K-slice partials are fully written before they are read); gemm_run clears them on the stream once all
+  // of its own checks have passed, and only when this plan sums K slices through the scratch memory.
+  return gemm_run(A, B, C, bias, gate, residual, p, scratch, kStaticScratchBytes, stream, nullptr, true);
 }

@@ -285,6 +285,39 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
   }
 }
 
+// One CTA per row: row maximum of |x| (a maximum does not depend on the order it is taken in), scale = amax / 448,
+// out = e4m3(x * (1 / scale)).  Weights are narrowed once, at load time: nothing here is tuned.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* __restrict__ X, uint8_t* __restrict__ out,
+                                                            float* __restrict__ scale_out, int cols) {
+  __shared__ float red[8];
+  const uint16_t* x = X + static_cast<size_t>(blockIdx.x) * cols;
+  float m = 0.f;
+  for (int i8 = threadIdx.x * 8; i8 < cols; i8 += 256 * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + i8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+  const float scale = m > 0.f ? __fdiv_rn(m, 448.0f) : 1.0f;
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (threadIdx.x == 0) scale_out[blockIdx.x] = scale;
+  uint8_t* o = out + static_cast<size_t>(blockIdx.x) * cols;
+  for (int i8 = threadIdx.x * 8; i8 < cols; i8 += 256 * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + i8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(f[j], inv);
+    *reinterpret_cast<uint2*>(o + i8) = pack8_e4m3(f);
+  }
+}
+
 __global__ void increment_kernel(int32_t* c) {
   grid_dep_wait();    // inputs come from the kernels before this one
   grid_dep_launch();  // the next kernel may begin its set-up
@@ -569,6 +602,14 @@ int32_t qb_quantize_e4m3(const void* X, void* out, size_t n, int32_t src_dtype, 
   QB_REQUIRE(n == 0 || (X && out), QB_ERR_INVALID_ARG, "quantize_e4m3: NULL pointer");
   QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "quantize_e4m3: pointers must be 16-byte aligned");
   return quantize_e4m3_launch(X, out, n, src_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int32_t qb_quantize_e4m3_rows(const void* X, void* out, float* scale_out, int32_t rows, int32_t cols, void* stream) {
+  QB_REQUIRE(X && out && scale_out, QB_ERR_INVALID_ARG, "quantize_e4m3_rows: NULL pointer");
+  QB_REQUIRE(rows > 0 && cols > 0 && cols % 8 == 0, QB_ERR_INVALID_ARG, "quantize_e4m3_rows: [%d, %d] (cols must be a positive multiple of 8)", rows, cols);
+  QB_REQUIRE(aligned16(X) && (reinterpret_cast<uintptr_t>(out) & 7u) == 0, QB_ERR_ALIGN, "quantize_e4m3_rows: X must be 16-byte and out 8-byte aligned");
+  quantize_rows_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(X), static_cast<uint8_t*>(out), scale_out, cols);
+  return check_launch("quantize_e4m3_rows");
 }
 
 int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void* out, void* out_q, int32_t rows, int32_t D,

@@ -27,6 +27,8 @@ struct KvArgs {
   int32_t* segments;
   int32_t* n_segments;
   const float* rope_xy;
+  const float* k_scale;  // optional per-head scales: the cache holds value * (1 / scale[head])
+  const float* v_scale;
   // Quilt: the cache keeps every quilt-th token of a frame, cached token i being token qoff + i * quilt; tpf below is
   // the cached count, so slots, capacity and the segment table are those of a frame of tpf tokens
   // (src/quark/kernels/kv_cache_update/reference.py:201-207, spec.py:66-76).  quilt = 1, qoff = 0: every token.
@@ -54,6 +56,9 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
   const bool ring = is_write && frozen == 0;
 
   if (threadIdx.x < 8) temporal_cos_sin(ft, threadIdx.x, tm);
+  // multiplying by exactly 1 changes no bit, so the scale-free call stays what it was
+  const float inv_k = a.k_scale != nullptr ? __fdiv_rn(1.0f, __ldg(a.k_scale + head)) : 1.0f;
+  const float inv_v = a.v_scale != nullptr ? __fdiv_rn(1.0f, __ldg(a.v_scale + head)) : 1.0f;
 
   // segment table: one thread of the whole grid
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32) {
@@ -108,8 +113,8 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
         float c, s;
         pair_cos_sin(p, xy, tm, c, s);
         const float x0 = bf16lo(w[j]), x1 = bf16hi(w[j]);
-        y0[pl] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        y1[pl] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+        y0[pl] = __fmul_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)), inv_k);
+        y1[pl] = __fmul_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s)), inv_k);
       }
     }
     uint4 o0, o1;
@@ -150,14 +155,17 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        w[i] = pack_e4m3x4(bf16_bits_to_f32(vt[(tt + 4 * i) * kVPitch + d]), bf16_bits_to_f32(vt[(tt + 4 * i + 1) * kVPitch + d]),
-                           bf16_bits_to_f32(vt[(tt + 4 * i + 2) * kVPitch + d]), bf16_bits_to_f32(vt[(tt + 4 * i + 3) * kVPitch + d]));
+        w[i] = pack_e4m3x4(__fmul_rn(bf16_bits_to_f32(vt[(tt + 4 * i) * kVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(vt[(tt + 4 * i + 1) * kVPitch + d]), inv_v),
+                           __fmul_rn(bf16_bits_to_f32(vt[(tt + 4 * i + 2) * kVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(vt[(tt + 4 * i + 3) * kVPitch + d]), inv_v));
       o = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
       uint32_t w[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        w[i] = static_cast<uint32_t>(vt[(tt + 2 * i) * kVPitch + d]) | (static_cast<uint32_t>(vt[(tt + 2 * i + 1) * kVPitch + d]) << 16);
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t lo = vt[(tt + 2 * i) * kVPitch + d], hi = vt[(tt + 2 * i + 1) * kVPitch + d];
+        w[i] = a.v_scale != nullptr ? pack_bf16x2(__fmul_rn(bf16_bits_to_f32(lo), inv_v), __fmul_rn(bf16_bits_to_f32(hi), inv_v))
+                                    : static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+      }
       o = make_uint4(w[0], w[1], w[2], w[3]);
     }
     const size_t ch = (static_cast<size_t>(head) * 64 + d) * cap;
@@ -236,6 +244,7 @@ static int32_t kv_append(const void* k_src, const void* v_src, size_t row_stride
   a.K_cache = K_cache; a.Vt_cache = Vt_cache;
   a.segments = segments; a.n_segments = n_segments;
   a.rope_xy = rope_xy;
+  a.k_scale = p->k_scale; a.v_scale = p->v_scale;
   a.quilt = p->quilt_factor; a.qoff = p->quilt_offset;
   a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation; a.max_segments = p->max_segments;
   dim3 grid((tpf + kKvTile - 1) / kKvTile, p->n_kv_heads);

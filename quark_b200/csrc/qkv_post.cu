@@ -27,6 +27,8 @@ struct QkvPostArgs {
   int32_t* segments;
   int32_t* n_segments;
   const float* rope_xy;
+  const float* k_scale;  // optional per-head cache scales (see qb_kv_params)
+  const float* v_scale;
   int qkv_dim, n_q_heads, n_kv_heads, gqa;
   int tpf, nb, pd, max_segments;
   float eps;
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
   const int k_off = a.n_q_heads * 64, v_off = (a.n_q_heads + a.n_kv_heads) * 64;
 
   if (threadIdx.x < 8) temporal_cos_sin(ft, threadIdx.x, tm);
+  const float inv_k = a.k_scale != nullptr ? __fdiv_rn(1.0f, __ldg(a.k_scale + head)) : 1.0f;  // * 1 changes no bit
+  const float inv_v = a.v_scale != nullptr ? __fdiv_rn(1.0f, __ldg(a.v_scale + head)) : 1.0f;
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32) {  // segment table: one thread of the grid
     int s[6] = {0, 0, 0, 0, 0, 0};
     int n;
@@ -188,8 +192,8 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
     for (int j = 0; j < 8; ++j) {
       float c, s;
       pair_cos_sin(q * 8 + j, xy, tm, c, s);
-      y0[j] = __fsub_rn(__fmul_rn(f[2 * j], c), __fmul_rn(f[2 * j + 1], s));
-      y1[j] = __fadd_rn(__fmul_rn(f[2 * j + 1], c), __fmul_rn(f[2 * j], s));
+      y0[j] = __fmul_rn(__fsub_rn(__fmul_rn(f[2 * j], c), __fmul_rn(f[2 * j + 1], s)), inv_k);
+      y1[j] = __fmul_rn(__fadd_rn(__fmul_rn(f[2 * j + 1], c), __fmul_rn(f[2 * j], s)), inv_k);
     }
     uint8_t* kc = static_cast<uint8_t*>(a.K_cache);
     const size_t row_bytes = 64 * kEs;
@@ -232,12 +236,15 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
     if (kFp8) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        w[i] = pack_e4m3x4(bf16_bits_to_f32(vt[(t1 + 4 * i) * kPostVPitch + d]), bf16_bits_to_f32(vt[(t1 + 4 * i + 1) * kPostVPitch + d]),
-                           bf16_bits_to_f32(vt[(t1 + 4 * i + 2) * kPostVPitch + d]), bf16_bits_to_f32(vt[(t1 + 4 * i + 3) * kPostVPitch + d]));
+        w[i] = pack_e4m3x4(__fmul_rn(bf16_bits_to_f32(vt[(t1 + 4 * i) * kPostVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(vt[(t1 + 4 * i + 1) * kPostVPitch + d]), inv_v),
+                           __fmul_rn(bf16_bits_to_f32(vt[(t1 + 4 * i + 2) * kPostVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(vt[(t1 + 4 * i + 3) * kPostVPitch + d]), inv_v));
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        w[i] = static_cast<uint32_t>(vt[(t1 + 2 * i) * kPostVPitch + d]) | (static_cast<uint32_t>(vt[(t1 + 2 * i + 1) * kPostVPitch + d]) << 16);
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t lo = vt[(t1 + 2 * i) * kPostVPitch + d], hi = vt[(t1 + 2 * i + 1) * kPostVPitch + d];
+        w[i] = a.v_scale != nullptr ? pack_bf16x2(__fmul_rn(bf16_bits_to_f32(lo), inv_v), __fmul_rn(bf16_bits_to_f32(hi), inv_v))
+                                    : static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+      }
     }
     const uint4 o = make_uint4(w[0], w[1], w[2], w[3]);
     const size_t ch = (static_cast<size_t>(head) * 64 + d) * cap;
@@ -279,6 +286,7 @@ extern "C" int32_t qb_qkv_post(const void* qkv_in, const void* qkv_first, const 
   a.K_cache = K_cache; a.Vt_cache = Vt_cache;
   a.segments = segments; a.n_segments = n_segments;
   a.rope_xy = rope_xy;
+  a.k_scale = p->k_scale; a.v_scale = p->v_scale;
   a.qkv_dim = (p->n_q_heads + 2 * p->n_kv_heads) * 64;
   a.n_q_heads = p->n_q_heads; a.n_kv_heads = p->n_kv_heads; a.gqa = p->n_q_heads / p->n_kv_heads;
   a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation; a.max_segments = p->max_segments;

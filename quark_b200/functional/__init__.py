@@ -20,7 +20,7 @@ from ..runtime.tensor import QuarkTensor
 
 __all__ = [
     "gemm", "owl_attn", "kv_cache_update", "quantize_e4m3", "ada_rmsnorm", "head_rmsnorm", "value_residual_packed",
-    "ada_gate_residual", "silu", "euler_step", "patchify", "unpatchify", "increment", "rope_table", "qkv_post",
+    "ada_gate_residual", "silu", "euler_step", "patchify", "unpatchify", "increment", "rope_table", "qkv_post", "quantize_e4m3_rows",
 ]  # fmt: skip
 
 
@@ -51,19 +51,29 @@ def _code(name: str | None, default: str) -> int:
 # ---------------------------------------------------------------------------
 
 _WS: QuarkTensor | None = None
+_ATTN_WS: QuarkTensor | None = None
+# Workspaces that were replaced by larger ones.  A CUDA graph captured while a smaller workspace was current
+# (an Engine's frame graph, say) still holds that buffer's device address, so a superseded workspace is never
+# freed: it stays referenced here for the life of the process (a few MB each, and growth is rare).
+_RETIRED_WS: list = []
+
+
+def _grow(current: QuarkTensor | None, nbytes: int) -> QuarkTensor:
+    if current is not None:
+        _RETIRED_WS.append(current)
+    return QuarkTensor.zeros(int(nbytes), dtype="e4m3")
 
 
 def _workspace(nbytes: int) -> QuarkTensor | None:
-    """One zero-initialised scratch buffer shared by every call (calls on one stream never overlap)."""
+    """One zero-initialised scratch buffer shared by every GEMM call (calls on one stream never overlap).  The
+    library keeps the tile counters in a fixed area at its start, whatever the shape, so calls of different
+    shapes can share it."""
     global _WS
     if nbytes <= 0:
         return _WS
     if _WS is None or _WS.nbytes < nbytes:
-        _WS = QuarkTensor.zeros(max(int(nbytes), 1 << 20), dtype="e4m3")
+        _WS = _grow(_WS, max(int(nbytes), 1 << 20))
     return _WS
-
-
-_ATTN_WS: QuarkTensor | None = None
 
 
 def _attn_workspace(nbytes: int) -> QuarkTensor | None:
@@ -72,7 +82,7 @@ def _attn_workspace(nbytes: int) -> QuarkTensor | None:
     if nbytes <= 0:
         return None
     if _ATTN_WS is None or _ATTN_WS.nbytes < nbytes:
-        _ATTN_WS = QuarkTensor.zeros(int(nbytes), dtype="e4m3")
+        _ATTN_WS = _grow(_ATTN_WS, int(nbytes))
     return _ATTN_WS
 
 
@@ -202,6 +212,32 @@ def quantize_e4m3(X, *, out=None):
     return out
 
 
+def quantize_e4m3_rows(X, *, out=None, scale_out=None):
+    """Per-row scaled narrowing of a bf16 matrix (a weight ``[out, in]``): ``scale[r] = max|X[r]| / 448``,
+    ``out[r] = e4m3(X[r] * (1 / scale[r]))``.  Returns ``(out, scale)``; ``scale`` is what ``qf.gemm`` takes as
+    ``w_scale``.  An extension: the reference narrows without a scale (``src/quark/nn/layers.py:291-304``)."""
+    if _dt(X) != "bf16" or X.ndim != 2:
+        raise TypeError("qf.quantize_e4m3_rows: X must be a bf16 matrix")
+    rows, cols = int(X.shape[0]), int(X.shape[1])
+    if cols % 8:
+        raise ValueError(f"qf.quantize_e4m3_rows: {cols} columns (must be a multiple of 8)")
+    if out is None:
+        out = QuarkTensor.empty(rows, cols, dtype="e4m3")
+    if scale_out is None:
+        scale_out = QuarkTensor.empty(rows, dtype="f32")
+    if out.numel != X.numel or out.dtype != "e4m3" or scale_out.numel != rows or scale_out.dtype != "f32":
+        raise ValueError("qf.quantize_e4m3_rows: out must be e4m3 of X's size and scale_out f32 [rows]")
+    _lib.check(_lib.load().qb_quantize_e4m3_rows(_p(X), _p(out), _p(scale_out), rows, cols, _s()))
+    return out, scale_out
+
+
+def _head_scales(who, n_kv_heads, k_scale, v_scale):
+    for name, t in (("k_scale", k_scale), ("v_scale", v_scale)):
+        if t is not None and (_dt(t) != "f32" or t.numel != n_kv_heads):
+            raise ValueError(f"{who}: {name} must be an f32 tensor of {n_kv_heads} per-head scales")
+    return (k_scale.data_ptr() if k_scale is not None else None, v_scale.data_ptr() if v_scale is not None else None)
+
+
 def dequantize_e4m3(X, *, out=None):
     """e4m3 -> bf16, exact (every e4m3 value is a bf16 value)."""
     if _dt(X) != "e4m3":
@@ -230,8 +266,10 @@ def _quilt_checks(who: str, tpf: int, quilt_factor: int, quilt_offset: int) -> N
 
 def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, B, n_kv_heads, H_spatial,
                     W_spatial, num_buckets, pinned_dilation, kv_dtype=None, max_segments=3, packed_qkv=False,
-                    n_q_heads=0, rope_n_frames=1, quilt_factor=1, quilt_offset=0):  # fmt: skip
+                    n_q_heads=0, rope_n_frames=1, quilt_factor=1, quilt_offset=0, k_scale=None, v_scale=None):  # fmt: skip
     """In-place RoPE + cache append (``src/quark/functional/kv_cache_update.py:187-265``).
+
+    ``k_scale`` / ``v_scale`` (extension, f32 ``[n_kv_heads]``): the caches receive ``K / k_scale[h]`` and ``V / v_scale[h]``.
 
     ``K`` is the packed QKV tensor when ``packed_qkv=True`` (``V`` is then ignored, as upstream); otherwise ``K`` and
     ``V`` are head-major ``[B * n_kv_heads * tpf, 64]`` tensors of their own.
@@ -271,10 +309,11 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
         raise TypeError(f"qf.kv_cache_update: kv_dtype={want!r} but the caches are {kvd!r}")
     if _dt(Vt_cache) != kvd or kvd not in ("bf16", "e4m3"):
         raise TypeError(f"qf.kv_cache_update: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
+    ks, vs = _head_scales("qf.kv_cache_update", n_kv_heads, k_scale, v_scale)
     p = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=quilt_factor,
-        packed_qkv=1 if packed_qkv else 0, quilt_offset=quilt_offset,
+        packed_qkv=1 if packed_qkv else 0, quilt_offset=quilt_offset, k_scale=ks, v_scale=vs,
     )  # fmt: skip
     tail = (_p(frame_t), _p(frozen), _p(K_cache), _p(Vt_cache), _p(segments), _p(n_segments), _p(rope_table(H_spatial, W_spatial)),
             C.byref(p), _s())  # fmt: skip
@@ -284,7 +323,7 @@ def kv_cache_update(K, V, frame_t, frozen, Vt_cache, segments, n_segments, K_cac
 
 
 def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, n_q_heads, n_kv_heads, H_spatial,
-             W_spatial, num_buckets, pinned_dilation, eps: float = 1e-6, max_segments=3, out=None):  # fmt: skip
+             W_spatial, num_buckets, pinned_dilation, eps: float = 1e-6, max_segments=3, out=None, k_scale=None, v_scale=None):  # fmt: skip
     """``head_rmsnorm`` + ``value_residual_packed`` + ``kv_cache_update`` in one launch (no reference
     counterpart as a single call; bit-identical to the three calls of
     ``src/quark/models/waypoint_15.py:398-407``).  ``QKV_first`` / ``lamb`` may both be None.
@@ -307,9 +346,11 @@ def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segmen
     if _dt(Vt_cache) != kvd or kvd not in ("bf16", "e4m3"):
         raise TypeError(f"qf.qkv_post: cache dtypes {kvd!r} / {_dt(Vt_cache)!r}")
     out = _like(QKV, out, "qf.qkv_post")
+    ks, vs = _head_scales("qf.qkv_post", n_kv_heads, k_scale, v_scale)
     p = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+        k_scale=ks, v_scale=vs,
     )  # fmt: skip
     _lib.check(
         _lib.load().qb_qkv_post(
@@ -321,7 +362,8 @@ def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segmen
 
 
 def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, n_q_heads, n_kv_heads,
-                  H_spatial, W_spatial, num_buckets, pinned_dilation, compute_dtype=None, eps: float = 1e-6, max_segments=3, out=None):  # fmt: skip
+                  H_spatial, W_spatial, num_buckets, pinned_dilation, compute_dtype=None, eps: float = 1e-6, max_segments=3, out=None,
+                  a_scale=None, w_scale=None, k_scale=None, v_scale=None):  # fmt: skip
     """``qkv_post(gemm(A, B))`` in one launch: the QKV projection whose epilogue normalises the Q and K heads,
     mixes V with the first block's, rotates K and appends K / V to the caches (same bytes as the two calls;
     no reference counterpart as a single call).  Returns the packed QKV that ``owl_attn`` reads."""
@@ -351,11 +393,16 @@ def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_
         raise ValueError(f"qf.gemm_qkv_post: out is {out.shape} {out.dtype}, expected ({M}, {N}) bf16")
     gp = _lib.GemmParams(
         M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code("bf16", "bf16"),
-        compute_dtype=_code(cd, "bf16"), activation=0, gate_groups=1, split_k=1, tile_n=128, reserved=2, a_scale=None, w_scale=None,
+        compute_dtype=_code(cd, "bf16"), activation=0, gate_groups=1, split_k=1, tile_n=128, reserved=2,
+        a_scale=a_scale.data_ptr() if a_scale is not None else None, w_scale=w_scale.data_ptr() if w_scale is not None else None,
     )  # fmt: skip
+    if w_scale is not None and (_dt(w_scale) != "f32" or w_scale.numel != N):
+        raise ValueError(f"qf.gemm_qkv_post: w_scale must be f32 [{N}]")
+    ks, vs = _head_scales("qf.gemm_qkv_post", n_kv_heads, k_scale, v_scale)
     kp = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
         pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
+        k_scale=ks, v_scale=vs,
     )  # fmt: skip
     lib = _lib.load()
     ws = _workspace(int(lib.qb_gemm_workspace_bytes(C.byref(gp))))

@@ -87,6 +87,10 @@ class Waypoint15Config:
     fuse_qkv_post: bool = True
     # ... and that launch folded into the QKV projection's epilogue (same bytes again); needs fuse_qkv_post.
     fuse_qkv_gemm: bool = True
+    # Scaled e4m3 (an extension; the reference's e4m3 is scale free): linear weights narrowed with one scale per
+    # output channel (amax / 448), the caches with one scale per KV head (`k_scale` / `v_scale` of each block's
+    # parameters).  Only meaningful where quant says fp8; the mixture-of-experts weights stay unscaled.
+    fp8_scales: bool = False
     # Tensor parallelism by KV-head group: rank `tp_rank` of `tp_world` owns n_kv_heads / tp_world KV heads
     # with their Q heads (QKV and fc1 column-parallel, out-proj and fc2 row-parallel, partial outputs summed
     # over the ranks).  The reference is single-GPU; tp_world = 1 is its wiring.
@@ -253,6 +257,10 @@ def make_params(cfg: Waypoint15Config, seed: int = 0, *, weight_std: float = 0.0
             "fc2.weight": _randn_bf16(r, (d, cfg.mlp_dim), weight_std),
             "lamb": 0.5,
         }
+        if cfg.fp8_scales:  # per-KV-head cache scales: what a calibration run would leave (K is RMS-normalised: |k| <= 8)
+            rs = np.random.default_rng([seed, i, 13])
+            blk["k_scale"] = ((8.0 / 448.0) * (1.0 + 0.25 * rs.random(cfg.n_kv_heads))).astype(np.float32)
+            blk["v_scale"] = ((6.0 / 448.0) * (1.0 + 0.25 * rs.random(cfg.n_kv_heads))).astype(np.float32)
         if cfg.moe:  # a generator of its own; layouts of src/quark/nn/moe.py:35-38
             rm = np.random.default_rng([seed, i, 11])
             E, Hm = cfg.moe_n_experts, cfg.mlp_dim // cfg.moe_top_k
@@ -298,6 +306,9 @@ def shard_block_params(cfg: Waypoint15Config, blk: dict) -> dict:
     m = cfg.mlp_dim_local
     out["fc1.weight"] = np.ascontiguousarray(np.asarray(blk["fc1.weight"])[r * m : (r + 1) * m])
     out["fc2.weight"] = np.ascontiguousarray(np.asarray(blk["fc2.weight"])[:, r * m : (r + 1) * m])
+    for k in ("k_scale", "v_scale"):
+        if blk.get(k) is not None:
+            out[k] = np.ascontiguousarray(np.asarray(blk[k])[r * cfg.n_kv_heads_local : (r + 1) * cfg.n_kv_heads_local])
     return out
 
 
@@ -365,6 +376,7 @@ class TransformerBlock(nn.Module):
                 kc.K_cache, n_q_heads=self._cfg.n_heads_local, n_kv_heads=self._cfg.n_kv_heads_local, H_spatial=self._cfg.height,
                 W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
                 out=nn._cached(self, "qkv_post", (h0.numel // int(h0.shape[-1]), self._cfg.qkv_dim_local), "bf16"),
+                w_scale=self.qkv_proj.w_scale, k_scale=kc.k_scale, v_scale=kc.v_scale,
             )  # fmt: skip
         elif self._cfg.fuse_qkv_post and not quilted:
             qkv = self.qkv_proj(h0)
@@ -374,7 +386,7 @@ class TransformerBlock(nn.Module):
                 frame_t if frame_t is not None else kc.frame_t, kc._frozen[1 if frozen else 0], kc.Vt_cache, kc.segments, kc.n_segments,
                 kc.K_cache, n_q_heads=self._cfg.n_heads_local, n_kv_heads=self._cfg.n_kv_heads_local, H_spatial=self._cfg.height,
                 W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
-                out=nn._cached(self, "qkv_post", qkv.shape, "bf16"),
+                out=nn._cached(self, "qkv_post", qkv.shape, "bf16"), k_scale=kc.k_scale, v_scale=kc.v_scale,
             )  # fmt: skip
         else:
             qkv = self.head_norm(self.qkv_proj(h0))
@@ -449,12 +461,15 @@ class Waypoint15(nn.Module):
                 blk.ctrl_fusion.fc2.weight.data = up(p["ctrl.fc2.weight"])
             if hasattr(blk, "v_residual"):
                 blk.v_residual.lamb.data = QuarkTensor.from_numpy(np.array([p["lamb"]], dtype=np.float32))
+            if self.cfg.fp8_scales and self.cfg.quant.kv_cache == "fp8":
+                blk.kv_cache.set_scales(p.get("k_scale"), p.get("v_scale"))
             blk._cond_lut = [tuple(up(r) for r in rows) for rows in p["lut"]]
         return self
 
     def prepare(self, **kwargs):
         """Quantise linear weights when ``cfg.quant.linear == "fp8"`` (``waypoint_15.py:502-535``)."""
         kwargs.setdefault("fp8", self.cfg.quant.linear == "fp8")
+        kwargs.setdefault("fp8_scaled", self.cfg.fp8_scales)
         for blk in self.blocks:
             for lin in (blk.qkv_proj, blk.out_proj) + (() if self.cfg.moe else (blk.mlp.fc1, blk.mlp.fc2)):
                 lin.prepare(**kwargs)

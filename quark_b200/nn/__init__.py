@@ -123,14 +123,20 @@ class Linear(Module):
         self._out_dtype = out_dtype
         self._fp8_skip = fp8_skip
         self._fp8 = False
+        self.w_scale = None  # f32 [out_features] after prepare(fp8=True, fp8_scaled=True)
         if bias:
             self.bias = Parameter(QuarkTensor.zeros(out_features, dtype="bf16"))
 
-    def prepare(self, *, shuffle: bool = False, fp8: bool = False, **kwargs):
+    def prepare(self, *, shuffle: bool = False, fp8: bool = False, fp8_scaled: bool = False, **kwargs):
+        """``fp8_scaled`` (extension): narrow with one scale per output channel (``amax / 448``) instead of unscaled;
+        the scales stay with the layer and are applied in the GEMM's epilogue."""
         if shuffle:
             raise RuntimeError("weight shuffling is not supported (it is disabled upstream as well)")
         if fp8 and not self._fp8_skip and not self._fp8:
-            self.weight.data = qf.quantize_e4m3(self.weight.data)
+            if fp8_scaled:
+                self.weight.data, self.w_scale = qf.quantize_e4m3_rows(self.weight.data)
+            else:
+                self.weight.data = qf.quantize_e4m3(self.weight.data)
             self._fp8 = True
 
     def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None):
@@ -153,6 +159,7 @@ class Linear(Module):
         return qf.gemm(
             x, self.weight.data, out_dtype=od, compute_dtype=b_dt if b_dt == "e4m3" else None, activation=activation,
             bias=self.bias.data if self._has_bias else bias, gate=gate, residual=residual, gate_groups=gate_groups, out=out,
+            w_scale=self.w_scale,
             b_constant=True,  # a Parameter: written by load_params only, never by a kernel of the forward pass
         )  # fmt: skip
 
@@ -359,13 +366,21 @@ class KVCacheUpdate(Module):
         # frozen = 1 and frozen = 0 as two constant device scalars: no per-call memset in the graph
         self._frozen = (QuarkTensor.from_numpy(np.array([0], dtype=np.int32)), QuarkTensor.from_numpy(np.array([1], dtype=np.int32)))
         self._L, self._tpf = L, tpf
+        # optional per-head quantisation scales (f32 [n_kv_heads]); None = the reference's scale-free caches
+        self.k_scale = self.v_scale = None
         self._kw = dict(B=B, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
                         pinned_dilation=pinned_dilation, packed_qkv=packed_qkv, n_q_heads=n_q_heads, quilt_factor=quilt_factor,
                         quilt_offset=quilt_offset)  # fmt: skip
 
     def forward(self, qkv, frame_t=None, frozen: bool = False):
         ft = frame_t if frame_t is not None else self.frame_t
-        qf.kv_cache_update(qkv, qkv, ft, self._frozen[1 if frozen else 0], self.Vt_cache, self.segments, self.n_segments, self.K_cache, **self._kw)
+        qf.kv_cache_update(qkv, qkv, ft, self._frozen[1 if frozen else 0], self.Vt_cache, self.segments, self.n_segments, self.K_cache,
+                           k_scale=self.k_scale, v_scale=self.v_scale, **self._kw)  # fmt: skip
+
+    def set_scales(self, k_scale, v_scale) -> None:
+        """Per-KV-head scales as host arrays (or None): the caches then hold ``K / k_scale[h]`` and ``V / v_scale[h]``."""
+        up = lambda a: None if a is None else QuarkTensor.from_numpy(np.ascontiguousarray(a, dtype=np.float32))  # noqa: E731
+        self.k_scale, self.v_scale = up(k_scale), up(v_scale)
 
     def set_frame_t(self, value: int) -> None:
         self.frame_t.copy_from_numpy(np.array([value], dtype=np.int32))
@@ -396,5 +411,5 @@ class OwlAttn(Module):
         out = _cached(self, "out", (int(qkv.shape[0]), n_q * Dh), qkv.dtype)
         out_q = _cached(self, "out_q", out.shape, "e4m3") if emit_e4m3 else None
         qf.owl_attn(qkv, kv_cache.K_cache, kv_cache.Vt_cache, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
-                    out=out, out_q=out_q, compute_dtype=self._compute_dtype, **self._kw)  # fmt: skip
+                    out=out, out_q=out_q, compute_dtype=self._compute_dtype, k_scale=kv_cache.k_scale, v_scale=kv_cache.v_scale, **self._kw)  # fmt: skip
         return out_q if emit_e4m3 else out

@@ -92,10 +92,60 @@ def _check(rc: int, what: str) -> None:
         raise NcclError(f"{what}: {load().ncclGetErrorString(rc).decode()} ({rc})")
 
 
+class Watchdog:
+    """Host-side guard around work that contains collectives: when a guarded region does not finish within
+    ``timeout_s`` (a peer died, or never joined), ``comm.abort()`` is called from a timer thread, which makes the
+    communicator's kernels on this GPU return instead of waiting for the missing rank for ever; the blocked host
+    call then raises.  ``fired`` tells whether that happened.  The reference is single-GPU and has no counterpart.
+
+        wd = Watchdog(comm, timeout_s=5 * median_frame_seconds)
+        with wd.guard():
+            engine.gen_frame()
+    """
+
+    def __init__(self, comm, timeout_s: float):
+        if timeout_s <= 0:
+            raise ValueError("Watchdog: timeout_s must be positive")
+        self.comm, self.timeout_s, self.fired = comm, float(timeout_s), False
+
+    class _Guard:
+        def __init__(self, wd):
+            import threading
+
+            self.wd, self.done = wd, threading.Event()
+            self.thread = threading.Thread(target=self._run, daemon=True)
+
+        def _run(self):
+            if not self.done.wait(self.wd.timeout_s):
+                self.wd.fired = True
+                try:
+                    self.wd.comm.abort()
+                except Exception:
+                    pass
+
+        def __enter__(self):
+            self.thread.start()
+            return self
+
+        def __exit__(self, exc_type, exc, tb):
+            self.done.set()
+            self.thread.join()
+            if self.wd.fired and exc_type is None:
+                raise NcclError(f"Watchdog: the guarded region took longer than {self.wd.timeout_s:.1f} s; the communicator was aborted")
+            return False
+
+    def guard(self):
+        return Watchdog._Guard(self)
+
+
 class LocalComm:
     """World of one: nothing to exchange."""
 
     rank, world = 0, 1
+    reduction_name = "none (one rank)"
+
+    def abort(self):
+        pass
 
     def all_reduce_sum(self, t):
         return t
@@ -110,10 +160,13 @@ class LocalComm:
 class NcclComm:
     """``NcclComm(rank, world, id_path)``: the calling process must already have selected its GPU."""
 
-    def __init__(self, rank: int, world: int, id_path: str, *, timeout_s: float = 120.0):
+    reduction_name = "ncclAllReduce (bf16 sum) + gate / residual kernel"
+
+    def __init__(self, rank: int, world: int, id_path: str, *, timeout_s: float = 120.0, fused: bool = False):
         if not (0 <= rank < world):
             raise ValueError(f"NcclComm: rank {rank} of {world}")
         self.rank, self.world = int(rank), int(world)
+        self.fused = bool(fused)
         lib = load()
         uid = _UniqueId()
         if rank == 0:

@@ -75,7 +75,8 @@ def test_argument_validation_needs_no_gpu():
 def test_attention_key_split_choice_and_workspace_size_need_no_gpu():
     """How many CTAs share the keys of one (query tile, head) follows from the geometry alone: none at 720p
     (4 x 32 items fill the GPU), four at 360p (32 items), eight for a tensor-parallel rank with two KV heads;
-    the workspace is one ticket per item (rounded to 1 KiB) plus 66 x 128 floats per item and share."""
+    the workspace is a fixed 16 KiB ticket area (the same for every geometry, so that calls can share a
+    workspace) plus 66 x 128 floats per item and share."""
     import ctypes as C
 
     from quark_b200 import _lib
@@ -89,7 +90,7 @@ def test_attention_key_split_choice_and_workspace_size_need_no_gpu():
 
     per = 66 * 128 * 4
     assert ws(32, 16, 16) == 0
-    assert ws(16, 8, 16) == 1024 + 32 * 4 * per
-    assert ws(32, 16, 2) == 1024 + 16 * 8 * per
+    assert ws(16, 8, 16) == 16384 + 32 * 4 * per
+    assert ws(32, 16, 2) == 16384 + 16 * 8 * per
     assert ws(32, 16, 16, splits=1) == 0
-    assert ws(32, 16, 16, splits=2) == 1024 + 128 * 2 * per
+    assert ws(32, 16, 16, splits=2) == 16384 + 128 * 2 * per

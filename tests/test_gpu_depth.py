@@ -1,0 +1,196 @@
+"""Parity at depth: every layer of a deep model held to the single-kernel tolerance, and the benchmarked geometry chained.
+
+A free-running 24-layer comparison mixes two things: the error each layer adds and the way 24 random-weight layers
+amplify any difference in their input (the reference's own truncating and round-to-nearest narrowings drift apart
+by more than the single-kernel tolerance over that depth).  The tests here separate them by *teacher forcing*:
+layer ``l`` on the GPU is given the oracle's input to layer ``l`` (residual stream, first block's QKV, cache
+contents), so its outputs carry one layer's error only and are held to the strict per-tensor tolerance of
+``tests/util.py`` at every layer and for both layer kinds:
+
+* residual stream out of the block and packed QKV: bf16 ``max|d| / max|want| <= 2e-2`` and cosine >= 0.999; with
+  e4m3 linears, cache and attention: cosine >= 0.999;
+* segment table: exact;
+* cache bytes: what the oracle's append writes when it is handed the very QKV tensor the GPU block produced -
+  V bytes exact, K bytes exact up to the rare one-code flips of ``sincosf`` against numpy's ``sin`` / ``cos``
+  (bounded as in ``tests/test_gpu_kernels.py``), rows outside the written slots untouched.
+
+The oracle chain runs with round-to-nearest bf16 narrowing, the rule of the reference's GPU kernels
+(``oracle/codec.py``).  The block wiring under test is ``src/quark/models/waypoint_15.py:389-440``.
+
+With ``QB_PARITY_REPORT`` set to a file name, the achieved figures are appended to it as JSON lines.
+"""
+
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import codec
+from oracle import model as omodel
+from oracle import ops
+from tests import util
+from tests.test_gpu_model import oquant, oracle_params
+from tests.util import f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def qb():
+    import quark_b200 as q
+
+    q._lib.require_device(0)
+    yield q
+    q.runtime.synchronize()
+    assert q._lib.device_status() == 0
+
+
+def _report(rec: dict) -> None:
+    path = os.environ.get("QB_PARITY_REPORT")
+    print(json.dumps(rec))
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(rec) + "\n")
+
+
+def _err(got_u16, want_u16):
+    g, w = f32(got_u16, "bf16").ravel(), f32(want_u16, "bf16").ravel()
+    assert np.all(np.isfinite(g))
+    return 1.0 - util.cosine(g, w), util.max_rel(g, w)
+
+
+def _strict(got_u16, want_u16, what, fp8):
+    c, m = _err(got_u16, want_u16)
+    assert c <= 1.0 - util.COS_MIN, f"{what}: 1-cos={c:.3e} max_rel={m:.3e}"
+    if not fp8:
+        assert m <= util.BF16_MAX_REL, f"{what}: 1-cos={c:.3e} max_rel={m:.3e}"
+    return c, m
+
+
+def _check_cache_bytes(gK, gV, wK, wV, kv_dt, what):
+    """Device caches against the oracle's append of the same QKV tensor onto the same previous contents."""
+    np.testing.assert_array_equal(gV, wV, err_msg=f"{what}: V bytes")
+    diff = gK != wK
+    if kv_dt == "e4m3":
+        assert diff.mean() <= 2e-3, f"{what}: {diff.sum()} of {gK.size} K bytes differ"
+        assert np.all(np.abs(gK.astype(np.int16)[diff] - wK.astype(np.int16)[diff]) <= 1), what
+    else:
+        big = np.abs(f32(wK, "bf16")) > 1e-2
+        assert np.max(util.bf16_ulp_diff(gK, wK)[big]) <= 2, what
+    # rows the append did not write are the previous contents in both, so whole rows differ only inside the slots
+    return float(diff.mean())
+
+
+def _prefill(cfg, model, states, kd, seed):
+    for li, blk in enumerate(model.blocks):
+        r = util.rng([seed, li])
+        for name in ("K_cache", "Vt_cache"):
+            a = codec.from_f32(r.standard_normal(states[li][name].shape, dtype=np.float32), kd)
+            states[li][name][...] = a
+            getattr(blk.kv_cache, name).copy_from_numpy(a)
+
+
+def _teacher_forced_nfe(qb, cfg, model, op, oq, states, lat, ft_val, sigma_idx, frozen, quant, tag):
+    """One NFE through the oracle, layer by layer; each GPU block runs on the oracle's input to that layer.
+    Returns the worst figures over the layers and the oracle's output latent."""
+    fp8 = quant == "fp8"
+    kd = "e4m3" if fp8 else "bf16"
+    ph, pw = cfg.patch
+    H2, W2 = cfg.height * ph, cfg.width * pw
+    ft = qb.QuarkTensor.from_numpy(np.array([ft_val], dtype=np.int32))
+    x = ops.patchify(lat, op["patchify.weight"], C=cfg.channels, H=H2, Wd=W2, ph=ph, pw=pw)
+    _strict(model.patchify(qb.QuarkTensor.from_numpy(lat, dtype="bf16")).to_numpy(), x, f"{tag} patchify", False)
+    qkv_first = None
+    worst = dict(x_1mcos=0.0, x_max_rel=0.0, qkv_1mcos=0.0, qkv_max_rel=0.0, k_byte_flips=0.0)
+    for li, blk in enumerate(model.blocks):
+        st = states[li]
+        kc = blk.kv_cache
+        kc.K_cache.copy_from_numpy(st["K_cache"])  # the oracle's cache contents before this layer's append
+        kc.Vt_cache.copy_from_numpy(st["Vt_cache"])
+        preK, preV = st["K_cache"].copy(), st["Vt_cache"].copy()
+        xg, qkvg = blk(qb.QuarkTensor.from_numpy(x, dtype="bf16"), sigma_idx, ft,
+                       qkv_first=None if qkv_first is None else qb.QuarkTensor.from_numpy(qkv_first, dtype="bf16"), frozen=frozen)
+        xg, qkvg = xg.to_numpy(), qkvg.to_numpy()
+        x, qkv = omodel.block_forward(cfg, li, op["blocks"][li], st, x, sigma_idx, ft_val, qkv_first=qkv_first, frozen=frozen, quant=oq)
+        kind = "global" if cfg.is_global(li) else "local"
+        c, m = _strict(xg, x, f"{tag} layer {li} ({kind}) residual stream", fp8)
+        cq, mq = _strict(qkvg, qkv, f"{tag} layer {li} ({kind}) qkv", fp8)
+        np.testing.assert_array_equal(kc.segments.to_numpy(), st["segments"], err_msg=f"{tag} layer {li}")
+        np.testing.assert_array_equal(kc.n_segments.to_numpy(), st["n_segments"])
+        wK, wV, _, _ = ops.kv_cache_update(qkvg, ft_val, int(frozen), n_kv_heads=cfg.n_kv_heads, n_q_heads=cfg.n_heads, H_spatial=cfg.height,
+                                           W_spatial=cfg.width, num_buckets=cfg.num_buckets(li), pinned_dilation=cfg.pinned_dilation(li),
+                                           kv_dtype=kd, K_cache=preK, Vt_cache=preV)  # fmt: skip
+        flips = _check_cache_bytes(kc.K_cache.to_numpy(), kc.Vt_cache.to_numpy(), wK, wV, kd, f"{tag} layer {li} cache")
+        worst = dict(x_1mcos=max(worst["x_1mcos"], c), x_max_rel=max(worst["x_max_rel"], m), qkv_1mcos=max(worst["qkv_1mcos"], cq),
+                     qkv_max_rel=max(worst["qkv_max_rel"], mq), k_byte_flips=max(worst["k_byte_flips"], flips))  # fmt: skip
+        if li == 0 and cfg.value_residual:
+            qkv_first = qkv
+    s_on, b_on = op["out_norm.lut"][sigma_idx]
+    hn = ops.ada_rmsnorm(x, s_on, b_on, activation="silu")
+    want = ops.unpatchify(hn, op["unpatchify.weight"], op["unpatchify.bias"], C=cfg.channels, H=H2, Wd=W2, ph=ph, pw=pw)
+    s_dev, b_dev = model._out_norm_luts[sigma_idx]
+    got = model.unpatchify(model.out_norm(qb.QuarkTensor.from_numpy(x, dtype="bf16"), s_dev, b_dev, activation="silu")).to_numpy()
+    _strict(got, want, f"{tag} out-norm + unpatchify", False)
+    return worst, want
+
+
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_every_layer_of_the_360p_model_within_the_single_kernel_tolerance(qb, quant):
+    """24 layers at 360p (128 tokens, d_model 2048, 32 / 16 heads), caches holding 128 frames of seeded K / V:
+    frame_t = 128 (a write frame of the global layers, commit pass) and 129 (denoise pass), teacher forced."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    q = QuantConfig.all_fp8() if quant == "fp8" else QuantConfig.all_bf16()
+    cfg = Waypoint15Config(height=16, width=8, quant=q)
+    params = make_params(cfg, seed=0)
+    model = qb.Waypoint15(cfg).load_params(params)
+    model.prepare()
+    op, oq = oracle_params(params, quant), oquant(quant)
+    states = omodel.new_state(cfg, oq)
+    _prefill(cfg, model, states, "e4m3" if quant == "fp8" else "bf16", 9)
+    lat = codec.f32_to_bf16(util.rng(1).standard_normal((1, cfg.latent_numel)).astype(np.float32))
+    with codec.bf16_rounding("rne"):
+        for ft_val, sigma_idx, frozen in [(128, 4, False), (129, 0, True)]:
+            worst, _ = _teacher_forced_nfe(qb, cfg, model, op, oq, states, lat, ft_val, sigma_idx, frozen, quant, f"360p {quant} ft={ft_val}")
+            _report(dict(test="teacher_forced_24_layers_360p", quant=quant, frame_t=ft_val, **{k: float(f"{v:.3e}") for k, v in worst.items()}))
+
+
+def test_bench_geometry_720p_fp8_chained(qb):
+    """The benchmarked configuration: 512 tokens (32 x 16), d_model 2048, 32 / 16 heads of 64, linears, cache and
+    attention all e4m3, the default (fully fused) wiring: QKV projection with head norm, value residual, RoPE(K)
+    and the cache append as its epilogue, attention emitting its e4m3 copy, out-proj with gate + residual, AdaRMSNorm
+    emitting e4m3, fc1 with SiLU to e4m3, fc2 with gate + residual.  Four layers (three local, one global), caches
+    pre-filled; a write frame (frame_t = 128: the global ring has wrapped, three segments) and the frame after.
+    Teacher forced per layer at the strict tolerance, then the same NFE free running against the oracle's latent."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    cfg = Waypoint15Config(height=32, width=16, n_layers=4, quant=QuantConfig.all_fp8())
+    assert [cfg.is_global(i) for i in range(4)] == [False, False, False, True]
+    assert cfg.fuse_gate_residual and cfg.fuse_silu and cfg.fuse_qkv_post and cfg.fuse_qkv_gemm
+    params = make_params(cfg, seed=2)
+    model = qb.Waypoint15(cfg).load_params(params)
+    model.prepare()
+    op, oq = oracle_params(params, "fp8"), oquant("fp8")
+    states = omodel.new_state(cfg, oq)
+    _prefill(cfg, model, states, "e4m3", 21)
+    lat = codec.f32_to_bf16(util.rng(3).standard_normal((1, cfg.latent_numel)).astype(np.float32))
+    with codec.bf16_rounding("rne"):
+        for ft_val, sigma_idx, frozen in [(128, 4, False), (129, 0, True)]:
+            before = [{k: v.copy() for k, v in st.items()} for st in states]
+            worst, want = _teacher_forced_nfe(qb, cfg, model, op, oq, states, lat, ft_val, sigma_idx, frozen, "fp8", f"720p fp8 ft={ft_val}")
+            assert [int(st["n_segments"][0]) for st in states] == ([3, 3, 3, 3] if ft_val == 128 else [2, 2, 2, 2])
+            # free running: the device's own chain from the same starting state
+            for blk, st in zip(model.blocks, before):
+                blk.kv_cache.K_cache.copy_from_numpy(st["K_cache"])
+                blk.kv_cache.Vt_cache.copy_from_numpy(st["Vt_cache"])
+            ft = qb.QuarkTensor.from_numpy(np.array([ft_val], dtype=np.int32))
+            got = model(qb.QuarkTensor.from_numpy(lat, dtype="bf16"), sigma_idx, ft, frozen=frozen).to_numpy()
+            c, m = _err(got, want)
+            assert c <= 1.0 - util.COS_MIN, f"720p fp8 4-layer NFE ft={ft_val}: 1-cos={c:.3e} max_rel={m:.3e}"
+            _report(dict(test="bench_geometry_720p_fp8", frame_t=ft_val, free_running_1mcos=float(f"{c:.3e}"), free_running_max_rel=float(f"{m:.3e}"),
+                         **{k: float(f"{v:.3e}") for k, v in worst.items()}))  # fmt: skip
+            # leave the device caches as the oracle's, so that the next frame starts from equal state
+            for blk, st in zip(model.blocks, states):
+                blk.kv_cache.K_cache.copy_from_numpy(st["K_cache"])
+                blk.kv_cache.Vt_cache.copy_from_numpy(st["Vt_cache"])

@@ -560,6 +560,97 @@ def test_owl_attn_empty_segments_give_zero(qb):
     assert not got.any()
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("nb", [64, 256])
+def test_owl_attn_long_histories(qb, kv_dt, nb):
+    """The histories of the isolated attention sweep: 64 and 256 buckets of 512 tokens (capacity up to 131 584 rows
+    per head, tensor maps of 2.1 M rows), global-bucket geometry (dilation 8), on a write frame after the ring has
+    wrapped (three segments, one bucket masked) and on the frame after (two segments).  The kernel runs on all 32
+    heads; the oracle (src/quark/kernels/owl_attn/reference.py:47-111) on the four Q heads of the first and the last
+    KV head, which it finishes in seconds."""
+    H, W, Hk, gqa, pd = 32, 16, 16, 2, 8
+    tpf, cap = H * W, (nb + 1) * H * W
+    r = util.rng(500 + nb)
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, 4096)), n_q_heads=32, n_kv_heads=16)
+    Kf = r.standard_normal((Hk * cap, 64), dtype=np.float32)
+    Vf = r.standard_normal((Hk * 64, cap), dtype=np.float32)
+    if kv_dt == "bf16":
+        Kd, Vd = T(qb, codec.f32_to_bf16(Kf), "bf16"), T(qb, codec.f32_to_bf16(Vf), "bf16")
+    else:  # the device narrowing is bit-exact against the oracle's encoder (tested above); the host encodes the compared heads only
+        Kd, Vd = qb.qf.quantize_e4m3(T(qb, Kf)), qb.qf.quantize_e4m3(T(qb, Vf))
+    heads = [0, Hk - 1]
+    to = codec.f32_to_bf16 if kv_dt == "bf16" else codec.f32_to_e4m3
+    Ks = to(np.concatenate([Kf[h * cap : (h + 1) * cap] for h in heads]))
+    Vs = to(np.concatenate([Vf[h * 64 : (h + 1) * 64] for h in heads]))
+    del Kf, Vf
+    qcols = np.concatenate([np.arange(2 * h * 64, (2 * h + 2) * 64) for h in heads])
+    qkv_sub = np.concatenate([qkv[:, qcols], np.zeros((tpf, 2 * len(heads) * 64), np.uint16)], axis=1)
+    for ft in (nb * pd, nb * pd + 1):
+        segs, n = ops.compute_segments(ft, nb, tpf, pd)
+        assert n == (3 if ft == nb * pd else 2)
+        got = qb.qf.owl_attn(T(qb, qkv, "bf16"), Kd, Vd, T(qb, np.asarray(segs, np.int32)), T(qb, np.array([n], np.int32)), 1, Hk, gqa, H, W, nb, pd,
+                             compute_dtype="e4m3" if kv_dt == "e4m3" else None, packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32))).to_numpy()  # fmt: skip
+        want = ops.owl_attn(qkv_sub, Ks, Vs, segs, [n], ft, n_kv_heads=len(heads), gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype=kv_dt,
+                            q_quant="e4m3" if kv_dt == "e4m3" else None)  # fmt: skip
+        _attn_check(got[:, qcols], want, f"attn {nb} buckets ft={ft} {kv_dt}", kv_dt == "e4m3")
+        assert np.all(np.isfinite(f32(got, "bf16")))
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_owl_attn_per_head_scales(qb, splits):
+    """k_scale / v_scale (an extension: the reference's e4m3 is scale free): the caches hold K / k_scale[h] and
+    V / v_scale[h] in e4m3 and the kernel computes S = (Q . Kq^T) * k_scale[h] / 8, O = (P . Vq) * v_scale[h].
+    Against the oracle run on the de-scaled caches; NULL scales are the scale-free kernel, bit for bit."""
+    r = util.rng(61)
+    Hk, gqa, H, W, nb, pd, ft = 4, 2, 16, 16, 8, 1, 11
+    tpf, cap = H * W, (nb + 1) * H * W
+    qkv = ops.head_rmsnorm(bf16_randn(r, (tpf, (Hk * gqa + 2 * Hk) * 64)), n_q_heads=Hk * gqa, n_kv_heads=Hk)
+    ks = np.array([0.5, 0.03125, 1.75, 0.011], np.float32)
+    vs = np.array([2.0, 0.0625, 0.4, 0.02], np.float32)
+    Kf = r.standard_normal((Hk, cap, 64), dtype=np.float32)
+    Vf = r.standard_normal((Hk, 64, cap), dtype=np.float32)
+    Kq = codec.f32_to_e4m3(Kf * (np.float32(1) / ks)[:, None, None]).reshape(Hk * cap, 64)
+    Vq = codec.f32_to_e4m3(Vf * (np.float32(1) / vs)[:, None, None]).reshape(Hk * 64, cap)
+    segs, n = ops.compute_segments(ft, nb, tpf, pd)
+    args = (T(qb, qkv, "bf16"), T(qb, Kq, "e4m3"), T(qb, Vq, "e4m3"), T(qb, np.asarray(segs, np.int32)), T(qb, np.array([n], np.int32)), 1, Hk, gqa, H, W, nb, pd)
+    kw = dict(compute_dtype="e4m3", packed_qkv=True, frame_t=T(qb, np.array([ft], np.int32)), kv_splits=splits)
+    got = qb.qf.owl_attn(*args, k_scale=T(qb, ks), v_scale=T(qb, vs), **kw).to_numpy()
+    # the oracle on the values the scaled bytes stand for
+    Kd = (codec.e4m3_to_f32(Kq).reshape(Hk, cap, 64) * ks[:, None, None]).reshape(Hk * cap, 64)
+    Vd = (codec.e4m3_to_f32(Vq).reshape(Hk, 64, cap) * vs[:, None, None]).reshape(Hk * 64, cap)
+    want = ops.owl_attn(qkv, Kd, Vd, segs, [n], ft, n_kv_heads=Hk, gqa_ratio=gqa, H_spatial=H, W_spatial=W, kv_dtype="f32", q_quant="e4m3")
+    _attn_check(got, want, f"attn with per-head scales, splits={splits}", True)
+    for h in range(Hk * gqa):  # per head, so that a scale applied to the wrong head cannot hide in the average
+        _attn_check(got[:, h * 64 : (h + 1) * 64], want[:, h * 64 : (h + 1) * 64], f"scaled attn head {h}", True)
+    ones = np.ones(Hk, np.float32)
+    a = qb.qf.owl_attn(*args, **kw).to_numpy()
+    b = qb.qf.owl_attn(*args, k_scale=T(qb, ones), v_scale=T(qb, ones), **kw).to_numpy()
+    np.testing.assert_array_equal(a, b)
+
+
+def test_gemm_calls_of_different_shapes_share_one_workspace(qb):
+    """The tile counters sit in a fixed area at the start of the workspace: a call that leaves an e4m3 copy of A
+    (or partial sums) in the workspace must not disturb a later call that sums K slices through it with more
+    tiles than the first call had, and a workspace that grows is retired, not freed (a captured CUDA graph may
+    still hold its address)."""
+    from quark_b200 import functional as qfm
+
+    got1, want1 = _gemm_case(qb, 128, 256, 512, fp8=True, seed=21)  # bf16 A: narrowed into the workspace
+    _check_gemm(got1, want1, "fp8 GEMM with a bf16 A", True)
+    ws_before = qfm._workspace(0)
+    # 512 x 4096 in 64-column tiles = 256 tiles... and 1024 x 4096 = 512 tiles, three K slices through the workspace
+    for M in (512, 1024):
+        one, want = _gemm_case(qb, M, 4096, 768, fp8=True, split_k=1, tile_n=64, seed=22)
+        got, _ = _gemm_case(qb, M, 4096, 768, fp8=True, split_k=3, tile_n=64, slice_mode=1, seed=22)
+        _check_gemm(got, want, f"workspace K slices after another shape, M={M}", True)
+        again, _ = _gemm_case(qb, M, 4096, 768, fp8=True, split_k=3, tile_n=64, slice_mode=1, seed=22)
+        np.testing.assert_array_equal(got.to_numpy(), again.to_numpy())
+        assert util.cosine(f32(got.to_numpy(), "bf16"), f32(one.to_numpy(), "bf16")) >= 0.99999
+    ws_after = qfm._workspace(0)
+    if ws_after is not ws_before:  # it grew: the old buffer must still be owned
+        assert any(t is ws_before for t in qfm._RETIRED_WS)
+
+
 # --------------------------------------------------------------------------- randn
 
 
