@@ -54,7 +54,8 @@ int32_t qb_device_count(void);
 int32_t qb_device_check(int32_t device);
 int32_t qb_set_device(int32_t device);
 /* Reads and clears the device status word that kernels set when a bounded wait ran out
- * (bit 0 GEMM, bit 1 attention) or a segment table was malformed (bit 2).  Synchronises. */
+ * (bit 0 GEMM, bit 1 attention, bit 3 the cross-GPU reduction) or a segment table was malformed (bit 2).
+ * Synchronises. */
 int32_t qb_device_status(uint32_t* status_host);
 /* Number of kernels this library has launched since it was loaded (launches recorded into a CUDA
  * graph during capture count once, replays do not count). */
@@ -327,6 +328,54 @@ int32_t qb_unpatchify(const void* X, const void* W, const void* bias, void* out,
  * (ref: src/quark/kernels/patchify/reference.py:8-23, src/quark/kernels/unpatchify/reference.py:8-24). */
 int32_t qb_patch_gather(const void* latent, void* tokens_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream);
 int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int32_t H, int32_t Wd, int32_t ph, int32_t pw, void* stream);
+
+/* ------------------------------------------------------------------ one session over several GPUs
+ * The reference is single-GPU (ref: src/quark/models/waypoint_15.py:318, :333: B = 1, one device); nothing below has a
+ * counterpart there.  When a block is sharded by KV-head group, out-proj and fc2 are row-parallel and their partial
+ * outputs [rows, D] bf16 must be summed over the ranks before gate and residual are applied.  qb_tp_reduce does that
+ * sum, `x + gate * sum`, and optionally the AdaRMSNorm that follows, as one kernel per rank over peer-mapped memory
+ * (plain loads and stores over NVLink; no TMA, no multicast), in place of an NCCL all-reduce and two more launches:
+ *   x_new[m, :] = residual[m, :] + gate[m / (rows / G), :] * bf16(sum over ranks r, in rank order, of y_r[m, :])
+ *   h[m, :]     = ada_rmsnorm(x_new[m, :]; norm_scale, norm_bias, eps, norm_activation)        (when norm_scale != NULL)
+ * with the rounding points of qb_ada_gate_residual and qb_ada_rmsnorm, so every rank ends up with the same bytes.
+ *
+ * Each rank owns an arena of qb_tp_arena_bytes(rows, D) bytes from qb_malloc, zeroed once, laid out as
+ * [4 KiB of flags | y | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)] (byte offsets of the five buffers from
+ * qb_tp_arena_offsets).  The rank's row-parallel GEMM writes its partial into its own y; the kernel reads every rank's
+ * y and writes its share of the rows of x_new (slot p->x_slot), h and hq (if emit_h / emit_hq) into EVERY rank's arena.
+ * arena[r] is rank r's arena as mapped in the calling process: arena[rank] the rank's own pointer, the others from
+ * qb_ipc_open of a handle that rank r made with qb_ipc_export.  Consecutive calls must alternate x_slot when the
+ * residual of one call is the x_new of the call before (the block does: 0 after attention, 1 after the MLP).
+ * All ranks must make the same sequence of calls.  A rank waits (bounded: wait_limit_us, 0 = about one second) for its
+ * peers' kernels of the same call to start and to deliver their rows; when the limit runs out the kernel raises bit 3
+ * of the device status word and returns with the outputs unspecified.  Stream-capturable. */
+typedef struct {
+  int32_t world, rank;
+  int32_t rows, D;                   /* the partial is [rows, D] bf16; rows % world == 0, D % 8 == 0, D <= 8192 */
+  int32_t gate_groups, norm_groups;  /* gate [gate_groups, D], norm_scale / norm_bias [norm_groups, D] */
+  int32_t norm_activation;           /* 0 none, 1 SiLU (the output norm) */
+  int32_t x_slot;                    /* 0 or 1: which x buffer of the arenas receives x_new */
+  int32_t emit_h, emit_hq;           /* write the norm's result as bf16 / as e4m3 */
+  int32_t wait_limit_us;             /* 0 = default */
+  float eps;
+  void* arena[8];
+} qb_tp_params;
+
+size_t qb_tp_arena_bytes(int32_t rows, int32_t D);
+/* offsets5_host[0..4] = byte offsets of y, x slot 0, x slot 1, h, hq inside an arena. */
+int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets5_host);
+int32_t qb_tp_reduce(const void* residual, const void* gate, const void* norm_scale, const void* norm_bias, const qb_tp_params* p,
+                     void* stream);
+/* The same protocol with all `world` ranks run as ONE cooperative launch on the calling GPU, over arenas that all live on
+ * it (residuals[r] is rank r's residual): for tests on a single GPU, where kernels that wait on one another must not be
+ * separate launches.  p->rank is ignored. */
+int32_t qb_tp_reduce_emulated(const void* const* residuals, const void* gate, const void* norm_scale, const void* norm_bias,
+                              const qb_tp_params* p, void* stream);
+/* CUDA IPC for the arenas: a 64-byte handle of a qb_malloc allocation, and its mapping in another process of the same
+ * node (the exporting GPU must be visible to the importing process and peer access possible). */
+int32_t qb_ipc_export(void* device_ptr, void* handle64_host);
+int32_t qb_ipc_open(const void* handle64_host, void** ptr_host);
+int32_t qb_ipc_close(void* ptr);
 
 #ifdef __cplusplus
 }

@@ -71,6 +71,15 @@ class AttnParams(C.Structure):
     ]  # fmt: skip
 
 
+class TpParams(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("rows", C.c_int32), ("D", C.c_int32),
+        ("gate_groups", C.c_int32), ("norm_groups", C.c_int32), ("norm_activation", C.c_int32), ("x_slot", C.c_int32),
+        ("emit_h", C.c_int32), ("emit_hq", C.c_int32), ("wait_limit_us", C.c_int32), ("eps", C.c_float),
+        ("arena", C.c_void_p * 8),
+    ]  # fmt: skip
+
+
 _P, _I, _Z, _F, _U = C.c_void_p, C.c_int32, C.c_size_t, C.c_float, C.c_uint32
 
 # name -> (restype, argtypes); every symbol include/quark_b200.h declares
@@ -133,6 +142,13 @@ SIGNATURES = {
     "qb_unpatchify": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
+    "qb_tp_arena_bytes": (_Z, [_I, _I]),
+    "qb_tp_arena_offsets": (_I, [_I, _I, C.POINTER(_Z)]),
+    "qb_tp_reduce": (_I, [_P, _P, _P, _P, C.POINTER(TpParams), _P]),
+    "qb_tp_reduce_emulated": (_I, [C.POINTER(_P), _P, _P, _P, C.POINTER(TpParams), _P]),
+    "qb_ipc_export": (_I, [_P, _P]),
+    "qb_ipc_open": (_I, [_P, C.POINTER(_P)]),
+    "qb_ipc_close": (_I, [_P]),
 }
 
 _lib = None

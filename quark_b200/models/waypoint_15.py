@@ -357,15 +357,24 @@ class TransformerBlock(nn.Module):
             self.mlp = nn.MLP(d, cfg.mlp_dim_local, d, out_dtype="bf16", fuse_silu=cfg.fuse_silu)
         self.mlp_gate = nn.AdaGateResidual()
 
-    def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None):
-        """Returns ``(x, qkv)`` (``src/quark/models/waypoint_15.py:389-440``)."""
+    def forward(self, x, sigma_idx: int, frame_t, *, qkv_first, ctrl_emb=None, frozen: bool = False, x_out=None, h_in=None, next_norm=None):
+        """Returns ``(x, qkv)`` (``src/quark/models/waypoint_15.py:389-440``).
+
+        Tensor-parallel ranks with a fused reduction (``comm.fused``): the sum over the ranks, gate + residual and the
+        AdaRMSNorm that follows are one kernel, so the pre-MLP norm never runs as a launch of its own, and the norm that
+        follows the block (``next_norm = (scale, bias, activation, emit_e4m3)``: the next block's pre-attention norm, or
+        the output norm) is produced by this block's last reduction and left in ``self.h_next``; ``h_in`` is what the
+        previous block left there."""
         s0, b0, g0, s1, b1, g1 = self._cond_lut[sigma_idx]
         fp8 = self.qkv_proj.weight.data.dtype == "e4m3"
         tp = self._cfg.tp_world > 1
+        tp_fused = tp and getattr(self._comm, "fused", False)
         # row-parallel partial outputs are summed over the ranks before gate and residual are applied (once)
         fuse = self._cfg.fuse_gate_residual and not tp
+        self.h_next = None
+        arena = self._comm.arena(x.numel // int(x.shape[-1]), int(x.shape[-1])) if tp_fused else None
 
-        h0 = self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)
+        h0 = h_in if h_in is not None else self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)
         use_first = hasattr(self, "v_residual") and qkv_first is not None
         quilted = self._cfg.quilt_factor > 1  # the fused passes append every token; a quilted cache takes the plain kernels
         if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm and not quilted:
@@ -394,8 +403,12 @@ class TransformerBlock(nn.Module):
                 qkv = self.v_residual(qkv, qkv_first)
             self.kv_cache(qkv, frame_t, frozen=frozen)
         attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8)
+        h = None
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
+        elif tp_fused:
+            self.out_proj(attn_out, out=arena.y)  # the partial goes straight into the peer-mapped buffer
+            x, h = arena.reduce(x, g0, s1, b1, x_slot=0, emit_e4m3=fp8)
         else:
             y = self.out_proj(attn_out)
             if tp:
@@ -404,11 +417,16 @@ class TransformerBlock(nn.Module):
         if ctrl_emb is not None and hasattr(self, "ctrl_fusion"):
             x = self.ctrl_residual(x, self.ctrl_fusion(self.ctrl_x_norm(x), self.ctrl_emb_norm(ctrl_emb)))
         moe = self._cfg.moe
-        h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8 and not moe)  # the router reads bf16; MoE narrows for its experts itself
+        if h is None:
+            h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8 and not moe)  # the router reads bf16; MoE narrows for its experts itself
         if moe:
             x = self.mlp_gate(x, self.mlp(h), g1)
         elif fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
+        elif tp_fused:
+            self.mlp(h, out=arena.y)
+            ns, nb_, act, emit = next_norm if next_norm is not None else (None, None, None, False)
+            x, self.h_next = arena.reduce(x, g1, ns, nb_, activation=act, x_slot=1, emit_e4m3=emit)
         else:
             y = self.mlp(h)
             if tp:
@@ -503,11 +521,21 @@ class Waypoint15(nn.Module):
         if self._x_bufs is None:
             self._x_bufs = (QuarkTensor.empty(*x.shape, dtype="bf16"), QuarkTensor.empty(*x.shape, dtype="bf16"))
         qkv_first = None
+        fp8 = self.cfg.quant.linear == "fp8"
+        h_in = None
         for li, block in enumerate(self.blocks):
-            x, qkv = block(x, sigma_idx, frame_t, qkv_first=qkv_first, ctrl_emb=ctrl_emb, frozen=frozen, x_out=self._x_bufs[li & 1])
+            # what follows this block's last reduction (used by tensor-parallel ranks with the fused reduction only)
+            if li + 1 < len(self.blocks):
+                nlut = self.blocks[li + 1]._cond_lut[sigma_idx]
+                next_norm = (nlut[0], nlut[1], None, fp8)
+            else:
+                next_norm = (s_on, b_on, "silu", False)
+            x, qkv = block(x, sigma_idx, frame_t, qkv_first=qkv_first, ctrl_emb=ctrl_emb, frozen=frozen, x_out=self._x_bufs[li & 1], h_in=h_in,
+                           next_norm=next_norm)  # fmt: skip
+            h_in = block.h_next
             if li == 0 and self.cfg.value_residual:
                 qkv_first = qkv
-        x = self.out_norm(x, s_on, b_on, activation="silu")
+        x = h_in if h_in is not None else self.out_norm(x, s_on, b_on, activation="silu")
         return self.unpatchify(x)
 
 

@@ -18,8 +18,8 @@ import time
 
 from . import stream as _stream
 
-_NCCL_BF16, _NCCL_F32, _NCCL_SUM, _NCCL_MAX = 9, 7, 0, 2
-_DT = {"bf16": _NCCL_BF16, "f32": _NCCL_F32}
+_NCCL_BF16, _NCCL_F32, _NCCL_S32, _NCCL_SUM, _NCCL_MAX = 9, 7, 2, 0, 2
+_DT = {"bf16": _NCCL_BF16, "f32": _NCCL_F32, "s32": _NCCL_S32}
 
 
 class NcclError(RuntimeError):
@@ -177,6 +177,35 @@ class NcclComm:
         comm = C.c_void_p()
         _check(lib.ncclCommInitRank(C.byref(comm), self.world, uid, self.rank), "ncclCommInitRank")
         self._comm = comm
+        self._arenas = {}
+        if self.fused:
+            self.reduction_name = "one kernel per rank over peer-mapped buffers: sum + gate / residual + the next AdaRMSNorm (qb_tp_reduce)"
+
+    def all_gather_bytes(self, mine: bytes) -> list:
+        """Every rank's byte string (all of one length, a multiple of 4), in rank order; synchronises the stream."""
+        import numpy as np
+
+        from .tensor import QuarkTensor
+
+        n = len(mine) // 4
+        host = np.zeros((self.world, n), dtype=np.int32)
+        host[self.rank] = np.frombuffer(mine, dtype=np.int32)
+        t = QuarkTensor.from_numpy(host)
+        self._all_reduce(t, _NCCL_SUM)  # every slot is zero on all ranks but its owner
+        out = t.to_numpy()
+        return [out[r].tobytes() for r in range(self.world)]
+
+    def arena(self, rows: int, D: int):
+        """The peer-mapped arena for partial outputs of shape [rows, D] (made on first use: call once eagerly on every
+        rank before a CUDA graph is captured)."""
+        key = (int(rows), int(D))
+        a = self._arenas.get(key)
+        if a is None:
+            from .tp import TpArena
+
+            a = TpArena(self.rank, self.world, rows, D, self.all_gather_bytes)
+            self._arenas[key] = a
+        return a
 
     def _all_reduce(self, t, op):
         if t.dtype not in _DT:
@@ -205,6 +234,10 @@ class NcclComm:
         if self._comm is None:
             return True
         import threading
+
+        for a in self._arenas.values():  # every kernel of this rank has finished (the caller synchronised): unmap the peers
+            a.close()
+        self._arenas = {}
 
         comm, self._comm = self._comm, None
         th = threading.Thread(target=lambda: load().ncclCommDestroy(comm), daemon=True)

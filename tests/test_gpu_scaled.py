@@ -64,7 +64,7 @@ def test_row_scaled_narrowing_is_bit_exact(qb):
     np.testing.assert_array_equal(s.to_numpy(), ws)
     np.testing.assert_array_equal(q.to_numpy(), wq)
     assert ws[5] == 1.0 and not wq[5].any()
-    assert np.all(np.max(codec.e4m3_to_f32(wq[ws != 1.0]), axis=1) == 448.0)  # every row uses the top code
+    assert np.all(np.max(np.abs(codec.e4m3_to_f32(wq[ws != 1.0])), axis=1) == 448.0)  # every row uses the top code
 
 
 @pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])

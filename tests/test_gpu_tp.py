@@ -22,9 +22,8 @@ ROOT = Path(__file__).resolve().parent.parent
 _CHILD = r"""
 import os, sys, time
 import numpy as np
-rank, world, tmp, quant = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
-os.environ["CUDA_VISIBLE_DEVICES"] = str(rank)
-os.environ["NCCL_NVLS_ENABLE"] = "0"
+rank, world, tmp, quant, fused = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[6] == "1"
+os.environ["NCCL_NVLS_ENABLE"] = "0"  # every GPU stays visible: the fused reduction maps the peers' buffers (CUDA IPC)
 sys.path.insert(0, sys.argv[5])
 import quark_b200 as qb
 from quark_b200.models import QuantConfig, Waypoint15Config, make_params
@@ -44,10 +43,11 @@ cfg = Waypoint15Config(**{**base.__dict__, "tp_world": world, "tp_rank": rank})
 params = make_params(base, seed=8, weight_std=0.08)
 r = np.random.default_rng(44)
 lats = [r.standard_normal((1, base.latent_numel)).astype(np.float32) for _ in range(4)]
-qb._lib.require_device(0)
+qb._lib.require_device(rank)
+qb._lib.check(qb._lib.load().qb_set_device(rank))
 barrier("loaded")                      # both ranks have a working library and a GPU
-comm = NcclComm(rank, world, os.path.join(tmp, "nccl.id"))
-eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, comm=comm, use_graph=True)
+comm = NcclComm(rank, world, os.path.join(tmp, "nccl.id"), fused=fused)
+eng = qb.Engine(cfg=cfg, quant=cfg.quant, params=params, comm=comm, use_graph=True, device=rank)
 barrier("built")
 eng.append_frame(lats[0])
 blk0 = eng.model.blocks[0].kv_cache
@@ -60,7 +60,7 @@ eng.close()                            # the frame graph holds the communicator'
 assert comm.destroy(), "ncclCommDestroy did not return"
 res = dict(status=status, k0=k0, v0=v0, **{f"out{k}": o for k, o in enumerate(outs)})
 if rank == 0:                          # the single-GPU session with the same weights and inputs
-    ref = qb.Engine(cfg=base, quant=base.quant, params=params, use_graph=True)
+    ref = qb.Engine(cfg=base, quant=base.quant, params=params, use_graph=True, device=rank)
     ref.append_frame(lats[0])
     b0 = ref.model.blocks[0].kv_cache
     res.update(ref_k0=b0.K_cache.to_numpy(), ref_v0=b0.Vt_cache.to_numpy())
@@ -71,8 +71,11 @@ print("TP_CHILD_OK", rank)
 """
 
 
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl", "fused"])
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
-def test_two_rank_session_matches_the_single_gpu_session(tmp_path, quant):
+def test_two_rank_session_matches_the_single_gpu_session(tmp_path, quant, fused):
+    """`fused`: the sum over the ranks, gate + residual and the following AdaRMSNorm as one kernel over peer-mapped
+    buffers (`qb_tp_reduce`); otherwise ncclAllReduce followed by the gate and norm kernels."""
     import quark_b200 as qb
 
     if qb._lib.device_count() < 2:
@@ -80,7 +83,7 @@ def test_two_rank_session_matches_the_single_gpu_session(tmp_path, quant):
     world = 2
     script = tmp_path / "child.py"
     script.write_text(_CHILD)
-    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), str(tmp_path), quant, str(ROOT)], stdout=subprocess.PIPE,
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), str(tmp_path), quant, str(ROOT), "1" if fused else "0"], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(world)]  # fmt: skip
     # wait for both; as soon as one rank fails the other is stopped (it would wait for its peer otherwise)
     import time

@@ -1,0 +1,141 @@
+"""The fused cross-GPU reduction (``qb_tp_reduce``) on ONE GPU.
+
+Kernels that wait on one another must never be separate launches on one GPU, so the protocol is exercised through
+``qb_tp_reduce_emulated``: all ranks run as one cooperative launch over arenas that all live on this GPU, with the same
+flags, epochs, peer loads and peer stores as the multi-GPU kernel (the peers' arenas are simply local pointers).
+Checked: every rank's arena ends up with the bytes of the unfused chain (sum in rank order rounded to bf16, then
+``qf.ada_gate_residual``, then ``qf.ada_rmsnorm`` with its bf16 and e4m3 outputs), over consecutive calls that reuse
+the buffers the way a block does.  The bounded wait is checked with a peer that never shows up: the kernel must come
+back on its own, with bit 3 of the device status word raised, and the context must stay usable.  The multi-process path
+is covered by ``tests/test_gpu_tp.py`` (needs two GPUs).  The reference is single-GPU and has no counterpart.
+"""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import codec
+from tests import util
+from tests.util import bf16_randn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def qb():
+    import quark_b200 as q
+
+    q._lib.require_device(0)
+    yield q
+    q.runtime.synchronize()
+    assert q._lib.device_status() == 0
+
+
+def T(qb, arr, dtype=None):
+    return qb.QuarkTensor.from_numpy(np.asarray(arr), dtype=dtype)
+
+
+class Arenas:
+    def __init__(self, qb, world, rows, D):
+        lib = qb._lib.load()
+        self.qb, self.world, self.rows, self.D = qb, world, rows, D
+        n = int(lib.qb_tp_arena_bytes(rows, D))
+        assert n == 4096 + rows * D * 9
+        self.bufs = [qb.QuarkTensor.zeros(n, dtype="e4m3") for _ in range(world)]
+        off = (C.c_size_t * 5)()
+        qb._lib.check(lib.qb_tp_arena_offsets(rows, D, off))
+        self.off = [int(o) for o in off]
+
+    def view(self, r, i, dt="bf16"):
+        return self.qb.QuarkTensor.borrow(self.bufs[r].data_ptr() + self.off[i], (self.rows, self.D), dt, keepalive=self.bufs[r])
+
+    def params(self, **kw):
+        p = self.qb._lib.TpParams(world=self.world, rank=0, rows=self.rows, D=self.D, gate_groups=1, norm_groups=1, eps=1e-6, **kw)
+        for r in range(self.world):
+            p.arena[r] = self.bufs[r].data_ptr()
+        return p
+
+
+def rank_order_sum_bf16(parts):
+    acc = np.zeros(parts[0].shape, np.float32)
+    for y in parts:
+        acc = (acc + codec.bf16_to_f32(y)).astype(np.float32)
+    return codec.f32_to_bf16_rne(acc)
+
+
+@pytest.mark.parametrize("world,rows,D", [(2, 64, 256), (4, 512, 2048), (8, 128, 2048)])
+def test_emulated_ranks_reproduce_the_unfused_chain(qb, world, rows, D):
+    r = util.rng(900 + world)
+    lib = qb._lib.load()
+    ar = Arenas(qb, world, rows, D)
+    gate, ns, nb = (T(qb, bf16_randn(r, (1, D)), "bf16") for _ in range(3))
+    x_host = bf16_randn(r, (rows, D))
+    residuals = [T(qb, x_host, "bf16") for _ in range(world)]  # x is replicated on the ranks
+    ptr = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    s = C.c_void_p(qb.runtime.active_stream())
+    for call, (slot, act, emit_q) in enumerate([(0, None, True), (1, None, False), (0, "silu", False), (1, None, True)]):
+        parts = [bf16_randn(r, (rows, D), 0.5) for _ in range(world)]
+        for rk in range(world):
+            ar.view(rk, 0).copy_from_numpy(parts[rk])
+        p = ar.params(x_slot=slot, norm_activation=1 if act else 0, emit_h=0 if emit_q else 1, emit_hq=1 if emit_q else 0)
+        res = (C.c_void_p * world)(*[t.data_ptr() for t in residuals])
+        qb._lib.check(lib.qb_tp_reduce_emulated(res, ptr(gate), ptr(ns), ptr(nb), C.byref(p), s))
+        qb.runtime.synchronize()
+        assert qb._lib.device_status() == 0
+        # the unfused chain on the same inputs
+        summed = T(qb, rank_order_sum_bf16(parts), "bf16")
+        want_x = qb.qf.ada_gate_residual(residuals[0], summed, gate)
+        want_q = qb.QuarkTensor.empty(rows, D, dtype="e4m3")
+        want_h = qb.qf.ada_rmsnorm(want_x, ns, nb, activation=act, out_q=want_q)
+        for rk in range(world):
+            np.testing.assert_array_equal(ar.view(rk, 1 + slot).to_numpy(), want_x.to_numpy(), err_msg=f"call {call} rank {rk}: x")
+            if emit_q:
+                np.testing.assert_array_equal(ar.view(rk, 4, "e4m3").to_numpy(), want_q.to_numpy(), err_msg=f"call {call} rank {rk}: hq")
+            else:
+                np.testing.assert_array_equal(ar.view(rk, 3).to_numpy(), want_h.to_numpy(), err_msg=f"call {call} rank {rk}: h")
+        residuals = [ar.view(rk, 1 + slot) for rk in range(world)]  # the next call's residual is this call's x, as in a block
+
+
+def test_reduction_without_a_norm_and_with_gate_groups(qb):
+    r = util.rng(950)
+    lib = qb._lib.load()
+    world, rows, D, G = 2, 64, 512, 4
+    ar = Arenas(qb, world, rows, D)
+    gate = T(qb, bf16_randn(r, (G, D)), "bf16")
+    x_host = bf16_randn(r, (rows, D))
+    residuals = [T(qb, x_host, "bf16") for _ in range(world)]
+    parts = [bf16_randn(r, (rows, D)) for _ in range(world)]
+    for rk in range(world):
+        ar.view(rk, 0).copy_from_numpy(parts[rk])
+    p = ar.params(x_slot=0)
+    p.gate_groups = G
+    res = (C.c_void_p * world)(*[t.data_ptr() for t in residuals])
+    qb._lib.check(lib.qb_tp_reduce_emulated(res, C.c_void_p(gate.data_ptr()), None, None, C.byref(p), C.c_void_p(qb.runtime.active_stream())))
+    want = qb.qf.ada_gate_residual(residuals[0], T(qb, rank_order_sum_bf16(parts), "bf16"), gate)
+    for rk in range(world):
+        np.testing.assert_array_equal(ar.view(rk, 1).to_numpy(), want.to_numpy())
+
+
+def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit(qb):
+    """Rank 0 of a world of two, launched alone through the multi-GPU entry point: nothing ever sets rank 1's flags.
+    The wait is given 2 ms; the kernel must return by itself, report bit 3, and leave the GPU usable."""
+    r = util.rng(960)
+    lib = qb._lib.load()
+    rows, D = 64, 256
+    ar = Arenas(qb, 2, rows, D)
+    gate = T(qb, bf16_randn(r, (1, D)), "bf16")
+    x = T(qb, bf16_randn(r, (rows, D)), "bf16")
+    ar.view(0, 0).copy_from_numpy(bf16_randn(r, (rows, D)))
+    p = ar.params(x_slot=0, wait_limit_us=2000)
+    qb._lib.check(lib.qb_tp_reduce(C.c_void_p(x.data_ptr()), C.c_void_p(gate.data_ptr()), None, None, C.byref(p), C.c_void_p(qb.runtime.active_stream())))
+    qb.runtime.synchronize()
+    assert qb._lib.device_status() == 8  # bit 3: the cross-GPU reduction's wait ran out (reading clears it)
+    assert qb._lib.device_status() == 0
+    # the context is alive: an ordinary kernel runs and is right
+    y = T(qb, bf16_randn(r, (rows, D)), "bf16")
+    got = qb.qf.ada_gate_residual(x, y, gate).to_numpy()
+    assert np.all(np.isfinite(codec.bf16_to_f32(got)))
+    # bad arguments are refused on the host
+    p.rows = 63
+    assert lib.qb_tp_reduce(C.c_void_p(x.data_ptr()), C.c_void_p(gate.data_ptr()), None, None, C.byref(p), None) == -1
