@@ -429,6 +429,12 @@ def tp_record(args, qb, rank, world, local, dist, ref_latent, noise0):
     wd = Watchdog(comm, timeout_s=60.0)
     with wd.guard():
         out = eng.gen_frame(noise=noise0)  # captures the graph, then the first frame from the pre-filled state
+    # a reduction whose wait ran out leaves a bit in the device status word: if any rank saw one, nothing is timed
+    bad = torch.tensor([float(qb._lib.device_status())], device="cuda")
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if float(bad.item()) != 0.0:
+        rec["error"] = f"device status {int(bad.item())} after the first sharded frame (a bounded wait of the cross-GPU reduction ran out)"
+        return rec
     if rank == 0 and ref_latent is not None:
         g = (out.reshape(-1).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         w = (ref_latent.reshape(-1).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
@@ -443,24 +449,35 @@ def tp_record(args, qb, rank, world, local, dist, ref_latent, noise0):
         dev_ms, per = timed_steps(qb, args.steps, lambda i: eng.gen(eng._noise_dev))
     dist.barrier()
     # the reduction alone: a graph of 48 (one NFE's worth) on the [512, 2048] bf16 partial
+    def graph_of_48(fn):
+        fn(-1)  # an odd call first: the 48 in the graph then go on alternating
+        with qb.runtime.capture_graph() as cap:
+            for i in range(48):
+                fn(i)
+        with wd.guard():
+            cap.graph.launch()
+            e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+            e0.record()
+            cap.graph.launch()
+            e1.record()
+            e1.synchronize()
+        us = e0.elapsed_ms(e1) * 1e3 / 48
+        del cap
+        return us
+
     y = qb.QuarkTensor.zeros(eng.cfg.tpf, eng.cfg.d_model, dtype="bf16")
-    comm.all_reduce_sum(y)
-    with qb.runtime.capture_graph() as cap:
-        for _ in range(48):
-            comm.all_reduce_sum(y)
-    with wd.guard():
-        cap.graph.launch()
-        e0, e1 = qb.runtime.Event(), qb.runtime.Event()
-        e0.record()
-        cap.graph.launch()
-        e1.record()
-        e1.synchronize()
-    ar_us = e0.elapsed_ms(e1) * 1e3 / 48
-    del cap
-    dev_ms, ar_us = max_over_ranks([dev_ms, ar_us], dist, "cuda")
+    ar_us = graph_of_48(lambda i: comm.all_reduce_sum(y))  # ncclAllReduce alone (without the gate and norm kernels)
+    fused_us = 0.0
+    if comm.fused:  # sum + gate / residual + AdaRMSNorm (e4m3 out) in the one kernel
+        arena = comm.arena(eng.cfg.tpf, eng.cfg.d_model)
+        s0, b0, g0 = eng.model.blocks[0]._cond_lut[0][:3]
+        fused_us = graph_of_48(lambda i: arena.reduce(y, g0, s0, b0, x_slot=i & 1, emit_e4m3=True))  # alternating slots, as the blocks do
+    dev_ms, ar_us, fused_us = max_over_ranks([dev_ms, ar_us, fused_us], dist, "cuda")
     rec.update(fps=round(args.steps * 1000.0 / dev_ms, 3), ms_per_step=round(dev_ms / args.steps, 4), ms_per_nfe=round(dev_ms / args.steps / 5.0, 4),
                allreduce_us=round(ar_us, 2), launches_per_frame=int(eng.launches_per_frame), device_status=qb._lib.device_status(),
                ms_per_step_spread=spread(per), scaling="strong")  # fmt: skip
+    if comm.fused:
+        rec["fused_reduction_us"] = round(fused_us, 2)
     eng.close()  # the frame graph holds the communicator's collectives: it goes first
     comm.destroy()
     return rec
@@ -520,12 +537,14 @@ def run_ours(args):
     dev_ms, e2e_ms = max_over_ranks([dev_ms, e2e_ms], dist, "cuda")
     status = qb._lib.device_status()
 
-    kernels = own_peak = None
+    kernels = own_peak = kernel_clocks = None
     if rank == 0:
-        own_peak = measure_e4m3_peak_own(qb)
-        peaks["e4m3_tflops"] = own_peak["burst_tflops"]
         eng.set_frame_t(FRAME_T0 + 1)  # every run times the same segment tables (17 buckets on the global layers)
-        kernels = time_kernels(qb, eng, peaks)
+        peaks["e4m3_tflops"] = 2.0 * peaks["bf16_tflops"]  # provisional: the fractions are recomputed below
+        with ClockSampler(local) as kc:  # the kernels alone first, before the seconds-long peak measurement heats the GPU
+            kernels = time_kernels(qb, eng, peaks)
+        kernel_clocks = kc.summary()
+        own_peak = measure_e4m3_peak_own(qb)
     cpu = cpu_baseline_sample() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     scaled = scaled_record(args, qb, local, params) if want_scaled else None
 
@@ -619,6 +638,7 @@ def run_ours(args):
             },
             "e4m3_peak": e4m3_peak,
             "kernels": kernels,
+            "kernel_clocks": kernel_clocks,
             "owl_attn_sfu_bound": sfu,
             "gemm_us_per_layer": round(gemm_us, 2),
             "clocks": clocks.summary(),

@@ -340,30 +340,37 @@ int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int
  * with the rounding points of qb_ada_gate_residual and qb_ada_rmsnorm, so every rank ends up with the same bytes.
  *
  * Each rank owns an arena of qb_tp_arena_bytes(rows, D) bytes from qb_malloc, zeroed once, laid out as
- * [4 KiB of flags | y | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)] (byte offsets of the five buffers from
- * qb_tp_arena_offsets).  The rank's row-parallel GEMM writes its partial into its own y; the kernel reads every rank's
- * y and writes its share of the rows of x_new (slot p->x_slot), h and hq (if emit_h / emit_hq) into EVERY rank's arena.
+ * [4 KiB of flags | y slot 0 | y slot 1 | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)] (byte offsets of the six buffers from
+ * qb_tp_arena_offsets).  The rank's row-parallel GEMM writes its partial into its own y slot p->x_slot; the kernel reads
+ * every rank's y and leaves x_new (x slot p->x_slot), h and hq (if emit_h / emit_hq) complete in every rank's arena.
+ * Two schedules (p->schedule: 0 = choose, 1 = one-shot, 2 = two-shot; all ranks must agree): one-shot, chosen for up to
+ * four ranks, has every rank read all rows of every peer's y and compute the whole result for itself (one exchange of
+ * flags, nothing written to a peer); two-shot has rank r reduce rows [r * rows / world, (r + 1) * rows / world) only and
+ * store them into EVERY rank's arena (traffic stays near twice the partial, a second exchange of flags).
  * arena[r] is rank r's arena as mapped in the calling process: arena[rank] the rank's own pointer, the others from
- * qb_ipc_open of a handle that rank r made with qb_ipc_export.  Consecutive calls must alternate x_slot when the
- * residual of one call is the x_new of the call before (the block does: 0 after attention, 1 after the MLP).
- * All ranks must make the same sequence of calls.  A rank waits (bounded: wait_limit_us, 0 = about one second) for its
- * peers' kernels of the same call to start and to deliver their rows; when the limit runs out the kernel raises bit 3
- * of the device status word and returns with the outputs unspecified.  Stream-capturable. */
+ * qb_ipc_open of a handle that rank r made with qb_ipc_export.  Consecutive calls must alternate x_slot (the block does:
+ * 0 after attention, 1 after the MLP): the residual of one call is the x_new of the call before, and a y slot is
+ * rewritten two calls later.  All ranks must make the same sequence of calls.  A rank waits (bounded: wait_limit_us,
+ * 0 = about one second) for its peers' kernels of the same call to start and, two-shot, to deliver their rows; when
+ * the limit runs out the kernel raises bit 3 of the device status word and returns with the outputs unspecified.
+ * Stream-capturable. */
 typedef struct {
   int32_t world, rank;
   int32_t rows, D;                   /* the partial is [rows, D] bf16; rows % world == 0, D % 8 == 0, D <= 8192 */
   int32_t gate_groups, norm_groups;  /* gate [gate_groups, D], norm_scale / norm_bias [norm_groups, D] */
   int32_t norm_activation;           /* 0 none, 1 SiLU (the output norm) */
-  int32_t x_slot;                    /* 0 or 1: which x buffer of the arenas receives x_new */
+  int32_t x_slot;                    /* 0 or 1: which y buffer holds the partials and which x buffer receives x_new */
   int32_t emit_h, emit_hq;           /* write the norm's result as bf16 / as e4m3 */
   int32_t wait_limit_us;             /* 0 = default */
   float eps;
+  int32_t schedule;                  /* 0 = choose by world, 1 = one-shot, 2 = two-shot */
+  int32_t reserved;
   void* arena[8];
 } qb_tp_params;
 
 size_t qb_tp_arena_bytes(int32_t rows, int32_t D);
-/* offsets5_host[0..4] = byte offsets of y, x slot 0, x slot 1, h, hq inside an arena. */
-int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets5_host);
+/* offsets6_host[0..5] = byte offsets of y slot 0, y slot 1, x slot 0, x slot 1, h, hq inside an arena. */
+int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets6_host);
 int32_t qb_tp_reduce(const void* residual, const void* gate, const void* norm_scale, const void* norm_bias, const qb_tp_params* p,
                      void* stream);
 /* The same protocol with all `world` ranks run as ONE cooperative launch on the calling GPU, over arenas that all live on

@@ -76,6 +76,7 @@ class TpParams(C.Structure):
         ("world", C.c_int32), ("rank", C.c_int32), ("rows", C.c_int32), ("D", C.c_int32),
         ("gate_groups", C.c_int32), ("norm_groups", C.c_int32), ("norm_activation", C.c_int32), ("x_slot", C.c_int32),
         ("emit_h", C.c_int32), ("emit_hq", C.c_int32), ("wait_limit_us", C.c_int32), ("eps", C.c_float),
+        ("schedule", C.c_int32), ("reserved", C.c_int32),
         ("arena", C.c_void_p * 8),
     ]  # fmt: skip
 

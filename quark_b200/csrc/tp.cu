@@ -4,21 +4,25 @@
 // as ONE kernel per rank over peer-mapped buffers, in place of ncclAllReduce + two more launches.
 //
 // Every rank owns an "arena" of the same layout in its own device memory, mapped into every peer (CUDA IPC):
-//   flags | y (this rank's partial, written by its GEMM) | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)
-// Two-shot scheme: rank r sums rows [r * rows / world, (r + 1) * rows / world) of all ranks' y with plain peer loads,
-// in rank order (so every rank would compute the same bits), applies gate, residual and the norm, and stores its
-// rows of x_new / h / hq into EVERY rank's arena with plain peer stores.  No TMA, no multicast, no multimem: ordinary
-// ld / st over NVLink, so the kernel runs unchanged on any number of GPUs.
+//   flags | y slot 0 | y slot 1 (this rank's partial, written by its GEMM) | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)
+// Partials are summed in rank order with plain peer loads, so every rank computes the same bits.  No TMA, no multicast,
+// no multimem: ordinary ld / st over NVLink, so the kernel runs unchanged on any number of GPUs.  Two schedules:
+//   one-shot (few ranks)  every rank reads ALL rows of every peer's y and computes the whole result for itself; one
+//                         exchange of flags, (world - 1) x the partial read over NVLink, nothing written to a peer;
+//   two-shot (many ranks) rank r sums rows [r * rows / world, (r + 1) * rows / world) only and stores them into EVERY
+//                         rank's arena; the traffic per rank stays near 2 x the partial, at the price of a second
+//                         exchange of flags (a rank's kernel ends only when every peer's rows have arrived).
 //
 // Synchronisation is by epoch counters in the arenas, pushed into the memory of the rank that polls them:
 //   y_ready[r]   = e   written into every peer by rank r when its kernel e starts (its GEMM before it has finished)
-//   x_arrived[r] = e   written into every peer by rank r's last CTA after all of its stores
-// A rank reads its peers' y only after y_ready, and its kernel ends only when every x_arrived has come in, so the
-// next kernel in the stream finds complete rows.  Every wait is bounded: when it runs out the kernel raises
-// QB_DEV_WAIT_TIMEOUT_TP in the device status word, skips the data phase and returns; nothing spins for ever.
-// Buffer reuse is safe with one y and two x slots: a rank that has received every x_arrived[e] knows that every peer
-// has finished reading its y for epoch e, and a peer can write slot (e + 1) only after this rank announced epoch
-// e + 1, which is after its own kernel e (the reader of the other slot) has ended.
+//   x_arrived[r] = e   (two-shot) written into every peer by rank r's last CTA after all of its stores
+// Every wait is bounded: when it runs out the kernel raises QB_DEV_WAIT_TIMEOUT_TP in the device status word, skips
+// the data phase and returns; nothing spins for ever.
+// Buffer reuse: consecutive calls alternate between the two y slots and the two x slots.  A rank rewrites a y slot two
+// calls later, after its own kernel of the call in between has ended; that kernel waited for every peer's y_ready of
+// that call, which a peer sends only after its kernel of the call before (the reader of the slot) has ended.  In the
+// two-shot schedule a peer writes x slot (e + 1) only after this rank announced epoch e + 1, i.e. after its own
+// kernel e, the last reader of the other slot as a residual, has ended.
 //
 // Kernels that wait on one another must not be separate launches on one GPU, so the single-GPU test entry
 // (qb_tp_reduce_emulated) runs all ranks as the y-dimension of ONE cooperative launch over arenas that all live on
@@ -46,7 +50,7 @@ struct TpArgs {
   const uint16_t* gate;                   // [gate groups, D]
   const uint16_t* nscale;                 // [norm groups, D] or null: no norm
   const uint16_t* nbias;
-  int world, rank, emulate;
+  int world, rank, emulate, one_shot;
   int rows, D, gate_rows_per_group, norm_rows_per_group;
   int xslot, activation, emit_h, emit_hq;
   float eps;
@@ -94,13 +98,14 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
   constexpr int kMaxVec = 4;  // D <= 8 * kTpThreads * kMaxVec
   __shared__ float red[kTpThreads / 32];
   __shared__ unsigned int s_epoch;
-  __shared__ int s_ok, s_last;
+  __shared__ int s_ok;
 
   const int rank = a.emulate ? static_cast<int>(blockIdx.y) : a.rank;
   uint8_t* mine = a.arena[rank];
   unsigned int* flags = reinterpret_cast<unsigned int*>(mine);
   const size_t plane = static_cast<size_t>(a.rows) * a.D * 2;  // one bf16 [rows, D] buffer
-  const size_t off_y = kTpFlagBytes, off_x = off_y + plane * (1 + a.xslot), off_h = off_y + plane * 3, off_hq = off_y + plane * 4;
+  const size_t off_y = kTpFlagBytes + plane * a.xslot, off_x = kTpFlagBytes + plane * (2 + a.xslot), off_h = kTpFlagBytes + plane * 4,
+               off_hq = kTpFlagBytes + plane * 5;
 
   if (threadIdx.x == 0) {
     const unsigned int e = flags[kFlagEpoch] + 1u;  // written by this rank's previous launch, which has ended
@@ -108,7 +113,10 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
     if (blockIdx.x == 0) {
       for (int p = 0; p < a.world; ++p) st_release_sys(reinterpret_cast<unsigned int*>(a.arena[p]) + kFlagYReady + 32 * rank, e);
     }
-    const bool ok = tp_wait_all(flags, kFlagYReady, a.world, e, a.wait_cycles);
+    // Once a wait has run out on this GPU (the bit stays up until the host reads the status word) the session is
+    // broken: later calls do not wait their full limit again, they pass straight through.
+    const bool broken = (*reinterpret_cast<volatile unsigned int*>(a.status) & QB_DEV_WAIT_TIMEOUT_TP) != 0;
+    const bool ok = !broken && tp_wait_all(flags, kFlagYReady, a.world, e, a.wait_cycles);
     if (!ok) atomicOr(a.status, QB_DEV_WAIT_TIMEOUT_TP);
     s_ok = ok ? 1 : 0;
   }
@@ -116,9 +124,11 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
   const unsigned int e = s_epoch;
 
   if (s_ok) {
-    const int rpr = a.rows / a.world;
+    // one-shot: every row, results kept on this rank; two-shot: this rank's share of the rows, results sent to every rank
+    const int rpr = a.one_shot ? a.rows : a.rows / a.world;
+    const int first_dst = a.one_shot ? rank : 0, end_dst = a.one_shot ? rank + 1 : a.world;
     for (int lr = blockIdx.x; lr < rpr; lr += gridDim.x) {
-      const int row = rank * rpr + lr;
+      const int row = a.one_shot ? lr : rank * rpr + lr;
       const size_t roff = static_cast<size_t>(row) * a.D;
       const size_t goff = static_cast<size_t>(row / a.gate_rows_per_group) * a.D;
       uint4 xv[kMaxVec];
@@ -191,7 +201,7 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
             tp_unpack8(hv, q);  // the e4m3 copy is narrowed from the bf16-rounded value
             hq = make_uint2(pack_e4m3x4(q[0], q[1], q[2], q[3]), pack_e4m3x4(q[4], q[5], q[6], q[7]));
           }
-          for (int p = 0; p < a.world; ++p) {
+          for (int p = first_dst; p < end_dst; ++p) {
             uint8_t* dst = a.arena[p];
             *reinterpret_cast<uint4*>(dst + off_x + (roff + c) * 2) = xv[i];
             if (a.nscale != nullptr && a.emit_h) *reinterpret_cast<uint4*>(dst + off_h + (roff + c) * 2) = hv;
@@ -202,20 +212,24 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
     }
   }
 
-  // every store of this CTA is visible system-wide before its ticket; the CTA that draws the last ticket tells the peers
-  __threadfence_system();
+  // The CTA that draws the last ticket closes the epoch.  Two-shot: its stores to the peers must be visible system-wide
+  // before the peers are told, so one thread per CTA fences after the CTA's barrier (the barrier orders the other
+  // threads' stores before that thread, and its fence is cumulative), draws the ticket, and the last one signals and
+  // then waits for every peer's rows.
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (!a.one_shot) __threadfence_system();
     const unsigned int ticket = atomicAdd(flags + kFlagDone, 1u);
-    s_last = ticket == gridDim.x - 1 ? 1 : 0;
-  }
-  __syncthreads();
-  if (s_last && threadIdx.x == 0) {
-    __threadfence_system();
-    flags[kFlagDone] = 0;  // ready for the next launch
-    for (int p = 0; p < a.world; ++p) st_release_sys(reinterpret_cast<unsigned int*>(a.arena[p]) + kFlagXArrived + 32 * rank, e);
-    if (!tp_wait_all(flags, kFlagXArrived, a.world, e, a.wait_cycles)) atomicOr(a.status, QB_DEV_WAIT_TIMEOUT_TP);
-    flags[kFlagEpoch] = e;
+    if (ticket == gridDim.x - 1) {
+      flags[kFlagDone] = 0;  // ready for the next launch
+      if (!a.one_shot) {
+        __threadfence_system();
+        for (int p = 0; p < a.world; ++p) st_release_sys(reinterpret_cast<unsigned int*>(a.arena[p]) + kFlagXArrived + 32 * rank, e);
+        const bool broken = (*reinterpret_cast<volatile unsigned int*>(a.status) & QB_DEV_WAIT_TIMEOUT_TP) != 0;
+        if (!broken && !tp_wait_all(flags, kFlagXArrived, a.world, e, a.wait_cycles)) atomicOr(a.status, QB_DEV_WAIT_TIMEOUT_TP);
+      }
+      flags[kFlagEpoch] = e;
+    }
   }
 }
 
@@ -225,13 +239,13 @@ using namespace qb;
 
 extern "C" size_t qb_tp_arena_bytes(int32_t rows, int32_t D) {
   if (rows <= 0 || D <= 0) return 0;
-  return kTpFlagBytes + static_cast<size_t>(rows) * D * 9;  // y, x0, x1, h in bf16, hq in e4m3
+  return kTpFlagBytes + static_cast<size_t>(rows) * D * 11;  // y0, y1, x0, x1, h in bf16, hq in e4m3
 }
 
-extern "C" int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets5_host) {
-  QB_REQUIRE(rows > 0 && D > 0 && offsets5_host != nullptr, QB_ERR_INVALID_ARG, "tp_arena_offsets: bad arguments");
+extern "C" int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets6_host) {
+  QB_REQUIRE(rows > 0 && D > 0 && offsets6_host != nullptr, QB_ERR_INVALID_ARG, "tp_arena_offsets: bad arguments");
   const size_t plane = static_cast<size_t>(rows) * D * 2;
-  for (int i = 0; i < 5; ++i) offsets5_host[i] = kTpFlagBytes + plane * i;
+  for (int i = 0; i < 6; ++i) offsets6_host[i] = kTpFlagBytes + plane * i;
   return QB_OK;
 }
 
@@ -283,6 +297,8 @@ static int32_t tp_fill(TpArgs& a, const qb_tp_params* p, const void* gate, const
   a.rows = p->rows; a.D = p->D;
   a.gate_rows_per_group = p->rows / p->gate_groups;
   a.norm_rows_per_group = norm_scale ? p->rows / p->norm_groups : p->rows;
+  QB_REQUIRE(p->schedule >= 0 && p->schedule <= 2, QB_ERR_INVALID_ARG, "tp_reduce: schedule %d", p->schedule);
+  a.one_shot = p->schedule == 1 || (p->schedule == 0 && p->world <= 4);  // few ranks: the extra reads cost less than a second exchange
   a.xslot = p->x_slot; a.activation = p->norm_activation;
   a.emit_h = p->emit_h != 0; a.emit_hq = p->emit_hq != 0;
   a.eps = p->eps;
@@ -303,8 +319,8 @@ extern "C" int32_t qb_tp_reduce(const void* residual, const void* gate, const vo
   a.emulate = 0;
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  const int rpr = p->rows / p->world;
-  const int grid = rpr < 2 * sms ? rpr : 2 * sms;
+  const int rpr = a.one_shot ? p->rows : p->rows / p->world;
+  const int grid = rpr < 4 * sms ? rpr : 4 * sms;
   return launch_dep("tp_reduce", tp_reduce_kernel, dim3(grid), dim3(kTpThreads), 0, static_cast<cudaStream_t>(stream), a);
 }
 
@@ -319,7 +335,7 @@ extern "C" int32_t qb_tp_reduce_emulated(const void* const* residuals, const voi
     a.residual[r] = static_cast<const uint16_t*>(residuals[r]);
   }
   a.emulate = 1;
-  const int rpr = p->rows / p->world;
+  const int rpr = a.one_shot ? p->rows : p->rows / p->world;
   int dev = 0, sms = 0, per_sm = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
   QB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

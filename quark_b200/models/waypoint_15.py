@@ -407,7 +407,7 @@ class TransformerBlock(nn.Module):
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
         elif tp_fused:
-            self.out_proj(attn_out, out=arena.y)  # the partial goes straight into the peer-mapped buffer
+            self.out_proj(attn_out, out=arena.y[0])  # the partial goes straight into the peer-mapped buffer
             x, h = arena.reduce(x, g0, s1, b1, x_slot=0, emit_e4m3=fp8)
         else:
             y = self.out_proj(attn_out)
@@ -424,7 +424,7 @@ class TransformerBlock(nn.Module):
         elif fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
         elif tp_fused:
-            self.mlp(h, out=arena.y)
+            self.mlp(h, out=arena.y[1])
             ns, nb_, act, emit = next_norm if next_norm is not None else (None, None, None, False)
             x, self.h_next = arena.reduce(x, g1, ns, nb_, activation=act, x_slot=1, emit_e4m3=emit)
         else:

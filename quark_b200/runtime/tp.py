@@ -27,13 +27,13 @@ class TpArena:
             raise ValueError(f"TpArena: [{rows}, {D}] over {world} ranks")
         self.buf = QuarkTensor.zeros(nbytes, dtype="e4m3")  # flags start at zero: epoch 0
         _stream.synchronize()
-        off = (C.c_size_t * 5)()
+        off = (C.c_size_t * 6)()
         _lib.check(lib.qb_tp_arena_offsets(rows, D, off))
         base = self.buf.data_ptr()
         view = lambda i, dt: QuarkTensor.borrow(base + int(off[i]), (rows, D), dt, keepalive=self.buf)  # noqa: E731
-        self.y = view(0, "bf16")  # this rank's row-parallel GEMM writes its partial here
-        self.x = (view(1, "bf16"), view(2, "bf16"))
-        self.h, self.hq = view(3, "bf16"), view(4, "e4m3")
+        self.y = (view(0, "bf16"), view(1, "bf16"))  # this rank's row-parallel GEMM writes its partial into y[x_slot]
+        self.x = (view(2, "bf16"), view(3, "bf16"))
+        self.h, self.hq = view(4, "bf16"), view(5, "e4m3")
         handle = (C.c_uint8 * 64)()
         _lib.check(lib.qb_ipc_export(C.c_void_p(base), handle))
         handles = exchange(bytes(handle))
@@ -52,8 +52,8 @@ class TpArena:
             self.ptrs.append(int(p.value))
 
     def reduce(self, residual, gate, norm_scale=None, norm_bias=None, *, activation=None, x_slot: int, emit_e4m3: bool = False, eps: float = 1e-6,
-               wait_limit_us: int = 0):  # fmt: skip
-        """``x_new = residual + gate * sum over ranks of y`` and, with ``norm_scale`` / ``norm_bias``, ``h = ada_rmsnorm(x_new)``.
+               wait_limit_us: int = 0, schedule: int = 0):  # fmt: skip
+        """``x_new = residual + gate * sum over ranks of y[x_slot]`` and, with ``norm_scale`` / ``norm_bias``, ``h = ada_rmsnorm(x_new)``.
         Returns ``(x_new, h)``: views into this rank's arena (``h`` is the e4m3 buffer when ``emit_e4m3``; None without a norm)."""
         if activation not in (None, "silu"):
             raise ValueError(f"TpArena.reduce: activation {activation!r}")
@@ -61,7 +61,7 @@ class TpArena:
         Gn = norm_scale.numel // self.D if norm_scale is not None else 1
         p = _lib.TpParams(world=self.world, rank=self.rank, rows=self.rows, D=self.D, gate_groups=G, norm_groups=Gn,
                           norm_activation=1 if activation == "silu" else 0, x_slot=int(x_slot), emit_h=0 if emit_e4m3 else 1,
-                          emit_hq=1 if emit_e4m3 else 0, wait_limit_us=int(wait_limit_us), eps=float(eps))  # fmt: skip
+                          emit_hq=1 if emit_e4m3 else 0, wait_limit_us=int(wait_limit_us), eps=float(eps), schedule=int(schedule))  # fmt: skip
         for r in range(self.world):
             p.arena[r] = self.ptrs[r]
         ptr = lambda t: C.c_void_p(t.data_ptr() if t is not None else None)  # noqa: E731

@@ -41,9 +41,9 @@ class Arenas:
         lib = qb._lib.load()
         self.qb, self.world, self.rows, self.D = qb, world, rows, D
         n = int(lib.qb_tp_arena_bytes(rows, D))
-        assert n == 4096 + rows * D * 9
+        assert n == 4096 + rows * D * 11
         self.bufs = [qb.QuarkTensor.zeros(n, dtype="e4m3") for _ in range(world)]
-        off = (C.c_size_t * 5)()
+        off = (C.c_size_t * 6)()
         qb._lib.check(lib.qb_tp_arena_offsets(rows, D, off))
         self.off = [int(o) for o in off]
 
@@ -64,8 +64,12 @@ def rank_order_sum_bf16(parts):
     return codec.f32_to_bf16_rne(acc)
 
 
+@pytest.mark.parametrize("schedule", [1, 2], ids=["one-shot", "two-shot"])
 @pytest.mark.parametrize("world,rows,D", [(2, 64, 256), (4, 512, 2048), (8, 128, 2048)])
-def test_emulated_ranks_reproduce_the_unfused_chain(qb, world, rows, D):
+def test_emulated_ranks_reproduce_the_unfused_chain(qb, world, rows, D, schedule):
+    """Both schedules (every rank reduces every row for itself / every rank reduces its share and sends it to all),
+    four consecutive calls that alternate the y and x slots the way a block does, each call's residual being the
+    x of the call before."""
     r = util.rng(900 + world)
     lib = qb._lib.load()
     ar = Arenas(qb, world, rows, D)
@@ -77,8 +81,8 @@ def test_emulated_ranks_reproduce_the_unfused_chain(qb, world, rows, D):
     for call, (slot, act, emit_q) in enumerate([(0, None, True), (1, None, False), (0, "silu", False), (1, None, True)]):
         parts = [bf16_randn(r, (rows, D), 0.5) for _ in range(world)]
         for rk in range(world):
-            ar.view(rk, 0).copy_from_numpy(parts[rk])
-        p = ar.params(x_slot=slot, norm_activation=1 if act else 0, emit_h=0 if emit_q else 1, emit_hq=1 if emit_q else 0)
+            ar.view(rk, slot).copy_from_numpy(parts[rk])  # y slot = x slot
+        p = ar.params(x_slot=slot, norm_activation=1 if act else 0, emit_h=0 if emit_q else 1, emit_hq=1 if emit_q else 0, schedule=schedule)
         res = (C.c_void_p * world)(*[t.data_ptr() for t in residuals])
         qb._lib.check(lib.qb_tp_reduce_emulated(res, ptr(gate), ptr(ns), ptr(nb), C.byref(p), s))
         qb.runtime.synchronize()
@@ -89,15 +93,16 @@ def test_emulated_ranks_reproduce_the_unfused_chain(qb, world, rows, D):
         want_q = qb.QuarkTensor.empty(rows, D, dtype="e4m3")
         want_h = qb.qf.ada_rmsnorm(want_x, ns, nb, activation=act, out_q=want_q)
         for rk in range(world):
-            np.testing.assert_array_equal(ar.view(rk, 1 + slot).to_numpy(), want_x.to_numpy(), err_msg=f"call {call} rank {rk}: x")
+            np.testing.assert_array_equal(ar.view(rk, 2 + slot).to_numpy(), want_x.to_numpy(), err_msg=f"call {call} rank {rk}: x")
             if emit_q:
-                np.testing.assert_array_equal(ar.view(rk, 4, "e4m3").to_numpy(), want_q.to_numpy(), err_msg=f"call {call} rank {rk}: hq")
+                np.testing.assert_array_equal(ar.view(rk, 5, "e4m3").to_numpy(), want_q.to_numpy(), err_msg=f"call {call} rank {rk}: hq")
             else:
-                np.testing.assert_array_equal(ar.view(rk, 3).to_numpy(), want_h.to_numpy(), err_msg=f"call {call} rank {rk}: h")
-        residuals = [ar.view(rk, 1 + slot) for rk in range(world)]  # the next call's residual is this call's x, as in a block
+                np.testing.assert_array_equal(ar.view(rk, 4).to_numpy(), want_h.to_numpy(), err_msg=f"call {call} rank {rk}: h")
+        residuals = [ar.view(rk, 2 + slot) for rk in range(world)]  # the next call's residual is this call's x, as in a block
 
 
-def test_reduction_without_a_norm_and_with_gate_groups(qb):
+@pytest.mark.parametrize("schedule", [1, 2], ids=["one-shot", "two-shot"])
+def test_reduction_without_a_norm_and_with_gate_groups(qb, schedule):
     r = util.rng(950)
     lib = qb._lib.load()
     world, rows, D, G = 2, 64, 512, 4
@@ -108,13 +113,43 @@ def test_reduction_without_a_norm_and_with_gate_groups(qb):
     parts = [bf16_randn(r, (rows, D)) for _ in range(world)]
     for rk in range(world):
         ar.view(rk, 0).copy_from_numpy(parts[rk])
-    p = ar.params(x_slot=0)
+    p = ar.params(x_slot=0, schedule=schedule)
     p.gate_groups = G
     res = (C.c_void_p * world)(*[t.data_ptr() for t in residuals])
     qb._lib.check(lib.qb_tp_reduce_emulated(res, C.c_void_p(gate.data_ptr()), None, None, C.byref(p), C.c_void_p(qb.runtime.active_stream())))
     want = qb.qf.ada_gate_residual(residuals[0], T(qb, rank_order_sum_bf16(parts), "bf16"), gate)
     for rk in range(world):
-        np.testing.assert_array_equal(ar.view(rk, 1).to_numpy(), want.to_numpy())
+        np.testing.assert_array_equal(ar.view(rk, 2).to_numpy(), want.to_numpy())
+
+
+def test_emulated_reduction_time(qb, capsys):
+    """Not a parity check: the time of one emulated call at the benchmark's shape, printed for the record (the flag
+    exchange here crosses only this GPU's L2, so this is the kernel's own cost without the NVLink latencies)."""
+    r = util.rng(970)
+    lib = qb._lib.load()
+    rows, D = 512, 2048
+    out = {}
+    for world in (2, 4, 8):
+        for schedule in (1, 2):
+            ar = Arenas(qb, world, rows, D)
+            gate, ns, nb = (T(qb, bf16_randn(r, (1, D)), "bf16") for _ in range(3))
+            x = [T(qb, bf16_randn(r, (rows, D)), "bf16") for _ in range(world)]
+            res = (C.c_void_p * world)(*[t.data_ptr() for t in x])
+            s = C.c_void_p(qb.runtime.active_stream())
+            call = lambda i: qb._lib.check(lib.qb_tp_reduce_emulated(res, C.c_void_p(gate.data_ptr()), C.c_void_p(ns.data_ptr()), C.c_void_p(nb.data_ptr()),
+                                                                     C.byref(ar.params(x_slot=i & 1, emit_hq=1, schedule=schedule)), s))  # noqa: E731
+            for i in range(4):
+                call(i)
+            e0, e1 = qb.runtime.Event(), qb.runtime.Event()
+            e0.record()
+            for i in range(40):
+                call(i)
+            e1.record()
+            e1.synchronize()
+            out[f"world{world}_{'one' if schedule == 1 else 'two'}_shot_us"] = round(e0.elapsed_ms(e1) * 1e3 / 40, 2)
+    assert qb._lib.device_status() == 0
+    with capsys.disabled():
+        print("\nemulated tp_reduce [512, 2048]:", out)
 
 
 def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit(qb):
@@ -127,7 +162,7 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit(qb):
     gate = T(qb, bf16_randn(r, (1, D)), "bf16")
     x = T(qb, bf16_randn(r, (rows, D)), "bf16")
     ar.view(0, 0).copy_from_numpy(bf16_randn(r, (rows, D)))
-    p = ar.params(x_slot=0, wait_limit_us=2000)
+    p = ar.params(x_slot=0, wait_limit_us=2000, schedule=2)
     qb._lib.check(lib.qb_tp_reduce(C.c_void_p(x.data_ptr()), C.c_void_p(gate.data_ptr()), None, None, C.byref(p), C.c_void_p(qb.runtime.active_stream())))
     qb.runtime.synchronize()
     assert qb._lib.device_status() == 8  # bit 3: the cross-GPU reduction's wait ran out (reading clears it)
