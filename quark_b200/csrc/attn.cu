@@ -43,9 +43,7 @@
 // conversion is four times slower than f32 -> e4m3x2.
 #include <cuda.h>
 
-#include "common.cuh"
-#include "rope.cuh"
-#include "sm100.cuh"
+#include "attn_common.cuh"
 
 namespace qb {
 
@@ -77,29 +75,6 @@ constexpr int kQTile = 128;
 constexpr int kKeyTile = 128;
 constexpr int kVRows = 80;  // 64 channels + 16 rows of ones (row sum of P)
 
-struct AttnArgs {
-  const uint16_t* qkv;
-  const int32_t* segments;
-  const int32_t* n_segments;
-  const int32_t* frame_t;
-  uint16_t* out;
-  uint8_t* out_q;  // optional e4m3 copy of the output
-  const float* rope_xy;
-  const float* k_scale;
-  const float* v_scale;
-  unsigned int* status;
-  int tpf, n_q_heads, gqa, capacity, max_segments;
-  // Q of token t, head h starts at qkv + t * q_row + h * q_head (16-bit words), its output row at out + t * o_row +
-  // h * o_head: the packed projection has q_row = qkv_dim, q_head = 64, o_row = Hq * 64, o_head = 64; the head-major
-  // layout [Hq * tpf, 64] of Q and of the output has 64 and tpf * 64 for both
-  int q_row, q_head, o_row, o_head;
-  // Key splits (gridDim.z > 1): CTA z walks its share of the key tiles and leaves (m, row sum, 64 outputs)
-  // per query row in `partials`; the CTA that draws the last ticket of a (query tile, head) sums the
-  // shares in order of z and writes the output.
-  float* partials;  // [heads][query tiles][splits][66][128]
-  int* tickets;     // [heads][query tiles], zero between launches
-};
-
 template <bool kFp8>
 struct AttnSmem {
   static constexpr int kEs = kFp8 ? 1 : 2;
@@ -119,11 +94,6 @@ struct AttnSmem {
   static_assert(kStages * kStageBytes >= 66 * 128 * 4, "merge buffer aliases the stage area");
 };
 
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 // 2^x on the FMA and integer pipes, for the share of the exponentials that the special-function unit
 // has no time for: x = n + f with n = round(x) taken from the low mantissa bits of x + 1.5 * 2^23, a
 // minimax polynomial for 2^f on [-0.5, 0.5] (degree 2: 1.7e-3 relative error, below what an e4m3
@@ -149,28 +119,6 @@ template <bool kFp8, int kPolyOf8>
 __device__ __forceinline__ float p_exp(int q, float x) {
   return (q & 7) < kPolyOf8 ? ex2_poly<kFp8 ? 2 : 3>(x) : ex2_approx(x);
 }
-// One arrival for the whole warp: an mbarrier arrival is an atomic on shared memory.  __syncwarp orders the
-// lanes' earlier writes (and fences) before lane 0's arrival, which releases them to the waiting thread.
-__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-}
-__device__ __forceinline__ float max3f(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-// UMMA descriptor for a K-major tile with 64-byte rows and the 64-byte swizzle (fp8, head_dim 64).
-__device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(512 >> 4) << 32;  // 8 rows x 64 B
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(4) << 61;         // SWIZZLE_64B
-  return d;
-}
-
 // Which 128-key tile is the j-th valid one?  Returns its first cache row and how many of its
 // keys are valid.  Segments are (start, length) pairs; zero-length entries are legal.  Fully
 // unrolled so the table stays in registers.
@@ -767,6 +715,19 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 
 }  // namespace qb
 
+namespace qb {
+int32_t launch_attn4(const void* K_cache, const void* Vt_cache, const AttnArgs& a, int n_kv_heads, bool fp8, cudaStream_t st);
+// bf16 calls with one (query tile, head) per CTA go to the three-group kernel of attn4.cu; QB_ATTN4=0 in the environment
+// when the library is loaded keeps the two-group kernel of this file for everything (e4m3 and key splits always use it).
+static bool attn4_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("QB_ATTN4");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+}  // namespace qb
+
 using namespace qb;
 
 #ifdef QB_ATTN_TRACE
@@ -869,6 +830,9 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
   }
   dim3 grid((tpf + kQTile - 1) / kQTile, Hq, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // bf16, one CTA per (query tile, head): the three-group kernel of attn4.cu (66.7 against 70.3 us at 720p).  In the
+  // e4m3 path it is the slower one (57.7 against 52.2 us): its per-chunk fixed work outweighs the extra warps.
+  if (splits == 1 && !fp8 && attn4_enabled()) return launch_attn4(K_cache, Vt_cache, a, p->n_kv_heads, fp8, st);
   auto launch = [&](auto kernel, int smem_bytes) -> int32_t {
     QB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     return launch_dep("owl_attn kernel", kernel, grid, dim3(kAttnThreads), smem_bytes, st, tmK, tmV, a);

@@ -8,10 +8,10 @@ FLAGS="-gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 -Xcompil
 [ "$1" = "-v" ] && FLAGS="$FLAGS -Xptxas -v"
 mkdir -p "$HERE/build"
 pids=()
-for f in runtime gemm attn kv glue qkv_post tp; do
+for f in runtime gemm attn attn4 kv glue qkv_post tp; do
   $NVCC $FLAGS -c "$HERE/$f.cu" -o "$HERE/build/$f.o" &
   pids+=($!)
 done
 for p in "${pids[@]}"; do wait $p; done
-$NVCC -shared -o "$OUT" "$HERE"/build/{runtime,gemm,attn,kv,glue,qkv_post,tp}.o -cudart static
+$NVCC -shared -o "$OUT" "$HERE"/build/{runtime,gemm,attn,attn4,kv,glue,qkv_post,tp}.o -cudart static
 echo "built $OUT"

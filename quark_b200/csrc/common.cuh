@@ -91,6 +91,9 @@ __device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// Joining the halves with a register-pair move inside one asm block (mov.b32 {lo, hi}) instead of the shift and OR
+// below was measured on the attention kernel: 52.2 -> 58.4 us (the instruction schedule the compiler finds for the
+// softmax loop changes for the worse), so the plain form stays.
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   return static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
 }
