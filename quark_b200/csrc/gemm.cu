@@ -50,6 +50,9 @@ struct QkvTail {
   const float* k_scale;  // optional per-KV-head cache scales (see qb_kv_params)
   const float* v_scale;
   int n_q_heads, n_kv_heads, tpf, nb, pd, max_segments, kv_fp8;
+  // Quilt: the cache keeps tokens qoff, qoff + quilt, ... of the frame (tpf / quilt of them); slots, capacity and the
+  // segment table are those of a frame of tpf / quilt tokens (src/quark/kernels/kv_cache_update/reference.py:201-207)
+  int quilt, qoff;
   float eps;
 };
 
@@ -173,8 +176,12 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
   const bool in_n = col0 < g.N;
   const int ft = __ldg(q.frame_t);
   const int frozen = __ldg(q.frozen);
-  const int L = q.nb * q.tpf;
-  const int cap = L + q.tpf;
+  const int tpf_c = q.tpf / q.quilt;  // tokens of a frame that the cache keeps
+  const int L = q.nb * tpf_c;
+  const int cap = L + tpf_c;
+  // this thread's token in the cache: kept iff it is one of the quilt's residue class
+  const bool kept = (t - q.qoff) >= 0 && (t - q.qoff) % q.quilt == 0;
+  const int tc = (t - q.qoff) / q.quilt;
   const int bucket = (ft + q.pd - 1) / q.pd;
   const int slot = bucket % q.nb;
   const bool is_write = (ft % q.pd) == 0;
@@ -185,16 +192,16 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
     int sg[6] = {0, 0, 0, 0, 0, 0};
     int n;
     if (is_write && bucket >= q.nb) {
-      sg[1] = slot * q.tpf;
-      sg[2] = (slot + 1) * q.tpf;
-      sg[3] = (q.nb - slot - 1) * q.tpf;
+      sg[1] = slot * tpf_c;
+      sg[2] = (slot + 1) * tpf_c;
+      sg[3] = (q.nb - slot - 1) * tpf_c;
       sg[4] = L;
-      sg[5] = q.tpf;
+      sg[5] = tpf_c;
       n = 3;
     } else {
-      sg[1] = min(bucket, q.nb) * q.tpf;
+      sg[1] = min(bucket, q.nb) * tpf_c;
       sg[2] = L;
-      sg[3] = q.tpf;
+      sg[3] = tpf_c;
       n = 2;
     }
 #pragma unroll
@@ -290,7 +297,7 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
         st_global_v8(dst + 16 * h, w);
       }
     }
-    if (kind == 1 && valid && in_n) {
+    if (kind == 1 && valid && in_n && kept) {
       // rotate what the stand-alone append would read back (the bf16-rounded normalised K): y0 = pairs' first
       // outputs, y1 = their second outputs; a cache row is y0[0..31] followed by y1[0..31]
       const int head = (col0 - k_off) >> 6;
@@ -306,8 +313,8 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
       }
       uint8_t* kc = static_cast<uint8_t*>(q.K_cache);
       const size_t row_bytes = 64 * kEs;
-      uint8_t* tail = kc + (static_cast<size_t>(head) * cap + L + t) * row_bytes;
-      uint8_t* rr = kc + (static_cast<size_t>(head) * cap + static_cast<size_t>(slot) * q.tpf + t) * row_bytes;
+      uint8_t* tail = kc + (static_cast<size_t>(head) * cap + L + tc) * row_bytes;
+      uint8_t* rr = kc + (static_cast<size_t>(head) * cap + static_cast<size_t>(slot) * tpf_c + tc) * row_bytes;
       if (kCacheFp8) {
         uint32_t w0[8], w1[8];
 #pragma unroll
@@ -344,9 +351,11 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
   }
   asm volatile("bar.sync 2, 256;" ::: "memory");  // V staging complete
   if (ok) {
-    // transposed 16-byte stores: one channel x (8 | 16) consecutive tokens each, for the V heads of this tile
+    // transposed 16-byte stores: one channel x (8 | 16) consecutive cached tokens each, for the V heads of this tile.
+    // The tile's cached tokens are its rows qoff, qoff + quilt, ... (m0 is a multiple of the quilt factor).
     constexpr int kTokPerVec = 16 / kEs;
-    constexpr int kVecPerCh = 128 / kTokPerVec;
+    const int cached_rows = 128 / q.quilt;
+    const int vec_per_ch = cached_rows / kTokPerVec;
     uint8_t* vc = static_cast<uint8_t*>(q.Vt_cache);
 #pragma unroll 1
     for (int hh = 0; hh < 2; ++hh) {
@@ -355,28 +364,30 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
       const int head = (hcol - v_off) >> 6;
       const float inv_v = q.v_scale != nullptr ? __fdiv_rn(1.0f, __ldg(q.v_scale + head)) : 1.0f;
       const uint16_t* src = vt + hh * 128 * kQkvVPitch;
-      for (int v = et; v < 64 * kVecPerCh; v += 256) {
-        const int d = v / kVecPerCh, j = v % kVecPerCh;
-        const int t1 = j * kTokPerVec;
-        if (m0 + t1 + kTokPerVec > q.tpf) continue;
+      for (int v = et; v < 64 * vec_per_ch; v += 256) {
+        const int d = v / vec_per_ch, j = v % vec_per_ch;
+        const int c1 = j * kTokPerVec;                  // first cached token of the vector, inside the tile
+        const int c_abs = m0 / q.quilt + c1;            // ... and inside the frame's cached tokens
+        if (c_abs + kTokPerVec > tpf_c) continue;
+        auto sv = [&](int i) { return src[(q.qoff + (c1 + i) * q.quilt) * kQkvVPitch + d]; };
         uint32_t w[4];
         if (kCacheFp8) {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            w[i] = pack_e4m3x4(__fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i) * kQkvVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 1) * kQkvVPitch + d]), inv_v),
-                               __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 2) * kQkvVPitch + d]), inv_v), __fmul_rn(bf16_bits_to_f32(src[(t1 + 4 * i + 3) * kQkvVPitch + d]), inv_v));
+            w[i] = pack_e4m3x4(__fmul_rn(bf16_bits_to_f32(sv(4 * i)), inv_v), __fmul_rn(bf16_bits_to_f32(sv(4 * i + 1)), inv_v),
+                               __fmul_rn(bf16_bits_to_f32(sv(4 * i + 2)), inv_v), __fmul_rn(bf16_bits_to_f32(sv(4 * i + 3)), inv_v));
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint16_t lo = src[(t1 + 2 * i) * kQkvVPitch + d], hi = src[(t1 + 2 * i + 1) * kQkvVPitch + d];
+            const uint16_t lo = sv(2 * i), hi = sv(2 * i + 1);
             w[i] = q.v_scale != nullptr ? pack_bf16x2(__fmul_rn(bf16_bits_to_f32(lo), inv_v), __fmul_rn(bf16_bits_to_f32(hi), inv_v))
                                         : static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
           }
         }
         const uint4 ov = make_uint4(w[0], w[1], w[2], w[3]);
         const size_t ch = (static_cast<size_t>(head) * 64 + d) * cap;
-        *reinterpret_cast<uint4*>(vc + (ch + L + m0 + t1) * kEs) = ov;
-        if (ring) *reinterpret_cast<uint4*>(vc + (ch + static_cast<size_t>(slot) * q.tpf + m0 + t1) * kEs) = ov;
+        *reinterpret_cast<uint4*>(vc + (ch + L + c_abs) * kEs) = ov;
+        if (ring) *reinterpret_cast<uint4*>(vc + (ch + static_cast<size_t>(slot) * tpf_c + c_abs) * kEs) = ov;
       }
     }
   }
@@ -1056,7 +1067,13 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
   QB_REQUIRE(qkv_out && frame_t && frozen && K_cache && Vt_cache && segments && n_segments && rope_xy, QB_ERR_INVALID_ARG,
              "gemm_qkv_post: NULL pointer");
   QB_REQUIRE((qkv_first == nullptr) == (lamb == nullptr), QB_ERR_INVALID_ARG, "gemm_qkv_post: qkv_first and lamb come together");
-  QB_REQUIRE(kp->quilt_factor == 1 && kp->packed_qkv == 1, QB_ERR_UNSUPPORTED, "gemm_qkv_post: packed QKV without quilting only");
+  QB_REQUIRE(kp->packed_qkv == 1, QB_ERR_UNSUPPORTED, "gemm_qkv_post: the packed QKV layout only");
+  // a 128-token tile must hold whole 16-byte vectors of cached V tokens (8 bf16 / 16 e4m3 per vector)
+  QB_REQUIRE(kp->quilt_factor >= 1 && (kp->quilt_factor & (kp->quilt_factor - 1)) == 0 &&
+                 kp->quilt_factor * (kp->kv_dtype == QB_E4M3 ? 16 : 8) <= 128,
+             QB_ERR_UNSUPPORTED, "gemm_qkv_post: quilt_factor %d (a power of two, at most %d for this cache dtype)", kp->quilt_factor,
+             kp->kv_dtype == QB_E4M3 ? 8 : 16);
+  QB_REQUIRE(kp->quilt_offset >= 0 && kp->quilt_offset < kp->quilt_factor, QB_ERR_INVALID_ARG, "gemm_qkv_post: quilt_offset %d", kp->quilt_offset);
   QB_REQUIRE(kp->n_kv_heads > 0 && kp->n_q_heads > 0 && kp->n_q_heads % kp->n_kv_heads == 0, QB_ERR_INVALID_ARG,
              "gemm_qkv_post: %d Q heads over %d KV heads", kp->n_q_heads, kp->n_kv_heads);
   QB_REQUIRE(kp->H_spatial > 0 && kp->W_spatial > 0 && kp->num_buckets > 0 && kp->pinned_dilation > 0, QB_ERR_INVALID_ARG,
@@ -1067,7 +1084,8 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
   QB_REQUIRE(gp->M == tpf && gp->N == (kp->n_q_heads + 2 * kp->n_kv_heads) * 64, QB_ERR_INVALID_ARG,
              "gemm_qkv_post: the projection is [%d, %d] but the geometry needs [%d, %d]", gp->M, gp->N, tpf,
              (kp->n_q_heads + 2 * kp->n_kv_heads) * 64);
-  QB_REQUIRE(tpf % 16 == 0, QB_ERR_UNSUPPORTED, "gemm_qkv_post: H*W = %d must be a multiple of 16", tpf);
+  QB_REQUIRE((tpf / kp->quilt_factor) % 16 == 0 && tpf % kp->quilt_factor == 0, QB_ERR_UNSUPPORTED,
+             "gemm_qkv_post: H*W / quilt_factor = %d / %d must be a multiple of 16", tpf, kp->quilt_factor);
   QB_REQUIRE(gp->c_dtype == QB_BF16 && gp->activation == 0, QB_ERR_INVALID_ARG, "gemm_qkv_post: bf16 output without activation");
   QB_REQUIRE((reinterpret_cast<uintptr_t>(qkv_out) & 31u) == 0 && (reinterpret_cast<uintptr_t>(K_cache) & 31u) == 0 && aligned16(Vt_cache) &&
                  aligned16(qkv_first) && aligned16(rope_xy),
@@ -1082,6 +1100,7 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
   t.n_q_heads = kp->n_q_heads; t.n_kv_heads = kp->n_kv_heads; t.tpf = tpf; t.nb = kp->num_buckets; t.pd = kp->pinned_dilation;
   t.max_segments = kp->max_segments; t.kv_fp8 = kp->kv_dtype == QB_E4M3; t.eps = eps;
   t.k_scale = kp->k_scale; t.v_scale = kp->v_scale;
+  t.quilt = kp->quilt_factor; t.qoff = kp->quilt_offset;
   return gemm_run(A, B, qkv_out, nullptr, nullptr, nullptr, &p, workspace, workspace_bytes, stream, &t);
 }
 

@@ -363,7 +363,7 @@ def qkv_post(QKV, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segmen
 
 def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_segments, K_cache, *, n_q_heads, n_kv_heads,
                   H_spatial, W_spatial, num_buckets, pinned_dilation, compute_dtype=None, eps: float = 1e-6, max_segments=3, out=None,
-                  a_scale=None, w_scale=None, k_scale=None, v_scale=None):  # fmt: skip
+                  a_scale=None, w_scale=None, k_scale=None, v_scale=None, quilt_factor=1, quilt_offset=0):  # fmt: skip
     """``qkv_post(gemm(A, B))`` in one launch: the QKV projection whose epilogue normalises the Q and K heads,
     mixes V with the first block's, rotates K and appends K / V to the caches (same bytes as the two calls;
     no reference counterpart as a single call).  Returns the packed QKV that ``owl_attn`` reads."""
@@ -379,7 +379,8 @@ def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_
         raise ValueError("qf.gemm_qkv_post: QKV_first and lamb must be given together")
     if QKV_first is not None and (tuple(QKV_first.shape) != (M, N) or _dt(QKV_first) != "bf16" or _dt(lamb) != "f32"):
         raise ValueError("qf.gemm_qkv_post: QKV_first must be the packed bf16 QKV of the first block and lamb an f32 tensor")
-    cap = num_buckets * tpf + tpf
+    _quilt_checks("qf.gemm_qkv_post", tpf, quilt_factor, quilt_offset)
+    cap = (num_buckets + 1) * (tpf // quilt_factor)  # a quilted cache keeps tpf / quilt_factor tokens per frame
     if tuple(K_cache.shape) != (n_kv_heads * cap, 64) or tuple(Vt_cache.shape) != (n_kv_heads * 64, cap):
         raise ValueError(f"qf.gemm_qkv_post: cache shapes {tuple(K_cache.shape)} / {tuple(Vt_cache.shape)} do not match capacity {cap}")
     if int(segments.shape[0]) != max_segments * 2 or int(n_segments.shape[0]) != 1:
@@ -401,8 +402,8 @@ def gemm_qkv_post(A, B, QKV_first, lamb, frame_t, frozen, Vt_cache, segments, n_
     ks, vs = _head_scales("qf.gemm_qkv_post", n_kv_heads, k_scale, v_scale)
     kp = _lib.KvParams(
         n_q_heads=n_q_heads, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets,
-        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=1, packed_qkv=1,
-        k_scale=ks, v_scale=vs,
+        pinned_dilation=pinned_dilation, kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=max_segments, quilt_factor=quilt_factor, packed_qkv=1,
+        quilt_offset=quilt_offset, k_scale=ks, v_scale=vs,
     )  # fmt: skip
     lib = _lib.load()
     ws = _workspace(int(lib.qb_gemm_workspace_bytes(C.byref(gp))))

@@ -376,8 +376,13 @@ class TransformerBlock(nn.Module):
 
         h0 = h_in if h_in is not None else self.pre_attn_norm(x, s0, b0, emit_e4m3=fp8)
         use_first = hasattr(self, "v_residual") and qkv_first is not None
-        quilted = self._cfg.quilt_factor > 1  # the fused passes append every token; a quilted cache takes the plain kernels
-        if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm and not quilted:
+        # the stand-alone fused post-processing kernel appends every token; a quilted cache goes through the GEMM epilogue
+        # (which knows the quilt) or the plain kernels.  The epilogue stores whole 16-byte vectors of cached V tokens per
+        # 128-token tile, which bounds the quilt factor it takes (8 for e4m3 caches, 16 for bf16)
+        quilted = self._cfg.quilt_factor > 1
+        kc = self.kv_cache
+        quilt_fits = self._cfg.quilt_factor * (16 if kc.K_cache.dtype == "e4m3" else 8) <= 128
+        if self._cfg.fuse_qkv_post and self._cfg.fuse_qkv_gemm and quilt_fits:
             kc = self.kv_cache
             qkv = qf.gemm_qkv_post(
                 h0, self.qkv_proj.weight.data, qkv_first if use_first else None, self.v_residual.lamb.data if use_first else None,
@@ -386,6 +391,7 @@ class TransformerBlock(nn.Module):
                 W_spatial=self._cfg.width, num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"],
                 out=nn._cached(self, "qkv_post", (h0.numel // int(h0.shape[-1]), self._cfg.qkv_dim_local), "bf16"),
                 w_scale=self.qkv_proj.w_scale, k_scale=kc.k_scale, v_scale=kc.v_scale,
+                quilt_factor=kc._kw["quilt_factor"], quilt_offset=kc._kw["quilt_offset"],
             )  # fmt: skip
         elif self._cfg.fuse_qkv_post and not quilted:
             qkv = self.qkv_proj(h0)

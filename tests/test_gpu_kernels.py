@@ -316,6 +316,47 @@ def test_gemm_qkv_post_is_bit_identical_to_gemm_then_qkv_post(qb, kv_dt, lin, H,
     np.testing.assert_array_equal(nb_.to_numpy(), na.to_numpy())
 
 
+@pytest.mark.parametrize("kv_dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("lin", ["bf16", "e4m3"])
+@pytest.mark.parametrize("H,W,Hq,Hk,nb,pd,quilt,qoff,ft,frozen", [(16, 8, 4, 2, 4, 1, 2, 1, 6, 0), (16, 16, 4, 2, 4, 2, 4, 2, 10, 0), (32, 16, 32, 16, 16, 8, 8, 5, 128, 0),
+                                                                  (32, 16, 32, 16, 16, 1, 2, 0, 129, 1)])  # fmt: skip
+def test_gemm_qkv_post_with_a_quilted_cache(qb, kv_dt, lin, H, W, Hq, Hk, nb, pd, quilt, qoff, ft, frozen):
+    """quilt_factor > 1 in the fused QKV epilogue (src/quark/models/waypoint_15.py:108-112, :315-330: each layer's cache
+    keeps one residue class of the frame's tokens): the bytes of the projection followed by head norm, value residual
+    and the stand-alone append with the same quilt, which is pinned to the reference's quilted append elsewhere."""
+    r = util.rng(H * W + ft + quilt)
+    qf = qb.qf
+    tpf, D, Kd = H * W, (Hq + 2 * Hk) * 64, 256
+    cap = (nb + 1) * (tpf // quilt)
+    x = bf16_randn(r, (tpf, Kd))
+    first = T(qb, bf16_randn(r, (tpf, D)), "bf16")
+    if lin == "e4m3":
+        A, Wt = T(qb, codec.f32_to_e4m3(f32(x, "bf16")), "e4m3"), T(qb, e4m3_randn(r, (D, Kd), 0.5), "e4m3")
+    else:
+        A, Wt = T(qb, x, "bf16"), T(qb, bf16_randn(r, (D, Kd), 0.1), "bf16")
+    lam = T(qb, np.array([0.37], np.float32))
+
+    def state():
+        carrier = np.uint16 if kv_dt == "bf16" else np.uint8
+        return (T(qb, np.full((Hk * cap, 64), 0x11, carrier), kv_dt), T(qb, np.full((Hk * 64, cap), 0x22, carrier), kv_dt),
+                T(qb, np.full(6, -7, np.int32)), T(qb, np.array([-7], np.int32)))  # fmt: skip
+
+    ftt, frz = T(qb, np.array([ft], np.int32)), T(qb, np.array([frozen], np.int32))
+    geo = dict(n_q_heads=Hq, n_kv_heads=Hk, H_spatial=H, W_spatial=W, num_buckets=nb, pinned_dilation=pd)
+    Ka, Va, sa, na = state()
+    raw = qf.gemm(A, Wt, out_dtype="bf16", compute_dtype="e4m3" if lin == "e4m3" else None, tile_n=128)
+    q1 = qf.value_residual_packed(qf.head_rmsnorm(raw, Hq, Hk, 64), first, lam, v_col_offset=(Hq + Hk) * 64, v_width=Hk * 64)
+    qf.kv_cache_update(q1, None, ftt, frz, Va, sa, na, Ka, B=1, packed_qkv=True, quilt_factor=quilt, quilt_offset=qoff, **geo)
+    Kb, Vb, sb, nb_ = state()
+    q2 = qf.gemm_qkv_post(A, Wt, first, lam, ftt, frz, Vb, sb, nb_, Kb, quilt_factor=quilt, quilt_offset=qoff, **geo)
+    np.testing.assert_array_equal(q2.to_numpy(), q1.to_numpy())
+    np.testing.assert_array_equal(Kb.to_numpy(), Ka.to_numpy())
+    np.testing.assert_array_equal(Vb.to_numpy(), Va.to_numpy())
+    np.testing.assert_array_equal(sb.to_numpy(), sa.to_numpy())
+    np.testing.assert_array_equal(nb_.to_numpy(), na.to_numpy())
+    assert np.any(Ka.to_numpy() != 0x11)
+
+
 # --------------------------------------------------------------------------- GEMM
 
 
