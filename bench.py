@@ -471,7 +471,9 @@ def tp_record(args, qb, rank, world, local, dist, ref_latent, noise0):
     if comm.fused:  # sum + gate / residual + AdaRMSNorm (e4m3 out) in the one kernel
         arena = comm.arena(eng.cfg.tpf, eng.cfg.d_model)
         s0, b0, g0 = eng.model.blocks[0]._cond_lut[0][:3]
-        fused_us = graph_of_48(lambda i: arena.reduce(y, g0, s0, b0, x_slot=i & 1, emit_e4m3=True))  # alternating slots, as the blocks do
+        sched = comm.tp_schedule  # the pushed schedule sums what is in the staging area (here: whatever the last frame left)
+        fused_us = graph_of_48(lambda i: arena.reduce(y, g0, s0, b0, x_slot=i & 1, emit_e4m3=True, schedule=sched))  # alternating slots, as the blocks do
+        rec["reduction_schedule"] = {0: "chosen by rank count", 1: "one-shot", 2: "two-shot", 3: "pushed by the GEMM, two-shot"}.get(sched, str(sched))
     dev_ms, ar_us, fused_us = max_over_ranks([dev_ms, ar_us, fused_us], dist, "cuda")
     rec.update(fps=round(args.steps * 1000.0 / dev_ms, 3), ms_per_step=round(dev_ms / args.steps, 4), ms_per_nfe=round(dev_ms / args.steps / 5.0, 4),
                allreduce_us=round(ar_us, 2), launches_per_frame=int(eng.launches_per_frame), device_status=qb._lib.device_status(),

@@ -343,7 +343,8 @@ int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int
  * [4 KiB of flags | y slot 0 | y slot 1 | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)] (byte offsets of the six buffers from
  * qb_tp_arena_offsets).  The rank's row-parallel GEMM writes its partial into its own y slot p->x_slot; the kernel reads
  * every rank's y and leaves x_new (x slot p->x_slot), h and hq (if emit_h / emit_hq) complete in every rank's arena.
- * Two schedules (p->schedule: 0 = choose, 1 = one-shot, 2 = two-shot; all ranks must agree): one-shot, chosen for up to
+ * Schedules (p->schedule: 0 = choose between the first two, 1 = one-shot, 2 = two-shot, 3 = pushed, see qb_gemm_tp; all
+ * ranks must agree): one-shot, chosen for up to
  * four ranks, has every rank read all rows of every peer's y and compute the whole result for itself (one exchange of
  * flags, nothing written to a peer); two-shot has rank r reduce rows [r * rows / world, (r + 1) * rows / world) only and
  * store them into EVERY rank's arena (traffic stays near twice the partial, a second exchange of flags).
@@ -363,11 +364,20 @@ typedef struct {
   int32_t emit_h, emit_hq;           /* write the norm's result as bf16 / as e4m3 */
   int32_t wait_limit_us;             /* 0 = default */
   float eps;
-  int32_t schedule;                  /* 0 = choose by world, 1 = one-shot, 2 = two-shot */
+  int32_t schedule;                  /* 0 = choose by world, 1 = one-shot, 2 = two-shot, 3 = two-shot over partials that qb_gemm_tp
+                                        has already stored into the owners' staging areas */
   int32_t reserved;
   void* arena[8];
 } qb_tp_params;
 
+/* The row-parallel GEMM of a rank with its output sent straight to where it is summed: row m of the bf16 partial
+ * [p->M, p->N] = A . B^T (no epilogue, one K slice) is stored into y slot 0 of the arena of rank m / (M / world), at
+ * block tp->rank of that area ([source rank][M / world rows][N]), with plain stores over NVLink.  Follow it with
+ * qb_tp_reduce with schedule = 3 on every rank, which sums the blocks of its own area.  tp: world, rank, rows = M,
+ * D = N and the arenas are read; the other fields are ignored.  Workspace as for qb_gemm.  No counterpart in the
+ * reference. */
+int32_t qb_gemm_tp(const void* A, const void* B, const qb_gemm_params* p, const qb_tp_params* tp, void* workspace, size_t workspace_bytes,
+                   void* stream);
 size_t qb_tp_arena_bytes(int32_t rows, int32_t D);
 /* offsets6_host[0..5] = byte offsets of y slot 0, y slot 1, x slot 0, x slot 1, h, hq inside an arena. */
 int32_t qb_tp_arena_offsets(int32_t rows, int32_t D, size_t* offsets6_host);

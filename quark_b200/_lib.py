@@ -143,6 +143,7 @@ SIGNATURES = {
     "qb_unpatchify": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
+    "qb_gemm_tp": (_I, [_P, _P, C.POINTER(GemmParams), C.POINTER(TpParams), _P, _Z, _P]),
     "qb_tp_arena_bytes": (_Z, [_I, _I]),
     "qb_tp_arena_offsets": (_I, [_I, _I, C.POINTER(_Z)]),
     "qb_tp_reduce": (_I, [_P, _P, _P, _P, C.POINTER(TpParams), _P]),

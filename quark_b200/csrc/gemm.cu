@@ -73,6 +73,11 @@ struct GemmArgs {
   unsigned int* status;
   int qkv_mode;  // the fused QKV epilogue below replaces the plain one (128-column tiles only)
   QkvTail qkv;
+  // Row-parallel GEMM of a tensor-parallel rank: row m of the bf16 partial goes to the rank that owns that row in the
+  // cross-GPU reduction (m / tp_rpo), into that rank's staging area for partials from this rank (peer-mapped memory,
+  // plain stores over NVLink): tp_dst[owner] + (m % tp_rpo) * N.  tp_world == 0: the ordinary output C.
+  int tp_world, tp_rpo;
+  uint16_t* tp_dst[8];
 };
 
 template <int BN>
@@ -630,12 +635,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           const size_t off = static_cast<size_t>(m) * g.N + n;
           if (g.c_dtype == QB_BF16) {
+            uint16_t* dst = static_cast<uint16_t*>(g.C) + off;
+            if (g.tp_world != 0) {
+              const int owner = m / g.tp_rpo;
+              dst = g.tp_dst[owner] + static_cast<size_t>(m - owner * g.tp_rpo) * g.N + n;
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               uint32_t w[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[16 * h + 2 * j], v[16 * h + 2 * j + 1]);
-              st_global_v8(static_cast<uint16_t*>(g.C) + off + 16 * h, w);
+              st_global_v8(dst + 16 * h, w);
             }
           } else if (g.c_dtype == QB_E4M3) {
             uint32_t w[8];
@@ -980,9 +990,14 @@ extern "C" size_t qb_gemm_workspace_bytes(const qb_gemm_params* p) {
 
 // clear_counters: the workspace may hold anything (the built-in scratch array keeps the last call's contents), so the
 // tile counters are zeroed on the stream first, after every check has passed and only if this plan reads them.
+struct TpDest {
+  int world, rpo;
+  uint16_t* dst[8];
+};
+
 static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                         const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail,
-                        bool clear_counters = false) {
+                        bool clear_counters = false, const TpDest* tp = nullptr) {
   int32_t rc = validate_gemm(p);
   if (rc != QB_OK) return rc;
   QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
@@ -1038,6 +1053,14 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
   g.counters = reinterpret_cast<int*>(ws);
   g.partials = pl.partial_bytes ? reinterpret_cast<float*>(ws + pl.counters_bytes + pl.aq_bytes) : nullptr;
   g.status = status;
+  if (tp != nullptr) {
+    // the per-row destinations exist in the one-slice fast epilogue only: whole 32-column chunks, bf16, no gate
+    QB_REQUIRE(pl.splits == 1 && p->N % 32 == 0 && p->c_dtype == QB_BF16 && gate == nullptr && tail == nullptr, QB_ERR_UNSUPPORTED,
+               "gemm_tp: needs one K slice, N a multiple of 32, bf16 output, no gate");
+    g.tp_world = tp->world;
+    g.tp_rpo = tp->rpo;
+    for (int r = 0; r < tp->world; ++r) g.tp_dst[r] = tp->dst[r];
+  }
   if (tail != nullptr) {
     g.qkv_mode = 1;
     g.qkv = *tail;
@@ -1102,6 +1125,30 @@ extern "C" int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out,
   t.k_scale = kp->k_scale; t.v_scale = kp->v_scale;
   t.quilt = kp->quilt_factor; t.qoff = kp->quilt_offset;
   return gemm_run(A, B, qkv_out, nullptr, nullptr, nullptr, &p, workspace, workspace_bytes, stream, &t);
+}
+
+extern "C" int32_t qb_gemm_tp(const void* A, const void* B, const qb_gemm_params* p, const qb_tp_params* tp, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(p != nullptr && tp != nullptr, QB_ERR_INVALID_ARG, "gemm_tp: params are NULL");
+  QB_REQUIRE(tp->world >= 1 && tp->world <= 8 && tp->rank >= 0 && tp->rank < tp->world, QB_ERR_INVALID_ARG, "gemm_tp: rank %d of %d", tp->rank,
+             tp->world);
+  QB_REQUIRE(tp->rows == p->M && tp->D == p->N && p->M % tp->world == 0, QB_ERR_INVALID_ARG,
+             "gemm_tp: the partial is [%d, %d] but the arenas are laid out for [%d, %d] over %d ranks", p->M, p->N, tp->rows, tp->D, tp->world);
+  qb_gemm_params q = *p;
+  q.split_k = 1;  // the partial must leave the kernel in one piece
+  TpDest d{};
+  d.world = tp->world;
+  d.rpo = p->M / tp->world;
+  size_t off[6];
+  int32_t rc = qb_tp_arena_offsets(tp->rows, tp->D, off);
+  if (rc != QB_OK) return rc;
+  for (int r = 0; r < tp->world; ++r) {
+    QB_REQUIRE(tp->arena[r] != nullptr, QB_ERR_INVALID_ARG, "gemm_tp: arena %d is NULL", r);
+    // rank r's staging area (its y slot 0) holds one block of rows per source rank: [source][rows / world][D]
+    d.dst[r] = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(tp->arena[r]) + off[0]) + static_cast<size_t>(tp->rank) * d.rpo * p->N;
+  }
+  // C is unused (every row has a destination of its own); the rank's own staging block stands in for the pointer checks
+  return gemm_run(A, B, d.dst[tp->rank], nullptr, nullptr, nullptr, &q, workspace, workspace_bytes, stream, nullptr, false, &d);
 }
 
 // ---------------------------------------------------------------- GEMM on built-in scratch memory

@@ -12,6 +12,10 @@
 //   two-shot (many ranks) rank r sums rows [r * rows / world, (r + 1) * rows / world) only and stores them into EVERY
 //                         rank's arena; the traffic per rank stays near 2 x the partial, at the price of a second
 //                         exchange of flags (a rank's kernel ends only when every peer's rows have arrived).
+//   pushed                two-shot, but the partials are already where they are summed: the row-parallel GEMM (qb_gemm_tp)
+//                         stored each row of its partial into the staging area of the rank that owns the row (y slot 0 of
+//                         that rank's arena, one block of rows per source rank), so the kernel reads local memory only and
+//                         no load crosses NVLink; the flag exchange at its start tells it that the peers' GEMMs have ended.
 //
 // Synchronisation is by epoch counters in the arenas, pushed into the memory of the rank that polls them:
 //   y_ready[r]   = e   written into every peer by rank r when its kernel e starts (its GEMM before it has finished)
@@ -50,7 +54,7 @@ struct TpArgs {
   const uint16_t* gate;                   // [gate groups, D]
   const uint16_t* nscale;                 // [norm groups, D] or null: no norm
   const uint16_t* nbias;
-  int world, rank, emulate, one_shot;
+  int world, rank, emulate, one_shot, pushed;
   int rows, D, gate_rows_per_group, norm_rows_per_group;
   int xslot, activation, emit_h, emit_hq;
   float eps;
@@ -141,7 +145,9 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
           uint4 yv[kTpMaxWorld];
 #pragma unroll
           for (int p = 0; p < kTpMaxWorld; ++p)
-            if (p < a.world) yv[p] = ld_volatile_v4(a.arena[p] + off_y + (roff + c) * 2);
+            if (p < a.world)
+              yv[p] = a.pushed ? ld_volatile_v4(mine + kTpFlagBytes + ((static_cast<size_t>(p) * rpr + lr) * a.D + c) * 2)  // local staging
+                               : ld_volatile_v4(a.arena[p] + off_y + (roff + c) * 2);
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int p = 0; p < kTpMaxWorld; ++p) {  // rank order: every rank that summed these rows would get the same bits
@@ -297,8 +303,9 @@ static int32_t tp_fill(TpArgs& a, const qb_tp_params* p, const void* gate, const
   a.rows = p->rows; a.D = p->D;
   a.gate_rows_per_group = p->rows / p->gate_groups;
   a.norm_rows_per_group = norm_scale ? p->rows / p->norm_groups : p->rows;
-  QB_REQUIRE(p->schedule >= 0 && p->schedule <= 2, QB_ERR_INVALID_ARG, "tp_reduce: schedule %d", p->schedule);
+  QB_REQUIRE(p->schedule >= 0 && p->schedule <= 3, QB_ERR_INVALID_ARG, "tp_reduce: schedule %d", p->schedule);
   a.one_shot = p->schedule == 1 || (p->schedule == 0 && p->world <= 4);  // few ranks: the extra reads cost less than a second exchange
+  a.pushed = p->schedule == 3;
   a.xslot = p->x_slot; a.activation = p->norm_activation;
   a.emit_h = p->emit_h != 0; a.emit_hq = p->emit_hq != 0;
   a.eps = p->eps;

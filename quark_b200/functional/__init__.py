@@ -199,6 +199,27 @@ def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=
     return out
 
 
+def gemm_tp(A, B, arena, *, compute_dtype=None, b_constant=False):
+    """The row-parallel GEMM of a tensor-parallel rank, ``A @ B.T`` in bf16 with no epilogue, whose rows go straight to
+    the ranks that sum them: row ``m`` lands in the staging area of rank ``m // (M / world)`` (``runtime.tp.TpArena``;
+    plain stores over NVLink).  Follow it with ``arena.reduce(..., schedule=3)`` on every rank.  No reference counterpart."""
+    K = int(A.shape[-1])
+    M = A.numel // K
+    N = int(B.shape[0])
+    if int(B.shape[1]) != K or (M, N) != (arena.rows, arena.D):
+        raise ValueError(f"qf.gemm_tp: A {tuple(A.shape)} x B {tuple(B.shape)} is not the [{arena.rows}, {arena.D}] partial of the arena")
+    a_dt, b_dt = _dt(A), _dt(B)
+    cd = compute_dtype or (b_dt if b_dt == "e4m3" else a_dt)
+    gp = _lib.GemmParams(
+        M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code("bf16", "bf16"), compute_dtype=_code(cd, "bf16"),
+        activation=0, gate_groups=1, split_k=1, tile_n=0, reserved=2 if b_constant else 0, a_scale=None, w_scale=None,
+    )  # fmt: skip
+    tp = arena.params()
+    lib = _lib.load()
+    ws = _workspace(int(lib.qb_gemm_workspace_bytes(C.byref(gp))))
+    _lib.check(lib.qb_gemm_tp(_p(A), _p(B), C.byref(gp), C.byref(tp), _p(ws), ws.nbytes if ws is not None else 0, _s()))
+
+
 def quantize_e4m3(X, *, out=None):
     """bf16 / f32 -> e4m3, unscaled, RN-even, saturating (``src/quark/functional/quantize_e4m3.py:25-69``)."""
     dt = _dt(X)

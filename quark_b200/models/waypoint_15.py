@@ -413,8 +413,13 @@ class TransformerBlock(nn.Module):
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
         elif tp_fused:
-            self.out_proj(attn_out, out=arena.y[0])  # the partial goes straight into the peer-mapped buffer
-            x, h = arena.reduce(x, g0, s1, b1, x_slot=0, emit_e4m3=fp8)
+            sched = self._comm.tp_schedule
+            pushed = sched == 3 and self.out_proj.w_scale is None  # scaled weights need the GEMM's epilogue: keep the partial local
+            if pushed:
+                self.out_proj(attn_out, tp_arena=arena)  # every row of the partial goes straight to the rank that sums it
+            else:
+                self.out_proj(attn_out, out=arena.y[0])  # the partial goes into this rank's peer-mapped buffer
+            x, h = arena.reduce(x, g0, s1, b1, x_slot=0, emit_e4m3=fp8, schedule=sched if pushed or sched != 3 else 0)
         else:
             y = self.out_proj(attn_out)
             if tp:
@@ -430,9 +435,12 @@ class TransformerBlock(nn.Module):
         elif fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
         elif tp_fused:
-            self.mlp(h, out=arena.y[1])
+            if pushed:
+                self.mlp(h, tp_arena=arena)
+            else:
+                self.mlp(h, out=arena.y[1])
             ns, nb_, act, emit = next_norm if next_norm is not None else (None, None, None, False)
-            x, self.h_next = arena.reduce(x, g1, ns, nb_, activation=act, x_slot=1, emit_e4m3=emit)
+            x, self.h_next = arena.reduce(x, g1, ns, nb_, activation=act, x_slot=1, emit_e4m3=emit, schedule=sched if pushed or sched != 3 else 0)
         else:
             y = self.mlp(h)
             if tp:

@@ -139,8 +139,15 @@ class Linear(Module):
                 self.weight.data = qf.quantize_e4m3(self.weight.data)
             self._fp8 = True
 
-    def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None):
+    def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None, tp_arena=None):
+        """``tp_arena``: a row-parallel linear of a tensor-parallel rank; the partial output is stored straight into the
+        staging areas of the ranks that sum it (``qf.gemm_tp``) and nothing is returned."""
         a_dt = x.dtype
+        if tp_arena is not None:
+            if activation is not None or bias is not None or gate is not None or self._has_bias or self.w_scale is not None:
+                raise ValueError("Linear: a partial output sent to its reducers takes no epilogue")
+            b_dt = self.weight.data.dtype
+            return qf.gemm_tp(x, self.weight.data, tp_arena, compute_dtype=b_dt if b_dt == "e4m3" else None, b_constant=True)
         if a_dt not in ("bf16", "e4m3"):
             raise TypeError(f"Linear: activation dtype {a_dt!r} not in ('bf16', 'e4m3'). Insert a cast upstream.")
         fused_gate = gate is not None and residual is not None
@@ -231,12 +238,14 @@ class MLP(Module):
         self.silu = SiLU()
         self._fuse_silu = fuse_silu
 
-    def forward(self, x, *, gate=None, residual=None, gate_groups: int = 1, out=None):
+    def forward(self, x, *, gate=None, residual=None, gate_groups: int = 1, out=None, tp_arena=None):
         fp8 = self.fc2.weight.data.dtype == "e4m3"
         if self._fuse_silu:
             h = self.fc1(x, activation="silu", out_dtype="e4m3" if fp8 else None)
         else:
             h = self.silu(self.fc1(x), emit_e4m3=fp8)
+        if tp_arena is not None:
+            return self.fc2(h, tp_arena=tp_arena)
         return self.fc2(h, gate=gate, residual=residual, gate_groups=gate_groups, out=out)
 
 

@@ -51,6 +51,12 @@ class TpArena:
             self._opened.append(int(p.value))
             self.ptrs.append(int(p.value))
 
+    def params(self, **kw):
+        p = _lib.TpParams(world=self.world, rank=self.rank, rows=self.rows, D=self.D, **kw)
+        for r in range(self.world):
+            p.arena[r] = self.ptrs[r]
+        return p
+
     def reduce(self, residual, gate, norm_scale=None, norm_bias=None, *, activation=None, x_slot: int, emit_e4m3: bool = False, eps: float = 1e-6,
                wait_limit_us: int = 0, schedule: int = 0):  # fmt: skip
         """``x_new = residual + gate * sum over ranks of y[x_slot]`` and, with ``norm_scale`` / ``norm_bias``, ``h = ada_rmsnorm(x_new)``.

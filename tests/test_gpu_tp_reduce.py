@@ -122,6 +122,58 @@ def test_reduction_without_a_norm_and_with_gate_groups(qb, schedule):
         np.testing.assert_array_equal(ar.view(rk, 2).to_numpy(), want.to_numpy())
 
 
+class _RankView:
+    """What qf.gemm_tp needs of an arena set, from the point of view of one emulated rank."""
+
+    def __init__(self, ar, rank):
+        self.ar, self.rank, self.rows, self.D = ar, rank, ar.rows, ar.D
+
+    def params(self, **kw):
+        p = self.ar.params(**kw)
+        p.rank = self.rank
+        return p
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_partials_pushed_by_the_gemm_then_reduced(qb, world, fp8):
+    """The pushed schedule end to end on one GPU: every emulated rank's row-parallel GEMM (qb_gemm_tp) stores the rows of
+    its partial into the staging areas of their owners, then the reduction (schedule 3) sums each owner's local blocks.
+    Same bytes as plain GEMMs, a rank-order sum rounded to bf16, qf.ada_gate_residual and qf.ada_rmsnorm."""
+    r = util.rng(930 + world)
+    lib = qb._lib.load()
+    rows, D, K = 512, 2048, 256
+    ar = Arenas(qb, world, rows, D)
+    gate, ns, nb = (T(qb, bf16_randn(r, (1, D)), "bf16") for _ in range(3))
+    x = [T(qb, bf16_randn(r, (rows, D)), "bf16") for _ in range(1)] * world
+    parts = []
+    for rk in range(world):
+        if fp8:
+            A, B = T(qb, util.e4m3_randn(r, (rows, K)), "e4m3"), T(qb, util.e4m3_randn(r, (D, K), 0.25), "e4m3")
+        else:
+            A, B = T(qb, bf16_randn(r, (rows, K)), "bf16"), T(qb, bf16_randn(r, (D, K), 0.1), "bf16")
+        qb.qf.gemm_tp(A, B, _RankView(ar, rk), compute_dtype="e4m3" if fp8 else None)
+        parts.append(qb.qf.gemm(A, B, out_dtype="bf16", compute_dtype="e4m3" if fp8 else None, split_k=1).to_numpy())
+    # the staging area of owner o holds, per source rank, the owner's rows of that rank's partial
+    rpo = rows // world
+    for o in range(world):
+        got = ar.view(o, 0).to_numpy().reshape(world, rpo, D)
+        for src in range(world):
+            np.testing.assert_array_equal(got[src], parts[src][o * rpo : (o + 1) * rpo], err_msg=f"owner {o}, source {src}")
+    p = ar.params(x_slot=1, emit_hq=1, schedule=3)
+    res = (C.c_void_p * world)(*[t.data_ptr() for t in x])
+    qb._lib.check(lib.qb_tp_reduce_emulated(res, C.c_void_p(gate.data_ptr()), C.c_void_p(ns.data_ptr()), C.c_void_p(nb.data_ptr()), C.byref(p),
+                                            C.c_void_p(qb.runtime.active_stream())))
+    qb.runtime.synchronize()
+    assert qb._lib.device_status() == 0
+    want_x = qb.qf.ada_gate_residual(x[0], T(qb, rank_order_sum_bf16(parts), "bf16"), gate)
+    want_q = qb.QuarkTensor.empty(rows, D, dtype="e4m3")
+    qb.qf.ada_rmsnorm(want_x, ns, nb, out_q=want_q)
+    for rk in range(world):
+        np.testing.assert_array_equal(ar.view(rk, 3).to_numpy(), want_x.to_numpy(), err_msg=f"rank {rk}: x")
+        np.testing.assert_array_equal(ar.view(rk, 5, "e4m3").to_numpy(), want_q.to_numpy(), err_msg=f"rank {rk}: hq")
+
+
 def test_emulated_reduction_time(qb, capsys):
     """Not a parity check: the time of one emulated call at the benchmark's shape, printed for the record (the flag
     exchange here crosses only this GPU's L2, so this is the kernel's own cost without the NVLink latencies)."""
