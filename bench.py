@@ -775,14 +775,15 @@ def run_tp(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    os.environ["CUDA_VISIBLE_DEVICES"] = str(local)
     import quark_b200 as qb
     from quark_b200.runtime.nccl import LocalComm, NcclComm
 
-    qb._lib.require_device(0)
+    # every GPU of the job stays visible to every rank: the fused reduction maps the peers' buffers (CUDA IPC)
+    qb._lib.require_device(local)
+    qb._lib.check(qb._lib.load().qb_set_device(local))
     id_path = f"/tmp/qb_nccl_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}.id"
-    comm = NcclComm(rank, world, id_path) if world > 1 else LocalComm()
-    _, eng = build_engine(seed=0, device=0, tp_rank=rank, tp_world=world, comm=comm)  # same weights and noise on every rank
+    comm = NcclComm(rank, world, id_path, fused=not args.tp_nccl_only) if world > 1 else LocalComm()
+    _, eng = build_engine(seed=0, device=local, tp_rank=rank, tp_world=world, comm=comm)  # same weights and noise on every rank
     n = eng.cfg.latent_numel
     noises = [np.random.default_rng([1234, i]).standard_normal(n, dtype=np.float32) for i in range(4)]
     for i in range(max(args.warmup, 3)):
@@ -831,7 +832,7 @@ def run_tp(args):
             "dtype": "e4m3", "data": "synthetic", "impl": "ours",
             "config": {"workload": "gen_frame 720p fp8, ONE session sharded over the GPUs (BASELINE configs[4])",
                        "parallelism": f"tp{world} by KV-head group: {16 // world} KV heads per GPU, QKV / fc1 column-parallel, out-proj / fc2 "
-                                      "row-parallel, 2 NCCL all-reduces of [512, 2048] bf16 per block (48 per NFE) inside the CUDA graph",
+                                      f"row-parallel, 2 sums of [512, 2048] bf16 per block (48 per NFE) inside the CUDA graph: {comm.reduction_name}",
                        "frame_t": FRAME_T0 + 1, "l2": "inputs larger than L2"},
             "e2e": {"value": round(args.steps * 1000.0 / e2e_ms, 3), "unit": "frames/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},

@@ -49,7 +49,8 @@ class CtrlInput:
 
 class Engine:
     def __init__(self, model_uri=None, *, cfg: Waypoint15Config | None = None, quant="fp8", load_weights=True, seed: int = 0,
-                 params: dict | None = None, device: int = 0, use_graph: bool = True, comm=None, device_noise: bool = False):  # fmt: skip
+                 params: dict | None = None, device: int = 0, use_graph: bool = True, comm=None, device_noise: bool = False,
+                 watchdog_s: float | None = None):  # fmt: skip
         if isinstance(model_uri, Waypoint15Config):
             cfg, model_uri = model_uri, None
         if model_uri is not None:
@@ -75,6 +76,14 @@ class Engine:
             self.model.prepare()
         self.gen = GenerateFrame(self.model)
         self._use_graph = use_graph
+        # A sharded session (comm.world > 1) waits for its peers inside every frame.  With `watchdog_s` set, a frame that
+        # takes longer aborts the communicator from a timer thread, so that a rank whose peer died returns with an error
+        # instead of waiting inside a collective (runtime.nccl.Watchdog).  The reference is single-GPU: no counterpart.
+        self._watchdog = None
+        if watchdog_s is not None and comm is not None and getattr(comm, "world", 1) > 1:
+            from .runtime.nccl import Watchdog
+
+            self._watchdog = Watchdog(comm, watchdog_s)
         self._frame = 0
         n = cfg.latent_numel
         self._noise_host = _Pinned(n * 2, np.uint16)
@@ -223,7 +232,12 @@ class Engine:
             self._h2d(self._noise_dev, self._noise_host.ptr, n * 2)
         if self._use_graph and self.gen._graph is None:
             self._capture()
-        out = self.gen(self._noise_dev, ctrl_dev)
+        if self._watchdog is not None:  # the guard ends only when the frame has: the host waits for the stream inside it
+            with self._watchdog.guard():
+                out = self.gen(self._noise_dev, ctrl_dev)
+                _stream.synchronize()
+        else:
+            out = self.gen(self._noise_dev, ctrl_dev)
         self._frame += 1
         if not return_img:
             return None
