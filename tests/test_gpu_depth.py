@@ -20,8 +20,6 @@ The oracle chain runs with round-to-nearest bf16 narrowing, the rule of the refe
 With ``QB_PARITY_REPORT`` set to a file name, the achieved figures are appended to it as JSON lines.
 """
 
-import json
-import os
 
 import numpy as np
 import pytest
@@ -46,12 +44,7 @@ def qb():
     assert q._lib.device_status() == 0
 
 
-def _report(rec: dict) -> None:
-    path = os.environ.get("QB_PARITY_REPORT")
-    print(json.dumps(rec))
-    if path:
-        with open(path, "a") as f:
-            f.write(json.dumps(rec) + "\n")
+_report = util.parity_report
 
 
 def _err(got_u16, want_u16):

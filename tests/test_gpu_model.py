@@ -493,7 +493,8 @@ def test_full_depth_nfe_360p(qb, quant, height, width):
         floor_c, floor_m = err(want["trunc"], want["rne"])
         for mode in ("trunc", "rne"):
             c, m = err(got, want[mode])
-            print(f"24-layer NFE {quant} frame_t={ft_val} vs {mode} oracle: 1-cos={c:.2e} max_rel={m:.2e} (oracle-vs-oracle floor 1-cos={floor_c:.2e} max_rel={floor_m:.2e})")
+            util.parity_report({"test": "free_running_24_layers_360p", "quant": quant, "frame_t": ft_val, "oracle_rounding": mode, "1mcos": float(f"{c:.4g}"),
+                                "max_rel": float(f"{m:.4g}"), "oracle_rne_vs_trunc_floor_1mcos": float(f"{floor_c:.4g}"), "oracle_rne_vs_trunc_floor_max_rel": float(f"{floor_m:.4g}")})  # fmt: skip
             assert c <= max(1.0 - util.COS_MIN, 1.5 * floor_c), (mode, c, floor_c)
             if quant == "bf16":
                 assert m <= max(util.BF16_MAX_REL, 1.5 * floor_m), (mode, m, floor_m)

@@ -62,3 +62,15 @@ def bf16_ulp_diff(a_u16, b_u16):
         return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
 
     return np.abs(key(np.asarray(a_u16)) - key(np.asarray(b_u16)))
+
+
+def parity_report(rec: dict) -> None:
+    """Print one achieved-parity record as a JSON line; with ``QB_PARITY_REPORT`` naming a file, append it there too."""
+    import json
+    import os
+
+    print(json.dumps(rec))
+    path = os.environ.get("QB_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(rec) + "\n")
