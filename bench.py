@@ -330,6 +330,12 @@ def time_kernels(qb, eng, peaks):
         "owl_attn": (lambda b: b.attn(qkv, b.kv_cache, ft), None),
         "kv_cache_update": (lambda b: b.kv_cache(qkv, ft, frozen=True), None),
     }
+    # the forms the frame launches when the AdaRMSNorm after out-proj / fc2 runs as that GEMM's tail, and the norm alone
+    s1, b1 = eng.model.blocks[0]._cond_lut[0][3], eng.model.blocks[0]._cond_lut[0][4]
+    if qb.qf.gemm_norm_fits(tpf, cfg.d_model):
+        shapes["gemm_out_with_norm"] = (lambda b: b.out_proj(aq, gate=g, residual=xr, norm=(s1, b1, None, True)), gemm_flops(tpf, cfg.d_model, cfg.d_model))
+        shapes["gemm_fc2_with_norm"] = (lambda b: b.mlp.fc2(hq, gate=g, residual=xr, norm=(s1, b1, None, True)), gemm_flops(tpf, cfg.d_model, cfg.mlp_dim))
+    shapes["ada_rmsnorm"] = (lambda b: b.pre_mlp_norm(xr, s1, b1, emit_e4m3=True), None)
     for name, (fn, flops) in shapes.items():
         us = timed(fn)
         entry = dict(us_per_launch=round(us, 2))
@@ -340,6 +346,9 @@ def time_kernels(qb, eng, peaks):
             entry["keys_attended_mean"] = float(S)
         if flops is not None:
             entry.update(tflops=round(flops / us / 1e6, 1), frac_of_peak=round(flops / us / 1e6 / fp8_peak, 3))
+        elif name == "ada_rmsnorm":
+            bytes_ = tpf * cfg.d_model * (2 + 2 + 1)  # x in, bf16 and e4m3 out
+            entry.update(gbs=round(bytes_ / us / 1e3, 1), frac_of_peak=round(bytes_ / us / 1e3 / peaks["hbm_gbs"], 3))
         else:
             bytes_ = 2 * tpf * 1024 * 2 + 2 * tpf * 1024 * 1 + 28
             entry.update(gbs=round(bytes_ / us / 1e3, 1), frac_of_peak=round(bytes_ / us / 1e3 / peaks["hbm_gbs"], 3))

@@ -154,6 +154,29 @@ size_t qb_gemm_static_scratch_capacity(void);
 int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                                const qb_gemm_params* p, void* stream);
 
+/* qb_gemm followed, in the same kernel, by the AdaRMSNorm of the finished rows: C = epilogue(A B^T) as qb_gemm writes
+ * it (bf16), and norm_out [M, N] bf16 and / or norm_out_q [M, N] e4m3 = ada_rmsnorm(C, norm_scale, norm_bias) with the
+ * arithmetic of qb_ada_rmsnorm (the e4m3 copy narrowed from the bf16-rounded result).  Replaces the pair
+ * `out_proj / fc2 (+ gate, residual)` -> `pre_mlp_norm / next block's pre_attn_norm`
+ * (ref: src/quark/models/waypoint_15.py:413-440, src/quark/functional/ada_rmsnorm.py).  norm_scale / norm_bias are bf16
+ * [np->groups, N].  The tiles of a 128-row block exchange their sums of squares through the workspace and wait for one
+ * another (bounded; bit 0 of the device status word when the limit runs out), so the whole grid must be resident at
+ * once: at most one tile per SM (rejected otherwise), and no other grid of this kind may share the device at the same
+ * time from another stream.  The sum of squares is taken tile by tile in a fixed order: deterministic, and equal to
+ * qb_ada_rmsnorm of C up to the rounding of that f32 sum (at most one bf16 ulp in an output, rarely).  Needs one K
+ * slice, tiles of 64 or 128 columns dividing N, gate and norm row groups made of whole 128-row tiles; the workspace
+ * (qb_gemm_norm_workspace_bytes, zero-initialised once, shared as for qb_gemm) is required. */
+typedef struct {
+  int32_t groups;     /* rows of norm_scale / norm_bias; row m of C uses row m / (M / groups) */
+  int32_t activation; /* 0 none, 1 SiLU on the normalised value (the output norm) */
+  float eps;
+  int32_t reserved;
+} qb_norm_params;
+size_t qb_gemm_norm_workspace_bytes(const qb_gemm_params* p);
+int32_t qb_gemm_norm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
+                     const void* norm_scale, const void* norm_bias, void* norm_out, void* norm_out_q, const qb_gemm_params* p,
+                     const qb_norm_params* np, void* workspace, size_t workspace_bytes, void* stream);
+
 /* X -> e4m3, round-to-nearest-even, saturate to +-448, NaN -> 0x7F, no scale.
  * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
  * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */

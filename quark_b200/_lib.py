@@ -81,6 +81,10 @@ class TpParams(C.Structure):
     ]  # fmt: skip
 
 
+class NormParams(C.Structure):
+    _fields_ = [("groups", C.c_int32), ("activation", C.c_int32), ("eps", C.c_float), ("reserved", C.c_int32)]
+
+
 _P, _I, _Z, _F, _U = C.c_void_p, C.c_int32, C.c_size_t, C.c_float, C.c_uint32
 
 # name -> (restype, argtypes); every symbol include/quark_b200.h declares
@@ -144,6 +148,8 @@ SIGNATURES = {
     "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_gemm_tp": (_I, [_P, _P, C.POINTER(GemmParams), C.POINTER(TpParams), _P, _Z, _P]),
+    "qb_gemm_norm_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
+    "qb_gemm_norm": (_I, [_P] * 10 + [C.POINTER(GemmParams), C.POINTER(NormParams), _P, _Z, _P]),
     "qb_tp_arena_bytes": (_Z, [_I, _I]),
     "qb_tp_arena_offsets": (_I, [_I, _I, C.POINTER(_Z)]),
     "qb_tp_reduce": (_I, [_P, _P, _P, _P, C.POINTER(TpParams), _P]),
