@@ -328,8 +328,33 @@ int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype
 /* Mixture-of-experts routing ("correct" mode: every token goes to its own top_k experts, no capacity bound):
  * weights[e][m] (f32, [E, M]) = softmax over token m's top_k logits at its top_k experts, 0 elsewhere; ties go to
  * the lower expert index.  logits bf16 [M, E], E <= 32.  ref: src/quark/kernels/moe_router_correct/reference.py:38-49.
- * The reference's slot tables (token_ids, offsets, work list) have no counterpart: the experts run dense here. */
+ * For the dense schedule (every expert over every token); the slot-sorted schedule below is the default. */
 int32_t qb_moe_route(const void* logits, float* weights, int32_t M, int32_t E, int32_t top_k, void* stream);
+/* The same routing as slot tables for the slot-sorted schedule (ref: the tables of
+ * src/quark/kernels/moe_router_correct/reference.py:51-120, src/quark/nn/moe.py:252-363, whose row tile is 32; here
+ * 128, the GEMM kernel's).  n = qb_moe_slots(M, E, top_k) rows, a multiple of 128 that holds every expert's run padded
+ * to whole tiles.  slot_token [n]: the token in each slot, -1 for padding; slot_weight [n]: its routing weight;
+ * tile_expert [n / 128]: the expert of each 128-row tile, -1 past the last used tile; token_slot [M, top_k]: the slot of
+ * token m's k-th choice, k in order of decreasing logit; counts [E] (may be NULL): tokens per expert.  Within an expert
+ * the slots follow (token, k) order: the tables are a function of the logits alone. */
+size_t qb_moe_slots(int32_t M, int32_t E, int32_t top_k);
+int32_t qb_moe_route_slots(const void* logits, int32_t* slot_token, float* slot_weight, int32_t* tile_expert, int32_t* token_slot,
+                           int32_t* counts, int32_t M, int32_t E, int32_t top_k, void* stream);
+/* out[s, :] = X[slot_token[s], :] for rows of row_bytes bytes (a multiple of 16), zeros where slot_token[s] < 0: the
+ * activations in slot order, the A operand of the grouped in-projection (the reference's moe_inproj gathers while it
+ * loads, src/quark/functional/moe_inproj.py). */
+int32_t qb_moe_gather(const void* X, const int32_t* slot_token, void* out, int32_t n_slots, int32_t row_bytes, void* stream);
+/* Grouped GEMM: C[128 i .. 128 i + 127, :] = epilogue(A[same rows] . B[e N .. e N + N - 1, :]^T) with e = tile_expert[i];
+ * tiles with e < 0 are skipped (their rows of C are left as they are).  A [p->M, K] with p->M a multiple of 128,
+ * B [n_experts * p->N, K], C [p->M, p->N]; plain or SiLU epilogue, no bias / gate / scales.  Replaces qf.moe_inproj and
+ * qf.moe_outproj (ref: src/quark/nn/moe.py:307-338). */
+size_t qb_gemm_grouped_workspace_bytes(const qb_gemm_params* p);
+int32_t qb_gemm_grouped(const void* A, const void* B, void* C, const int32_t* tile_expert, int32_t n_experts, const qb_gemm_params* p,
+                        void* workspace, size_t workspace_bytes, void* stream);
+/* out[m, :] = bf16(sum over k of slot_weight[s] * partials[s, :], s = token_slot[m, k]), the sum in f32 in order of k, one
+ * narrowing.  Replaces qf.moe_reduce (ref: src/quark/kernels/moe_reduce/reference.py:16-33). */
+int32_t qb_moe_reduce(const float* partials, const float* slot_weight, const int32_t* token_slot, void* out, int32_t M, int32_t D, int32_t top_k,
+                      void* stream);
 /* out[m, :] (bf16 [M, D]) = sum over experts with weights[e][m] != 0 of weights[e][m] * partials[e][m][:] (f32
  * [E, M, D]), summed in f32, narrowed once.  ref: src/quark/kernels/moe_reduce/reference.py:16-33. */
 int32_t qb_moe_combine(const float* partials, const float* weights, void* out, int32_t M, int32_t D, int32_t E, void* stream);

@@ -148,6 +148,12 @@ SIGNATURES = {
     "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_gemm_tp": (_I, [_P, _P, C.POINTER(GemmParams), C.POINTER(TpParams), _P, _Z, _P]),
+    "qb_moe_slots": (_Z, [_I, _I, _I]),
+    "qb_moe_route_slots": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "qb_moe_gather": (_I, [_P, _P, _P, _I, _I, _P]),
+    "qb_gemm_grouped_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
+    "qb_gemm_grouped": (_I, [_P, _P, _P, _P, _I, C.POINTER(GemmParams), _P, _Z, _P]),
+    "qb_moe_reduce": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "qb_gemm_norm_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
     "qb_gemm_norm": (_I, [_P] * 10 + [C.POINTER(GemmParams), C.POINTER(NormParams), _P, _Z, _P]),
     "qb_tp_arena_bytes": (_Z, [_I, _I]),

@@ -89,6 +89,9 @@ struct GemmArgs {
   uint8_t* norm_out_q;
   float* norm_part;  // [M, 2 * gridDim.x] sums of squares, one per (row, tile, half)
   int* norm_sync;    // per row block: arrivals, departures; both zero between launches
+  // Grouped GEMM (mixture of experts): the 128-row tile i of A belongs to expert tile_expert[i] and is multiplied with
+  // rows [expert * N, expert * N + N) of B; a tile with expert -1 is skipped.  NULL: the ordinary GEMM.
+  const int* tile_expert;
 };
 
 template <int BN>
@@ -434,6 +437,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) QB_GT(0);
+  int b_row0 = 0;  // first row of this tile's expert in B
+  if (g.tile_expert != nullptr) {
+    grid_dep_wait();  // the table is written by the routing kernel just before
+    const int expert = g.tile_expert[blockIdx.y];
+    if (expert < 0) return;  // a padding tile: nothing allocated yet, the whole CTA leaves
+    b_row0 = expert * g.N;
+  }
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
   const int split = blockIdx.z;
@@ -476,7 +486,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int it = 0; it < ahead; ++it) {
         const uint32_t fb = smem_u32(&full_bar[it]);
         mbar_arrive_expect_tx(fb, L::kStageBytes);
-        tma_load_2d(smem_u32(smem + it * L::kStageBytes + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, n0);
+        tma_load_2d(smem_u32(smem + it * L::kStageBytes + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, b_row0 + n0);
       }
       grid_dep_wait();
       QB_GT(2);
@@ -491,7 +501,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         mbar_arrive_expect_tx(fb, L::kStageBytes);
         uint8_t* a_s = smem + s * L::kStageBytes;
         tma_load_2d(smem_u32(a_s), &tmA, fb, (kb0 + it) * kKElems, m0);
-        tma_load_2d(smem_u32(a_s + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, n0);
+        tma_load_2d(smem_u32(a_s + kBM * kRowBytes), &tmB, fb, (kb0 + it) * kKElems, b_row0 + n0);
         issued = it + 1;
       }
       if (*abort_flag) {
@@ -1125,7 +1135,8 @@ static size_t norm_part_bytes(const qb_gemm_params& p, int bn) {
 
 static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                         const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail,
-                        bool clear_counters = false, const TpDest* tp = nullptr, const NormDest* norm = nullptr) {
+                        bool clear_counters = false, const TpDest* tp = nullptr, const NormDest* norm = nullptr, const int* tile_expert = nullptr,
+                        int n_experts = 1) {
   int32_t rc = validate_gemm(p);
   if (rc != QB_OK) return rc;
   QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
@@ -1165,7 +1176,7 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
   const int es = fp8 ? 1 : 2;
   rc = make_tmap_2d(&tmA, a_ptr, es, p->M, p->K, kBM);
   if (rc != QB_OK) return rc;
-  rc = make_tmap_2d(&tmB, B, es, p->N, p->K, pl.bn);
+  rc = make_tmap_2d(&tmB, B, es, static_cast<uint64_t>(p->N) * n_experts, p->K, pl.bn);
   if (rc != QB_OK) return rc;
 
   GemmArgs g{};
@@ -1193,6 +1204,14 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
   if (tail != nullptr) {
     g.qkv_mode = 1;
     g.qkv = *tail;
+  }
+  if (tile_expert != nullptr) {
+    // per-column vectors would have to be per expert
+    // (a B tile that runs past the expert's last row only feeds columns >= N, which no epilogue stores)
+    QB_REQUIRE(pl.splits == 1 && p->M % kBM == 0, QB_ERR_UNSUPPORTED, "gemm_grouped: needs one K slice and M = %d a multiple of 128", p->M);
+    QB_REQUIRE(tail == nullptr && tp == nullptr && norm == nullptr && bias == nullptr && gate == nullptr && p->w_scale == nullptr,
+               QB_ERR_UNSUPPORTED, "gemm_grouped: takes the plain or the SiLU epilogue only");
+    g.tile_expert = tile_expert;
   }
   if (norm != nullptr) {
     // What the tail relies on: the fast epilogue for every tile (whole tiles in N, one gate row and one norm row per
@@ -1308,6 +1327,22 @@ extern "C" int32_t qb_gemm_tp(const void* A, const void* B, const qb_gemm_params
   }
   // C is unused (every row has a destination of its own); the rank's own staging block stands in for the pointer checks
   return gemm_run(A, B, d.dst[tp->rank], nullptr, nullptr, nullptr, &q, workspace, workspace_bytes, stream, nullptr, false, &d);
+}
+
+extern "C" size_t qb_gemm_grouped_workspace_bytes(const qb_gemm_params* p) {
+  if (validate_gemm(p) != QB_OK) return 0;
+  qb_gemm_params q = *p;
+  q.split_k = 1;
+  return qb_gemm_workspace_bytes(&q);
+}
+
+extern "C" int32_t qb_gemm_grouped(const void* A, const void* B, void* C, const int32_t* tile_expert, int32_t n_experts, const qb_gemm_params* p,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(p != nullptr && tile_expert != nullptr, QB_ERR_INVALID_ARG, "gemm_grouped: params or tile table are NULL");
+  QB_REQUIRE(n_experts >= 1 && static_cast<long long>(n_experts) * p->N < (1ll << 31), QB_ERR_INVALID_ARG, "gemm_grouped: %d experts", n_experts);
+  qb_gemm_params q = *p;
+  q.split_k = 1;  // a padding tile leaves before any K slice could wait for it
+  return gemm_run(A, B, C, nullptr, nullptr, nullptr, &q, workspace, workspace_bytes, stream, nullptr, false, nullptr, nullptr, tile_expert, n_experts);
 }
 
 // The plan of a GEMM with a norm tail: one K slice, tiles of at most 128 columns.

@@ -406,6 +406,154 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   }
 }
 
+// ---------------------------------------------------------------- mixture of experts: slot-sorted schedule
+// The routing of moe_route_kernel laid out as slots sorted by expert, every expert's run padded to whole 128-row
+// tiles (the row tile of the GEMM kernel), so that the expert projections are two grouped GEMMs over
+// M * top_k (+ padding) rows instead of E dense GEMMs over M rows each (ref: the slot tables of
+// src/quark/kernels/moe_router_correct/reference.py:51-120, whose tile is 32 rows).  One CTA: the tables are tiny.
+//   slot_token[s]   token whose row occupies slot s, -1 for padding
+//   slot_weight[s]  its routing weight (0 for padding)
+//   tile_expert[i]  expert of rows [128 i, 128 i + 128), -1 past the last used tile
+//   token_slot[m,k] slot of token m's k-th choice (k in order of decreasing logit)
+// Within an expert the slots follow (token, k) order, whatever order the threads run in.
+constexpr int kMoeTile = 128;
+constexpr int kMoeRouteThreads = 1024;
+
+__device__ __forceinline__ void moe_topk(const uint16_t* __restrict__ row, int E, int top_k, int (&ex)[kMoeMaxExperts], float (&wt)[kMoeMaxExperts]) {
+  float l[kMoeMaxExperts];
+  for (int e = 0; e < E; ++e) l[e] = bf16_bits_to_f32(row[e]);
+  unsigned taken = 0;
+  float top = 0.f, sum = 0.f;
+  for (int k = 0; k < top_k; ++k) {
+    int best = -1;
+    for (int e = 0; e < E; ++e)
+      if (!((taken >> e) & 1u) && (best < 0 || l[e] > l[best])) best = e;
+    taken |= 1u << best;
+    if (k == 0) top = l[best];
+    ex[k] = best;
+    wt[k] = expf(l[best] - top);
+    sum += wt[k];
+  }
+  for (int k = 0; k < top_k; ++k) wt[k] = wt[k] / sum;
+}
+
+__global__ void __launch_bounds__(kMoeRouteThreads) moe_route_slots_kernel(const uint16_t* __restrict__ logits, int* __restrict__ slot_token,
+                                                                            float* __restrict__ slot_weight, int* __restrict__ tile_expert,
+                                                                            int* __restrict__ token_slot, int* __restrict__ counts_out, int M, int E,
+                                                                            int top_k, int n_slots) {
+  grid_dep_wait();
+  grid_dep_launch();
+  __shared__ int count[kMoeMaxExperts], offset[kMoeMaxExperts + 1], base[kMoeMaxExperts];
+  __shared__ int warp_tot[kMoeMaxExperts][kMoeRouteThreads / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kMoeMaxExperts) count[tid] = 0;
+  __syncthreads();
+  int ex[kMoeMaxExperts];
+  float wt[kMoeMaxExperts];
+  // pass 1: how many tokens each expert receives
+  for (int t = tid; t < M; t += kMoeRouteThreads) {
+    moe_topk(logits + static_cast<size_t>(t) * E, E, top_k, ex, wt);
+    for (int k = 0; k < top_k; ++k) atomicAdd(&count[ex[k]], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int cum = 0;
+    for (int e = 0; e < E; ++e) {
+      offset[e] = cum;
+      base[e] = 0;
+      cum += (count[e] + kMoeTile - 1) / kMoeTile * kMoeTile;
+      if (counts_out != nullptr) counts_out[e] = count[e];
+    }
+    offset[E] = cum;
+  }
+  __syncthreads();
+  // pass 2: tokens in chunks of one per thread, in order; a choice's rank among its expert's = choices of earlier chunks
+  // + of earlier warps of this chunk + of earlier lanes of this warp
+  for (int t0 = 0; t0 < M; t0 += kMoeRouteThreads) {
+    const int t = t0 + tid;
+    const bool live = t < M;
+    if (live) moe_topk(logits + static_cast<size_t>(t) * E, E, top_k, ex, wt);
+    unsigned mine = 0;
+    if (live)
+      for (int k = 0; k < top_k; ++k) mine |= 1u << ex[k];
+    unsigned before[kMoeMaxExperts];  // lanes of this warp that chose expert e, below this lane
+    for (int e = 0; e < E; ++e) {
+      const unsigned b = __ballot_sync(0xffffffffu, (mine >> e) & 1u);
+      before[e] = __popc(b & ((1u << lane) - 1u));
+      if (lane == 0) warp_tot[e][warp] = __popc(b);
+    }
+    __syncthreads();
+    if (live) {
+      for (int k = 0; k < top_k; ++k) {
+        const int e = ex[k];
+        int rank = base[e] + static_cast<int>(before[e]);
+        for (int w = 0; w < warp; ++w) rank += warp_tot[e][w];
+        const int slot = offset[e] + rank;
+        slot_token[slot] = t;
+        slot_weight[slot] = wt[k];
+        token_slot[static_cast<size_t>(t) * top_k + k] = slot;
+      }
+    }
+    __syncthreads();
+    if (tid < E) {
+      int tot = 0;
+      for (int w = 0; w < kMoeRouteThreads / 32; ++w) tot += warp_tot[tid][w];
+      base[tid] += tot;
+    }
+    __syncthreads();
+  }
+  // padding slots and the tile table
+  for (int e = 0; e < E; ++e)
+    for (int s = offset[e] + count[e] + tid; s < offset[e + 1]; s += kMoeRouteThreads) {
+      slot_token[s] = -1;
+      slot_weight[s] = 0.f;
+    }
+  for (int s = offset[E] + tid; s < n_slots; s += kMoeRouteThreads) {
+    slot_token[s] = -1;
+    slot_weight[s] = 0.f;
+  }
+  for (int i = tid; i < n_slots / kMoeTile; i += kMoeRouteThreads) {
+    const int s = i * kMoeTile;
+    int e = -1;
+    for (int q = 0; q < E; ++q)
+      if (s >= offset[q] && s < offset[q + 1]) e = q;
+    tile_expert[i] = e;
+  }
+}
+
+// out[s, :] = X[slot_token[s], :] (rows of `row_bytes` bytes, a multiple of 16), zeros for padding slots
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint8_t* __restrict__ X, const int* __restrict__ slot_token, uint8_t* __restrict__ out,
+                                                          int row_bytes) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int s = blockIdx.x;
+  const int t = slot_token[s];
+  for (int b = threadIdx.x * 16; b < row_bytes; b += blockDim.x * 16) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t >= 0) v = *reinterpret_cast<const uint4*>(X + static_cast<size_t>(t) * row_bytes + b);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(s) * row_bytes + b) = v;
+  }
+}
+
+// out[m, :] = bf16( sum over k, in order, of slot_weight[slot] * partials[slot][:] ), slot = token_slot[m, k]; the sum in
+// f32, one narrowing at the end (ref: src/quark/kernels/moe_reduce/reference.py:16-33)
+__global__ void __launch_bounds__(256) moe_reduce_kernel(const float* __restrict__ partials, const float* __restrict__ slot_weight,
+                                                          const int* __restrict__ token_slot, uint16_t* __restrict__ out, int D, int top_k) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int m = blockIdx.x;
+  for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      const int slot = token_slot[static_cast<size_t>(m) * top_k + k];
+      const float w = slot_weight[slot];
+      const float4 y = *reinterpret_cast<const float4*>(partials + static_cast<size_t>(slot) * D + d);
+      acc[0] = fmaf(w, y.x, acc[0]); acc[1] = fmaf(w, y.y, acc[1]); acc[2] = fmaf(w, y.z, acc[2]); acc[3] = fmaf(w, y.w, acc[3]);
+    }
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(m) * D + d) = make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]));
+  }
+}
+
 // ---------------------------------------------------------------- randn
 // Standard normals from a counter: Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3")
 // on the counter (group, 0, seed0, seed1) with the key (seed0, seed1), the four words turned into uniforms
@@ -722,6 +870,40 @@ int32_t qb_moe_combine(const float* partials, const float* weights, void* out, i
   QB_REQUIRE(aligned16(partials) && aligned16(out), QB_ERR_ALIGN, "moe_combine: pointers must be 16-byte aligned");
   return launch_dep("moe_combine", moe_combine_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), partials, weights,
                     static_cast<uint16_t*>(out), M, D, E);
+}
+
+size_t qb_moe_slots(int32_t M, int32_t E, int32_t top_k) {
+  if (M <= 0 || E <= 0 || top_k <= 0 || top_k > E) return 0;
+  // every expert's run is padded to whole tiles: at most E * (tile - 1) padding rows
+  const size_t worst = static_cast<size_t>(M) * top_k + static_cast<size_t>(E) * (kMoeTile - 1);
+  return (worst + kMoeTile - 1) / kMoeTile * kMoeTile;
+}
+
+int32_t qb_moe_route_slots(const void* logits, int32_t* slot_token, float* slot_weight, int32_t* tile_expert, int32_t* token_slot,
+                           int32_t* counts, int32_t M, int32_t E, int32_t top_k, void* stream) {
+  QB_REQUIRE(logits && slot_token && slot_weight && tile_expert && token_slot, QB_ERR_INVALID_ARG, "moe_route_slots: NULL pointer");
+  QB_REQUIRE(M > 0 && E > 0 && E <= kMoeMaxExperts && top_k > 0 && top_k <= E, QB_ERR_INVALID_ARG, "moe_route_slots: M %d, E %d (at most %d), top_k %d", M, E,
+             kMoeMaxExperts, top_k);
+  const int n_slots = static_cast<int>(qb_moe_slots(M, E, top_k));
+  return launch_dep("moe_route_slots", moe_route_slots_kernel, dim3(1), dim3(kMoeRouteThreads), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(logits), slot_token, slot_weight, tile_expert, token_slot, counts, M, E, top_k, n_slots);
+}
+
+int32_t qb_moe_gather(const void* X, const int32_t* slot_token, void* out, int32_t n_slots, int32_t row_bytes, void* stream) {
+  QB_REQUIRE(X && slot_token && out, QB_ERR_INVALID_ARG, "moe_gather: NULL pointer");
+  QB_REQUIRE(n_slots > 0 && row_bytes > 0 && row_bytes % 16 == 0, QB_ERR_INVALID_ARG, "moe_gather: %d slots of %d bytes (a multiple of 16)", n_slots, row_bytes);
+  QB_REQUIRE(aligned16(X) && aligned16(out), QB_ERR_ALIGN, "moe_gather: pointers must be 16-byte aligned");
+  return launch_dep("moe_gather", moe_gather_kernel, dim3(n_slots), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint8_t*>(X),
+                    slot_token, static_cast<uint8_t*>(out), row_bytes);
+}
+
+int32_t qb_moe_reduce(const float* partials, const float* slot_weight, const int32_t* token_slot, void* out, int32_t M, int32_t D, int32_t top_k,
+                      void* stream) {
+  QB_REQUIRE(partials && slot_weight && token_slot && out, QB_ERR_INVALID_ARG, "moe_reduce: NULL pointer");
+  QB_REQUIRE(M > 0 && D > 0 && D % 4 == 0 && top_k > 0, QB_ERR_INVALID_ARG, "moe_reduce: M %d, D %d (a multiple of 4), top_k %d", M, D, top_k);
+  QB_REQUIRE(aligned16(partials) && aligned16(out), QB_ERR_ALIGN, "moe_reduce: pointers must be 16-byte aligned");
+  return launch_dep("moe_reduce", moe_reduce_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), partials, slot_weight, token_slot,
+                    static_cast<uint16_t*>(out), D, top_k);
 }
 
 int32_t qb_randn(const uint32_t* counter, void* out, size_t n, int32_t out_dtype, uint32_t counter_stride, uint32_t seed0, uint32_t seed1,

@@ -761,6 +761,85 @@ def moe_combine(partials, weights, *, out=None):
     return out
 
 
+def moe_slots(M: int, E: int, top_k: int) -> int:
+    """Rows of the slot tables of ``moe_route_slots``: every expert's run padded to whole 128-row tiles."""
+    return int(_lib.load().qb_moe_slots(int(M), int(E), int(top_k)))
+
+
+def moe_route_slots(logits, *, top_k: int, slot_token=None, slot_weight=None, tile_expert=None, token_slot=None, counts=None):
+    """The "correct" routing as slot tables sorted by expert (``src/quark/kernels/moe_router_correct/reference.py:51-120``;
+    row tile 128 here).  Returns ``(slot_token, slot_weight, tile_expert, token_slot)``."""
+    if _dt(logits) != "bf16" or logits.ndim != 2:
+        raise TypeError("qf.moe_route_slots: logits must be a bf16 [M, E] tensor")
+    M, E = int(logits.shape[0]), int(logits.shape[1])
+    n = moe_slots(M, E, top_k)
+    slot_token = slot_token if slot_token is not None else QuarkTensor.empty(n, dtype="s32")
+    slot_weight = slot_weight if slot_weight is not None else QuarkTensor.empty(n, dtype="f32")
+    tile_expert = tile_expert if tile_expert is not None else QuarkTensor.empty(n // 128, dtype="s32")
+    token_slot = token_slot if token_slot is not None else QuarkTensor.empty(M, int(top_k), dtype="s32")
+    if slot_token.numel != n or slot_weight.numel != n or tile_expert.numel != n // 128 or token_slot.numel != M * int(top_k):
+        raise ValueError(f"qf.moe_route_slots: tables must hold {n} slots, {n // 128} tiles and [{M}, {top_k}] token slots")
+    _lib.check(_lib.load().qb_moe_route_slots(_p(logits), _p(slot_token), _p(slot_weight), _p(tile_expert), _p(token_slot), _p(counts), M, E,
+                                              int(top_k), _s()))  # fmt: skip
+    return slot_token, slot_weight, tile_expert, token_slot
+
+
+def moe_gather(x, slot_token, *, out=None):
+    """``out[s] = x[slot_token[s]]`` (zeros for padding slots): the activations in slot order."""
+    D = int(x.shape[-1])
+    n = slot_token.numel
+    es = {"bf16": 2, "e4m3": 1, "f32": 4}[_dt(x)]
+    if out is None:
+        out = QuarkTensor.empty(n, D, dtype=_dt(x))
+    elif out.numel != n * D or _dt(out) != _dt(x):
+        raise ValueError(f"qf.moe_gather: out must be {_dt(x)} [{n}, {D}]")
+    _lib.check(_lib.load().qb_moe_gather(_p(x), _p(slot_token), _p(out), n, D * es, _s()))
+    return out
+
+
+def gemm_grouped(A, B, tile_expert, *, n_experts: int, out_dtype="bf16", compute_dtype=None, activation=None, out=None, b_constant=False):
+    """``C[tile i] = A[tile i] @ B[expert(i)].T`` over 128-row tiles of slot-sorted rows; tiles whose expert is -1 are skipped.
+    ``B`` is ``[n_experts * N, K]``.  Replaces ``qf.moe_inproj`` / ``qf.moe_outproj`` (``src/quark/nn/moe.py:307-338``)."""
+    K = int(A.shape[-1])
+    M = A.numel // K
+    if int(B.shape[0]) % int(n_experts) or int(B.shape[1]) != K:
+        raise ValueError(f"qf.gemm_grouped: B {tuple(B.shape)} is not [{n_experts} * N, {K}]")
+    N = int(B.shape[0]) // int(n_experts)
+    if M % 128 or tile_expert.numel != M // 128:
+        raise ValueError(f"qf.gemm_grouped: {M} rows need {M // 128} whole tiles, the table has {tile_expert.numel}")
+    if activation not in (None, "silu"):
+        raise ValueError(f"qf.gemm_grouped: unsupported activation {activation!r}")
+    a_dt, b_dt = _dt(A), _dt(B)
+    cd = compute_dtype or (b_dt if b_dt == "e4m3" else a_dt)
+    if out is None:
+        out = QuarkTensor.empty(M, N, dtype=out_dtype)
+    elif out.numel != M * N or _dt(out) != out_dtype:
+        raise ValueError(f"qf.gemm_grouped: out must be {out_dtype} [{M}, {N}]")
+    p = _lib.GemmParams(
+        M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code(out_dtype, "bf16"), compute_dtype=_code(cd, "bf16"),
+        activation=1 if activation == "silu" else 0, gate_groups=1, split_k=1, tile_n=0, reserved=2 if b_constant else 0, a_scale=None, w_scale=None,
+    )  # fmt: skip
+    lib = _lib.load()
+    ws = _workspace(int(lib.qb_gemm_grouped_workspace_bytes(C.byref(p))))
+    _lib.check(lib.qb_gemm_grouped(_p(A), _p(B), _p(out), _p(tile_expert), int(n_experts), C.byref(p), _p(ws), ws.nbytes if ws is not None else 0, _s()))
+    return out
+
+
+def moe_reduce(partials, slot_weight, token_slot, *, out=None):
+    """``out[m] = sum_k slot_weight[s] * partials[s]``, ``s = token_slot[m, k]``, in f32, narrowed to bf16 once
+    (``src/quark/kernels/moe_reduce/reference.py:16-33``)."""
+    if _dt(partials) != "f32" or _dt(slot_weight) != "f32" or _dt(token_slot) != "s32":
+        raise TypeError("qf.moe_reduce: partials and slot_weight must be f32, token_slot s32")
+    M, top_k = int(token_slot.shape[0]), int(token_slot.shape[1])
+    D = int(partials.shape[-1])
+    if out is None:
+        out = QuarkTensor.empty(M, D, dtype="bf16")
+    elif out.numel != M * D or _dt(out) != "bf16":
+        raise ValueError(f"qf.moe_reduce: out must be bf16 [{M}, {D}]")
+    _lib.check(_lib.load().qb_moe_reduce(_p(partials), _p(slot_weight), _p(token_slot), _p(out), M, D, top_k, _s()))
+    return out
+
+
 def increment(counter):
     if _dt(counter) != "s32":
         raise TypeError("qf.increment: counter must be an s32 tensor")

@@ -195,18 +195,23 @@ class MoE(Module):
 
     Same parameters and layouts as upstream (``router.weight [E, D]``, ``expert_in [E * H, D]``, ``expert_out
     [E * D, H]``), same rounding points (bf16 logits, bf16 hidden activations, f32 partial outputs, one narrowing after
-    the weighted sum), so the result is the reference's.  The schedule is not: instead of sorting tokens into
-    per-expert slots and running grouped GEMMs over them, every expert runs over every token and the routing
-    weights, zero outside a token's top k, select what counts.  That costs E / top_k times the flops of the routed
-    form; it needs no data-dependent shapes and no new GEMM kernel.  The capacity-bounded ``"balanced"`` and
-    ``"shared_experts"`` routings change which experts a token reaches and are not implemented."""
+    the weighted sum), and the reference's schedule: the router emits slot tables sorted by expert (every expert's run
+    padded to whole 128-row tiles), the tokens are gathered into slot order, the two expert projections are grouped
+    GEMMs over ``M * top_k`` (+ padding) rows, and a reduction gathers each token's ``top_k`` partial rows.
+    ``schedule="dense"`` keeps the earlier form (every expert over every token, routing weights zero outside a token's
+    top k: E / top_k times the flops, no data-dependent tables).  The capacity-bounded ``"balanced"`` and
+    ``"shared_experts"`` routings are rejected, as upstream's own ``forward`` does (``src/quark/nn/moe.py:340-347``)."""
 
-    def __init__(self, M: int, d_model: int, d_intermediate: int, n_experts: int, top_k: int, *, routing: str = "correct", out_dtype: str = "bf16"):
+    def __init__(self, M: int, d_model: int, d_intermediate: int, n_experts: int, top_k: int, *, routing: str = "correct", out_dtype: str = "bf16",
+                 schedule: str = "sorted"):  # fmt: skip
         if routing != "correct":
             raise NotImplementedError(f"MoE: routing {routing!r} is not implemented (only 'correct')")
+        if schedule not in ("sorted", "dense"):
+            raise ValueError(f"MoE: schedule {schedule!r} (sorted or dense)")
         if not (1 <= top_k <= n_experts <= 32) or n_experts % 8:
             raise ValueError(f"MoE: top_k {top_k} of {n_experts} experts (8, 16, 24 or 32: the router is a GEMM with one column per expert)")
         self._M, self._D, self._H, self._E, self._K = M, d_model, d_intermediate, n_experts, top_k
+        self._schedule = schedule
         self.router = Linear(d_model, n_experts, out_dtype="bf16", fp8_skip=True)  # stays bf16: few columns, precision matters
         self.expert_in = Parameter(QuarkTensor.zeros(n_experts * d_intermediate, d_model, dtype="bf16"))
         self.expert_out = Parameter(QuarkTensor.zeros(n_experts * d_model, d_intermediate, dtype="bf16"))
@@ -222,8 +227,26 @@ class MoE(Module):
     def forward(self, x):
         M, D, H, E = x.numel // int(x.shape[-1]), self._D, self._H, self._E
         cd = "e4m3" if self._fp8 else None
-        weights = qf.moe_route(self.router(x), top_k=self._K, out=_cached(self, "weights", (E, M), "f32"))
+        logits = self.router(x)
         xq = qf.quantize_e4m3(x, out=_cached(self, "xq", (M, D), "e4m3")) if self._fp8 else x  # once, not per expert
+        if self._schedule == "sorted":
+            n = qf.moe_slots(M, E, self._K)
+            slot_token, slot_weight, tile_expert, token_slot = qf.moe_route_slots(
+                logits, top_k=self._K, slot_token=_cached(self, "slot_token", (n,), "s32"), slot_weight=_cached(self, "slot_weight", (n,), "f32"),
+                tile_expert=_cached(self, "tile_expert", (n // 128,), "s32"), token_slot=_cached(self, "token_slot", (M, self._K), "s32"),
+            )  # fmt: skip
+            xs = qf.moe_gather(xq, slot_token, out=_cached(self, "xs", (n, D), xq.dtype))
+            if not getattr(self, "_partials_cleared", False):
+                # rows of padding tiles are never written nor read; start them from zero once so the buffer holds no junk
+                self._partials_cleared = True
+                _cached(self, "h_s", (n, H), "bf16").zero_()
+                _cached(self, "partials_s", (n, D), "f32").zero_()
+            h = qf.gemm_grouped(xs, self.expert_in.data, tile_expert, n_experts=E, compute_dtype=cd, activation="silu",
+                                out=_cached(self, "h_s", (n, H), "bf16"), b_constant=True)  # fmt: skip
+            partials = qf.gemm_grouped(h, self.expert_out.data, tile_expert, n_experts=E, out_dtype="f32", compute_dtype=cd,
+                                       out=_cached(self, "partials_s", (n, D), "f32"), b_constant=True)  # fmt: skip
+            return qf.moe_reduce(partials, slot_weight, token_slot, out=_cached(self, "out", (M, D), "bf16"))
+        weights = qf.moe_route(logits, top_k=self._K, out=_cached(self, "weights", (E, M), "f32"))
         h = _cached(self, "h", (M, H), "bf16")
         partials = _cached(self, "partials", (E * M, D), "f32")
         for e in range(E):

@@ -943,3 +943,82 @@ def test_moe_route_and_combine(qb):
         wantb = codec.f32_to_bf16(ref)
     assert np.all(np.abs(got.astype(np.int32) - wantb.astype(np.int32)) <= 1)
     assert float((got == wantb).mean()) > 0.99
+
+
+@pytest.mark.parametrize("M,E,K", [(200, 8, 2), (1500, 16, 3), (64, 8, 1)])
+def test_moe_slot_tables(qb, M, E, K):
+    """The routing as slot tables sorted by expert, every run padded to whole 128-row tiles: the tables are a function of
+    the logits alone (slots of an expert in (token, k) order) and say the same as the dense weights
+    (``src/quark/kernels/moe_router_correct/reference.py:38-120``)."""
+    r = util.rng([72, M])
+    logits = bf16_randn(r, (M, E))
+    logits[5, :] = logits[5, 0]
+    qf = qb.qf
+    n = qf.moe_slots(M, E, K)
+    assert n % 128 == 0 and n >= M * K
+    counts = T(qb, np.full(E, -1, np.int32))
+    st, sw, te, ts = qf.moe_route_slots(T(qb, logits, "bf16"), top_k=K, counts=counts)
+    st, sw, te, ts, counts = st.to_numpy(), sw.to_numpy(), te.to_numpy(), ts.to_numpy().reshape(M, K), counts.to_numpy()
+    dense = ops.moe_route(logits, K)  # [E, M]
+    np.testing.assert_array_equal(counts, (dense != 0).sum(axis=1))
+    # expected layout
+    L = f32(logits, "bf16")
+    order = np.argsort(-L, axis=1, kind="stable")[:, :K]
+    off = np.concatenate([[0], np.cumsum((counts + 127) // 128 * 128)])
+    assert off[-1] <= n
+    cursor = off[:-1].copy()
+    want_st = np.full(n, -1, np.int32)
+    want_ts = np.zeros((M, K), np.int32)
+    for t in range(M):
+        for k in range(K):
+            e = order[t, k]
+            want_st[cursor[e]] = t
+            want_ts[t, k] = cursor[e]
+            cursor[e] += 1
+    np.testing.assert_array_equal(st, want_st)
+    np.testing.assert_array_equal(ts, want_ts)
+    want_te = np.full(n // 128, -1, np.int32)
+    for e in range(E):
+        want_te[off[e] // 128 : off[e + 1] // 128] = e
+    np.testing.assert_array_equal(te, want_te)
+    used = st >= 0
+    assert np.all(sw[~used] == 0)
+    exp_of_slot = np.repeat(te, 128)
+    np.testing.assert_allclose(sw[used], dense[exp_of_slot[used], st[used]], atol=1e-6)
+    # gather: rows in slot order, zeros for padding
+    x = bf16_randn(r, (M, 64))
+    xs = qf.moe_gather(T(qb, x, "bf16"), T(qb, st)).to_numpy()
+    np.testing.assert_array_equal(xs[used], x[st[used]])
+    assert not xs[~used].any()
+    # reduce: each token's top_k partial rows, weighted, summed in f32 in order of k
+    parts = r.standard_normal((n, 32)).astype(np.float32)
+    parts[~used] = np.nan  # padding rows are never read
+    got = qf.moe_reduce(T(qb, parts), T(qb, sw), T(qb, ts)).to_numpy()
+    ref = np.zeros((M, 32), np.float32)
+    for k in range(K):
+        ref = ref + sw[ts[:, k]][:, None] * parts[ts[:, k]]
+    with codec.bf16_rounding("rne"):
+        wantb = codec.f32_to_bf16(ref)
+    assert np.all(util.bf16_ulp_diff(got, wantb) <= 1) and float((got == wantb).mean()) > 0.99
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemm_grouped_rows_use_their_experts_weights(qb, fp8):
+    """128-row tiles of A against the weight block of the tile's expert; tiles marked -1 are left alone."""
+    r = util.rng(73)
+    E, N, K = 4, 96, 256
+    tiles = np.array([2, 0, -1, 3, 3, -1], np.int32)
+    Mrows = 128 * len(tiles)
+    dt = "e4m3" if fp8 else "bf16"
+    A = e4m3_randn(r, (Mrows, K)) if fp8 else bf16_randn(r, (Mrows, K))
+    B = e4m3_randn(r, (E * N, K), 0.05) if fp8 else bf16_randn(r, (E * N, K), 0.05)
+    out = T(qb, np.full((Mrows, N), 0x7FC0, np.uint16), "bf16")  # NaN: what a skipped tile must leave behind
+    qb.qf.gemm_grouped(T(qb, A, dt), T(qb, B, dt), T(qb, tiles), n_experts=E, activation="silu", out=out, compute_dtype=dt)
+    got = out.to_numpy()
+    for i, e in enumerate(tiles):
+        rows = slice(128 * i, 128 * i + 128)
+        if e < 0:
+            assert np.all(got[rows] == 0x7FC0)
+            continue
+        want = ops.gemm(A[rows], B[e * N : (e + 1) * N], a_dtype=dt, b_dtype=dt, activation="silu", return_f32=True)
+        _check_gemm(T(qb, got[rows], "bf16"), want, f"tile {i} expert {e} fp8={fp8}", fp8)
