@@ -126,12 +126,12 @@ __device__ __forceinline__ float p_exp(int q, float x) {
 // is v's bit pattern times 2^15 plus a constant: 2^floor(x) * (1 + frac(x) - 0.052), the chord of 2^x lowered by 0.052 so
 // that its mean error over the fraction is near zero (-5.2 % .. +2.3 %; an e4m3 code is 6.25 % wide; in a simulation of
 // 8192-key rows the output's 1 - cosine against exact arithmetic goes from 3.6e-4 to 4.3e-4 at worst).  x is clamped at -120 (the result then
-// narrows to zero).  Every second probability of a row is built this way when QB_LINEXP is on: the exponentials no
-// longer queue behind one another in the special-function unit, at the same number of instructions issued.
-#ifndef QB_LINEXP
-#define QB_LINEXP 1
-#endif
-constexpr bool kLinExp = QB_LINEXP != 0;
+// narrows to zero).  Every second probability of a row is built this way in the kLin instantiations of the e4m3 kernel
+// (the default; qb_set_attn_exact_exp(1) or QB_ATTN_EXACT_EXP=1 selects the instantiations that use the special-function
+// unit for every element): the exponentials no longer queue behind one another there, at the same number of
+// instructions issued.  Measured at 720p, 8320 keys, us per launch: 52.0 exact; 49.5 with the turn passing at chunk 2 as
+// in the exact kernel; 46.5 with the turn passing before chunk 0 (the groups then overlap almost fully, which the exact
+// kernel cannot afford: 62.6); 47.9 without turns; 3 / 5 of every 8 elements instead of 4: 51.6 / 47.2; all: 56.0.
 constexpr float kLinMagic = 49152.0f;  // 1.5 * 2^15: floats in [2^15, 2^16) have an ulp of 2^-8
 __device__ __forceinline__ float ex2_lin_from_biased(float v) {
   v = fmaxf(v, kLinMagic - 120.0f);
@@ -158,12 +158,12 @@ __device__ __forceinline__ void locate_tile(const int (&seg)[6], int j, int& row
 }
 
 // 32 scores of one row (registers) -> probabilities -> the P tile in shared memory (layout of a TMA tile).
-template <bool kFp8, int kPolyOf8>
+template <bool kFp8, int kPolyOf8, bool kLin>
 __device__ __forceinline__ void p_chunk(const uint32_t (&sc)[32], int c, float sl2, float nshift, uint8_t* p_s, int r) {
   const int sw = r & 7;
   const float nshift_lin = nshift + kLinMagic;
   auto pr = [&](int q) {
-    if (kFp8 && kLinExp && (q & 1)) return ex2_lin_from_biased(fmaf(__uint_as_float(sc[q]), sl2, nshift_lin));
+    if (kFp8 && kLin && (q & 1)) return ex2_lin_from_biased(fmaf(__uint_as_float(sc[q]), sl2, nshift_lin));
     return p_exp<kFp8, kPolyOf8>(q, fmaf(__uint_as_float(sc[q]), sl2, nshift));
   };
   if (kFp8) {
@@ -188,7 +188,7 @@ __device__ __forceinline__ void p_chunk(const uint32_t (&sc)[32], int c, float s
 
 // kSplit: the keys of a (query tile, head) are shared by gridDim.z CTAs (see AttnArgs::partials).  The
 // unsplit kernel is an instantiation of its own so that none of this reaches its instruction stream.
-template <bool kFp8, bool kSplit>
+template <bool kFp8, bool kSplit, bool kLin>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
   using L = AttnSmem<kFp8>;
@@ -591,8 +591,8 @@ owl_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       for (int c = 0; c < 4; ++c) {
         // handed over before the last chunks: the other group needs a while to wake up, and two warps
         // per scheduler keep the special-function unit busier than one
-        if (c == kHandoffChunk && lane == 0) mbar_arrive(smem_u32(&turn[1 - g]));
-        p_chunk<kFp8, kPolyOf8>(sc[c], c, sl2, nshift, p_s, r);
+        if (c == (kLin ? 0 : kHandoffChunk) && lane == 0) mbar_arrive(smem_u32(&turn[1 - g]));
+        p_chunk<kFp8, kPolyOf8, kLin>(sc[c], c, sl2, nshift, p_s, r);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -742,6 +742,11 @@ namespace qb {
 int32_t launch_attn4(const void* K_cache, const void* Vt_cache, const AttnArgs& a, int n_kv_heads, bool fp8, cudaStream_t st);
 // bf16 calls with one (query tile, head) per CTA go to the three-group kernel of attn4.cu; QB_ATTN4=0 in the environment
 // when the library is loaded keeps the two-group kernel of this file for everything (e4m3 and key splits always use it).
+// e4m3 probabilities: 0 = every second exponential on the FMA pipe (ex2_lin_from_biased), 1 = all on the special-function unit
+static int g_attn_exact_exp = [] {
+  const char* e = getenv("QB_ATTN_EXACT_EXP");
+  return (e != nullptr && e[0] == '1') ? 1 : 0;
+}();
 static bool attn4_enabled() {
   static const bool on = [] {
     const char* e = getenv("QB_ATTN4");
@@ -752,6 +757,12 @@ static bool attn4_enabled() {
 }  // namespace qb
 
 using namespace qb;
+
+extern "C" int32_t qb_set_attn_exact_exp(int32_t on) {
+  const int32_t was = g_attn_exact_exp;
+  g_attn_exact_exp = on ? 1 : 0;
+  return was;
+}
 
 #ifdef QB_ATTN_TRACE
 extern "C" int32_t qb_debug_attn_trace(void* host_out) {
@@ -860,6 +871,8 @@ extern "C" int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void*
     QB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     return launch_dep("owl_attn kernel", kernel, grid, dim3(kAttnThreads), smem_bytes, st, tmK, tmV, a);
   };
-  if (fp8) return splits > 1 ? launch(owl_attn_kernel<true, true>, AttnSmem<true>::kTotal) : launch(owl_attn_kernel<true, false>, AttnSmem<true>::kTotal);
-  return splits > 1 ? launch(owl_attn_kernel<false, true>, AttnSmem<false>::kTotal) : launch(owl_attn_kernel<false, false>, AttnSmem<false>::kTotal);
+  if (fp8 && !g_attn_exact_exp)
+    return splits > 1 ? launch(owl_attn_kernel<true, true, true>, AttnSmem<true>::kTotal) : launch(owl_attn_kernel<true, false, true>, AttnSmem<true>::kTotal);
+  if (fp8) return splits > 1 ? launch(owl_attn_kernel<true, true, false>, AttnSmem<true>::kTotal) : launch(owl_attn_kernel<true, false, false>, AttnSmem<true>::kTotal);
+  return splits > 1 ? launch(owl_attn_kernel<false, true, false>, AttnSmem<false>::kTotal) : launch(owl_attn_kernel<false, false, false>, AttnSmem<false>::kTotal);
 }
