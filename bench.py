@@ -330,11 +330,8 @@ def time_kernels(qb, eng, peaks):
         "owl_attn": (lambda b: b.attn(qkv, b.kv_cache, ft), None),
         "kv_cache_update": (lambda b: b.kv_cache(qkv, ft, frozen=True), None),
     }
-    # the forms the frame launches when the AdaRMSNorm after out-proj / fc2 runs as that GEMM's tail, and the norm alone
+    # the norm that follows out-proj and fc2, alone
     s1, b1 = eng.model.blocks[0]._cond_lut[0][3], eng.model.blocks[0]._cond_lut[0][4]
-    if qb.qf.gemm_norm_fits(tpf, cfg.d_model):
-        shapes["gemm_out_with_norm"] = (lambda b: b.out_proj(aq, gate=g, residual=xr, norm=(s1, b1, None, True)), gemm_flops(tpf, cfg.d_model, cfg.d_model))
-        shapes["gemm_fc2_with_norm"] = (lambda b: b.mlp.fc2(hq, gate=g, residual=xr, norm=(s1, b1, None, True)), gemm_flops(tpf, cfg.d_model, cfg.mlp_dim))
     shapes["ada_rmsnorm"] = (lambda b: b.pre_mlp_norm(xr, s1, b1, emit_e4m3=True), None)
     for name, (fn, flops) in shapes.items():
         us = timed(fn)

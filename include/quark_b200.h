@@ -154,29 +154,6 @@ size_t qb_gemm_static_scratch_capacity(void);
 int32_t qb_gemm_static_scratch(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                                const qb_gemm_params* p, void* stream);
 
-/* qb_gemm followed, in the same kernel, by the AdaRMSNorm of the finished rows: C = epilogue(A B^T) as qb_gemm writes
- * it (bf16), and norm_out [M, N] bf16 and / or norm_out_q [M, N] e4m3 = ada_rmsnorm(C, norm_scale, norm_bias) with the
- * arithmetic of qb_ada_rmsnorm (the e4m3 copy narrowed from the bf16-rounded result).  Replaces the pair
- * `out_proj / fc2 (+ gate, residual)` -> `pre_mlp_norm / next block's pre_attn_norm`
- * (ref: src/quark/models/waypoint_15.py:413-440, src/quark/functional/ada_rmsnorm.py).  norm_scale / norm_bias are bf16
- * [np->groups, N].  The tiles of a 128-row block exchange their sums of squares through the workspace and wait for one
- * another (bounded; bit 0 of the device status word when the limit runs out), so the whole grid must be resident at
- * once: at most one tile per SM (rejected otherwise), and no other grid of this kind may share the device at the same
- * time from another stream.  The sum of squares is taken tile by tile in a fixed order: deterministic, and equal to
- * qb_ada_rmsnorm of C up to the rounding of that f32 sum (at most one bf16 ulp in an output, rarely).  Needs one K
- * slice, tiles of 64 or 128 columns dividing N, gate and norm row groups made of whole 128-row tiles; the workspace
- * (qb_gemm_norm_workspace_bytes, zero-initialised once, shared as for qb_gemm) is required. */
-typedef struct {
-  int32_t groups;     /* rows of norm_scale / norm_bias; row m of C uses row m / (M / groups) */
-  int32_t activation; /* 0 none, 1 SiLU on the normalised value (the output norm) */
-  float eps;
-  int32_t reserved;
-} qb_norm_params;
-size_t qb_gemm_norm_workspace_bytes(const qb_gemm_params* p);
-int32_t qb_gemm_norm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
-                     const void* norm_scale, const void* norm_bias, void* norm_out, void* norm_out_q, const qb_gemm_params* p,
-                     const qb_norm_params* np, void* workspace, size_t workspace_bytes, void* stream);
-
 /* X -> e4m3, round-to-nearest-even, saturate to +-448, NaN -> 0x7F, no scale.
  * Replaces qf.quantize_e4m3 (ref: src/quark/functional/quantize_e4m3.py:25-69,
  * src/quark/kernels/quantize_e4m3/kernel.py:107-176). src_dtype: QB_BF16 or QB_F32. */
@@ -278,6 +255,14 @@ typedef struct {
   const float* v_scale;
 } qb_attn_params;
 
+/* e4m3 probabilities: by default every second exponential of a score row is built on the FMA pipe as
+ * 2^floor(x) * (1 + frac(x) - 0.052) (relative error -5.2 % .. +2.3 %, below the 6.25 % an e4m3 code spans) so that
+ * the special-function unit is not the kernel's bottleneck; on = 1 computes all of them with ex2.approx, as the
+ * reference kernel does (ref: src/quark/kernels/owl_attn/kernel.py:587-614), at about 12 % more time per call.
+ * Process-wide; returns the previous setting.  QB_ATTN_EXACT_EXP=1 in the environment sets it at load time.
+ * bf16 attention always uses ex2.approx. */
+int32_t qb_set_attn_exact_exp(int32_t on);
+
 /* Bytes of workspace qb_owl_attn needs for `p`: 0 unless the keys of one (query tile, head) are shared by
  * several CTAs, which is chosen when query tiles x heads would leave most SMs idle (360p; a tensor-parallel
  * rank with few heads) or forced with kv_splits.  The workspace starts with one ticket per (query tile,
@@ -351,8 +336,8 @@ int32_t qb_moe_gather(const void* X, const int32_t* slot_token, void* out, int32
 size_t qb_gemm_grouped_workspace_bytes(const qb_gemm_params* p);
 int32_t qb_gemm_grouped(const void* A, const void* B, void* C, const int32_t* tile_expert, int32_t n_experts, const qb_gemm_params* p,
                         void* workspace, size_t workspace_bytes, void* stream);
-/* out[m, :] = bf16(sum over k of slot_weight[s] * partials[s, :], s = token_slot[m, k]), the sum in f32 in order of k, one
- * narrowing.  Replaces qf.moe_reduce (ref: src/quark/kernels/moe_reduce/reference.py:16-33). */
+/* out[m, :] = bf16(sum over k of slot_weight[s] * partials[s, :], s = token_slot[m, k]), the sum in f32 in order of
+ * increasing slot (= expert index; the order of qb_moe_combine, so both schedules give the same bits), one narrowing.  Replaces qf.moe_reduce (ref: src/quark/kernels/moe_reduce/reference.py:16-33). */
 int32_t qb_moe_reduce(const float* partials, const float* slot_weight, const int32_t* token_slot, void* out, int32_t M, int32_t D, int32_t top_k,
                       void* stream);
 /* out[m, :] (bf16 [M, D]) = sum over experts with weights[e][m] != 0 of weights[e][m] * partials[e][m][:] (f32

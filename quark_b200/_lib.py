@@ -81,10 +81,6 @@ class TpParams(C.Structure):
     ]  # fmt: skip
 
 
-class NormParams(C.Structure):
-    _fields_ = [("groups", C.c_int32), ("activation", C.c_int32), ("eps", C.c_float), ("reserved", C.c_int32)]
-
-
 _P, _I, _Z, _F, _U = C.c_void_p, C.c_int32, C.c_size_t, C.c_float, C.c_uint32
 
 # name -> (restype, argtypes); every symbol include/quark_b200.h declares
@@ -148,14 +144,13 @@ SIGNATURES = {
     "qb_patch_gather": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_gemm_tp": (_I, [_P, _P, C.POINTER(GemmParams), C.POINTER(TpParams), _P, _Z, _P]),
+    "qb_set_attn_exact_exp": (_I, [_I]),
     "qb_moe_slots": (_Z, [_I, _I, _I]),
     "qb_moe_route_slots": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qb_moe_gather": (_I, [_P, _P, _P, _I, _I, _P]),
     "qb_gemm_grouped_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
     "qb_gemm_grouped": (_I, [_P, _P, _P, _P, _I, C.POINTER(GemmParams), _P, _Z, _P]),
     "qb_moe_reduce": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
-    "qb_gemm_norm_workspace_bytes": (_Z, [C.POINTER(GemmParams)]),
-    "qb_gemm_norm": (_I, [_P] * 10 + [C.POINTER(GemmParams), C.POINTER(NormParams), _P, _Z, _P]),
     "qb_tp_arena_bytes": (_Z, [_I, _I]),
     "qb_tp_arena_offsets": (_I, [_I, _I, C.POINTER(_Z)]),
     "qb_tp_reduce": (_I, [_P, _P, _P, _P, C.POINTER(TpParams), _P]),
@@ -215,6 +210,12 @@ def kernel_launch_count() -> int:
 def set_dependent_launch(enabled: bool) -> bool:
     """Turns the overlap of a kernel's set-up with its predecessor's tail on or off; returns the old setting."""
     return bool(load().qb_set_dependent_launch(1 if enabled else 0))
+
+
+def set_attn_exact_exp(enabled: bool) -> bool:
+    """e4m3 attention: ``True`` computes every probability with ``ex2.approx``; ``False`` (the default) builds every second one
+    on the FMA pipe from a centred chord of ``2^x`` (see ``qb_set_attn_exact_exp``).  Returns the old setting."""
+    return bool(load().qb_set_attn_exact_exp(1 if enabled else 0))
 
 
 def device_status() -> int:

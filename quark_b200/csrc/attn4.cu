@@ -162,14 +162,14 @@ owl_attn4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   grid_dep_wait();
 
   int seg[6] = {0, 0, 0, 0, 0, 0};
-  const int nseg = min(__ldg(a.n_segments), min(a.max_segments, 3));
+  const int nseg = min(*after_wait(a.n_segments), min(a.max_segments, 3));  // the table is the work of the kernel before: ordinary loads
   bool seg_ok = true;
   int n_chunks = 0;
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     if (i < nseg) {
-      seg[2 * i] = __ldg(a.segments + 2 * i);
-      seg[2 * i + 1] = __ldg(a.segments + 2 * i + 1);
+      seg[2 * i] = after_wait(a.segments)[2 * i];
+      seg[2 * i + 1] = after_wait(a.segments)[2 * i + 1];
       if (seg[2 * i] < 0 || seg[2 * i + 1] < 0 || (seg[2 * i] & 15) != 0 || seg[2 * i] + seg[2 * i + 1] > a.capacity) seg_ok = false;
       n_chunks += (seg[2 * i + 1] + kA4Chunk - 1) / kA4Chunk;
     }
@@ -181,7 +181,7 @@ owl_attn4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (threadIdx.x == 0) atomicOr(a.status, QB_DEV_BAD_SEGMENT);
   }
 
-  if (threadIdx.x < 8) temporal_cos_sin(__ldg(a.frame_t), threadIdx.x, tm);
+  if (threadIdx.x < 8) temporal_cos_sin(*after_wait(a.frame_t), threadIdx.x, tm);
   __syncthreads();
 
   if (warp < 4) {
@@ -296,7 +296,7 @@ owl_attn4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const uint4* src = reinterpret_cast<const uint4*>(a.qkv + static_cast<size_t>(t) * a.q_row + static_cast<size_t>(qh) * a.q_head + g * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          const uint4 x = __ldg(src + v);
+          const uint4 x = src[v];
           const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {

@@ -68,6 +68,16 @@ inline int32_t launch_dep(const char* what, void (*kernel)(KArgs...), dim3 grid,
 }
 
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// What an earlier kernel of the stream may have written is read with ordinary loads through a pointer that has passed
+// through after_wait(): a read-only load (ld.global.nc: __ldg, or what the compiler makes of a const __restrict__
+// parameter) counts as invariant for the whole kernel, so the compiler may issue it before griddepcontrol.wait, i.e.
+// while the earlier kernel is still writing.  __ldg stays for tables nothing on the device ever writes (RoPE table,
+// weights and their scales).
+template <class T>
+__device__ __forceinline__ T* after_wait(T* p) {
+  asm volatile("" : "+l"(p)::"memory");
+  return p;
+}
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -78,17 +78,6 @@ struct GemmArgs {
   // plain stores over NVLink): tp_dst[owner] + (m % tp_rpo) * N.  tp_world == 0: the ordinary output C.
   int tp_world, tp_rpo;
   uint16_t* tp_dst[8];
-  // AdaRMSNorm of the finished output rows as the tail of the fast epilogue (bf16 C, one K slice, whole tiles): the tiles
-  // of a 128-row block exchange their sums of squares through global memory (one bounded wait per CTA; the whole grid is
-  // resident, at most one CTA per SM) and each then normalises its own columns, which it still holds in registers.
-  int norm_on, norm_rows_per_group, norm_activation;
-  float norm_eps;
-  const uint16_t* norm_scale;
-  const uint16_t* norm_bias;
-  uint16_t* norm_out;
-  uint8_t* norm_out_q;
-  float* norm_part;  // [M, 2 * gridDim.x] sums of squares, one per (row, tile, half)
-  int* norm_sync;    // per row block: arrivals, departures; both zero between launches
   // Grouped GEMM (mixture of experts): the 128-row tile i of A belongs to expert tile_expert[i] and is multiplied with
   // rows [expert * N, expert * N + N) of B; a tile with expert -1 is skipped.  NULL: the ordinary GEMM.
   const int* tile_expert;
@@ -99,19 +88,19 @@ struct GemmSmem {
   static constexpr int kStageBytes = kBM * kRowBytes + BN * kRowBytes;
   static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
   static constexpr int kBarOffset = kStages * kStageBytes;
-  static constexpr int kColOffset = kBarOffset + 256;            // per-column scale, bias, gate (and norm scale, bias) of this tile as f32
-  static constexpr int kTotal = kColOffset + 5 * BN * 4 + 1024;  // + norm scale and bias; + alignment slack
+  static constexpr int kColOffset = kBarOffset + 256;            // per-column scale, bias, gate of this tile as f32
+  static constexpr int kTotal = kColOffset + 3 * BN * 4 + 1024;  // + alignment slack
 };
 
 // Applies the epilogue to 8 consecutive columns of one row and stores them.
 __device__ __forceinline__ void epilogue_store8(const GemmArgs& g, float (&v)[8], int m, int n) {
   if (g.a_scale != nullptr || g.w_scale != nullptr) {
-    const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+    const float sa = g.a_scale ? *g.a_scale : 1.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] *= g.w_scale ? sa * __ldg(g.w_scale + n + j) : sa;
   }
   if (g.bias != nullptr) {
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(g.bias + n));
+    const uint4 b = *reinterpret_cast<const uint4*>(g.bias + n);  // may be the output of the kernel before (MLPFusion)
     const uint32_t w[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -125,8 +114,8 @@ __device__ __forceinline__ void epilogue_store8(const GemmArgs& g, float (&v)[8]
   }
   if (g.gate != nullptr) {
     const size_t grow = static_cast<size_t>(m / g.rows_per_gate) * g.N;
-    const uint4 gt = __ldg(reinterpret_cast<const uint4*>(g.gate + grow + n));
-    const uint4 rs = __ldg(reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n));
+    const uint4 gt = *reinterpret_cast<const uint4*>(g.gate + grow + n);
+    const uint4 rs = *reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n);
     const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
     const uint32_t rw[4] = {rs.x, rs.y, rs.z, rs.w};
 #pragma unroll
@@ -193,8 +182,8 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
   const int k_off = q.n_q_heads * 64, v_off = (q.n_q_heads + q.n_kv_heads) * 64;
   const int kind = col0 < k_off ? 0 : col0 < v_off ? 1 : 2;  // Q, K or V head (uniform over the warp)
   const bool in_n = col0 < g.N;
-  const int ft = __ldg(q.frame_t);
-  const int frozen = __ldg(q.frozen);
+  const int ft = *after_wait(q.frame_t);  // written on the device: ordinary loads, after the grid dependency
+  const int frozen = *after_wait(q.frozen);
   const int tpf_c = q.tpf / q.quilt;  // tokens of a frame that the cache keeps
   const int L = q.nb * tpf_c;
   const int cap = L + tpf_c;
@@ -233,7 +222,7 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
   float xy[16];
   uint32_t vf[32];
   const bool mix = kind == 2 && q.qkv_first != nullptr;
-  const float lam = mix ? __ldg(q.lamb) : 0.f;
+  const float lam = mix ? *q.lamb : 0.f;
   if (kind == 1 && valid && in_n) {
     const float4* rp = reinterpret_cast<const float4*>(q.rope_xy + static_cast<size_t>(t) * 16);
 #pragma unroll
@@ -246,7 +235,7 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
     const uint4* fp = reinterpret_cast<const uint4*>(q.qkv_first + static_cast<size_t>(t) * g.N + col0);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint4 v = __ldg(fp + i);
+      const uint4 v = fp[i];  // the first block's QKV, written earlier in this pass
       vf[4 * i] = v.x; vf[4 * i + 1] = v.y; vf[4 * i + 2] = v.z; vf[4 * i + 3] = v.w;
     }
   }
@@ -266,7 +255,7 @@ __device__ __forceinline__ void qkv_tail_epilogue(const GemmArgs& g, uint8_t* sm
     // as the plain epilogue does) and rounded to bf16
     float f[64];
     if (g.a_scale != nullptr || g.w_scale != nullptr) {
-      const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+      const float sa = g.a_scale ? *g.a_scale : 1.0f;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float c0 = (g.w_scale && in_n) ? sa * __ldg(g.w_scale + col0 + j) : sa;
@@ -571,32 +560,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int kMyChunks = BN / 64;  // 32-column chunks per warp
     constexpr int kResInRegs = BN <= 128 ? 1 : 0;
     uint32_t res[kResInRegs ? kMyChunks * 16 : 1];
-    uint32_t xk[kResInRegs ? kMyChunks * 16 : 1];  // norm tail: this thread's columns of the finished row, as stored
-    float ss = 0.f;
     if (fast) {
       // while the main loop runs: per-column vectors of this tile to shared memory, this row's residual to registers
       float* col = reinterpret_cast<float*>(smem + L::kColOffset);
       const int et = threadIdx.x - 64;  // 0 .. 255
-      const float sa = g.a_scale ? __ldg(g.a_scale) : 1.0f;
+      const float sa = g.a_scale ? *g.a_scale : 1.0f;
       const size_t grow = g.gate ? static_cast<size_t>(m0 / g.rows_per_gate) * g.N : 0;
       for (int j = et; j < BN; j += 256) {
         const int n = n0 + j;
         const bool in = n < g.N;
         col[j] = (in && g.w_scale) ? sa * __ldg(g.w_scale + n) : sa;
-        col[BN + j] = (in && g.bias) ? bf16_bits_to_f32(__ldg(g.bias + n)) : 0.f;
-        col[2 * BN + j] = (in && g.gate) ? bf16_bits_to_f32(__ldg(g.gate + grow + n)) : 0.f;
-        if (g.norm_on) {
-          const size_t nrow = static_cast<size_t>(m0 / g.norm_rows_per_group) * g.N;
-          col[3 * BN + j] = in ? __fadd_rn(1.0f, bf16_bits_to_f32(__ldg(g.norm_scale + nrow + n))) : 0.f;
-          col[4 * BN + j] = in ? bf16_bits_to_f32(__ldg(g.norm_bias + nrow + n)) : 0.f;
-        }
+        col[BN + j] = (in && g.bias) ? bf16_bits_to_f32(g.bias[n]) : 0.f;
+        col[2 * BN + j] = (in && g.gate) ? bf16_bits_to_f32(g.gate[grow + n]) : 0.f;
       }
       if (kResInRegs && g.gate != nullptr && m < g.M) {
 #pragma unroll
         for (int q = 0; q < kMyChunks * 4; ++q) {
           const int n = n0 + (2 * (q >> 2) + half) * 32 + (q & 3) * 8;  // chunk 2 * (q / 4) + half, 8 columns at a time
           uint4 x = make_uint4(0u, 0u, 0u, 0u);
-          if (n < g.N) x = __ldg(reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n));
+          if (n < g.N) x = *reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n);
           res[(kResInRegs ? q : 0) * 4 + 0] = x.x;
           res[(kResInRegs ? q : 0) * 4 + 1] = x.y;
           res[(kResInRegs ? q : 0) * 4 + 2] = x.z;
@@ -651,7 +633,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               const uint4* rp = reinterpret_cast<const uint4*>(g.residual + static_cast<size_t>(m) * g.N + n);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const uint4 x = __ldg(rp + q);
+                const uint4 x = rp[q];
                 rw[4 * q] = x.x; rw[4 * q + 1] = x.y; rw[4 * q + 2] = x.z; rw[4 * q + 3] = x.w;
               }
             }
@@ -674,15 +656,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
               for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[16 * h + 2 * j], v[16 * h + 2 * j + 1]);
               st_global_v8(dst + 16 * h, w);
-              if (kResInRegs && g.norm_on) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  xk[kResInRegs ? lc * 16 + 8 * h + j : 0] = w[j];
-                  const float lo = bf16lo(w[j]), hi = bf16hi(w[j]);
-                  ss += lo * lo;
-                  ss += hi * hi;
-                }
-              }
             }
           } else if (g.c_dtype == QB_E4M3) {
             uint32_t w[8];
@@ -779,89 +752,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           epilogue_store8(g, v, mm, n);
         }
         if (threadIdx.x == 64) *counter = 0;  // ready for the next launch
-      }
-    }
-    if (kResInRegs && g.norm_on && fast) {
-      // ---- norm tail (all eight epilogue warps: `fast` is the same for the whole CTA).  Whether the tile was finished
-      // is decided once, by one thread, so that every warp takes the same side of the barriers below.
-      const float* col = reinterpret_cast<const float*>(smem + L::kColOffset);
-      if (threadIdx.x == 64) *last_flag = (*abort_flag == 0) ? 1 : 0;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      const bool go = *last_flag != 0;
-      asm volatile("bar.sync 2, 256;" ::: "memory");  // last_flag is read by everybody before it can change again
-      // exchange the sums of squares with the other tiles of this row block
-      const int slots = 2 * static_cast<int>(gridDim.x);
-      if (go && m < g.M) __stcg(g.norm_part + static_cast<size_t>(m) * slots + 2 * blockIdx.x + half, ss);
-      __threadfence();
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      if (go && threadIdx.x == 64) {
-        int* sync = g.norm_sync + 2 * blockIdx.y;
-        atomicAdd(sync, 1);
-        const long long t0 = clock64();
-        bool arrived = true;
-        while (ld_acquire_gpu_s32(sync) < static_cast<int>(gridDim.x)) {
-          if (clock64() - t0 > kWaitCycleLimit) {
-            arrived = false;
-            break;
-          }
-        }
-        if (!arrived) {
-          *abort_flag = 1;
-          atomicOr(g.status, QB_DEV_WAIT_TIMEOUT_GEMM);
-        } else if (atomicAdd(sync + 1, 1) == static_cast<int>(gridDim.x) - 1) {
-          // everybody has seen the full count: leave both counters at zero for the next launch
-          sync[0] = 0;
-          sync[1] = 0;
-          __threadfence();
-        }
-      }
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      if (go && *abort_flag == 0 && m < g.M) {
-        float tot = 0.f;
-        const float4* pp = reinterpret_cast<const float4*>(g.norm_part + static_cast<size_t>(m) * slots);
-        for (int q = 0; q < slots / 4; ++q) {
-          const float4 t = __ldcg(pp + q);
-          tot += t.x;
-          tot += t.y;
-          tot += t.z;
-          tot += t.w;
-        }
-        const float inv = 1.0f / sqrtf(tot / static_cast<float>(g.N) + g.norm_eps);
-#pragma unroll
-        for (int lc = 0; lc < kMyChunks; ++lc) {
-          const int c = 2 * lc + half;
-          const size_t off = static_cast<size_t>(m) * g.N + n0 + c * 32;
-          float y[32];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t w = xk[kResInRegs ? lc * 16 + j : 0];
-            float a = __fmul_rn(bf16lo(w), inv), b = __fmul_rn(bf16hi(w), inv);
-            a = __fadd_rn(__fmul_rn(a, col[3 * BN + c * 32 + 2 * j]), col[4 * BN + c * 32 + 2 * j]);
-            b = __fadd_rn(__fmul_rn(b, col[3 * BN + c * 32 + 2 * j + 1]), col[4 * BN + c * 32 + 2 * j + 1]);
-            y[2 * j] = g.norm_activation == 1 ? silu_f(a) : a;
-            y[2 * j + 1] = g.norm_activation == 1 ? silu_f(b) : b;
-          }
-          uint32_t ha[8], hb[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            ha[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
-            hb[j] = pack_bf16x2(y[16 + 2 * j], y[16 + 2 * j + 1]);
-          }
-          if (g.norm_out != nullptr) {
-            st_global_v8(g.norm_out + off, ha);
-            st_global_v8(g.norm_out + off + 16, hb);
-          }
-          if (g.norm_out_q != nullptr) {
-            // narrowed from the bf16-rounded value, as a separate cast of the bf16 output would
-            uint32_t qw[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              qw[j] = pack_e4m3x4(bf16lo(ha[2 * j]), bf16hi(ha[2 * j]), bf16lo(ha[2 * j + 1]), bf16hi(ha[2 * j + 1]));
-              qw[4 + j] = pack_e4m3x4(bf16lo(hb[2 * j]), bf16hi(hb[2 * j]), bf16lo(hb[2 * j + 1]), bf16hi(hb[2 * j + 1]));
-            }
-            st_global_v8(g.norm_out_q + off, qw);
-          }
-        }
       }
     }
   }
@@ -1017,7 +907,7 @@ static GemmPlan plan_gemm(const qb_gemm_params& p) {
       const double per_kb = per_sm > shared ? per_sm : shared;
       double cta = kbps * per_kb + 5000.0 + bn * 12.0;
       const bool cl = (p.reserved & 1) == 0 && (s == 2 || s == 4 || s == 8);
-      if (s > 1 && !cl && static_cast<size_t>(tiles) * sizeof(int) > kCounterBytes - 1024) continue;  // more tiles than tickets (the last KiB is the norm tail's)
+      if (s > 1 && !cl && static_cast<size_t>(tiles) * sizeof(int) > kCounterBytes) continue;  // more tiles than counters
       if (s > 1) cta += cl ? 7500.0 + bn * 20.0 + s * bn * 4.0 : 26000.0;
       const double cost = waves * cta;
       if (cost < best_cost) {
@@ -1115,28 +1005,9 @@ struct TpDest {
   uint16_t* dst[8];
 };
 
-struct NormDest {
-  const uint16_t* scale;
-  const uint16_t* bias;
-  uint16_t* out;
-  uint8_t* out_q;
-  int groups, activation;
-  float eps;
-};
-
-// The row blocks' arrival / departure counters of the norm tail sit at the end of the counter area, clear of the tile
-// tickets of the workspace K slices (which a call with a norm tail never uses, but calls sharing the workspace may).
-constexpr int kNormSyncRowBlocks = 128;
-constexpr size_t kNormSyncOffset = kCounterBytes - 2 * kNormSyncRowBlocks * sizeof(int);
-
-static size_t norm_part_bytes(const qb_gemm_params& p, int bn) {
-  return round_up(static_cast<size_t>(p.M) * 2 * ((p.N + bn - 1) / bn) * sizeof(float), 1024);
-}
-
 static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
                         const qb_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream, const QkvTail* tail,
-                        bool clear_counters = false, const TpDest* tp = nullptr, const NormDest* norm = nullptr, const int* tile_expert = nullptr,
-                        int n_experts = 1) {
+                        bool clear_counters = false, const TpDest* tp = nullptr, const int* tile_expert = nullptr, int n_experts = 1) {
   int32_t rc = validate_gemm(p);
   if (rc != QB_OK) return rc;
   QB_REQUIRE(A && B && C, QB_ERR_INVALID_ARG, "gemm: A, B and C must not be NULL");
@@ -1150,9 +1021,8 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
     rows_per_gate = p->M / p->gate_groups;
   }
   const GemmPlan pl = plan_gemm(*p);
-  const size_t norm_bytes = norm != nullptr ? norm_part_bytes(*p, pl.bn) : 0;
-  const size_t need = pl.counters_bytes + pl.aq_bytes + pl.partial_bytes + norm_bytes;
-  const bool uses_ws = pl.aq_bytes > 0 || pl.partial_bytes > 0 || norm_bytes > 0;
+  const size_t need = pl.counters_bytes + pl.aq_bytes + pl.partial_bytes;
+  const bool uses_ws = pl.aq_bytes > 0 || pl.partial_bytes > 0;
   if (uses_ws) {
     QB_REQUIRE(workspace != nullptr && workspace_bytes >= need, QB_ERR_WORKSPACE, "gemm: workspace of %zu bytes needed, %zu given", need,
                workspace_bytes);
@@ -1209,39 +1079,9 @@ static int32_t gemm_run(const void* A, const void* B, void* C, const void* bias,
     // per-column vectors would have to be per expert
     // (a B tile that runs past the expert's last row only feeds columns >= N, which no epilogue stores)
     QB_REQUIRE(pl.splits == 1 && p->M % kBM == 0, QB_ERR_UNSUPPORTED, "gemm_grouped: needs one K slice and M = %d a multiple of 128", p->M);
-    QB_REQUIRE(tail == nullptr && tp == nullptr && norm == nullptr && bias == nullptr && gate == nullptr && p->w_scale == nullptr,
+    QB_REQUIRE(tail == nullptr && tp == nullptr && bias == nullptr && gate == nullptr && p->w_scale == nullptr,
                QB_ERR_UNSUPPORTED, "gemm_grouped: takes the plain or the SiLU epilogue only");
     g.tile_expert = tile_expert;
-  }
-  if (norm != nullptr) {
-    // What the tail relies on: the fast epilogue for every tile (whole tiles in N, one gate row and one norm row per
-    // tile, bf16 rows the residual registers can hold) and a grid that is resident as a whole, so that the wait of a
-    // row block's tiles for one another cannot starve a tile that has not started.
-    const int tiles_n = (p->N + pl.bn - 1) / pl.bn, tiles_m = (p->M + kBM - 1) / kBM;
-    QB_REQUIRE(tail == nullptr && tp == nullptr, QB_ERR_UNSUPPORTED, "gemm_norm: not combined with the QKV tail or per-rank destinations");
-    QB_REQUIRE(pl.splits == 1 && pl.bn <= 128 && p->N % pl.bn == 0 && p->c_dtype == QB_BF16 && (reinterpret_cast<uintptr_t>(C) & 31u) == 0,
-               QB_ERR_UNSUPPORTED, "gemm_norm: needs one K slice, tiles of 64 or 128 columns that divide N = %d, a 32-byte aligned bf16 C", p->N);
-    QB_REQUIRE(norm->groups >= 1 && p->M % norm->groups == 0, QB_ERR_INVALID_ARG, "gemm_norm: norm groups %d do not divide M = %d", norm->groups, p->M);
-    const int rpn = p->M / norm->groups;
-    QB_REQUIRE((norm->groups == 1 || rpn % kBM == 0) && (gate == nullptr || p->gate_groups == 1 || rows_per_gate % kBM == 0), QB_ERR_UNSUPPORTED,
-               "gemm_norm: a 128-row tile must lie inside one gate row group and one norm row group");
-    QB_REQUIRE(tiles_n * tiles_m <= num_sms() && tiles_m <= kNormSyncRowBlocks, QB_ERR_UNSUPPORTED,
-               "gemm_norm: %d x %d tiles do not fit the device at one per SM", tiles_m, tiles_n);
-    QB_REQUIRE(norm->scale && norm->bias && (norm->out || norm->out_q), QB_ERR_INVALID_ARG, "gemm_norm: norm scale, bias and an output are required");
-    QB_REQUIRE(aligned16(norm->scale) && aligned16(norm->bias) && (reinterpret_cast<uintptr_t>(norm->out) & 31u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(norm->out_q) & 31u) == 0, QB_ERR_ALIGN, "gemm_norm: norm outputs must be 32-byte aligned");
-    QB_REQUIRE(norm->activation == 0 || norm->activation == 1, QB_ERR_INVALID_ARG, "gemm_norm: activation %d", norm->activation);
-    QB_REQUIRE(norm->eps > 0.f, QB_ERR_INVALID_ARG, "gemm_norm: eps must be positive");
-    g.norm_on = 1;
-    g.norm_rows_per_group = rpn;
-    g.norm_activation = norm->activation;
-    g.norm_eps = norm->eps;
-    g.norm_scale = norm->scale;
-    g.norm_bias = norm->bias;
-    g.norm_out = norm->out;
-    g.norm_out_q = norm->out_q;
-    g.norm_part = reinterpret_cast<float*>(ws + pl.counters_bytes + pl.aq_bytes + pl.partial_bytes);
-    g.norm_sync = reinterpret_cast<int*>(ws + kNormSyncOffset);
   }
 
   dim3 grid((p->N + pl.bn - 1) / pl.bn, (p->M + kBM - 1) / kBM, pl.splits);
@@ -1342,44 +1182,7 @@ extern "C" int32_t qb_gemm_grouped(const void* A, const void* B, void* C, const 
   QB_REQUIRE(n_experts >= 1 && static_cast<long long>(n_experts) * p->N < (1ll << 31), QB_ERR_INVALID_ARG, "gemm_grouped: %d experts", n_experts);
   qb_gemm_params q = *p;
   q.split_k = 1;  // a padding tile leaves before any K slice could wait for it
-  return gemm_run(A, B, C, nullptr, nullptr, nullptr, &q, workspace, workspace_bytes, stream, nullptr, false, nullptr, nullptr, tile_expert, n_experts);
-}
-
-// The plan of a GEMM with a norm tail: one K slice, tiles of at most 128 columns.
-static qb_gemm_params norm_plan_params(const qb_gemm_params& p) {
-  qb_gemm_params q = p;
-  q.split_k = 1;
-  if (q.tile_n == 0) {
-    const int bn = plan_gemm(q).bn;
-    const long tiles = static_cast<long>((q.M + kBM - 1) / kBM) * ((q.N + bn - 1) / bn);
-    if (bn > 128 || (bn < 128 && tiles > num_sms())) q.tile_n = 128;  // 128 columns where 64 would not leave one tile per SM
-  }
-  return q;
-}
-
-extern "C" size_t qb_gemm_norm_workspace_bytes(const qb_gemm_params* p) {
-  if (validate_gemm(p) != QB_OK) return 0;
-  const qb_gemm_params q = norm_plan_params(*p);
-  const GemmPlan pl = plan_gemm(q);
-  return pl.counters_bytes + pl.aq_bytes + pl.partial_bytes + norm_part_bytes(q, pl.bn);
-}
-
-extern "C" int32_t qb_gemm_norm(const void* A, const void* B, void* C, const void* bias, const void* gate, const void* residual,
-                                const void* norm_scale, const void* norm_bias, void* norm_out, void* norm_out_q, const qb_gemm_params* p,
-                                const qb_norm_params* np, void* workspace, size_t workspace_bytes, void* stream) {
-  QB_REQUIRE(p != nullptr && np != nullptr, QB_ERR_INVALID_ARG, "gemm_norm: params are NULL");
-  int32_t rc = validate_gemm(p);
-  if (rc != QB_OK) return rc;
-  const qb_gemm_params q = norm_plan_params(*p);
-  NormDest d{};
-  d.scale = static_cast<const uint16_t*>(norm_scale);
-  d.bias = static_cast<const uint16_t*>(norm_bias);
-  d.out = static_cast<uint16_t*>(norm_out);
-  d.out_q = static_cast<uint8_t*>(norm_out_q);
-  d.groups = np->groups;
-  d.activation = np->activation;
-  d.eps = np->eps;
-  return gemm_run(A, B, C, bias, gate, residual, &q, workspace, workspace_bytes, stream, nullptr, false, nullptr, &d);
+  return gemm_run(A, B, C, nullptr, nullptr, nullptr, &q, workspace, workspace_bytes, stream, nullptr, false, nullptr, tile_expert, n_experts);
 }
 
 // ---------------------------------------------------------------- GEMM on built-in scratch memory

@@ -34,9 +34,9 @@ __device__ __forceinline__ void round_through_bf16(float (&f)[8]) {
 // ---------------------------------------------------------------- AdaRMSNorm
 // One CTA per row; each thread owns D / (8 * blockDim) groups of 8 consecutive elements.
 template <int kThreads>
-__global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ scale,
-                                                                const uint16_t* __restrict__ bias, uint16_t* __restrict__ out,
-                                                                uint8_t* __restrict__ out_q, int D, int rows_per_group, float eps,
+__global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* X, const uint16_t* scale,
+                                                                const uint16_t* bias, uint16_t* out,
+                                                                uint8_t* out_q, int D, int rows_per_group, float eps,
                                                                 int activation) {
   grid_dep_wait();    // inputs come from the kernels before this one
   grid_dep_launch();  // the next kernel may begin its set-up
@@ -51,8 +51,8 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* _
     const int c = (i * kThreads + threadIdx.x) * 8;
     if (c < D) {
       xv[i] = *reinterpret_cast<const uint4*>(x + c);
-      sv[i] = __ldg(reinterpret_cast<const uint4*>(scale + goff + c));
-      bv[i] = __ldg(reinterpret_cast<const uint4*>(bias + goff + c));
+      sv[i] = *reinterpret_cast<const uint4*>(scale + goff + c);
+      bv[i] = *reinterpret_cast<const uint4*>(bias + goff + c);
       float f[8];
       unpack8(xv[i], f);
 #pragma unroll
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* _
 
 // ---------------------------------------------------------------- per-head RMSNorm on packed qkv
 // 8 threads per (row, head): 8 x 8 = 64 elements; heads >= n_norm_heads (the V heads) are copied.
-__global__ void __launch_bounds__(256) head_rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, int rows,
+__global__ void __launch_bounds__(256) head_rmsnorm_kernel(const uint16_t* X, uint16_t* out, int rows,
                                                             int heads_total, int n_norm_heads, float eps) {
   const size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   const size_t item = gid >> 3;  // (row, head)
@@ -121,15 +121,15 @@ __global__ void __launch_bounds__(256) head_rmsnorm_kernel(const uint16_t* __res
 }
 
 // ---------------------------------------------------------------- value residual on the V columns
-__global__ void __launch_bounds__(256) value_residual_kernel(const uint16_t* __restrict__ cur, const uint16_t* __restrict__ first,
-                                                              const float* __restrict__ lamb, uint16_t* __restrict__ out, int rows,
+__global__ void __launch_bounds__(256) value_residual_kernel(const uint16_t* cur, const uint16_t* first,
+                                                              const float* lamb, uint16_t* out, int rows,
                                                               int D_full, int v_off, int v_width) {
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
   if (i8 >= static_cast<size_t>(rows) * D_full) return;
   const int col = static_cast<int>(i8 % D_full);
   uint4 c = *reinterpret_cast<const uint4*>(cur + i8);
   if (col >= v_off && col < v_off + v_width) {
-    const float lam = __ldg(lamb);
+    const float lam = *lamb;
     float a[8], b[8];
     unpack8(c, a);
     unpack8(*reinterpret_cast<const uint4*>(first + i8), b);
@@ -141,8 +141,8 @@ __global__ void __launch_bounds__(256) value_residual_kernel(const uint16_t* __r
 }
 
 // ---------------------------------------------------------------- x + gate * y
-__global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ Y,
-                                                             const uint16_t* __restrict__ gate, uint16_t* __restrict__ out, int rows,
+__global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* X, const uint16_t* Y,
+                                                             const uint16_t* gate, uint16_t* out, int rows,
                                                              int D, int rows_per_group) {
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
   if (i8 >= static_cast<size_t>(rows) * D) return;
@@ -150,14 +150,14 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const uint16_t* __re
   float x[8], y[8], g[8];
   unpack8(*reinterpret_cast<const uint4*>(X + i8), x);
   unpack8(*reinterpret_cast<const uint4*>(Y + i8), y);
-  unpack8(__ldg(reinterpret_cast<const uint4*>(gate + static_cast<size_t>(row / rows_per_group) * D + col)), g);
+  unpack8(*reinterpret_cast<const uint4*>(gate + static_cast<size_t>(row / rows_per_group) * D + col), g);
 #pragma unroll
   for (int j = 0; j < 8; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(g[j], y[j]));
   *reinterpret_cast<uint4*>(out + i8) = pack8(x);
 }
 
 // ---------------------------------------------------------------- SiLU / Euler / quantise
-__global__ void __launch_bounds__(256) silu_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, uint8_t* __restrict__ out_q,
+__global__ void __launch_bounds__(256) silu_kernel(const uint16_t* X, uint16_t* out, uint8_t* out_q,
                                                     size_t n) {
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
   if (i8 + 8 <= n) {
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256) silu_kernel(const uint16_t* __restrict__ 
 // (the controller-conditioning path: src/quark/kernels/rmsnorm/reference.py:10-22, elementwise add)
 // One CTA per row, like ada_rmsnorm without the affine step.
 template <int kThreads>
-__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ out, int D, float eps) {
+__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const uint16_t* X, uint16_t* out, int D, float eps) {
   grid_dep_wait();
   grid_dep_launch();
   const int row = blockIdx.x;
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const uint16_t* __res
   }
 }
 
-__global__ void __launch_bounds__(256) add_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ Y, uint16_t* __restrict__ out,
+__global__ void __launch_bounds__(256) add_kernel(const uint16_t* X, const uint16_t* Y, uint16_t* out,
                                                    size_t n) {
   grid_dep_wait();
   grid_dep_launch();
@@ -244,12 +244,12 @@ __global__ void __launch_bounds__(256) add_kernel(const uint16_t* __restrict__ X
   }
 }
 
-__global__ void __launch_bounds__(256) euler_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ V,
-                                                     const float* __restrict__ dsig, uint16_t* __restrict__ out, size_t n) {
+__global__ void __launch_bounds__(256) euler_kernel(const uint16_t* X, const uint16_t* V,
+                                                     const float* dsig, uint16_t* out, size_t n) {
   grid_dep_wait();    // inputs come from the kernels before this one
   grid_dep_launch();  // the next kernel may begin its set-up
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
-  const float d = __ldg(dsig);
+  const float d = *dsig;
   if (i8 + 8 <= n) {
     float x[8], v[8];
     unpack8(*reinterpret_cast<const uint4*>(X + i8), x);
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(256) euler_kernel(const uint16_t* __restrict__
 }
 
 template <bool kFromF32>
-__global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ X, uint8_t* __restrict__ out, size_t n) {
+__global__ void __launch_bounds__(256) quantize_kernel(const void* X, uint8_t* out, size_t n) {
   const size_t i8 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
   if (i8 + 8 <= n) {
     float f[8];
@@ -287,8 +287,8 @@ __global__ void __launch_bounds__(256) quantize_kernel(const void* __restrict__ 
 
 // One CTA per row: row maximum of |x| (a maximum does not depend on the order it is taken in), scale = amax / 448,
 // out = e4m3(x * (1 / scale)).  Weights are narrowed once, at load time: nothing here is tuned.
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* __restrict__ X, uint8_t* __restrict__ out,
-                                                            float* __restrict__ scale_out, int cols) {
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* X, uint8_t* out,
+                                                            float* scale_out, int cols) {
   __shared__ float red[8];
   const uint16_t* x = X + static_cast<size_t>(blockIdx.x) * cols;
   float m = 0.f;
@@ -334,7 +334,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint16_t v) {
   return *reinterpret_cast<const uint32_t*>(&b);
 }
 
-__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ X, uint16_t* __restrict__ out, size_t n) {
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* X, uint16_t* out, size_t n) {
   grid_dep_wait();
   grid_dep_launch();
   const size_t i16 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 16;
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
 // (ref: src/quark/kernels/moe_router_correct/reference.py:38-49, the "correct" routing).
 constexpr int kMoeMaxExperts = 32;
 
-__global__ void __launch_bounds__(128) moe_route_kernel(const uint16_t* __restrict__ logits, float* __restrict__ weights, int M, int E,
+__global__ void __launch_bounds__(128) moe_route_kernel(const uint16_t* logits, float* weights, int M, int E,
                                                          int top_k) {
   grid_dep_wait();
   grid_dep_launch();
@@ -388,8 +388,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const uint16_t* __restri
 
 // out[m, :] = bf16( sum over the experts e with weights[e][m] != 0, in order of e, of weights[e][m] * partials[e][m][:] ),
 // the sum in f32 and one narrowing at the end (ref: src/quark/kernels/moe_reduce/reference.py:16-33).
-__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ partials, const float* __restrict__ weights,
-                                                           uint16_t* __restrict__ out, int M, int D, int E) {
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* partials, const float* weights,
+                                                           uint16_t* out, int M, int D, int E) {
   grid_dep_wait();
   grid_dep_launch();
   const int m = blockIdx.x;
@@ -419,7 +419,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 constexpr int kMoeTile = 128;
 constexpr int kMoeRouteThreads = 1024;
 
-__device__ __forceinline__ void moe_topk(const uint16_t* __restrict__ row, int E, int top_k, int (&ex)[kMoeMaxExperts], float (&wt)[kMoeMaxExperts]) {
+__device__ __forceinline__ void moe_topk(const uint16_t* row, int E, int top_k, int (&ex)[kMoeMaxExperts], float (&wt)[kMoeMaxExperts]) {
   float l[kMoeMaxExperts];
   for (int e = 0; e < E; ++e) l[e] = bf16_bits_to_f32(row[e]);
   unsigned taken = 0;
@@ -437,9 +437,9 @@ __device__ __forceinline__ void moe_topk(const uint16_t* __restrict__ row, int E
   for (int k = 0; k < top_k; ++k) wt[k] = wt[k] / sum;
 }
 
-__global__ void __launch_bounds__(kMoeRouteThreads) moe_route_slots_kernel(const uint16_t* __restrict__ logits, int* __restrict__ slot_token,
-                                                                            float* __restrict__ slot_weight, int* __restrict__ tile_expert,
-                                                                            int* __restrict__ token_slot, int* __restrict__ counts_out, int M, int E,
+__global__ void __launch_bounds__(kMoeRouteThreads) moe_route_slots_kernel(const uint16_t* logits, int* slot_token,
+                                                                            float* slot_weight, int* tile_expert,
+                                                                            int* token_slot, int* counts_out, int M, int E,
                                                                             int top_k, int n_slots) {
   grid_dep_wait();
   grid_dep_launch();
@@ -522,7 +522,7 @@ __global__ void __launch_bounds__(kMoeRouteThreads) moe_route_slots_kernel(const
 }
 
 // out[s, :] = X[slot_token[s], :] (rows of `row_bytes` bytes, a multiple of 16), zeros for padding slots
-__global__ void __launch_bounds__(256) moe_gather_kernel(const uint8_t* __restrict__ X, const int* __restrict__ slot_token, uint8_t* __restrict__ out,
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint8_t* X, const int* slot_token, uint8_t* out,
                                                           int row_bytes) {
   grid_dep_wait();
   grid_dep_launch();
@@ -535,17 +535,29 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint8_t* __restri
   }
 }
 
-// out[m, :] = bf16( sum over k, in order, of slot_weight[slot] * partials[slot][:] ), slot = token_slot[m, k]; the sum in
-// f32, one narrowing at the end (ref: src/quark/kernels/moe_reduce/reference.py:16-33)
-__global__ void __launch_bounds__(256) moe_reduce_kernel(const float* __restrict__ partials, const float* __restrict__ slot_weight,
-                                                          const int* __restrict__ token_slot, uint16_t* __restrict__ out, int D, int top_k) {
+// out[m, :] = bf16( sum over the token's top_k slots of slot_weight[slot] * partials[slot][:] ), the sum in f32 (fused
+// multiply-adds) in order of increasing slot, i.e. of increasing expert index - the order of the dense schedule's
+// moe_combine_kernel, so that both schedules give the same bits - and one narrowing at the end
+// (ref: src/quark/kernels/moe_reduce/reference.py:16-33)
+__global__ void __launch_bounds__(256) moe_reduce_kernel(const float* partials, const float* slot_weight,
+                                                          const int* token_slot, uint16_t* out, int D, int top_k) {
   grid_dep_wait();
   grid_dep_launch();
   const int m = blockIdx.x;
+  int slots[kMoeMaxExperts];
+  for (int k = 0; k < top_k; ++k) {  // insertion sort: top_k is small
+    const int s = token_slot[static_cast<size_t>(m) * top_k + k];
+    int j = k;
+    while (j > 0 && slots[j - 1] > s) {
+      slots[j] = slots[j - 1];
+      --j;
+    }
+    slots[j] = s;
+  }
   for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < top_k; ++k) {
-      const int slot = token_slot[static_cast<size_t>(m) * top_k + k];
+      const int slot = slots[k];
       const float w = slot_weight[slot];
       const float4 y = *reinterpret_cast<const float4*>(partials + static_cast<size_t>(slot) * D + d);
       acc[0] = fmaf(w, y.x, acc[0]); acc[1] = fmaf(w, y.y, acc[1]); acc[2] = fmaf(w, y.z, acc[2]); acc[3] = fmaf(w, y.w, acc[3]);
@@ -582,7 +594,7 @@ __device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uin
 __device__ __forceinline__ float randn_uniform(uint32_t x) { return fmaf(static_cast<float>(x >> 8), 5.9604644775390625e-8f, 2.98023223876953125e-8f); }
 
 template <typename Out>
-__global__ void __launch_bounds__(kRandnThreads) randn_kernel(const uint32_t* __restrict__ counter, Out* __restrict__ out, size_t n,
+__global__ void __launch_bounds__(kRandnThreads) randn_kernel(const uint32_t* counter, Out* out, size_t n,
                                                               uint32_t stride, uint32_t seed0, uint32_t seed1) {
   grid_dep_wait();
   grid_dep_launch();
@@ -623,8 +635,8 @@ __global__ void __launch_bounds__(kRandnThreads) randn_kernel(const uint32_t* __
 // reads its weight row once for all staged tokens.
 constexpr int kPatchTok = 8;
 
-__global__ void __launch_bounds__(256) patchify_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ W,
-                                                        uint16_t* __restrict__ out, int C, int H, int Wd, int ph, int pw, int d_model,
+__global__ void __launch_bounds__(256) patchify_kernel(const uint16_t* X, const uint16_t* W,
+                                                        uint16_t* out, int C, int H, int Wd, int ph, int pw, int d_model,
                                                         int tokens) {
   extern __shared__ float patch[];  // [kPatchTok][K]
   const int K = C * ph * pw;
@@ -664,8 +676,8 @@ __global__ void __launch_bounds__(256) patchify_kernel(const uint16_t* __restric
   }
 }
 
-__global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* __restrict__ X, const uint16_t* __restrict__ W,
-                                                          const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int C, int H,
+__global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* X, const uint16_t* W,
+                                                          const uint16_t* bias, uint16_t* out, int C, int H,
                                                           int Wd, int ph, int pw, int d_model, int tokens) {
   extern __shared__ float xs[];  // [kPatchTok][d_model]
   const int Nout = C * ph * pw;
@@ -709,7 +721,7 @@ __global__ void __launch_bounds__(128) unpatchify_kernel(const uint16_t* __restr
 // (token = patch (hp, wp), feature k = c*ph*pw + r*pw + q), so that patchify / unpatchify can run
 // their contraction on the tensor-core GEMM.  kToTokens: latent -> tokens, else tokens -> latent.
 template <bool kToTokens>
-__global__ void __launch_bounds__(256) patch_move_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C, int H, int Wd,
+__global__ void __launch_bounds__(256) patch_move_kernel(const uint16_t* src, uint16_t* dst, int C, int H, int Wd,
                                                           int ph, int pw, int tokens) {
   grid_dep_wait();    // inputs come from the kernels before this one
   grid_dep_launch();  // the next kernel may begin its set-up
@@ -900,7 +912,8 @@ int32_t qb_moe_gather(const void* X, const int32_t* slot_token, void* out, int32
 int32_t qb_moe_reduce(const float* partials, const float* slot_weight, const int32_t* token_slot, void* out, int32_t M, int32_t D, int32_t top_k,
                       void* stream) {
   QB_REQUIRE(partials && slot_weight && token_slot && out, QB_ERR_INVALID_ARG, "moe_reduce: NULL pointer");
-  QB_REQUIRE(M > 0 && D > 0 && D % 4 == 0 && top_k > 0, QB_ERR_INVALID_ARG, "moe_reduce: M %d, D %d (a multiple of 4), top_k %d", M, D, top_k);
+  QB_REQUIRE(M > 0 && D > 0 && D % 4 == 0 && top_k > 0 && top_k <= kMoeMaxExperts, QB_ERR_INVALID_ARG,
+             "moe_reduce: M %d, D %d (a multiple of 4), top_k %d (at most %d)", M, D, top_k, kMoeMaxExperts);
   QB_REQUIRE(aligned16(partials) && aligned16(out), QB_ERR_ALIGN, "moe_reduce: pointers must be 16-byte aligned");
   return launch_dep("moe_reduce", moe_reduce_kernel, dim3(M), dim3(256), 0, static_cast<cudaStream_t>(stream), partials, slot_weight, token_slot,
                     static_cast<uint16_t*>(out), D, top_k);

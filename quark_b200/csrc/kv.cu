@@ -46,8 +46,8 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
 
   const int head = blockIdx.y;
   const int t0 = blockIdx.x * kKvTile;
-  const int ft = __ldg(a.frame_t);
-  const int frozen = __ldg(a.frozen);
+  const int ft = *a.frame_t;
+  const int frozen = *a.frozen;
   const int L = a.nb * a.tpf;
   const int cap = L + a.tpf;
   const int bucket = (ft + a.pd - 1) / a.pd;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kKvThreads) kv_append_kernel(const KvArgs a) {
 // rope_xy[t][0..7] = cos, [8..15] = sin of the 4 x-angles and 4 y-angles of token t.
 // Angles are evaluated the way numpy evaluates the table: positions from an f64 linspace
 // narrowed to f32, multiplied in f64 by (1 + i * step) * pi, narrowed to f32.
-__global__ void rope_table_kernel(float* __restrict__ out, int H, int W) {
+__global__ void rope_table_kernel(float* out, int H, int W) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= H * W * 8) return;
   const int t = idx >> 3, i = idx & 7;

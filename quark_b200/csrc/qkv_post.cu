@@ -72,8 +72,8 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
 
   const int head = blockIdx.y;
   const int t0 = blockIdx.x * kPostTile;
-  const int ft = __ldg(a.frame_t);
-  const int frozen = __ldg(a.frozen);
+  const int ft = *after_wait(a.frame_t);  // written on the device (incremented after every frame): an ordinary load
+  const int frozen = *after_wait(a.frozen);
   const int L = a.nb * a.tpf;
   const int cap = L + a.tpf;
   const int bucket = (ft + a.pd - 1) / a.pd;
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(kPostThreads) qkv_post_kernel(const QkvPostArg
   }
 
   // ---- V: value residual, round, keep a copy for the transpose, write the packed output
-  const float lam = a.qkv_first != nullptr ? __ldg(a.lamb) : 0.f;
+  const float lam = a.qkv_first != nullptr ? *a.lamb : 0.f;
   for (int v = threadIdx.x; v < kPostTile * 8; v += kPostThreads) {
     const int tt = v >> 3, c = v & 7;
     const size_t off = static_cast<size_t>(t0 + tt) * a.qkv_dim + v_off + head * 64 + c * 8;

@@ -98,13 +98,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// A counter another CTA of the same grid increments: loaded with acquire semantics at device scope.
-__device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // ---------------------------------------------------------------- TMA (every copy lands in the issuing CTA only)
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

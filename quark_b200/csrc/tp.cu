@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
           }
           float r[8], g[8];
           tp_unpack8(*reinterpret_cast<const uint4*>(a.residual[rank] + roff + c), r);
-          tp_unpack8(__ldg(reinterpret_cast<const uint4*>(a.gate + goff + c)), g);
+          tp_unpack8(*reinterpret_cast<const uint4*>(a.gate + goff + c), g);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float s = __bfloat162float(__float2bfloat16_rn(acc[j]));  // the summed partial as a bf16 tensor
@@ -194,8 +194,8 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
           if (a.nscale != nullptr) {
             float f[8], s[8], b[8];
             tp_unpack8(xv[i], f);
-            tp_unpack8(__ldg(reinterpret_cast<const uint4*>(a.nscale + noff + c)), s);
-            tp_unpack8(__ldg(reinterpret_cast<const uint4*>(a.nbias + noff + c)), b);
+            tp_unpack8(*reinterpret_cast<const uint4*>(a.nscale + noff + c), s);
+            tp_unpack8(*reinterpret_cast<const uint4*>(a.nbias + noff + c), b);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float y = __fmul_rn(f[j], inv);

@@ -199,61 +199,6 @@ def gemm(A, B, out_dtype=None, compute_dtype=None, b_shuffled=False, activation=
     return out
 
 
-def gemm_norm(A, B, norm_scale, norm_bias, *, gate=None, residual=None, gate_groups=1, out=None, norm_out=None, norm_out_q=None,
-              emit_bf16=True, emit_e4m3=False, activation=None, eps=1e-6, compute_dtype=None, w_scale=None, a_scale=None,
-              b_constant=False):  # fmt: skip
-    """``x = residual + gate * (A @ B.T)`` and ``ada_rmsnorm(x, norm_scale, norm_bias)`` from one kernel: the row-block's
-    tiles exchange their sums of squares at the end of the GEMM and normalise their own columns.  Replaces
-    ``out_proj`` / ``fc2`` with the gate + residual epilogue followed by the next ``qf.ada_rmsnorm``
-    (``src/quark/models/waypoint_15.py:413-440``).  Returns ``(x, h, hq)`` (``h`` bf16 and ``hq`` e4m3 as asked for).
-    Shapes the kernel does not take (more tiles than SMs, 256-column tiles, ragged N) raise; ``gemm_norm_fits`` tells."""
-    K = int(A.shape[-1])
-    M = A.numel // K
-    N = int(B.shape[0])
-    if int(B.shape[1]) != K:
-        raise ValueError(f"qf.gemm_norm: A is [..., {K}] but B is {B.shape}")
-    if (gate is None) != (residual is None):
-        raise ValueError("qf.gemm_norm: gate and residual must be given together")
-    if activation not in (None, "silu"):
-        raise ValueError(f"qf.gemm_norm: unsupported activation {activation!r}")
-    groups = norm_scale.numel // N
-    if norm_scale.numel != groups * N or norm_bias.numel != groups * N or groups < 1:
-        raise ValueError(f"qf.gemm_norm: norm scale / bias must be [groups, {N}]")
-    a_dt, b_dt = _dt(A), _dt(B)
-    cd = compute_dtype or (b_dt if b_dt == "e4m3" else a_dt)
-    if out is None:
-        out = QuarkTensor.empty(M, N, dtype="bf16")
-    if emit_bf16 and norm_out is None:
-        norm_out = QuarkTensor.empty(M, N, dtype="bf16")
-    if emit_e4m3 and norm_out_q is None:
-        norm_out_q = QuarkTensor.empty(M, N, dtype="e4m3")
-    if norm_out is None and norm_out_q is None:
-        raise ValueError("qf.gemm_norm: ask for the bf16 result, the e4m3 result or both")
-    p = _lib.GemmParams(
-        M=M, N=N, K=K, a_dtype=_code(a_dt, "bf16"), b_dtype=_code(b_dt, "bf16"), c_dtype=_code("bf16", "bf16"), compute_dtype=_code(cd, "bf16"),
-        activation=0, gate_groups=int(gate_groups), split_k=1, tile_n=0, reserved=2 if b_constant else 0,
-        a_scale=a_scale.data_ptr() if a_scale is not None else None, w_scale=w_scale.data_ptr() if w_scale is not None else None,
-    )  # fmt: skip
-    np_ = _lib.NormParams(groups=int(groups), activation=1 if activation == "silu" else 0, eps=float(eps), reserved=0)
-    lib = _lib.load()
-    ws = _workspace(int(lib.qb_gemm_norm_workspace_bytes(C.byref(p))))
-    _lib.check(
-        lib.qb_gemm_norm(_p(A), _p(B), _p(out), None, _p(gate), _p(residual), _p(norm_scale), _p(norm_bias), _p(norm_out), _p(norm_out_q),
-                         C.byref(p), C.byref(np_), _p(ws), ws.nbytes if ws is not None else 0, _s())
-    )  # fmt: skip
-    return out, norm_out, norm_out_q
-
-
-def gemm_norm_fits(M: int, N: int, *, gate_groups: int = 1, norm_groups: int = 1, sms: int = 148) -> bool:
-    """Whether ``gemm_norm`` takes an ``[M, N]`` output: 64-column tiles at one per SM at most (the kernel's tiles wait for
-    one another, so the grid must be resident as a whole), row groups made of whole 128-row tiles."""
-    tiles_m = (M + 127) // 128
-    for g in (gate_groups, norm_groups):
-        if g != 1 and (M % g or (M // g) % 128):
-            return False
-    return N % 128 == 0 and tiles_m * (N // 128) <= sms
-
-
 def gemm_tp(A, B, arena, *, compute_dtype=None, b_constant=False):
     """The row-parallel GEMM of a tensor-parallel rank, ``A @ B.T`` in bf16 with no epilogue, whose rows go straight to
     the ranks that sum them: row ``m`` lands in the staging area of rank ``m // (M / world)`` (``runtime.tp.TpArena``;

@@ -87,10 +87,6 @@ class Waypoint15Config:
     fuse_qkv_post: bool = True
     # ... and that launch folded into the QKV projection's epilogue (same bytes again); needs fuse_qkv_post.
     fuse_qkv_gemm: bool = True
-    # The AdaRMSNorm after out-proj / fc2 as the tail of that GEMM (needs fuse_gate_residual): None = where it pays (at
-    # least 256 tokens; smaller frames prefer a GEMM in K slices, which the tail excludes), True = wherever the kernel
-    # takes the shape, False = never.  Equal to the separate launch up to the order of the f32 sum of squares.
-    fuse_norm: bool | None = None
     # Scaled e4m3 (an extension; the reference's e4m3 is scale free): linear weights narrowed with one scale per
     # output channel (amax / 448), the caches with one scale per KV head (`k_scale` / `v_scale` of each block's
     # parameters).  Only meaningful where quant says fp8; the mixture-of-experts weights stay unscaled.
@@ -414,21 +410,7 @@ class TransformerBlock(nn.Module):
             self.kv_cache(qkv, frame_t, frozen=frozen)
         attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8)
         h = None
-        M, D = x.numel // int(x.shape[-1]), int(x.shape[-1])
-        has_ctrl = ctrl_emb is not None and hasattr(self, "ctrl_fusion")
-        moe = self._cfg.moe
-
-        def norm_tail(gate, n_scale):
-            """Whether the AdaRMSNorm after a gate + residual GEMM runs as that kernel's tail (``qf.gemm_norm``)."""
-            want = self._cfg.fuse_norm
-            if not fuse or want is False or n_scale is None:
-                return False
-            fits = qf.gemm_norm_fits(M, D, gate_groups=int(gate.shape[0]), norm_groups=n_scale.numel // D)
-            return fits and (want is True or M >= 256)  # below that the GEMM prefers K slices, which the tail excludes
-
-        if fuse and norm_tail(g0, s1) and not has_ctrl:
-            x, h = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]), norm=(s1, b1, None, fp8 and not moe))
-        elif fuse:
+        if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))
         elif tp_fused:
             sched = self._comm.tp_schedule
@@ -443,14 +425,13 @@ class TransformerBlock(nn.Module):
             if tp:
                 self._comm.all_reduce_sum(y)
             x = self.attn_gate(x, y, g0)
-        if has_ctrl:
+        if ctrl_emb is not None and hasattr(self, "ctrl_fusion"):
             x = self.ctrl_residual(x, self.ctrl_fusion(self.ctrl_x_norm(x), self.ctrl_emb_norm(ctrl_emb)))
+        moe = self._cfg.moe
         if h is None:
             h = self.pre_mlp_norm(x, s1, b1, emit_e4m3=fp8 and not moe)  # the router reads bf16; MoE narrows for its experts itself
         if moe:
             x = self.mlp_gate(x, self.mlp(h), g1)
-        elif fuse and next_norm is not None and norm_tail(g1, next_norm[0]):
-            x, self.h_next = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out, norm=next_norm)
         elif fuse:
             x = self.mlp(h, gate=g1, residual=x, gate_groups=int(g1.shape[0]), out=x_out)
         elif tp_fused:

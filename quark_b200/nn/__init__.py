@@ -139,27 +139,10 @@ class Linear(Module):
                 self.weight.data = qf.quantize_e4m3(self.weight.data)
             self._fp8 = True
 
-    def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None, tp_arena=None,
-                norm=None):  # fmt: skip
+    def forward(self, x, *, activation=None, bias=None, gate=None, residual=None, gate_groups: int = 1, out_dtype=None, out=None, tp_arena=None):
         """``tp_arena``: a row-parallel linear of a tensor-parallel rank; the partial output is stored straight into the
-        staging areas of the ranks that sum it (``qf.gemm_tp``) and nothing is returned.
-
-        ``norm = (scale, bias, activation, emit_e4m3)``: the AdaRMSNorm that follows this linear runs as the tail of the
-        same kernel (``qf.gemm_norm``); returns ``(y, h)`` with ``h`` the normalised rows (e4m3 if asked for, else bf16)."""
+        staging areas of the ranks that sum it (``qf.gemm_tp``) and nothing is returned."""
         a_dt = x.dtype
-        if norm is not None:
-            if activation is not None or bias is not None or self._has_bias or tp_arena is not None:
-                raise ValueError("Linear: the norm tail goes with the plain or the gate + residual epilogue only")
-            n_scale, n_bias, n_act, emit = norm
-            M, N = x.numel // int(x.shape[-1]), int(self.weight.data.shape[0])
-            b_dt = self.weight.data.dtype
-            y = out if out is not None else _cached(self, "out", (M, N), "bf16")
-            h = None if emit else _cached(self, "norm_out", (M, N), "bf16")
-            hq = _cached(self, "norm_out_q", (M, N), "e4m3") if emit else None
-            qf.gemm_norm(x, self.weight.data, n_scale, n_bias, gate=gate, residual=residual, gate_groups=gate_groups, out=y, norm_out=h,
-                         norm_out_q=hq, emit_bf16=not emit, emit_e4m3=emit, activation=n_act, compute_dtype=b_dt if b_dt == "e4m3" else None,
-                         w_scale=self.w_scale, b_constant=True)  # fmt: skip
-            return y, (hq if emit else h)
         if tp_arena is not None:
             if activation is not None or bias is not None or gate is not None or self._has_bias or self.w_scale is not None:
                 raise ValueError("Linear: a partial output sent to its reducers takes no epilogue")
@@ -278,8 +261,7 @@ class MLP(Module):
         self.silu = SiLU()
         self._fuse_silu = fuse_silu
 
-    def forward(self, x, *, gate=None, residual=None, gate_groups: int = 1, out=None, tp_arena=None, norm=None):
-        """``norm``: see ``Linear.forward``; the call then returns ``(y, h)``."""
+    def forward(self, x, *, gate=None, residual=None, gate_groups: int = 1, out=None, tp_arena=None):
         fp8 = self.fc2.weight.data.dtype == "e4m3"
         if self._fuse_silu:
             h = self.fc1(x, activation="silu", out_dtype="e4m3" if fp8 else None)
@@ -287,7 +269,7 @@ class MLP(Module):
             h = self.silu(self.fc1(x), emit_e4m3=fp8)
         if tp_arena is not None:
             return self.fc2(h, tp_arena=tp_arena)
-        return self.fc2(h, gate=gate, residual=residual, gate_groups=gate_groups, out=out, norm=norm)
+        return self.fc2(h, gate=gate, residual=residual, gate_groups=gate_groups, out=out)
 
 
 class AdaRMSNorm(Module):

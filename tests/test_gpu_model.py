@@ -275,6 +275,14 @@ def test_moe_block_and_session_match_oracle(qb, quant):
         want = oracle_ops.moe(x, ob["moe.router.weight"], ob["moe.expert_in"], ob["moe.expert_out"], top_k=2, fp8=fp8,
                               a_quant="e4m3" if fp8 else None)  # fmt: skip
     compare(got.reshape(-1), want.reshape(-1), f"MoE module {quant}", fp8)
+    # the slot-sorted schedule (grouped GEMMs over M * top_k rows) and the dense one (every expert over every token)
+    # run the same arithmetic per row and sum in the same order: the same bits
+    from quark_b200 import nn as qnn
+
+    dense = qnn.MoE(cfg.tpf, cfg.d_model, cfg.mlp_dim // cfg.moe_top_k, 8, 2, schedule="dense")
+    dense.router.weight.data, dense.expert_in.data, dense.expert_out.data = blk.mlp.router.weight.data, blk.mlp.expert_in.data, blk.mlp.expert_out.data
+    dense._fp8 = blk.mlp._fp8
+    np.testing.assert_array_equal(dense(qb.QuarkTensor.from_numpy(x, dtype="bf16")).to_numpy(), got)
 
     lats = [codec.f32_to_bf16(r.standard_normal((1, cfg.latent_numel)).astype(np.float32)) for _ in range(2)]
     noise = r.standard_normal((1, cfg.latent_numel)).astype(np.float32)
