@@ -231,6 +231,18 @@ int32_t qb_gemm_qkv_post(const void* A, const void* B, void* qkv_out, const void
  * to f32); cos/sin are the CUDA single-precision functions. */
 int32_t qb_rope_table_build(float* rope_xy, int32_t H_spatial, int32_t W_spatial, void* stream);
 
+/* Keeps a second pair of caches (K_shadow, Vt_shadow: the shapes of K_cache, Vt_cache, in the OTHER of the two dtypes)
+ * equal to cast(cache) by converting the rows the append just before wrote: the tail slot always, the ring slot when
+ * frame_t is a write frame and *frozen == 0 (the same arithmetic as the append).  p describes the cache as for the
+ * append (p->kv_dtype = the dtype of K_cache / Vt_cache).  e4m3 -> bf16 is exact, bf16 -> e4m3 rounds to nearest even
+ * and saturates (qb_quantize_e4m3).  This is the reference's cast on load for a cache dtype that differs from the
+ * attention's compute dtype (ref: src/quark/kernels/owl_attn/kernel.py:342-348), done once per appended row instead of
+ * once per attended row per call; qb_owl_attn then runs on the shadow pair with kv_dtype = compute_dtype.  Call it after
+ * every append; a cache written by other means (restored, reset) is brought over whole with qb_quantize_e4m3 /
+ * qb_dequantize_e4m3. */
+int32_t qb_kv_cast_appended(const void* K_cache, const void* Vt_cache, void* K_shadow, void* Vt_shadow, const int32_t* frame_t,
+                            const int32_t* frozen, const qb_kv_params* p, void* stream);
+
 /* ------------------------------------------------------------------ owl_attn
  * Segment-sparse GQA flash attention with inline ortho-RoPE on Q, head_dim 64.
  * Replaces qf.owl_attn (ref: src/quark/functional/owl_attn.py:322-394,

@@ -145,6 +145,7 @@ SIGNATURES = {
     "qb_patch_scatter": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qb_gemm_tp": (_I, [_P, _P, C.POINTER(GemmParams), C.POINTER(TpParams), _P, _Z, _P]),
     "qb_set_attn_exact_exp": (_I, [_I]),
+    "qb_kv_cast_appended": (_I, [_P, _P, _P, _P, _P, _P, C.POINTER(KvParams), _P]),
     "qb_moe_slots": (_Z, [_I, _I, _I]),
     "qb_moe_route_slots": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qb_moe_gather": (_I, [_P, _P, _P, _I, _I, _P]),

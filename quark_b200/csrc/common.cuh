@@ -104,6 +104,14 @@ __device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
 // Joining the halves with a register-pair move inside one asm block (mov.b32 {lo, hi}) instead of the shift and OR
 // below was measured on the attention kernel: 52.2 -> 58.4 us (the instruction schedule the compiler finds for the
 // softmax loop changes for the worse), so the plain form stays.
+// Every e4m3 value is a bf16 value (3 mantissa bits, exponents -9 .. 8), so the widening is exact; NaN stays NaN.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint16_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
+  const __half2 h = *reinterpret_cast<const __half2*>(&h2);
+  const __nv_bfloat162 b = __floats2bfloat162_rn(__low2float(h), __high2float(h));
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   return static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
 }

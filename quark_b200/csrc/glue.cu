@@ -325,14 +325,7 @@ __global__ void increment_kernel(int32_t* c) {
 }
 
 // ---------------------------------------------------------------- e4m3 -> bf16
-// Every e4m3 value is a bf16 value (3 mantissa bits, exponents -9 .. 8), so the widening is exact; NaN stays NaN.
-__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint16_t v) {
-  uint32_t h2;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
-  const __half2 h = *reinterpret_cast<const __half2*>(&h2);
-  const __nv_bfloat162 b = __floats2bfloat162_rn(__low2float(h), __high2float(h));
-  return *reinterpret_cast<const uint32_t*>(&b);
-}
+// (e4m3x2_to_bf16x2 in common.cuh: the widening is exact)
 
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* X, uint16_t* out, size_t n) {
   grid_dep_wait();

@@ -205,6 +205,74 @@ __global__ void rope_table_kernel(float* out, int H, int W) {
   out[t * 16 + 8 + i] = s;
 }
 
+// ---------------------------------------------------------------- shadow cache in the attention's compute dtype
+// When the attention computes in another dtype than the cache stores (kv_cache = fp8 with attn_compute = bf16, or the
+// reverse), the reference casts K and V as it loads them (src/quark/kernels/owl_attn/kernel.py:342-348).  Tensor-core
+// operands go from shared memory to the MMA without passing through registers here, so the cast happens once per
+// appended row instead: a second pair of caches in the compute dtype is kept beside the first, and after every append
+// this kernel converts the rows that append wrote (the tail slot always, the ring slot on write frames), reading the
+// stored values, so the shadow holds exactly cast(cache) - what a cast on load would produce.  Traffic: the appended
+// rows only, not the whole cache.
+struct KvCastArgs {
+  const void* K_cache;
+  const void* Vt_cache;
+  void* K_shadow;
+  void* Vt_shadow;
+  const int32_t* frame_t;
+  const int32_t* frozen;
+  int tpf, nb, pd;
+};
+
+template <bool kSrcFp8>
+__device__ __forceinline__ void cast16(const void* src, void* dst, size_t idx) {
+  if (kSrcFp8) {  // 16 e4m3 -> 16 bf16, exact
+    const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(src) + idx);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = e4m3x2_to_bf16x2(static_cast<uint16_t>(w[j] & 0xFFFF));
+      o[2 * j + 1] = e4m3x2_to_bf16x2(static_cast<uint16_t>(w[j] >> 16));
+    }
+    uint16_t* d = static_cast<uint16_t*>(dst) + idx;
+    *reinterpret_cast<uint4*>(d) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(d + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {  // 16 bf16 -> 16 e4m3, nearest even, saturating (qb_quantize_e4m3)
+    const uint16_t* sp = static_cast<const uint16_t*>(src) + idx;
+    const uint4 a = *reinterpret_cast<const uint4*>(sp), b = *reinterpret_cast<const uint4*>(sp + 8);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_e4m3x4(bf16lo(w[2 * j]), bf16hi(w[2 * j]), bf16lo(w[2 * j + 1]), bf16hi(w[2 * j + 1]));
+    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst) + idx) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <bool kSrcFp8>
+__global__ void __launch_bounds__(kKvThreads) kv_cast_appended_kernel(const KvCastArgs a) {
+  grid_dep_wait();    // the rows were written by the append just before
+  grid_dep_launch();
+  const int head = blockIdx.y;
+  const int t0 = blockIdx.x * kKvTile;
+  const int ft = *after_wait(a.frame_t);
+  const int frozen = *after_wait(a.frozen);
+  const int L = a.nb * a.tpf;
+  const int cap = L + a.tpf;
+  const bool ring = (ft % a.pd) == 0 && frozen == 0;
+  if (blockIdx.z == 1 && !ring) return;
+  const int base = blockIdx.z == 0 ? L : (((ft + a.pd - 1) / a.pd) % a.nb) * a.tpf;
+  const int ntok = min(kKvTile, a.tpf - t0);  // a multiple of 16
+  // K: ntok rows of 64 values, contiguous
+  const size_t krow0 = (static_cast<size_t>(head) * cap + base + t0) * 64;
+  for (int i = threadIdx.x; i < ntok * 4; i += kKvThreads) cast16<kSrcFp8>(a.K_cache, a.K_shadow, krow0 + static_cast<size_t>(i) * 16);
+  // V^T: 64 channel rows, ntok consecutive tokens of each
+  const int per_row = ntok / 16;
+  for (int i = threadIdx.x; i < 64 * per_row; i += kKvThreads) {
+    const int d = i / per_row, j = i % per_row;
+    cast16<kSrcFp8>(a.Vt_cache, a.Vt_shadow, (static_cast<size_t>(head) * 64 + d) * cap + base + t0 + 16 * j);
+  }
+}
+
 }  // namespace qb
 
 using namespace qb;
@@ -274,4 +342,25 @@ extern "C" int32_t qb_kv_cache_update_kv(const void* K, const void* V, const int
   QB_REQUIRE(p->packed_qkv == 0, QB_ERR_INVALID_ARG, "kv_cache_update: the packed projection goes through qb_kv_cache_update");
   const size_t tpf = static_cast<size_t>(p->H_spatial) * p->W_spatial;  // K and V hold every token, quilt or not
   return kv_append(K, V, 64, tpf * 64, frame_t, frozen, K_cache, Vt_cache, segments, n_segments, rope_xy, p, stream);
+}
+
+extern "C" int32_t qb_kv_cast_appended(const void* K_cache, const void* Vt_cache, void* K_shadow, void* Vt_shadow, const int32_t* frame_t,
+                                       const int32_t* frozen, const qb_kv_params* p, void* stream) {
+  QB_REQUIRE(p != nullptr && K_cache && Vt_cache && K_shadow && Vt_shadow && frame_t && frozen, QB_ERR_INVALID_ARG, "kv_cast_appended: NULL pointer");
+  QB_REQUIRE(p->n_kv_heads > 0 && p->H_spatial > 0 && p->W_spatial > 0 && p->num_buckets > 0 && p->pinned_dilation > 0 && p->quilt_factor >= 1,
+             QB_ERR_INVALID_ARG, "kv_cast_appended: sizes must be positive");
+  QB_REQUIRE(p->kv_dtype == QB_BF16 || p->kv_dtype == QB_E4M3, QB_ERR_INVALID_ARG, "kv_cast_appended: kv_dtype %d", p->kv_dtype);
+  QB_REQUIRE((p->H_spatial * p->W_spatial) % p->quilt_factor == 0, QB_ERR_INVALID_ARG, "kv_cast_appended: H*W is not a multiple of quilt_factor");
+  const int tpf = p->H_spatial * p->W_spatial / p->quilt_factor;
+  QB_REQUIRE(tpf % 16 == 0, QB_ERR_UNSUPPORTED, "kv_cast_appended: H*W / quilt_factor = %d must be a multiple of 16", tpf);
+  QB_REQUIRE(aligned16(K_cache) && aligned16(Vt_cache) && aligned16(K_shadow) && aligned16(Vt_shadow), QB_ERR_ALIGN,
+             "kv_cast_appended: pointers must be 16-byte aligned");
+  KvCastArgs a{};
+  a.K_cache = K_cache; a.Vt_cache = Vt_cache; a.K_shadow = K_shadow; a.Vt_shadow = Vt_shadow;
+  a.frame_t = frame_t; a.frozen = frozen;
+  a.tpf = tpf; a.nb = p->num_buckets; a.pd = p->pinned_dilation;
+  const dim3 grid((tpf + kKvTile - 1) / kKvTile, p->n_kv_heads, 2);
+  if (p->kv_dtype == QB_E4M3)
+    return launch_dep("kv_cast_appended", kv_cast_appended_kernel<true>, grid, dim3(kKvThreads), 0, static_cast<cudaStream_t>(stream), a);
+  return launch_dep("kv_cast_appended", kv_cast_appended_kernel<false>, grid, dim3(kKvThreads), 0, static_cast<cudaStream_t>(stream), a);
 }

@@ -191,6 +191,7 @@ class Engine:
         for blk, saved in zip(self.model.blocks, snap["layers"]):
             for k, host in saved.items():
                 getattr(blk.kv_cache, k).copy_from_numpy(host)
+            blk.kv_cache.refresh_shadow()  # a captured frame only converts the rows its own appends write
         self.gen.set_frame_t(snap["frame_t"])
         self._frame = snap["frame"]
         self._rng.bit_generator.state = snap["rng"]
@@ -256,4 +257,6 @@ class Engine:
         for items in saved:
             for t, host in items:
                 t.copy_from_numpy(host)
+        for blk in self.model.blocks:
+            blk.kv_cache.refresh_shadow()
         _stream.synchronize()

@@ -706,6 +706,24 @@ def moe_combine(partials, weights, *, out=None):
     return out
 
 
+def kv_cast_appended(K_cache, Vt_cache, K_shadow, Vt_shadow, frame_t, frozen, *, n_kv_heads, H_spatial, W_spatial, num_buckets, pinned_dilation,
+                     quilt_factor=1, **_ignored):
+    """Brings the rows the last append wrote (tail slot; ring slot on a write frame) over into a second pair of caches in
+    the other dtype, so that ``K_shadow == cast(K_cache)`` stays true: the reference's cast on load for a cache whose dtype
+    differs from the attention's compute dtype (``src/quark/kernels/owl_attn/kernel.py:342-348``), done per appended row."""
+    kvd = _dt(K_cache)
+    other = "bf16" if kvd == "e4m3" else "e4m3"
+    if kvd not in ("bf16", "e4m3") or _dt(Vt_cache) != kvd or _dt(K_shadow) != other or _dt(Vt_shadow) != other:
+        raise TypeError("qf.kv_cast_appended: the shadow pair must have the other of the two cache dtypes")
+    if K_shadow.numel != K_cache.numel or Vt_shadow.numel != Vt_cache.numel:
+        raise ValueError("qf.kv_cast_appended: the shadow pair must have the caches' shapes")
+    p = _lib.KvParams(
+        n_q_heads=0, n_kv_heads=n_kv_heads, H_spatial=H_spatial, W_spatial=W_spatial, num_buckets=num_buckets, pinned_dilation=pinned_dilation,
+        kv_dtype=_lib.DTYPE_CODE[kvd], max_segments=3, quilt_factor=quilt_factor, packed_qkv=1, quilt_offset=0, k_scale=None, v_scale=None,
+    )  # fmt: skip
+    _lib.check(_lib.load().qb_kv_cast_appended(_p(K_cache), _p(Vt_cache), _p(K_shadow), _p(Vt_shadow), _p(frame_t), _p(frozen), C.byref(p), _s()))
+
+
 def moe_slots(M: int, E: int, top_k: int) -> int:
     """Rows of the slot tables of ``moe_route_slots``: every expert's run padded to whole 128-row tiles."""
     return int(_lib.load().qb_moe_slots(int(M), int(E), int(top_k)))

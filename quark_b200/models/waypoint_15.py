@@ -408,7 +408,7 @@ class TransformerBlock(nn.Module):
             if use_first:
                 qkv = self.v_residual(qkv, qkv_first)
             self.kv_cache(qkv, frame_t, frozen=frozen)
-        attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8)
+        attn_out = self.attn(qkv, self.kv_cache, frame_t, emit_e4m3=fp8, frozen=frozen)
         h = None
         if fuse:
             x = self.out_proj(attn_out, gate=g0, residual=x, gate_groups=int(g0.shape[0]))

@@ -409,6 +409,34 @@ class KVCacheUpdate(Module):
         qf.kv_cache_update(qkv, qkv, ft, self._frozen[1 if frozen else 0], self.Vt_cache, self.segments, self.n_segments, self.K_cache,
                            k_scale=self.k_scale, v_scale=self.v_scale, **self._kw)  # fmt: skip
 
+    # ---- a second pair of caches in the attention's compute dtype, when that differs from the cache dtype
+    def shadow(self, dtype: str, frame_t=None, frozen: bool = False):
+        """``(K, Vt)`` equal to ``cast(K_cache), cast(Vt_cache)`` in ``dtype``, to be called after the append of the step:
+        the rows that append wrote are converted (``qf.kv_cast_appended``); if the caches were written from the host since
+        the last call (loaded, restored, reset) or this is the first call, everything is.  The reference casts as the
+        attention loads (``src/quark/kernels/owl_attn/kernel.py:342-348``): same values."""
+        if dtype == self.K_cache.dtype:
+            return self.K_cache, self.Vt_cache
+        if getattr(self, "_shadow", None) is None or self._shadow[0].dtype != dtype:
+            self._shadow = (QuarkTensor.empty(*self.K_cache.shape, dtype=dtype), QuarkTensor.empty(*self.Vt_cache.shape, dtype=dtype))
+            self._shadow_seen = None
+        seen = (self.K_cache._storage.host_writes, self.Vt_cache._storage.host_writes)
+        if self._shadow_seen != seen:
+            self.refresh_shadow()
+        else:
+            qf.kv_cast_appended(self.K_cache, self.Vt_cache, self._shadow[0], self._shadow[1], frame_t if frame_t is not None else self.frame_t,
+                                self._frozen[1 if frozen else 0], **self._kw)  # fmt: skip
+        return self._shadow
+
+    def refresh_shadow(self) -> None:
+        """Converts both caches whole (after the caches were written by anything but the append)."""
+        if getattr(self, "_shadow", None) is None:
+            return
+        conv = qf.quantize_e4m3 if self._shadow[0].dtype == "e4m3" else qf.dequantize_e4m3
+        conv(self.K_cache, out=self._shadow[0])
+        conv(self.Vt_cache, out=self._shadow[1])
+        self._shadow_seen = (self.K_cache._storage.host_writes, self.Vt_cache._storage.host_writes)
+
     def set_scales(self, k_scale, v_scale) -> None:
         """Per-KV-head scales as host arrays (or None): the caches then hold ``K / k_scale[h]`` and ``V / v_scale[h]``."""
         up = lambda a: None if a is None else QuarkTensor.from_numpy(np.ascontiguousarray(a, dtype=np.float32))  # noqa: E731
@@ -423,6 +451,7 @@ class KVCacheUpdate(Module):
         self.segments.copy_from_numpy(np.array([0, 0, self._L, self._tpf, 0, 0], dtype=np.int32))
         self.n_segments.copy_from_numpy(np.array([2], dtype=np.int32))
         self.set_frame_t(0)
+        self.refresh_shadow()
 
 
 class OwlAttn(Module):
@@ -436,12 +465,15 @@ class OwlAttn(Module):
                         quilt_factor=quilt_factor, quilt_offset=quilt_offset)  # fmt: skip
         self._compute_dtype = compute_dtype
 
-    def forward(self, qkv, kv_cache: KVCacheUpdate, frame_t=None, *, emit_e4m3: bool = False):
+    def forward(self, qkv, kv_cache: KVCacheUpdate, frame_t=None, *, emit_e4m3: bool = False, frozen: bool = False):
+        """``frozen``: what the append of this step was called with (it decides which rows a shadow cache has to take over)."""
         n_kv, gqa = self._kw["n_kv_heads"], self._kw["gqa_ratio"]
         n_q = n_kv * gqa
         Dh = int(qkv.shape[1]) // (n_q + 2 * n_kv)
         out = _cached(self, "out", (int(qkv.shape[0]), n_q * Dh), qkv.dtype)
         out_q = _cached(self, "out_q", out.shape, "e4m3") if emit_e4m3 else None
-        qf.owl_attn(qkv, kv_cache.K_cache, kv_cache.Vt_cache, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
+        cd = self._compute_dtype or "bf16"  # as qf.owl_attn reads it
+        K, Vt = kv_cache.shadow(cd, frame_t, frozen)  # the caches themselves unless the attention computes in another dtype
+        qf.owl_attn(qkv, K, Vt, kv_cache.segments, kv_cache.n_segments, frame_t=frame_t,
                     out=out, out_q=out_q, compute_dtype=self._compute_dtype, k_scale=kv_cache.k_scale, v_scale=kv_cache.v_scale, **self._kw)  # fmt: skip
         return out_q if emit_e4m3 else out

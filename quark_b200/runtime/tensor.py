@@ -31,6 +31,7 @@ class _Storage:
         _lib.check(_lib.load().qb_malloc(C.byref(p), max(int(nbytes), 16)))
         self.ptr = int(p.value)
         self.nbytes = int(nbytes)
+        self.host_writes = 0  # copies and fills issued from the host (a cache's shadow copy notices them)
 
     def __del__(self):
         try:
@@ -48,6 +49,7 @@ class _Borrowed:
         self.ptr = int(ptr)
         self.nbytes = int(nbytes)
         self.keepalive = keepalive
+        self.host_writes = 0
 
 
 def _numel(shape) -> int:
@@ -149,6 +151,7 @@ class QuarkTensor:
 
     # ---- data movement (synchronous with respect to the host)
     def zero_(self) -> "QuarkTensor":
+        self._storage.host_writes += 1
         _lib.check(_lib.load().qb_memset_async(C.c_void_p(self.data_ptr()), 0, self.nbytes, C.c_void_p(_stream.active_stream())))
         return self
 
@@ -156,6 +159,7 @@ class QuarkTensor:
         arr = np.ascontiguousarray(arr)
         if arr.nbytes != self.nbytes:
             raise ValueError(f"copy_from_numpy: {arr.nbytes} bytes into a tensor of {self.nbytes}")
+        self._storage.host_writes += 1
         lib = _lib.load()
         s = C.c_void_p(_stream.active_stream())
         _lib.check(lib.qb_memcpy_async(C.c_void_p(self.data_ptr()), C.c_void_p(arr.ctypes.data), self.nbytes, 0, s))
@@ -166,6 +170,7 @@ class QuarkTensor:
         """Device-to-device copy on the active stream (asynchronous)."""
         if other.nbytes != self.nbytes:
             raise ValueError("copy_from: size mismatch")
+        self._storage.host_writes += 1
         _lib.check(
             _lib.load().qb_memcpy_async(C.c_void_p(self.data_ptr()), C.c_void_p(other.data_ptr()), self.nbytes, 2, C.c_void_p(_stream.active_stream()))
         )

@@ -213,6 +213,22 @@ def test_mixed_quant_session_matches_oracle(qb, linear, kv, attn):
     for k, nz in enumerate(noises):
         got = eng.gen_frame(noise=nz)
         compare(got.reshape(-1), want[k].reshape(-1), f"mixed linear={linear} kv={kv} attn={attn} frame {k}", True)
+    if kv != attn:
+        # the attention ran on a second pair of caches in its own dtype, kept up to date row by row as frames were appended
+        # (and brought over whole after the graph capture restored the caches): it must equal a cast of the whole cache
+        for blk in eng.model.blocks:
+            kc = blk.kv_cache
+            Ks, Vs = kc._shadow
+            assert Ks.dtype == ("e4m3" if attn == "fp8" else "bf16")
+            for cache, sh in ((kc.K_cache, Ks), (kc.Vt_cache, Vs)):
+                if attn == "fp8":
+                    np.testing.assert_array_equal(sh.to_numpy(), codec.f32_to_e4m3(f32(cache.to_numpy(), "bf16")))
+                else:
+                    np.testing.assert_array_equal(f32(sh.to_numpy(), "bf16"), f32(cache.to_numpy(), "e4m3"))
+        snap = eng.snapshot()
+        a = eng.gen_frame(noise=noises[0])
+        eng.restore(snap)
+        np.testing.assert_array_equal(eng.gen_frame(noise=noises[0]), a)  # a restored session also restores the shadow
 
 
 @pytest.mark.parametrize("quant", ["bf16", "fp8"])
