@@ -133,6 +133,9 @@ __device__ __forceinline__ float p_exp(int q, float x) {
 // in the exact kernel; 46.5 with the turn passing before chunk 0 (the groups then overlap almost fully, which the exact
 // kernel cannot afford: 62.6); 47.9 without turns; 3 / 5 of every 8 elements instead of 4: 51.6 / 47.2; all: 56.0.
 constexpr float kLinMagic = 49152.0f;  // 1.5 * 2^15: floats in [2^15, 2^16) have an ulp of 2^-8
+// (The clamp is a maximum on the ALU pipe, the busiest one of the kernel at 58 %; moving it to the FMA pipe as a
+// saturating multiply-add followed by a second multiply-add costs one instruction more and measured 49.5 against 46.5 us:
+// what counts is the number of instructions issued.)
 __device__ __forceinline__ float ex2_lin_from_biased(float v) {
   v = fmaxf(v, kLinMagic - 120.0f);
   constexpr uint32_t kC = 0x3F800000u - 0x47400000u * 32768u - 436208u;  // 0x47400000 = bits of 49152.0f; 436208 = 0.052 * 2^23

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* X
                                                                 uint8_t* out_q, int D, int rows_per_group, float eps,
                                                                 int activation) {
   grid_dep_wait();    // inputs come from the kernels before this one
-  grid_dep_launch();  // the next kernel may begin its set-up
+  grid_dep_launch();  // the next kernel may begin its set-up (triggering before the wait measured the same: 80.5 / 80.6 FPS)
   const int row = blockIdx.x;
   const uint16_t* x = X + static_cast<size_t>(row) * D;
   const size_t goff = static_cast<size_t>(row / rows_per_group) * D;
