@@ -330,6 +330,20 @@ def time_kernels(qb, eng, peaks):
         "owl_attn": (lambda b: b.attn(qkv, b.kv_cache, ft), None),
         "kv_cache_update": (lambda b: b.kv_cache(qkv, ft, frozen=True), None),
     }
+    # the QKV projection as the frame launches it: head norm, value residual, RoPE(K) and the cache append in its epilogue
+    # (frozen: the ring slot is left alone, as in the four denoising passes)
+    def qkv_fused(b):
+        kc = b.kv_cache
+        mix = hasattr(b, "v_residual")
+        return qb.qf.gemm_qkv_post(
+            xq, b.qkv_proj.weight.data, qkv if mix else None, b.v_residual.lamb.data if mix else None, ft, kc._frozen[1], kc.Vt_cache,
+            kc.segments, kc.n_segments, kc.K_cache, n_q_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, H_spatial=cfg.height, W_spatial=cfg.width,
+            num_buckets=kc._kw["num_buckets"], pinned_dilation=kc._kw["pinned_dilation"], out=qkv_out, w_scale=b.qkv_proj.w_scale,
+            k_scale=kc.k_scale, v_scale=kc.v_scale)  # fmt: skip
+
+    qkv_out = qb.QuarkTensor.zeros(tpf, cfg.qkv_dim, dtype="bf16")
+    if cfg.fuse_qkv_gemm and cfg.quilt_factor == 1:
+        shapes["gemm_qkv_fused_epilogue"] = (qkv_fused, gemm_flops(tpf, cfg.qkv_dim, cfg.d_model))
     # the norm that follows out-proj and fc2, alone
     s1, b1 = eng.model.blocks[0]._cond_lut[0][3], eng.model.blocks[0]._cond_lut[0][4]
     shapes["ada_rmsnorm"] = (lambda b: b.pre_mlp_norm(xr, s1, b1, emit_e4m3=True), None)
