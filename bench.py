@@ -577,7 +577,10 @@ def run_ours(args):
         import gc
 
         gc.collect()
-        tp = tp_record(args, qb, rank, world, local, dist, ref_latent, noise0)
+        try:
+            tp = tp_record(args, qb, rank, world, local, dist, ref_latent, noise0)
+        except Exception as e:  # the sessions measurement above stands whatever happens to the sharded one
+            tp = {"error": f"{type(e).__name__}: {e}"[:300]}
     base, base_err = cublaslt_baseline_subprocess() if (rank == 0 and not args.no_cublaslt) else (None, "skipped")
 
     if rank == 0:
