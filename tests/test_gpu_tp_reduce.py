@@ -226,3 +226,49 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_bit(qb):
     # bad arguments are refused on the host
     p.rows = 63
     assert lib.qb_tp_reduce(C.c_void_p(x.data_ptr()), C.c_void_p(gate.data_ptr()), None, None, C.byref(p), None) == -1
+
+
+class _AloneComm:
+    """Stands in for the communicator of one rank of a sharded session whose peers are not there: the partial sums stay
+    partial, so the numbers mean nothing, but every kernel runs with the shapes that rank would see."""
+
+    fused = False
+    reduction_name = "none (a rank alone)"
+
+    def __init__(self, rank, world):
+        self.rank, self.world = rank, world
+
+    def all_reduce_sum(self, t):
+        return t
+
+    def abort(self):
+        pass
+
+    def destroy(self):
+        return True
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_a_rank_of_the_bench_geometry_runs_at_wide_sharding(qb, world, quant):
+    """The shapes one rank of the 720p model sees when 16 KV heads are spread over 4 or 8 GPUs (2 KV heads, 4 Q heads,
+    512-column QKV, 256-wide out-proj K, 1024-wide MLP slices at 8): every kernel accepts them, the key-split attention
+    included, the frame is finite and no bounded wait runs out.  Parity of the sharded arithmetic is checked where all
+    ranks exist (``test_gpu_tp.py``, ``test_tp_host.py``)."""
+    from quark_b200.models import QuantConfig, Waypoint15Config, make_params
+
+    q = QuantConfig.all_fp8() if quant == "fp8" else QuantConfig.all_bf16()
+    base = Waypoint15Config(height=32, width=16, n_layers=2, quant=q)
+    params = make_params(base, seed=3)
+    for rank in (0, world - 1):
+        cfg = Waypoint15Config(**{**base.__dict__, "tp_world": world, "tp_rank": rank})
+        eng = qb.Engine(cfg=cfg, quant=q, params=params, comm=_AloneComm(rank, world), use_graph=True)
+        blk = eng.model.blocks[0]
+        assert int(blk.qkv_proj.weight.data.shape[0]) == (32 + 2 * 16) * 64 // world
+        r = util.rng(5)
+        eng.append_frame(r.standard_normal((1, base.latent_numel)).astype(np.float32))
+        out = eng.gen_frame(noise=r.standard_normal((1, base.latent_numel)).astype(np.float32))
+        qb.runtime.synchronize()
+        assert np.all(np.isfinite(util.f32(out, "bf16")))
+        assert qb._lib.device_status() == 0
+        eng.close()

@@ -22,7 +22,7 @@ ROOT = Path(__file__).resolve().parent.parent
 def _cfg(world=1, rank=0):
     from quark_b200.models import QuantConfig, Waypoint15Config
 
-    return Waypoint15Config(d_model=512, n_layers=1, n_heads=8, n_kv_heads=4, height=4, width=4, local_window=2, global_window=16,
+    return Waypoint15Config(d_model=1024, n_layers=1, n_heads=16, n_kv_heads=8, height=4, width=4, local_window=2, global_window=16,
                             quant=QuantConfig.all_bf16(), tp_world=world, tp_rank=rank)  # fmt: skip
 
 
@@ -47,7 +47,7 @@ def _inputs(cfg):
     return params["blocks"][0], x
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_shards_partition_every_weight(world):
     from quark_b200.models.waypoint_15 import shard_block_params
 
@@ -76,7 +76,7 @@ def _sum_bf16(parts):
     return codec.f32_to_bf16_rne(acc)
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_rank_local_blocks_sum_to_the_unsharded_block(world):
     """All ranks emulated in one process, in lock step: the reduce hook hands every rank the same sum."""
     from quark_b200.models.waypoint_15 import shard_block_params
