@@ -33,8 +33,10 @@ __device__ __forceinline__ void round_through_bf16(float (&f)[8]) {
 
 // ---------------------------------------------------------------- AdaRMSNorm
 // One CTA per row; each thread owns D / (8 * blockDim) groups of 8 consecutive elements.
-template <int kThreads>
-__global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* X, const uint16_t* scale,
+// kMaxVec: 16-byte vectors of the row per thread (D <= 8 * kThreads * kMaxVec); the narrow instantiation keeps four CTAs
+// on an SM, so that the 512 rows of a 720p frame are all resident at once instead of running as two waves.
+template <int kThreads, int kMaxVec>
+__global__ void __launch_bounds__(kThreads, kMaxVec == 1 ? 4 : 2) ada_rmsnorm_kernel(const uint16_t* X, const uint16_t* scale,
                                                                 const uint16_t* bias, uint16_t* out,
                                                                 uint8_t* out_q, int D, int rows_per_group, float eps,
                                                                 int activation) {
@@ -43,7 +45,6 @@ __global__ void __launch_bounds__(kThreads) ada_rmsnorm_kernel(const uint16_t* X
   const int row = blockIdx.x;
   const uint16_t* x = X + static_cast<size_t>(row) * D;
   const size_t goff = static_cast<size_t>(row / rows_per_group) * D;
-  constexpr int kMaxVec = 4;  // D <= 8 * kThreads * kMaxVec
   uint4 xv[kMaxVec], sv[kMaxVec], bv[kMaxVec];  // scale and bias are fetched with the row, not after the reduction
   float ss = 0.f;
 #pragma unroll
@@ -774,7 +775,8 @@ int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void*
   QB_REQUIRE(activation == 0 || activation == 1, QB_ERR_INVALID_ARG, "ada_rmsnorm: activation %d", activation);
   QB_REQUIRE(aligned16(X) && aligned16(scale) && aligned16(bias) && aligned16(out) && aligned16(out_q), QB_ERR_ALIGN,
              "ada_rmsnorm: pointers must be 16-byte aligned");
-  return launch_dep("ada_rmsnorm", ada_rmsnorm_kernel<256>, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
+  auto kernel = D <= 2048 ? ada_rmsnorm_kernel<256, 1> : D <= 4096 ? ada_rmsnorm_kernel<256, 2> : ada_rmsnorm_kernel<256, 4>;
+  return launch_dep("ada_rmsnorm", kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint16_t*>(X), static_cast<const uint16_t*>(scale), static_cast<const uint16_t*>(bias),
                     static_cast<uint16_t*>(out), static_cast<uint8_t*>(out_q), D, rows / groups, eps, activation);
 }

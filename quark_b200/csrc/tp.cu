@@ -77,6 +77,8 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
 }
 
 // Waits until flags[first + 32 * p] has reached epoch e for every rank p; false when the limit ran out.
+// (Polling with relaxed loads and one system-scope fence after the last flag was measured: the fence, which every CTA
+// then executes, costs far more than acquire loads do - 13.7 against 8.7 us for a launch without peers.)
 __device__ __forceinline__ bool tp_wait_all(const unsigned int* flags, int first, int world, unsigned int e, long long limit) {
   const long long t0 = clock64();
   for (int p = 0; p < world; ++p) {
@@ -96,10 +98,14 @@ __device__ __forceinline__ uint4 tp_pack8(const float (&f)[8]) {
   return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
 }
 
-__global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
+// kMaxVec: 16-byte vectors of a row per thread (D <= 8 * kTpThreads * kMaxVec); an instantiation per width keeps the
+// registers of the common D = 2048 low enough for every row's CTA to be resident at once.
+// kW: the most ranks the instantiation sums (2, 4 or 8): the partials of a vector are all requested before the first is
+// used, one register quadruple each.
+template <int kMaxVec, int kW>
+__global__ void __launch_bounds__(kTpThreads, kMaxVec == 1 ? 4 : 2) tp_reduce_kernel(const TpArgs a) {
   grid_dep_wait();    // this rank's partial comes from the GEMM before this kernel
   grid_dep_launch();
-  constexpr int kMaxVec = 4;  // D <= 8 * kTpThreads * kMaxVec
   __shared__ float red[kTpThreads / 32];
   __shared__ unsigned int s_epoch;
   __shared__ int s_ok;
@@ -110,6 +116,24 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
   const size_t plane = static_cast<size_t>(a.rows) * a.D * 2;  // one bf16 [rows, D] buffer
   const size_t off_y = kTpFlagBytes + plane * a.xslot, off_x = kTpFlagBytes + plane * (2 + a.xslot), off_h = kTpFlagBytes + plane * 4,
                off_hq = kTpFlagBytes + plane * 5;
+
+  // What does not depend on the peers is requested before the flags are looked at, so that it arrives while thread 0
+  // exchanges them: this rank's own partial (its GEMM has finished: the grid dependency above), the residual and the
+  // gate of the CTA's first row.
+  const int rpr_ = a.one_shot ? a.rows : a.rows / a.world;
+  const int row0 = a.one_shot ? static_cast<int>(blockIdx.x) : rank * rpr_ + static_cast<int>(blockIdx.x);
+  uint4 pre_y[kMaxVec], pre_r[kMaxVec], pre_g[kMaxVec];
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * kTpThreads + threadIdx.x) * 8;
+    pre_y[i] = pre_r[i] = pre_g[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (c < a.D && static_cast<int>(blockIdx.x) < rpr_) {
+      const size_t roff = static_cast<size_t>(row0) * a.D;
+      if (!a.pushed) pre_y[i] = ld_volatile_v4(mine + off_y + (roff + c) * 2);
+      pre_r[i] = *reinterpret_cast<const uint4*>(a.residual[rank] + roff + c);
+      pre_g[i] = *reinterpret_cast<const uint4*>(a.gate + static_cast<size_t>(row0 / a.gate_rows_per_group) * a.D + c);
+    }
+  }
 
   if (threadIdx.x == 0) {
     const unsigned int e = flags[kFlagEpoch] + 1u;  // written by this rank's previous launch, which has ended
@@ -142,15 +166,18 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
         const int c = (i * kTpThreads + threadIdx.x) * 8;
         if (c < a.D) {
           // every peer's vector is requested before the first is used: one NVLink round trip, not `world` of them
-          uint4 yv[kTpMaxWorld];
+          const bool first = lr == static_cast<int>(blockIdx.x);  // this row's own inputs are in registers already
+          uint4 yv[kW];
 #pragma unroll
-          for (int p = 0; p < kTpMaxWorld; ++p)
-            if (p < a.world)
-              yv[p] = a.pushed ? ld_volatile_v4(mine + kTpFlagBytes + ((static_cast<size_t>(p) * rpr + lr) * a.D + c) * 2)  // local staging
-                               : ld_volatile_v4(a.arena[p] + off_y + (roff + c) * 2);
+          for (int p = 0; p < kW; ++p)
+            if (p < a.world) {
+              if (a.pushed) yv[p] = ld_volatile_v4(mine + kTpFlagBytes + ((static_cast<size_t>(p) * rpr + lr) * a.D + c) * 2);  // local staging
+              else if (first && p == rank) yv[p] = pre_y[i];
+              else yv[p] = ld_volatile_v4(a.arena[p] + off_y + (roff + c) * 2);
+            }
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int p = 0; p < kTpMaxWorld; ++p) {  // rank order: every rank that summed these rows would get the same bits
+          for (int p = 0; p < kW; ++p) {  // rank order: every rank that summed these rows would get the same bits
             if (p < a.world) {
               float y[8];
               tp_unpack8(yv[p], y);
@@ -159,8 +186,8 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
             }
           }
           float r[8], g[8];
-          tp_unpack8(*reinterpret_cast<const uint4*>(a.residual[rank] + roff + c), r);
-          tp_unpack8(*reinterpret_cast<const uint4*>(a.gate + goff + c), g);
+          tp_unpack8(first ? pre_r[i] : *reinterpret_cast<const uint4*>(a.residual[rank] + roff + c), r);
+          tp_unpack8(first ? pre_g[i] : *reinterpret_cast<const uint4*>(a.gate + goff + c), g);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float s = __bfloat162float(__float2bfloat16_rn(acc[j]));  // the summed partial as a bf16 tensor
@@ -242,6 +269,19 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_kernel(const TpArgs a) {
 }  // namespace qb
 
 using namespace qb;
+
+typedef void (*TpKernel)(const TpArgs);
+template <int kW>
+static TpKernel tp_kernel_for_width(int D) {
+  if (D <= 8 * kTpThreads) return tp_reduce_kernel<1, kW>;
+  if (D <= 16 * kTpThreads) return tp_reduce_kernel<2, kW>;
+  return tp_reduce_kernel<4, kW>;
+}
+static TpKernel tp_kernel_for(int world, int D) {
+  if (world <= 2) return tp_kernel_for_width<2>(D);
+  if (world <= 4) return tp_kernel_for_width<4>(D);
+  return tp_kernel_for_width<8>(D);
+}
 
 extern "C" size_t qb_tp_arena_bytes(int32_t rows, int32_t D) {
   if (rows <= 0 || D <= 0) return 0;
@@ -328,7 +368,7 @@ extern "C" int32_t qb_tp_reduce(const void* residual, const void* gate, const vo
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   const int rpr = a.one_shot ? p->rows : p->rows / p->world;
   const int grid = rpr < 4 * sms ? rpr : 4 * sms;
-  return launch_dep("tp_reduce", tp_reduce_kernel, dim3(grid), dim3(kTpThreads), 0, static_cast<cudaStream_t>(stream), a);
+  return launch_dep("tp_reduce", tp_kernel_for(p->world, p->D), dim3(grid), dim3(kTpThreads), 0, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int32_t qb_tp_reduce_emulated(const void* const* residuals, const void* gate, const void* norm_scale, const void* norm_bias,
@@ -346,14 +386,15 @@ extern "C" int32_t qb_tp_reduce_emulated(const void* const* residuals, const voi
   int dev = 0, sms = 0, per_sm = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
   QB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  QB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_reduce_kernel, kTpThreads, 0));
+  TpKernel kernel = tp_kernel_for(p->world, p->D);
+  QB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kTpThreads, 0));
   int gx = rpr;
   while (gx > 1 && static_cast<long>(gx) * p->world > static_cast<long>(sms) * per_sm) gx = (gx + 1) / 2;  // all CTAs must be resident at once
   QB_REQUIRE(static_cast<long>(gx) * p->world <= static_cast<long>(sms) * per_sm, QB_ERR_UNSUPPORTED, "tp_reduce_emulated: %d ranks do not fit on the GPU at once",
              p->world);
   void* kargs[] = {&a};
   ++g_launch_count;
-  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(tp_reduce_kernel), dim3(gx, p->world), dim3(kTpThreads), kargs, 0,
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(gx, p->world), dim3(kTpThreads), kargs, 0,
                                               static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(QB_ERR_LAUNCH, "tp_reduce_emulated: %s", cudaGetErrorString(e));
   return QB_OK;
