@@ -103,7 +103,7 @@ __device__ __forceinline__ uint4 tp_pack8(const float (&f)[8]) {
 // kW: the most ranks the instantiation sums (2, 4 or 8): the partials of a vector are all requested before the first is
 // used, one register quadruple each.
 template <int kMaxVec, int kW>
-__global__ void __launch_bounds__(kTpThreads, kMaxVec == 1 ? 4 : 2) tp_reduce_kernel(const TpArgs a) {
+__global__ void __launch_bounds__(kTpThreads, (kMaxVec == 1 && kW <= 4) ? 4 : 2) tp_reduce_kernel(const TpArgs a) {
   grid_dep_wait();    // this rank's partial comes from the GEMM before this kernel
   grid_dep_launch();
   __shared__ float red[kTpThreads / 32];
