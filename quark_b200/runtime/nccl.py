@@ -178,13 +178,14 @@ class NcclComm:
         _check(lib.ncclCommInitRank(C.byref(comm), self.world, uid, self.rank), "ncclCommInitRank")
         self._comm = comm
         self._arenas = {}
-        # Schedule of the fused reduction (qb_tp_reduce).  Up to four ranks: one-shot (1): every rank reads all rows of its
-        # peers' partials and reduces for itself; one exchange of flags.  Measured on two B200s per [512, 2048] reduction
-        # with the norm: 15.2 us, against 22.9 us for the two-shot schedules, whose second exchange (system-wide fence, flag,
-        # wait) costs more than the extra megabyte of peer loads.  Eight ranks: the row-parallel GEMMs store their partials
-        # straight into the reducers' staging areas and the reduction is two-shot (3): one-shot would read 14 MB per rank.
+        # Schedule of the fused reduction (qb_tp_reduce): one-shot (1): every rank reads all rows of its peers' partials and
+        # reduces for itself; one exchange of flags.  Measured per [512, 2048] reduction with the norm, inside the 720p frame:
+        # two B200s 12.0 us (90.0 frames/s); four 25.5 us (81.3 frames/s) against 65.7 / 66.9 frames/s for the two-shot and
+        # the pushed two-shot schedules, whose second exchange makes every rank's kernel wait for the slowest peer.  Eight
+        # ranks were never available to measure; one-shot then pulls 14 MB per rank and reduction (about 18 us of NVLink
+        # time), which the four-rank figures suggest is still the lesser cost.
         # QB_TP_SCHEDULE overrides (0 = let the kernel choose, 1 one-shot, 2 two-shot, 3 pushed two-shot).
-        self.tp_schedule = int(os.environ.get("QB_TP_SCHEDULE", "3" if self.world > 4 else "1"))
+        self.tp_schedule = int(os.environ.get("QB_TP_SCHEDULE", "1"))
         if self.fused:
             self.reduction_name = "one kernel per rank over peer-mapped buffers: sum + gate / residual + the next AdaRMSNorm (qb_tp_reduce)"
 
