@@ -181,9 +181,8 @@ class NcclComm:
         # Schedule of the fused reduction (qb_tp_reduce): one-shot (1): every rank reads all rows of its peers' partials and
         # reduces for itself; one exchange of flags.  Measured per [512, 2048] reduction with the norm, inside the 720p frame:
         # two B200s 12.0 us (90.0 frames/s); four 25.5 us (81.3 frames/s) against 65.7 / 66.9 frames/s for the two-shot and
-        # the pushed two-shot schedules, whose second exchange makes every rank's kernel wait for the slowest peer.  Eight
-        # ranks were never available to measure; one-shot then pulls 14 MB per rank and reduction (about 18 us of NVLink
-        # time), which the four-rank figures suggest is still the lesser cost.
+        # the pushed two-shot schedules, whose second exchange makes every rank's kernel wait for the slowest peer; eight
+        # 54.0 us (53.7 frames/s) against 47.2 us (52.5 frames/s) for the pushed schedule.
         # QB_TP_SCHEDULE overrides (0 = let the kernel choose, 1 one-shot, 2 two-shot, 3 pushed two-shot).
         self.tp_schedule = int(os.environ.get("QB_TP_SCHEDULE", "1"))
         if self.fused:
