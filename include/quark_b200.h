@@ -388,9 +388,9 @@ int32_t qb_patch_scatter(const void* tokens_in, void* latent_out, int32_t C, int
  * [4 KiB of flags | y slot 0 | y slot 1 | x slot 0 | x slot 1 | h (bf16) | hq (e4m3)] (byte offsets of the six buffers from
  * qb_tp_arena_offsets).  The rank's row-parallel GEMM writes its partial into its own y slot p->x_slot; the kernel reads
  * every rank's y and leaves x_new (x slot p->x_slot), h and hq (if emit_h / emit_hq) complete in every rank's arena.
- * Schedules (p->schedule: 0 = choose between the first two, 1 = one-shot, 2 = two-shot, 3 = pushed, see qb_gemm_tp; all
- * ranks must agree): one-shot, chosen for up to
- * four ranks, has every rank read all rows of every peer's y and compute the whole result for itself (one exchange of
+ * Schedules (p->schedule: 0 = the library's choice, which is one-shot; 1 = one-shot, 2 = two-shot, 3 = pushed, see
+ * qb_gemm_tp; all ranks must agree): one-shot, the fastest measured at 2, 4 and 8 ranks,
+ * has every rank read all rows of every peer's y and compute the whole result for itself (one exchange of
  * flags, nothing written to a peer); two-shot has rank r reduce rows [r * rows / world, (r + 1) * rows / world) only and
  * store them into EVERY rank's arena (traffic stays near twice the partial, a second exchange of flags).
  * arena[r] is rank r's arena as mapped in the calling process: arena[rank] the rank's own pointer, the others from
@@ -409,7 +409,7 @@ typedef struct {
   int32_t emit_h, emit_hq;           /* write the norm's result as bf16 / as e4m3 */
   int32_t wait_limit_us;             /* 0 = default */
   float eps;
-  int32_t schedule;                  /* 0 = choose by world, 1 = one-shot, 2 = two-shot, 3 = two-shot over partials that qb_gemm_tp
+  int32_t schedule;                  /* 0 = choose (one-shot), 1 = one-shot, 2 = two-shot, 3 = two-shot over partials that qb_gemm_tp
                                         has already stored into the owners' staging areas */
   int32_t reserved;
   void* arena[8];

@@ -344,7 +344,7 @@ static int32_t tp_fill(TpArgs& a, const qb_tp_params* p, const void* gate, const
   a.gate_rows_per_group = p->rows / p->gate_groups;
   a.norm_rows_per_group = norm_scale ? p->rows / p->norm_groups : p->rows;
   QB_REQUIRE(p->schedule >= 0 && p->schedule <= 3, QB_ERR_INVALID_ARG, "tp_reduce: schedule %d", p->schedule);
-  a.one_shot = p->schedule == 1 || (p->schedule == 0 && p->world <= 4);  // few ranks: the extra reads cost less than a second exchange
+  a.one_shot = p->schedule <= 1;  // also the choice when none is made: measured ahead of the two-shot forms at 2, 4 and 8 ranks
   a.pushed = p->schedule == 3;
   a.xslot = p->x_slot; a.activation = p->norm_activation;
   a.emit_h = p->emit_h != 0; a.emit_hq = p->emit_hq != 0;
