@@ -290,7 +290,8 @@ int32_t qb_owl_attn(const void* qkv, const void* K_cache, const void* Vt_cache, 
  * narrowed to e4m3 so the next fp8 GEMM needs no separate cast. */
 
 /* y = x * rsqrt(mean(x^2) + eps) * (1 + scale[g]) + bias[g], then SiLU if activation == 1.
- * X [rows, D], scale / bias [G, D].  ref: src/quark/functional/ada_rmsnorm.py:61,
+ * X [rows, D], scale / bias [G, D]; out may be NULL when out_q is given (only the e4m3 result is wanted).
+ * ref: src/quark/functional/ada_rmsnorm.py:61,
  * src/quark/kernels/ada_rmsnorm/reference.py:10-29. */
 int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void* out, void* out_q, int32_t rows, int32_t D,
                        int32_t groups, float eps, int32_t activation, void* stream);

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kThreads, kMaxVec == 1 ? 4 : 2) ada_rmsnorm_ke
         y = __fadd_rn(__fmul_rn(y, __fadd_rn(1.0f, s[j])), b[j]);
         f[j] = activation == 1 ? silu_f(y) : y;
       }
-      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * D + c) = pack8(f);
+      if (out != nullptr) *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * D + c) = pack8(f);
       if (out_q != nullptr) {
         round_through_bf16(f);
         *reinterpret_cast<uint2*>(out_q + static_cast<size_t>(row) * D + c) = pack8_e4m3(f);
@@ -768,7 +768,7 @@ int32_t qb_quantize_e4m3_rows(const void* X, void* out, float* scale_out, int32_
 
 int32_t qb_ada_rmsnorm(const void* X, const void* scale, const void* bias, void* out, void* out_q, int32_t rows, int32_t D,
                        int32_t groups, float eps, int32_t activation, void* stream) {
-  QB_REQUIRE(X && scale && bias && out, QB_ERR_INVALID_ARG, "ada_rmsnorm: NULL pointer");
+  QB_REQUIRE(X && scale && bias && (out || out_q), QB_ERR_INVALID_ARG, "ada_rmsnorm: NULL pointer (out may be NULL only when out_q is given)");
   QB_REQUIRE(rows > 0 && D > 0 && groups > 0 && rows % groups == 0, QB_ERR_INVALID_ARG, "ada_rmsnorm: rows %d, D %d, groups %d", rows, D,
              groups);
   QB_REQUIRE(D % 8 == 0 && D <= 8192, QB_ERR_UNSUPPORTED, "ada_rmsnorm: D = %d must be a multiple of 8 and at most 8192", D);

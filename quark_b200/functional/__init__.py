@@ -546,10 +546,11 @@ def _bf16_only(who, *ts):
             raise TypeError(f"{who}: dtype {_dt(t)!r} (expected bf16)")
 
 
-def ada_rmsnorm(X, scale, bias, eps: float = 1e-6, activation: str | None = None, *, out=None, out_q=None):
+def ada_rmsnorm(X, scale, bias, eps: float = 1e-6, activation: str | None = None, *, out=None, out_q=None, only_q: bool = False):
     """``rmsnorm(x) * (1 + scale) + bias`` (+ SiLU) (``src/quark/functional/ada_rmsnorm.py:61``).
 
-    ``out_q`` (extension): an e4m3 tensor that also receives the result, for a following fp8 GEMM.
+    ``out_q`` (extension): an e4m3 tensor that also receives the result, for a following fp8 GEMM; with ``only_q`` the
+    bf16 result is not written at all (``out_q`` is returned).
     """
     _bf16_only("qf.ada_rmsnorm", X, scale, bias)
     D = int(X.shape[-1])
@@ -559,13 +560,15 @@ def ada_rmsnorm(X, scale, bias, eps: float = 1e-6, activation: str | None = None
         raise ValueError(f"qf.ada_rmsnorm: X {X.shape}, scale {scale.shape}, bias {bias.shape} do not broadcast")
     if activation not in (None, "silu"):
         raise ValueError(f"qf.ada_rmsnorm: unsupported activation {activation!r}")
-    out = _like(X, out, "qf.ada_rmsnorm")
+    if only_q and out_q is None:
+        raise ValueError("qf.ada_rmsnorm: only_q needs out_q")
+    out = None if only_q else _like(X, out, "qf.ada_rmsnorm")
     if out_q is not None and (out_q.dtype != "e4m3" or out_q.numel != X.numel):
         raise ValueError("qf.ada_rmsnorm: out_q must be an e4m3 tensor of the same size")
     _lib.check(
         _lib.load().qb_ada_rmsnorm(_p(X), _p(scale), _p(bias), _p(out), _p(out_q), rows, D, G, float(eps), 1 if activation == "silu" else 0, _s())
     )
-    return out
+    return out_q if only_q else out
 
 
 def head_rmsnorm(X, n_q_heads: int, n_kv_heads: int, Dh: int, eps: float = 1e-6, *, out=None):

@@ -276,10 +276,9 @@ class AdaRMSNorm(Module):
     """Stateless ``rmsnorm(x) * (1 + scale) + bias`` (``layers.py:609-619``)."""
 
     def forward(self, x, scale, bias, *, activation=None, emit_e4m3: bool = False):
-        out = _cached(self, "out", x.shape, x.dtype)
-        out_q = _cached(self, "out_q", x.shape, "e4m3") if emit_e4m3 else None
-        qf.ada_rmsnorm(x, scale, bias, activation=activation, out=out, out_q=out_q)
-        return out_q if emit_e4m3 else out
+        if emit_e4m3:  # the bf16 copy has no reader: only the e4m3 result is written
+            return qf.ada_rmsnorm(x, scale, bias, activation=activation, out_q=_cached(self, "out_q", x.shape, "e4m3"), only_q=True)
+        return qf.ada_rmsnorm(x, scale, bias, activation=activation, out=_cached(self, "out", x.shape, x.dtype))
 
 
 class RMSNorm(Module):
