@@ -515,6 +515,46 @@ def moe_route(logits, top_k: int) -> np.ndarray:
     return dense
 
 
+def moe_route_slots(logits, top_k: int, *, tile: int = 128, total_slots: int | None = None, order=None):
+    """The same routing as slot tables sorted by expert, every expert's run padded to a multiple of ``tile`` rows
+    (``src/quark/kernels/moe_router_correct/reference.py:51-108``, whose tile is 32; the GPU library uses 128, its GEMM's row
+    tile).  Returns ``slot_token`` (the token in each slot; -1 for padding here, where the reference leaves 0),
+    ``slot_weight``, ``tile_expert`` (-1 past the last used tile: the reference's ``work_list[2 i + 1]``), ``token_slot``
+    ``[M, top_k]`` (k in order of decreasing logit), ``offsets`` ``[E + 1]`` and ``counts`` ``[E]``.  Within an expert the
+    slots follow (token, k) order, as the reference's numpy oracle fills them.  Ties between logits go to the lower
+    expert index (see ``moe_route``); ``order`` ``[M, top_k]`` overrides the choice of experts (the golden test passes the
+    reference's, whose unstable sort may break a tie the other way), the layout follows from it."""
+    L = to_f32(logits, "bf16")
+    M, E = L.shape
+    if order is None:
+        order = np.argsort(-L, axis=1, kind="stable")[:, :top_k]
+    order = np.asarray(order, np.int64)
+    score = np.take_along_axis(L, order, axis=1)
+    ex = np.exp(score - score.max(axis=-1, keepdims=True))
+    w = (ex / ex.sum(axis=-1, keepdims=True)).astype(np.float32)
+    counts = np.bincount(order.ravel(), minlength=E).astype(np.int32)
+    offsets = np.concatenate([[0], np.cumsum((counts + tile - 1) // tile * tile)]).astype(np.int32)
+    if total_slots is None:
+        total_slots = (M * top_k + E * (tile - 1) + tile - 1) // tile * tile
+    if offsets[-1] > total_slots:
+        raise ValueError(f"moe_route_slots: {int(offsets[-1])} active slots exceed the {total_slots} provided")
+    slot_token = np.full(total_slots, -1, np.int32)
+    slot_weight = np.zeros(total_slots, np.float32)
+    token_slot = np.zeros((M, top_k), np.int32)
+    cursor = offsets[:-1].copy()
+    for t in range(M):
+        for k in range(top_k):
+            e = order[t, k]
+            slot_token[cursor[e]] = t
+            slot_weight[cursor[e]] = w[t, k]
+            token_slot[t, k] = cursor[e]
+            cursor[e] += 1
+    tile_expert = np.full(total_slots // tile, -1, np.int32)
+    for e in range(E):
+        tile_expert[offsets[e] // tile : offsets[e + 1] // tile] = e
+    return dict(slot_token=slot_token, slot_weight=slot_weight, tile_expert=tile_expert, token_slot=token_slot, offsets=offsets, counts=counts)
+
+
 def moe(x, router_w, expert_in, expert_out, *, top_k: int, fp8: bool = False, a_quant: str | None = None):
     """``out[m] = sum_k w_k * W_out[e_k] silu(W_in[e_k] x_m)`` with the reference's rounding points
     (``src/quark/nn/moe.py:252-363``): bf16 router logits, bf16 hidden activations, f32 per-expert outputs, one

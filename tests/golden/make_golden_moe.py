@@ -67,7 +67,11 @@ def main(ref_root: str) -> None:
             dense[e, m] = r["slot_weights"][slot]
     np.savez_compressed(HERE / "moe.npz", X=X, Wr=Wr, W_in=W_in, W_out=W_out, logits=np.asarray(logits, np.uint16),
                         weights=dense, counts=np.asarray(r["counts"], np.int32), out=np.asarray(out, np.uint16),
-                        geometry=np.array([M, D, H, E, K], np.int32))  # fmt: skip
+                        geometry=np.array([M, D, H, E, K], np.int32),
+                        # the router's slot tables as the reference lays them out (row tile 32)
+                        slot_token_ids=np.asarray(r["token_ids"], np.int32), slot_weights=np.asarray(r["slot_weights"], np.float32),
+                        slot_offsets=np.asarray(r["offsets"], np.int32), token_slot_table=np.asarray(r["token_slot_table"], np.int32),
+                        work_list=np.asarray(r["work_list"], np.int32), capacity=np.array([capacity], np.int32))  # fmt: skip
     print("moe.npz:", {k: int(v) for k, v in zip("MDHEK", (M, D, H, E, K))}, "counts", r["counts"].tolist())
 
 

@@ -211,3 +211,33 @@ def test_mixture_of_experts_against_the_reference_oracles():
         assert mine.sum() <= theirs.sum()
     got = ops.moe(z["X"], z["Wr"], z["W_in"], z["W_out"], top_k=K)
     assert_bf16_close(got[~tie], z["out"][~tie])
+
+
+def test_moe_slot_tables_match_the_reference_router():
+    """``ops.moe_route_slots`` at the reference's row tile (32) against the slot tables its own numpy router wrote
+    (``src/quark/kernels/moe_router_correct/reference.py:51-108``; ``tests/golden/make_golden_moe.py``): counts, offsets,
+    the slot of every (token, k), the token and weight in every slot, the expert of every 32-row chunk - all exact.
+    The fixture has one token with two equal logits, which the reference's unstable sort gives to the higher expert
+    index and this oracle (like the reference's kernel) to the lower: the choice of experts is compared first, tie
+    aside, and the layout is then derived from the reference's choice."""
+    z = load("moe.npz")
+    M, D, H, E, K = (int(v) for v in z["geometry"])
+    cap = int(z["capacity"][0])
+    ref_order = np.searchsorted(z["slot_offsets"][1:], z["token_slot_table"], side="right")  # expert of every (token, k)
+    own = ops.moe_route_slots(z["logits"], K, tile=32, total_slots=E * cap)
+    own_order = np.searchsorted(own["offsets"][1:], own["token_slot"], side="right")
+    differ = np.flatnonzero((own_order != ref_order).any(axis=1))
+    assert len(differ) <= 1
+    for m in differ:  # a tie: the same logit value at both experts
+        lg = z["logits"][m]
+        assert sorted(lg[own_order[m]].tolist()) == sorted(lg[ref_order[m]].tolist())
+    r = ops.moe_route_slots(z["logits"], K, tile=32, total_slots=E * cap, order=ref_order)
+    np.testing.assert_array_equal(r["counts"], z["counts"])
+    np.testing.assert_array_equal(r["offsets"], z["slot_offsets"])
+    np.testing.assert_array_equal(r["token_slot"], z["token_slot_table"])
+    np.testing.assert_array_equal(r["tile_expert"], z["work_list"][1::2])
+    np.testing.assert_array_equal(z["work_list"][0::2], 32 * np.arange(E * cap // 32))
+    used = r["slot_token"] >= 0
+    np.testing.assert_array_equal(r["slot_token"][used], z["slot_token_ids"][used])
+    assert not z["slot_token_ids"][~used].any() and not z["slot_weights"][~used].any()  # the reference pads with zeros
+    np.testing.assert_allclose(r["slot_weight"], z["slot_weights"], atol=1e-6)
